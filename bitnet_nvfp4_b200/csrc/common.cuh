@@ -1,0 +1,193 @@
+// Shared device/host helpers for the B200 (sm_100a) kernels of this library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <cstddef>
+#include <cstdint>
+
+// ---------------------------------------------------------------------------------------------
+// Error reporting. Every extern "C" entry point returns 0 on success or one of these codes and
+// records a message readable through bnf4_last_error().
+// ---------------------------------------------------------------------------------------------
+enum Bnf4Status : int {
+    BNF4_OK = 0,
+    BNF4_ERR_INVALID = 1,      // bad argument (null pointer, unsupported shape, misalignment)
+    BNF4_ERR_CUDA = 2,         // a CUDA runtime/driver call failed
+    BNF4_ERR_UNSUPPORTED = 3,  // entry point exists for link compatibility only
+    BNF4_ERR_DEVICE = 4,       // a kernel reported a device-side error (e.g. a bounded wait gave up)
+    BNF4_ERR_NO_DEVICE = 5,    // no sm_100 GPU present
+};
+
+namespace bnf4 {
+
+int set_error(int code, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+int check_launch(const char* what);
+
+// ---------------------------------------------------------------------------------------------
+// Counter-based rng (bit-compatible with the reference's src/rng.h:7-29 and
+// src/efla_lm_kernels.cu:49-86).
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint64_t splitmix64_next(uint64_t& state) {
+    uint64_t z = (state += 0x9e3779b97f4a7c15ULL);
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebULL;
+    return z ^ (z >> 31);
+}
+
+__host__ __device__ __forceinline__ uint64_t mix_u64(uint64_t a, uint64_t b) {
+    uint64_t x = a ^ (b + 0x9e3779b97f4a7c15ULL + (a << 6) + (a >> 2));
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdULL;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ULL;
+    x ^= x >> 33;
+    return x;
+}
+
+__host__ __device__ __forceinline__ int ternary_from_u64(uint64_t x) {
+    const uint32_t r = static_cast<uint32_t>(x & 0xFFu);
+    return (r < 85u) ? -1 : ((r < 170u) ? 0 : 1);
+}
+
+__host__ __device__ __forceinline__ int noise_hash(uint64_t seed, uint64_t idx, bool use_clt, int clt_k) {
+    if (!use_clt) return ternary_from_u64(mix_u64(seed, idx));
+    const int k = clt_k > 0 ? clt_k : 1;
+    uint64_t st = mix_u64(seed, idx);
+    int sum = 0;
+    for (int i = 0; i < k; ++i) sum += ternary_from_u64(splitmix64_next(st));
+    return sum;
+}
+
+// Salts of the per-matrix noise streams (reference: src/train_efla_lm.cpp:3822-3833).
+constexpr uint64_t kSaltEmb = 0x111111ULL, kSaltWin = 0x222222ULL, kSaltWq = 0x333333ULL, kSaltWk = 0x444444ULL,
+                   kSaltWv = 0x555555ULL, kSaltWbeta = 0x666666ULL, kSaltFf1 = 0x999999ULL, kSaltFf2 = 0xAAAAAAULL,
+                   kSaltHead = 0x777777ULL, kSaltHeadBias = 0x888888ULL, kSaltBetaBias = 0x9999999ULL,
+                   kSaltPos = 0xBEEFF00DULL;
+// Sub-streams of a matrix seed for the two rank-r factors.
+constexpr uint64_t kFactorA = 0xA11CEULL, kFactorB = 0xB0BULL;
+
+// ---------------------------------------------------------------------------------------------
+// Integer rounding / clipping (reference: src/cuda_kernels.cu:46-55, src/efla_lm_kernels.cu:12-26).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ int clip_int8(int v) { return max(-127, min(127, v)); }
+__device__ __forceinline__ int clip_ternary(int v) { return max(-1, min(1, v)); }
+__device__ __forceinline__ int rint_to_int(float x) { return __float2int_rn(x); }
+
+// tanh-form GELU (reference: src/cuda_kernels.cu:57-62).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float c = 0.7978845608028654f;
+    const float x3 = x * x * x;
+    return 0.5f * x * (1.0f + tanhf(c * fmaf(0.044715f, x3, x)));
+}
+
+// ---------------------------------------------------------------------------------------------
+// NVFP4 number formats.
+//   e2m1: magnitudes {0,.5,1,1.5,2,3,4,6}, bit 3 = sign, round-to-nearest-even, saturating.
+//   ue4m3: unsigned e4m3, bias 7, subnormal step 2^-9, max 448 (0x7e), RNE, saturating.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint32_t e2m1_encode(float x) {
+    const uint32_t sign = (x < 0.0f || (x == 0.0f && (1.0f / x) < 0.0f)) ? 8u : 0u;
+    const float a = x < 0.0f ? -x : x;
+    uint32_t c;
+    if (a <= 0.25f) c = 0;
+    else if (a < 0.75f) c = 1;
+    else if (a <= 1.25f) c = 2;
+    else if (a < 1.75f) c = 3;
+    else if (a <= 2.5f) c = 4;
+    else if (a < 3.5f) c = 5;
+    else if (a <= 5.0f) c = 6;
+    else c = 7;
+    return sign | c;
+}
+
+__device__ __forceinline__ uint32_t ue4m3_encode(float x) {
+    if (!(x > 0.0f)) return 0u;
+    if (x >= 448.0f) return 0x7eu;
+    if (x < 0.015625f) return static_cast<uint32_t>(__float2int_rn(x * 512.0f));
+    const uint32_t bits = __float_as_uint(x);
+    int e = static_cast<int>(bits >> 23) - 127;
+    const uint32_t man = bits & 0x7fffffu;
+    // round the 23-bit mantissa to 3 bits, ties to even
+    uint32_t q = man >> 20;
+    const uint32_t rem = man & 0xfffffu;
+    if (rem > 0x80000u || (rem == 0x80000u && (q & 1u))) q += 1;
+    if (q == 8u) { q = 0; e += 1; }
+    uint32_t code = (static_cast<uint32_t>(e + 7) << 3) | q;
+    return code > 0x7eu ? 0x7eu : code;
+}
+
+__host__ __device__ __forceinline__ float ue4m3_decode(uint32_t b) {
+    const uint32_t e = (b >> 3) & 0xfu;
+    const uint32_t m = b & 7u;
+    if (e == 0u) return static_cast<float>(m) * 0.001953125f;
+#if defined(__CUDA_ARCH__)
+    return __uint_as_float(((e + 120u) << 23) | (m << 20));
+#else
+    union { uint32_t u; float f; } cv;
+    cv.u = ((e + 120u) << 23) | (m << 20);
+    return cv.f;
+#endif
+}
+
+// Byte offset of the scale factor of (row r, 16-element K-block kb) of a [rows x K] operand:
+// 512-byte atoms of 128 rows x 4 K-blocks, (r%32)*16 + ((r%128)/32)*4 + kb%4 inside an atom,
+// atoms ordered K-fastest. One atom is exactly what one tcgen05.cp 32x128b.warpx4 moves to TMEM.
+__host__ __device__ __forceinline__ size_t sf_offset(int r, int kb, int k_atoms) {
+    return (static_cast<size_t>(r >> 7) * k_atoms + static_cast<size_t>(kb >> 2)) * 512 +
+           static_cast<size_t>(r & 31) * 16 + static_cast<size_t>((r & 127) >> 5) * 4 + static_cast<size_t>(kb & 3);
+}
+__host__ __device__ __forceinline__ int sf_k_atoms(int K) { return ((K + 15) / 16 + 3) / 4; }
+__host__ __device__ __forceinline__ size_t sf_bytes(int rows, int K) {
+    return static_cast<size_t>((rows + 127) / 128) * 128 * static_cast<size_t>(sf_k_atoms(K)) * 4;
+}
+
+// Quantise one block of 16 int8 values (already in registers as 4 packed words, little-endian) to
+// a ue4m3 scale byte and 16 e2m1 codes (two 32-bit words, element i in nibble i).
+// row_scale multiplies the scale before rounding when use_row_scale (stacked-QKV weights).
+__device__ __forceinline__ void quant_block16(const int (&w)[4], float row_scale, bool use_row_scale, uint32_t& sf_byte,
+                                              uint32_t& code_lo, uint32_t& code_hi) {
+    int amax = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int v = static_cast<int>(static_cast<int8_t>((w[i] >> (8 * j)) & 0xff));
+            amax = max(amax, abs(v));
+        }
+    }
+    float scale = (amax > 0) ? (static_cast<float>(amax) / 6.0f) : 1.0f;
+    if (use_row_scale) scale *= row_scale;
+    uint32_t sq = ue4m3_encode(scale);
+    float scale_f = ue4m3_decode(sq);
+    if (scale_f == 0.0f) { sq = 0x38u; scale_f = 1.0f; }
+    sf_byte = sq;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int v = static_cast<int>(static_cast<int8_t>((w[i] >> (8 * j)) & 0xff));
+            const uint32_t c = e2m1_encode(__fdiv_rn(static_cast<float>(v), scale_f));
+            const int e = i * 4 + j;
+            if (e < 8) lo |= c << (4 * e);
+            else hi |= c << (4 * (e - 8));
+        }
+    }
+    code_lo = lo;
+    code_hi = hi;
+}
+
+__device__ __forceinline__ int pack4_i8(int a, int b, int c, int d) {
+    return (a & 0xff) | ((b & 0xff) << 8) | ((c & 0xff) << 16) | ((d & 0xff) << 24);
+}
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace bnf4

@@ -1,0 +1,539 @@
+// Block-scaled FP4 (NVFP4: e2m1 data, one ue4m3 scale per 16 K-elements) GEMM for sm_100a.
+//
+//   D[m,n] = alpha * sum_kb sfa[m,kb] * sfb[n,kb] * sum_{k in kb} a[m,k] * b[n,k]  (+ beta * C[m,n])
+//            (+ s_member * sum_r t[m][g*rank+r] * A_pair[n][r])                      rank-r perturbation
+//
+// replaces the reference's CUTLASS Sm120 kernel behind gemm_ternary_f_nvfp4 /
+// gemm_ternary_f_nvfp4_gelu_i8 (reference: src/cuda_kernels.cu:3145-3310, 4342-4607) and fuses the
+// rank-r term of gemm_lora_f_kernel (reference: src/cuda_kernels.cu:1271-1305) into the tile epilogue.
+//
+// Structure of one CTA (one 128 x 128 output tile, 192 threads):
+//   warp 0      producer: TMA tiles of A and B (128 rows x 128 bytes = 256 K-elements, 128B swizzle) and
+//               bulk copies of the matching scale-factor atoms into a ring of shared-memory stages
+//   warp 1      owns TMEM; per stage copies the scale atoms to TMEM (tcgen05.cp 32x128b.warpx4) and issues
+//               tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x N128 x K64) accumulating fp32 in TMEM
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one TMEM lane quadrant per warp), apply
+//               alpha/beta/rank-r/GELU, and store (TMA store through swizzled staging, or direct)
+// Two CTAs fit per SM (shared memory and 256 TMEM columns each), so one tile's epilogue overlaps the
+// next tile's loads and MMAs. Every mbarrier wait is bounded: on expiry the kernel records an error
+// word, leaves its role loop, frees TMEM and returns.
+
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bnf4 {
+
+namespace {
+
+constexpr int BM = 128;             // tile rows
+constexpr int BN = 128;             // tile columns
+constexpr int BK = 256;             // K elements per stage (128 bytes of packed e2m1 per row)
+constexpr int UMMA_K = 64;          // K elements per tcgen05.mma
+constexpr int kStages = 2;
+constexpr int kStageABytes = BM * 128;
+constexpr int kStageBBytes = BN * 128;
+constexpr int kStageSfBytes = 4 * 512;  // four 128-row x 64-K atoms
+constexpr int kEpiWarps = 4;
+constexpr int kEpiBufBytes = 32 * 32 * 4;  // one 32 x 32 fp32 box
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;      // 128 accumulator + kStages * 32 scale columns, rounded to a power of two
+constexpr int kAccCol = 0;
+constexpr int kSfCol = 128;
+
+constexpr int kSmemA = 0;
+constexpr int kSmemB = kSmemA + kStages * kStageABytes;
+constexpr int kSmemSfa = kSmemB + kStages * kStageBBytes;
+constexpr int kSmemSfb = kSmemSfa + kStages * kStageSfBytes;
+constexpr int kSmemEpi = kSmemSfb + kStages * kStageSfBytes;
+constexpr int kSmemBar = kSmemEpi + kEpiWarps * 2 * kEpiBufBytes;
+constexpr int kSmemTotal = kSmemBar + 128;
+constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
+
+constexpr long long kWaitCycles = 2000000000LL;  // ~1 s bound on every mbarrier wait
+
+__device__ int g_gemm_error = 0;
+}  // namespace
+int g_gemm_allow_tma_store = 1;  // host toggle: 0 forces the direct-store epilogue
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and records `code`) if the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kWaitCycles) {
+            atomicCAS(&g_gemm_error, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa,
+                                            uint32_t tsfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading byte
+// offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48), layout type in [61,64).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= 1ull << 46;
+    d |= static_cast<uint64_t>(layout) << 61;
+    return d;
+}
+constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2;
+
+// Instruction descriptor of kind::mxf4nvf4 (block-scaled): a/b format e2m1 (=1) at bits 7 and 10,
+// K-major A and B, N>>3 at bit 17, ue4m3 scales (bit 23 = 0), M>>4 at bit 24, scale ids 0, dense K = 64.
+constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+
+struct KernelArgs {
+    GemmParams p;
+    int use_tma_store;
+    int k_atoms;  // scale atoms along K
+    int n_tiles;  // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile (N fastest: CTAs that share A rows run together)
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                              const __grid_constant__ CUtensorMap map_b,
+                                                              const __grid_constant__ CUtensorMap map_d,
+                                                              const KernelArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const GemmParams& p = args.p;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_tile = static_cast<int>(blockIdx.x % args.n_tiles), m_tile = static_cast<int>(blockIdx.x / args.n_tiles);
+    const int m0 = m_tile * BM, n0 = n_tile * BN;
+    const int num_ks = (p.k + BK - 1) / BK;
+
+    const uint32_t bar_full = smem_base + kSmemBar;          // kStages x 8 bytes
+    const uint32_t bar_empty = bar_full + 8 * kStages;       // kStages x 8 bytes
+    const uint32_t bar_accum = bar_empty + 8 * kStages;      // 8 bytes
+    const uint32_t tmem_slot = bar_accum + 8;                // 4 bytes
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBar + 16 * kStages + 8);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_gen;
+
+    if (warp == 0) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            const uint8_t* sfa_tile = static_cast<const uint8_t*>(p.sfa) + static_cast<size_t>(m_tile) * args.k_atoms * 512;
+            const uint8_t* sfb_tile = static_cast<const uint8_t*>(p.sfb) + static_cast<size_t>(n_tile) * args.k_atoms * 512;
+            for (int ks = 0; ks < num_ks; ++ks) {
+                const int s = ks % kStages;
+                if (ks >= kStages) {
+                    if (!mbar_wait(bar_empty + 8 * s, ((ks / kStages) - 1) & 1, 1)) break;
+                }
+                const int atoms = min(4, args.k_atoms - ks * 4);
+                const uint32_t sf_bytes_stage = static_cast<uint32_t>(atoms) * 512u;
+                const uint32_t bar = bar_full + 8 * s;
+                mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
+                tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, m0, bar);
+                tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, n0, bar);
+                bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
+                bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int ks = 0; ks < num_ks && ok; ++ks) {
+                const int s = ks % kStages;
+                ok = mbar_wait(bar_full + 8 * s, (ks / kStages) & 1, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const int nk = min(4, (p.k - ks * BK) / UMMA_K);
+                const uint32_t sfa_s = smem_base + kSmemSfa + s * kStageSfBytes;
+                const uint32_t sfb_s = smem_base + kSmemSfb + s * kStageSfBytes;
+                const uint32_t t_sfa = tmem_base + kSfCol + s * 32;
+                const uint32_t t_sfb = t_sfa + 16;
+                for (int j = 0; j < nk; ++j) {
+                    tc_cp_sf(t_sfa + 4 * j, smem_desc(sfa_s + 512 * j, 0, 128, kLayoutNone));
+                    tc_cp_sf(t_sfb + 4 * j, smem_desc(sfb_s + 512 * j, 0, 128, kLayoutNone));
+                }
+                const uint32_t a_s = smem_base + kSmemA + s * kStageABytes;
+                const uint32_t b_s = smem_base + kSmemB + s * kStageBBytes;
+                for (int j = 0; j < nk; ++j) {
+                    const uint64_t adesc = smem_desc(a_s + 32 * j, 16, 1024, kLayoutSw128);
+                    const uint64_t bdesc = smem_desc(b_s + 32 * j, 16, 1024, kLayoutSw128);
+                    tc_mma_nvf4(tmem_base + kAccCol, adesc, bdesc, kIdesc, t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
+                }
+                tc_commit(bar_empty + 8 * s);  // frees this smem stage once the MMAs above have read it
+            }
+            if (ok) tc_commit(bar_accum);     // accumulator complete
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+        const int row_in_tile = q * 32 + lane;
+        const long long row = static_cast<long long>(m0) + row_in_tile;
+        const bool row_ok = row < p.m;
+        bool ok = mbar_wait(bar_accum, 0, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+
+        // per-row perturbation context
+        int pair = 0;
+        float lsign = 0.0f;
+        if (p.rank > 0 && row_ok) {
+            const int member = p.rows_per_member > 0 ? static_cast<int>(row / p.rows_per_member) : 0;
+            pair = member >> 1;
+            lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
+        }
+        int next_acc[4] = {0, 0, 0, 0};
+
+        const uint32_t epi_buf0 = smem_base + kSmemEpi + (warp - 2) * 2 * kEpiBufBytes;
+        uint8_t* epi_gen0 = smem_gen + kSmemEpi + (warp - 2) * 2 * kEpiBufBytes;
+
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= p.n) break;  // warp-uniform
+                uint32_t acc[32];
+                tmem_ld32(tmem_base + kAccCol + (static_cast<uint32_t>(q * 32) << 16) + c * 32, acc);
+                tmem_ld_wait();
+
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(p.alpha, __uint_as_float(acc[j]));
+                if (p.beta != 0.0f && row_ok) {
+                    const float* crow = p.c + static_cast<size_t>(row) * p.ldc + col0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.n) v[j] = fmaf(p.beta, crow[j], v[j]);
+                }
+                if (p.rank > 0 && row_ok) {
+                    const int g = p.group_cols > 0 ? (col0 / p.group_cols) : 0;
+                    int tr[4] = {0, 0, 0, 0};
+                    for (int r = 0; r < p.rank; ++r) tr[r] = p.lora_t[static_cast<size_t>(row) * p.t_stride + g * p.rank + r];
+                    const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (col0 + j < p.n) {
+                            int pert = 0;
+                            for (int r = 0; r < p.rank; ++r) pert += tr[r] * static_cast<int>(Ap[j * p.rank + r]);
+                            v[j] = fmaf(lsign, static_cast<float>(pert), v[j]);
+                        }
+                    }
+                }
+
+                if constexpr (EPI == EPI_F32) {
+                    if (args.use_tma_store) {
+                        // stage the 32x32 box in 128B-swizzled shared memory, then one TMA store (clips at M and N)
+                        const int buf = c & 1;
+                        if (c >= 2) {
+                            if (lane == 0) bulk_wait_read<1>();
+                            __syncwarp();
+                        }
+                        float4* dst = reinterpret_cast<float4*>(epi_gen0 + buf * kEpiBufBytes + lane * 128);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&map_d, epi_buf0 + buf * kEpiBufBytes, col0, m0 + q * 32);
+                            bulk_commit();
+                        }
+                    } else if (row_ok) {
+                        float* drow = p.d + static_cast<size_t>(row) * p.ldd + col0;
+                        const bool vec = ((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && (col0 + 32 <= p.n);
+                        if (vec) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(drow)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.n) drow[j] = v[j];
+                        }
+                    }
+                } else {
+                    // GELU -> int8 (reference: src/cuda_kernels.cu:3178-3194; tanh-form GELU, clip to +-127)
+                    int qv[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) qv[j] = (col0 + j < p.n) ? clip_int8(rint_to_int(gelu_tanh(v[j]) * p.act_scale)) : 0;
+                    int w[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) w[j] = pack4_i8(qv[4 * j], qv[4 * j + 1], qv[4 * j + 2], qv[4 * j + 3]);
+                    if (row_ok && p.d_i8 != nullptr) {
+                        int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
+                        if (((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && col0 + 32 <= p.n) {
+                            reinterpret_cast<int4*>(drow)[0] = make_int4(w[0], w[1], w[2], w[3]);
+                            reinterpret_cast<int4*>(drow)[1] = make_int4(w[4], w[5], w[6], w[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.n) drow[j] = static_cast<int8_t>(qv[j]);
+                        }
+                    }
+                    if constexpr (EPI == EPI_GELU_FP4) {
+                        if (row_ok) {
+                            const int wa[4] = {w[0], w[1], w[2], w[3]};
+                            const int wb[4] = {w[4], w[5], w[6], w[7]};
+                            uint32_t s0, s1, lo0, hi0, lo1, hi1;
+                            quant_block16(wa, 1.0f, false, s0, lo0, hi0);
+                            quant_block16(wb, 1.0f, false, s1, lo1, hi1);
+                            *reinterpret_cast<uint4*>(p.d_codes + (static_cast<size_t>(row) * p.n + col0) / 2) = make_uint4(lo0, hi0, lo1, hi1);
+                            const int kb = col0 >> 4;
+                            *reinterpret_cast<uint16_t*>(p.d_sf + sf_offset(static_cast<int>(row), kb, sf_k_atoms(p.n))) =
+                                static_cast<uint16_t>(s0 | (s1 << 8));
+                            if (p.next_nvec > 0) {
+                                const int8_t* tv = p.next_tvec + static_cast<size_t>(pair) * p.next_tvec_pair_stride + col0;
+                                for (int vv = 0; vv < p.next_nvec; ++vv) {
+                                    const int4* bv = reinterpret_cast<const int4*>(tv + static_cast<size_t>(vv) * p.n);
+                                    const int4 b0 = bv[0], b1 = bv[1];
+                                    int a = next_acc[vv];
+                                    a = __dp4a(w[0], b0.x, a); a = __dp4a(w[1], b0.y, a); a = __dp4a(w[2], b0.z, a); a = __dp4a(w[3], b0.w, a);
+                                    a = __dp4a(w[4], b1.x, a); a = __dp4a(w[5], b1.y, a); a = __dp4a(w[6], b1.z, a); a = __dp4a(w[7], b1.w, a);
+                                    next_acc[vv] = a;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if constexpr (EPI == EPI_F32) {
+                if (args.use_tma_store) {
+                    if (lane == 0) bulk_wait_read<0>();
+                    __syncwarp();
+                }
+            }
+            if constexpr (EPI == EPI_GELU_FP4) {
+                if (row_ok && p.next_nvec > 0) {
+                    for (int vv = 0; vv < p.next_nvec; ++vv) atomicAdd(p.next_t + static_cast<size_t>(row) * p.next_nvec + vv, next_acc[vv]);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
+                uint32_t box0, uint32_t box1, const char* what) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return set_error(BNF4_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {stride1_bytes};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(BNF4_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with %d", what, static_cast<int>(r));
+    return BNF4_OK;
+}
+
+template <int EPI>
+int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const KernelArgs& args, dim3 grid,
+             cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
+        if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_nvfp4_kernel)");
+        configured = true;
+    }
+    gemm_nvfp4_kernel<EPI><<<grid, kThreads, kSmemAlloc, stream>>>(ma, mb, md, args);
+    return check_launch("gemm_nvfp4_kernel");
+}
+
+}  // namespace
+
+int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
+    if (p.m <= 0 || p.n <= 0) return BNF4_OK;
+    if (p.k <= 0 || (p.k % 64) != 0) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: k=%d must be a positive multiple of 64", p.k);
+    if (!p.a || !p.b || !p.sfa || !p.sfb) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null operand");
+    if ((reinterpret_cast<uintptr_t>(p.a) & 15) || (reinterpret_cast<uintptr_t>(p.b) & 15) || (reinterpret_cast<uintptr_t>(p.sfa) & 15) ||
+        (reinterpret_cast<uintptr_t>(p.sfb) & 15))
+        return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: operands and scale factors must be 16-byte aligned");
+    if (p.beta != 0.0f && p.c == nullptr) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: beta != 0 needs C");
+    if (p.rank < 0 || p.rank > 4) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: rank=%d outside [0,4]", p.rank);
+    if (p.rank > 0 && (!p.lora_t || !p.lora_A)) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: rank > 0 needs t and A");
+    if (p.group_cols > 0 && (p.group_cols % 32) != 0) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: group_cols must be a multiple of 32");
+    if (p.epilogue == EPI_F32 && !p.d) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null D");
+    if (p.epilogue == EPI_GELU_I8 && !p.d_i8) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null int8 D");
+    if (p.epilogue == EPI_GELU_FP4) {
+        if (!p.d_codes || !p.d_sf) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null FP4 D");
+        if ((p.n % 32) != 0) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: FP4 output needs n %% 32 == 0");
+        if ((reinterpret_cast<uintptr_t>(p.d_codes) & 15) || (reinterpret_cast<uintptr_t>(p.d_sf) & 3))
+            return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: FP4 output misaligned");
+        if (p.next_nvec < 0 || p.next_nvec > 4) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: next_nvec outside [0,4]");
+        if (p.next_nvec > 0 && ((reinterpret_cast<uintptr_t>(p.next_tvec) & 15) || (p.next_tvec_pair_stride & 15)))
+            return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: next_tvec misaligned");
+    }
+
+    CUtensorMap ma, mb, md;
+    int rc = make_map_2d(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.a, static_cast<uint64_t>(p.k) / 2, static_cast<uint64_t>(p.m),
+                         static_cast<uint64_t>(p.k) / 2, 128, BM, "A");
+    if (rc) return rc;
+    rc = make_map_2d(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.b, static_cast<uint64_t>(p.k) / 2, static_cast<uint64_t>(p.n),
+                     static_cast<uint64_t>(p.k) / 2, 128, BN, "B");
+    if (rc) return rc;
+    KernelArgs args;
+    args.p = p;
+    args.k_atoms = sf_k_atoms(p.k);
+    args.use_tma_store = 0;
+    if (p.epilogue == EPI_F32 && (reinterpret_cast<uintptr_t>(p.d) & 15) == 0 && (p.ldd % 4) == 0 && p.ldd >= p.n) {
+        rc = make_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.d, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.m),
+                         static_cast<uint64_t>(p.ldd) * 4, 32, 32, "D");
+        if (rc) return rc;
+        args.use_tma_store = g_gemm_allow_tma_store ? 1 : 0;
+    } else {
+        md = ma;  // unused
+    }
+    args.n_tiles = (p.n + BN - 1) / BN;
+    const long long tiles = static_cast<long long>(args.n_tiles) * ((p.m + BM - 1) / BM);
+    if (tiles > 0x7fffffffLL) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: too many tiles");
+    const dim3 grid(static_cast<unsigned>(tiles), 1, 1);
+    switch (p.epilogue) {
+        case EPI_F32: return launch_t<EPI_F32>(ma, mb, md, args, grid, stream);
+        case EPI_GELU_I8: return launch_t<EPI_GELU_I8>(ma, mb, md, args, grid, stream);
+        case EPI_GELU_FP4: return launch_t<EPI_GELU_FP4>(ma, mb, md, args, grid, stream);
+    }
+    return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: unknown epilogue %d", p.epilogue);
+}
+
+int gemm_nvfp4_device_error(cudaStream_t stream, int* out_code) {
+    int rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    if (rc) return rc;
+    int code = 0;
+    rc = check_cuda(cudaMemcpyFromSymbol(&code, g_gemm_error, sizeof(int)), "cudaMemcpyFromSymbol(g_gemm_error)");
+    if (rc) return rc;
+    if (code != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    }
+    if (out_code) *out_code = code;
+    if (code != 0) return set_error(BNF4_ERR_DEVICE, "gemm_nvfp4: a bounded wait expired in the kernel (role code %d)", code);
+    return BNF4_OK;
+}
+
+}  // namespace bnf4

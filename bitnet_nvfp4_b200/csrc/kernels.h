@@ -1,0 +1,50 @@
+// Internal launcher interface between the translation units of the library (not installed).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "bnf4.h"
+
+namespace bnf4 {
+
+// ---------------------------------------------------------------------------------------------
+// Row quantisers (rowquant.cu). Parameter block = the public bnf4_rowquant_desc.
+// ---------------------------------------------------------------------------------------------
+enum RowFrontEnd : int {
+    FE_INT8 = BNF4_FE_INT8,                          // int8 rows in
+    FE_WQKV = BNF4_FE_WQKV,                          // stacked [Wq;Wk;Wv;wbeta] rows, per-group scale folded into the block scale
+    FE_EMBED_DENSE = BNF4_FE_EMBED_DENSE,            // emb[tok] + ns * noise[tok]
+    FE_EMBED_LOWRANK = BNF4_FE_EMBED_LOWRANK,        // emb[tok] + ns*c_r * sum_r A[tok,r] B[j,r]
+    FE_POS_GELU = BNF4_FE_POS_GELU,                  // gelu(in + pos) * act_scale
+    FE_POS_GELU_ABSMEAN = BNF4_FE_POS_GELU_ABSMEAN,  // the above, kept as the residual stream, then abs-mean normalised
+    FE_ACT = BNF4_FE_ACT,                            // none / relu / tanh / gelu*act_scale
+    FE_ABSMEAN = BNF4_FE_ABSMEAN,                    // abs-mean norm of int8 rows
+    FE_ADD_ABSMEAN = BNF4_FE_ADD_ABSMEAN,            // x8 = clip8(x8 + rint(y*add_scale)); abs-mean norm
+};
+
+constexpr int kMaxTVec = 16;  // rank-r projections per row (4 stacked groups x rank 4)
+
+using RowQuantParams = bnf4_rowquant_desc;
+int rowquant_dispatch(int front_end, RowQuantParams p, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Block-scaled FP4 GEMM on tcgen05 (gemm_tcgen05.cu). Parameter block = the public bnf4_gemm_desc.
+// ---------------------------------------------------------------------------------------------
+enum GemmEpilogue : int {
+    EPI_F32 = BNF4_EPI_F32,            // fp32 D
+    EPI_GELU_I8 = BNF4_EPI_GELU_I8,    // int8 D = clip8(rint(gelu(v) * act_scale))
+    EPI_GELU_FP4 = BNF4_EPI_GELU_FP4,  // the above re-quantised to e2m1 codes + ue4m3 scales (+ int8 copy, + t of the next GEMM)
+};
+
+using GemmParams = bnf4_gemm_desc;
+int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream);
+// Reads and clears the device-side error word of the GEMM kernels (0 = none). Synchronises the stream.
+int gemm_nvfp4_device_error(cudaStream_t stream, int* out_code);
+extern int g_gemm_allow_tma_store;
+
+void count_launch();
+
+}  // namespace bnf4

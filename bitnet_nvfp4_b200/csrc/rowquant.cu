@@ -1,0 +1,314 @@
+// Row-wise NVFP4 quantisers and their fused front-ends (bandwidth-bound kernels).
+//
+// One warp owns one row; lane l owns the 16-element scale blocks l, l+32, ... of that row, so a
+// 512-wide int8 row is one coalesced 16-byte load per lane, the e2m1 codes leave as one 8-byte
+// store per lane and the four scale bytes of a 64-column group leave as one 32-bit word.
+// Every variant produces the same three things the reference's kernels produce -- the int8 copy,
+// the packed e2m1 codes and the ue4m3 scale bytes in the tcgen05-friendly atom layout -- and can
+// additionally emit the exact int32 projections t[row][v] = sum_k q[row][k] * vec[v][k] that the
+// rank-r GEMM epilogue consumes.
+//
+// Reference semantics restated here (file:line in the reference project):
+//   plain int8 rows            src/cuda_kernels.cu:1545-1625   (nvfp4_quantize_a / _b)
+//   stacked QKV weights        src/cuda_kernels.cu:2748-2854   (nvfp4_quantize_wqkv_fused)
+//   embedding (+dense noise)   src/cuda_kernels.cu:2014-2109
+//   embedding (+rank-r noise)  src/cuda_kernels.cu:1360-1389   (element formula of embed_update_lora)
+//   + pos, GELU                src/cuda_kernels.cu:2260-2349
+//   activation / GELU          src/cuda_kernels.cu:1783-1878, 2500-2589
+//   abs-mean norm              src/cuda_kernels.cu:2928-3031
+//   residual add + norm        src/cuda_kernels.cu:3033-3143
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bnf4 {
+
+namespace {
+
+constexpr int kMaxBlocksPerLane = 8;  // rows of up to 32*8*16 = 4096 columns
+
+template <int FE, int NB>
+__global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p) {
+    const int warps_per_cta = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
+    if (row >= p.rows) return;
+
+    const int nblk = p.cols_out >> 4;
+    const int member = p.rows_per_member > 0 ? static_cast<int>(row / p.rows_per_member) : 0;
+    const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row % p.rows_per_member) : static_cast<int>(row);
+    const int pair = member >> 1;
+    const float ns = p.rows_per_member > 0 ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
+
+    int xw[NB][4];  // stage-1 int8 values of this lane's blocks, four per word
+    int sum_abs = 0;
+
+    // ---------------- stage 1: produce integer values ----------------
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const int kb = lane + 32 * i;
+        xw[i][0] = xw[i][1] = xw[i][2] = xw[i][3] = 0;
+        if (kb >= nblk) continue;
+        const int k0 = kb << 4;
+        int vals[16];
+        if constexpr (FE == FE_INT8 || FE == FE_ABSMEAN || FE == FE_WQKV) {
+            const int8_t* src;
+            if constexpr (FE == FE_WQKV) {
+                const int H = p.cols_in;
+                const int g = static_cast<int>(row) / H;
+                const int rig = static_cast<int>(row) - g * H;
+                src = (g == 0 ? p.wq : (g == 1 ? p.wk : (g == 2 ? p.wv : p.wb))) + static_cast<size_t>(g < 3 ? rig : 0) * H;
+            } else {
+                src = p.in_i8 + static_cast<size_t>(row) * p.ld_in;
+            }
+            if (p.vec_ok && k0 + 16 <= p.cols_in) {
+                const int4 raw = *reinterpret_cast<const int4*>(src + k0);
+                const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int e = 0; e < 16; ++e) vals[e] = static_cast<int>(static_cast<int8_t>((w[e >> 2] >> (8 * (e & 3))) & 0xff));
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) vals[e] = (k0 + e < p.cols_in) ? static_cast<int>(src[k0 + e]) : 0;
+            }
+        } else if constexpr (FE == FE_EMBED_DENSE || FE == FE_EMBED_LOWRANK) {
+            const int trow = p.row_mod > 0 ? static_cast<int>(row % p.row_mod) : static_cast<int>(row);
+            const int tok = static_cast<int>(p.tokens[static_cast<size_t>(trow) * p.token_stride]);
+            const int8_t* e_w = p.emb_w + static_cast<size_t>(tok) * p.cols_in;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const int j = k0 + e;
+                float f = static_cast<float>(e_w[j]);
+                if constexpr (FE == FE_EMBED_DENSE) {
+                    if (p.emb_noise != nullptr && ns != 0.0f) {
+                        const int8_t* e_n = p.emb_noise + static_cast<size_t>(pair) * p.noise_pair_stride + static_cast<size_t>(tok) * p.cols_in;
+                        f = fmaf(ns, static_cast<float>(e_n[j]), f);
+                    }
+                } else {
+                    if (ns != 0.0f) {
+                        const int8_t* A = p.embA + static_cast<size_t>(pair) * p.embA_pair_stride + static_cast<size_t>(tok) * p.rank;
+                        const int8_t* B = p.embB + static_cast<size_t>(pair) * p.embB_pair_stride + static_cast<size_t>(j) * p.rank;
+                        int pert = 0;
+                        for (int r = 0; r < p.rank; ++r) pert += static_cast<int>(A[r]) * static_cast<int>(B[r]);
+                        f = fmaf(ns * p.c_rank, static_cast<float>(pert), f);
+                    }
+                }
+                vals[e] = clip_int8(rint_to_int(f));
+            }
+        } else if constexpr (FE == FE_POS_GELU || FE == FE_POS_GELU_ABSMEAN || FE == FE_ACT) {
+            const float* src = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
+            float f[16];
+            if (p.vec_ok && k0 + 16 <= p.cols_in) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v4 = *reinterpret_cast<const float4*>(src + k0 + 4 * q);
+                    f[4 * q + 0] = v4.x; f[4 * q + 1] = v4.y; f[4 * q + 2] = v4.z; f[4 * q + 3] = v4.w;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) f[e] = (k0 + e < p.cols_in) ? src[k0 + e] : 0.0f;
+            }
+            if constexpr (FE == FE_ACT) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    float x = f[e];
+                    if (p.act_mode == 1) x = x < 0.0f ? 0.0f : x;
+                    else if (p.act_mode == 2) x = tanhf(__fdiv_rn(x, 127.0f)) * 127.0f;
+                    else if (p.act_mode == 3) x = gelu_tanh(x) * p.act_scale;
+                    vals[e] = (k0 + e < p.cols_in) ? clip_int8(rint_to_int(x)) : 0;
+                }
+            } else {
+                const int prow = p.pos_mod > 0 ? (row_in_member % p.pos_mod) : 0;
+                const float* pos = p.pos + static_cast<size_t>(prow) * p.cols_in;
+                const int8_t* pn = p.pos_noise != nullptr
+                                       ? p.pos_noise + static_cast<size_t>(pair) * p.noise_pair_stride + static_cast<size_t>(prow) * p.cols_in
+                                       : nullptr;
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    float pv = pos[k0 + e];
+                    if (pn != nullptr) pv = fmaf(ns, static_cast<float>(pn[k0 + e]), pv);
+                    const float x = gelu_tanh(f[e] + pv) * p.act_scale;
+                    vals[e] = clip_int8(rint_to_int(x));
+                }
+            }
+        } else if constexpr (FE == FE_ADD_ABSMEAN) {
+            int8_t* xr = p.inout_i8 + static_cast<size_t>(row) * p.cols_in;
+            const float* yr = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
+            const int4 raw = *reinterpret_cast<const int4*>(xr + k0);
+            const int w[4] = {raw.x, raw.y, raw.z, raw.w};
+            int upd[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 y4 = *reinterpret_cast<const float4*>(yr + k0 + 4 * q);
+                const float yy[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int old = static_cast<int>(static_cast<int8_t>((w[q] >> (8 * j)) & 0xff));
+                    const int v = clip_int8(old + rint_to_int(__fmul_rn(yy[j], p.add_scale)));
+                    vals[4 * q + j] = v;
+                    upd[q] |= (v & 0xff) << (8 * j);
+                }
+            }
+            *reinterpret_cast<int4*>(xr + k0) = make_int4(upd[0], upd[1], upd[2], upd[3]);
+        }
+        if constexpr (FE == FE_ABSMEAN || FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) sum_abs += abs(vals[e]);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) xw[i][q] = pack4_i8(vals[4 * q], vals[4 * q + 1], vals[4 * q + 2], vals[4 * q + 3]);
+    }
+
+    // ---------------- stage 2: abs-mean normalisation (integer-exact row sum) ----------------
+    float inv = 1.0f;
+    if constexpr (FE == FE_ABSMEAN || FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN) {
+        const int total = __reduce_add_sync(0xffffffffu, sum_abs);
+        float abs_mean = __fdiv_rn(static_cast<float>(total), static_cast<float>(p.cols_in));
+        if (abs_mean < 1.0f) abs_mean = 1.0f;
+        inv = __fdiv_rn(p.norm_scale, abs_mean);
+    }
+
+    // ---------------- stage 3: emit int8 copy, codes, scales, rank-r projections ----------------
+    int tacc[kMaxTVec];
+#pragma unroll
+    for (int v = 0; v < kMaxTVec; ++v) tacc[v] = 0;
+
+    const int k_atoms = sf_k_atoms(p.cols_out);
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const int kb = lane + 32 * i;
+        const bool active = kb < nblk;
+        if (!__any_sync(0xffffffffu, active)) continue;
+        const int k0 = kb << 4;
+        int w[4] = {0, 0, 0, 0};
+        if (active) {
+            if constexpr (FE == FE_POS_GELU_ABSMEAN) {
+                // residual stream = the pre-norm values
+                *reinterpret_cast<int4*>(p.inout_i8 + static_cast<size_t>(row) * p.cols_in + k0) =
+                    make_int4(xw[i][0], xw[i][1], xw[i][2], xw[i][3]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                int b[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int v = static_cast<int>(static_cast<int8_t>((xw[i][q] >> (8 * j)) & 0xff));
+                    if constexpr (FE == FE_ABSMEAN || FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN)
+                        v = clip_int8(rint_to_int(__fmul_rn(static_cast<float>(v), inv)));
+                    b[j] = v;
+                }
+                w[q] = pack4_i8(b[0], b[1], b[2], b[3]);
+            }
+            if (p.out_q != nullptr) {
+                int8_t* dst = p.out_q + static_cast<size_t>(row) * p.ld_q + k0;
+                if (p.vec_ok_q) *reinterpret_cast<int4*>(dst) = make_int4(w[0], w[1], w[2], w[3]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) dst[e] = static_cast<int8_t>((w[e >> 2] >> (8 * (e & 3))) & 0xff);
+                }
+            }
+        }
+        float row_scale = 1.0f;
+        if constexpr (FE == FE_WQKV) {
+            const int g = static_cast<int>(row) / p.cols_in;
+            row_scale = g == 0 ? p.q_scale : (g == 1 ? p.k_scale : (g == 2 ? p.v_scale : p.b_scale));
+        }
+        uint32_t sfb = 0, lo = 0, hi = 0;
+        if (active) {
+            quant_block16(w, row_scale, FE == FE_WQKV, sfb, lo, hi);
+            *reinterpret_cast<uint2*>(p.out_codes + (static_cast<size_t>(row) * p.cols_out + k0) / 2) = make_uint2(lo, hi);
+        }
+        // four neighbouring lanes hold the four scale bytes of one 32-bit word of the atom layout
+        const int base_lane = lane & ~3;
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) word |= (__shfl_sync(0xffffffffu, sfb, base_lane + j) & 0xffu) << (8 * j);
+        if (active && (lane & 3) == 0)
+            *reinterpret_cast<uint32_t*>(p.out_sf + sf_offset(static_cast<int>(row), kb, k_atoms)) = word;
+
+        if (p.nvec > 0 && active) {
+            const int8_t* tv = p.tvec + static_cast<size_t>(pair) * p.tvec_pair_stride + k0;
+#pragma unroll
+            for (int v = 0; v < kMaxTVec; ++v) {
+                if (v < p.nvec) {
+                    const int4 bv = *reinterpret_cast<const int4*>(tv + static_cast<size_t>(v) * p.cols_out);
+                    int a = tacc[v];
+                    a = __dp4a(w[0], bv.x, a);
+                    a = __dp4a(w[1], bv.y, a);
+                    a = __dp4a(w[2], bv.z, a);
+                    a = __dp4a(w[3], bv.w, a);
+                    tacc[v] = a;
+                }
+            }
+        }
+    }
+    if (p.nvec > 0) {
+#pragma unroll
+        for (int v = 0; v < kMaxTVec; ++v) {
+            if (v < p.nvec) {
+                const int tot = __reduce_add_sync(0xffffffffu, tacc[v]);
+                if (lane == 0) p.t_out[static_cast<size_t>(row) * p.nvec + v] = tot;
+            }
+        }
+    }
+}
+
+template <int FE>
+int launch(const RowQuantParams& p, cudaStream_t stream) {
+    if (p.rows <= 0 || p.cols_out <= 0) return BNF4_OK;
+    if ((p.cols_out & 15) != 0) return set_error(BNF4_ERR_INVALID, "rowquant: cols_out=%d must be a multiple of 16", p.cols_out);
+    if (p.cols_out > 32 * 16 * kMaxBlocksPerLane) return set_error(BNF4_ERR_INVALID, "rowquant: cols_out=%d exceeds %d", p.cols_out, 32 * 16 * kMaxBlocksPerLane);
+    if (p.nvec > kMaxTVec) return set_error(BNF4_ERR_INVALID, "rowquant: nvec=%d exceeds %d", p.nvec, kMaxTVec);
+    if (p.out_codes == nullptr || p.out_sf == nullptr) return set_error(BNF4_ERR_INVALID, "rowquant: null output");
+    if ((reinterpret_cast<uintptr_t>(p.out_codes) & 7) || (reinterpret_cast<uintptr_t>(p.out_sf) & 3))
+        return set_error(BNF4_ERR_INVALID, "rowquant: outputs must be 8-byte (codes) / 4-byte (scales) aligned");
+    const int warps = 8;
+    const unsigned ctas = static_cast<unsigned>((static_cast<long long>(p.rows) + warps - 1) / warps);
+    const int nblk = p.cols_out >> 4;
+    if (nblk <= 32) rowquant_kernel<FE, 1><<<ctas, warps * 32, 0, stream>>>(p);
+    else if (nblk <= 64) rowquant_kernel<FE, 2><<<ctas, warps * 32, 0, stream>>>(p);
+    else if (nblk <= 128) rowquant_kernel<FE, 4><<<ctas, warps * 32, 0, stream>>>(p);
+    else rowquant_kernel<FE, 8><<<ctas, warps * 32, 0, stream>>>(p);
+    return check_launch("rowquant_kernel");
+}
+
+bool aligned16(const void* ptr, long long ld_bytes) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && (ld_bytes & 15) == 0; }
+
+}  // namespace
+
+int rowquant_dispatch(int fe, RowQuantParams p, cudaStream_t stream) {
+    // vectorised access is a property of the caller's pointers and strides; decided once on the host
+    switch (fe) {
+        case FE_INT8: case FE_ABSMEAN:
+            p.vec_ok = aligned16(p.in_i8, p.ld_in) ? 1 : 0; break;
+        case FE_WQKV:
+            p.vec_ok = (aligned16(p.wq, p.cols_in) && aligned16(p.wk, p.cols_in) && aligned16(p.wv, p.cols_in) && aligned16(p.wb, p.cols_in)) ? 1 : 0; break;
+        case FE_POS_GELU: case FE_POS_GELU_ABSMEAN: case FE_ACT:
+            p.vec_ok = aligned16(p.in_f32, static_cast<long long>(p.ld_in) * 4) ? 1 : 0; break;
+        default: p.vec_ok = 1; break;
+    }
+    p.vec_ok_q = (p.out_q != nullptr && aligned16(p.out_q, p.ld_q)) ? 1 : 0;
+    if (fe == FE_ADD_ABSMEAN || fe == FE_POS_GELU_ABSMEAN) {
+        if (!aligned16(p.inout_i8, p.cols_in))
+            return set_error(BNF4_ERR_INVALID, "rowquant: residual stream must be 16-byte aligned with hidden %% 16 == 0");
+    }
+    if (fe == FE_ADD_ABSMEAN && !aligned16(p.in_f32, static_cast<long long>(p.ld_in) * 4))
+        return set_error(BNF4_ERR_INVALID, "rowquant: fp32 input must be 16-byte aligned");
+    if ((fe == FE_POS_GELU || fe == FE_POS_GELU_ABSMEAN || fe == FE_EMBED_DENSE || fe == FE_EMBED_LOWRANK || fe == FE_ADD_ABSMEAN || fe == FE_ABSMEAN) &&
+        p.cols_in != p.cols_out)
+        return set_error(BNF4_ERR_INVALID, "rowquant: this front-end needs cols_in == cols_out");
+    if (p.nvec > 0 && !aligned16(p.tvec, p.cols_out)) return set_error(BNF4_ERR_INVALID, "rowquant: projection vectors must be 16-byte aligned");
+    switch (fe) {
+        case FE_INT8: return launch<FE_INT8>(p, stream);
+        case FE_WQKV: return launch<FE_WQKV>(p, stream);
+        case FE_EMBED_DENSE: return launch<FE_EMBED_DENSE>(p, stream);
+        case FE_EMBED_LOWRANK: return launch<FE_EMBED_LOWRANK>(p, stream);
+        case FE_POS_GELU: return launch<FE_POS_GELU>(p, stream);
+        case FE_POS_GELU_ABSMEAN: return launch<FE_POS_GELU_ABSMEAN>(p, stream);
+        case FE_ACT: return launch<FE_ACT>(p, stream);
+        case FE_ABSMEAN: return launch<FE_ABSMEAN>(p, stream);
+        case FE_ADD_ABSMEAN: return launch<FE_ADD_ABSMEAN>(p, stream);
+    }
+    return set_error(BNF4_ERR_INVALID, "rowquant: unknown front-end %d", fe);
+}
+
+}  // namespace bnf4

@@ -1,0 +1,205 @@
+/*
+ * bnf4.h -- C ABI of libbnf4: the population-evaluation hot path of catid/bitnet_nvfp4 for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name starts with h_.
+ *   - `stream` is a cudaStream_t passed as void*; all work is stream-ordered, nothing synchronises
+ *     unless the comment says so. The caller makes the target device current (cudaSetDevice) first.
+ *   - The caller owns every buffer. Size helpers below give the byte counts.
+ *   - Every function returns 0 on success, or a BNF4_ERR_* code; bnf4_last_error() then returns a
+ *     message (thread-local). The reference's functions return void and swallow errors.
+ *   - There is no CPU fallback: without an sm_100 device every compute entry point fails with
+ *     BNF4_ERR_NO_DEVICE / BNF4_ERR_CUDA.
+ *
+ * Each entry point names the reference interface it replaces (file:line in the reference project).
+ * The reference's own C++ names (namespaces bitnet_cuda / efla_lm_cuda) are exported by the same
+ * library as thin wrappers over these functions, so the reference driver links unchanged.
+ */
+#ifndef BNF4_H_
+#define BNF4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BNF4_OK 0
+#define BNF4_ERR_INVALID 1
+#define BNF4_ERR_CUDA 2
+#define BNF4_ERR_UNSUPPORTED 3
+#define BNF4_ERR_DEVICE 4
+#define BNF4_ERR_NO_DEVICE 5
+
+/* ---------------------------------------------------------------------------------------------
+ * Library state
+ * ------------------------------------------------------------------------------------------- */
+const char* bnf4_last_error(void);
+const char* bnf4_version(void);
+/* Number of kernels this library has launched from this process (all threads). */
+unsigned long long bnf4_launch_count(void);
+/* Options: "gemm_tma_store" (1 default; 0 = direct-store epilogue). Returns BNF4_ERR_INVALID if unknown. */
+int bnf4_set_option(const char* name, int value);
+/* Reads and clears the device-side error word set by a kernel whose bounded wait expired.
+ * Synchronises `stream`. *code = 0 when clean. */
+int bnf4_device_error(void* stream, int* code);
+/* sizeof() of the two descriptor structs below, for bindings that mirror them (ctypes, cgo, JNI). */
+int bnf4_struct_sizes(int* rowquant_desc_bytes, int* gemm_desc_bytes);
+
+/* ---------------------------------------------------------------------------------------------
+ * Size helpers.  reference: nvfp4_matrix_bytes src/cuda_kernels.h:351-354,
+ * nvfp4_sfa_bytes / nvfp4_sfb_bytes src/cuda_kernels.cu:3836-3848.
+ * Scale factors: one ue4m3 byte per 16 K-elements, stored in 512-byte atoms of 128 rows x 4 blocks.
+ * ------------------------------------------------------------------------------------------- */
+size_t bnf4_nvfp4_matrix_bytes(int rows, int cols);
+size_t bnf4_nvfp4_sfa_bytes(int m, int n, int k);
+size_t bnf4_nvfp4_sfb_bytes(int m, int n, int k);
+
+/* ---------------------------------------------------------------------------------------------
+ * Quantisers: int8 / fp32 rows -> int8 copy + packed e2m1 codes + ue4m3 scale bytes.
+ * Column counts must be multiples of 16 (the reference also handles ragged tails; unused by its driver).
+ * ------------------------------------------------------------------------------------------- */
+/* reference: nvfp4_quantize_a src/cuda_kernels.cu:4013-4037 (kernel :1545-1625) */
+int bnf4_nvfp4_quantize_a(const int8_t* in, int m, int n, int k_in, int k_out, void* out, void* sfa, void* stream);
+/* reference: nvfp4_quantize_b src/cuda_kernels.cu:4240-4264 */
+int bnf4_nvfp4_quantize_b(const int8_t* in, int m, int n, int k_in, int k_out, void* out, void* sfb, void* stream);
+/* reference: nvfp4_quantize_wqkv_fused src/cuda_kernels.cu:4266-4306 (kernel :2748-2854) */
+int bnf4_nvfp4_quantize_wqkv_fused(const int8_t* wq, const int8_t* wk, const int8_t* wv, const int8_t* wb, int batch,
+                                   int hidden, int k_out, int rows_total, float q_scale, float k_scale, float v_scale,
+                                   float b_scale, void* out, void* sfb, void* stream);
+/* reference: embedding_lookup_noise_quantize_nvfp4 src/cuda_kernels.cu:4039-4086 (kernel :2014-2109) */
+int bnf4_embedding_lookup_noise_quantize_nvfp4(const uint8_t* tokens_t, int token_stride, const int8_t* emb_w,
+                                               const int8_t* emb_noise, int hidden, int batch, float noise_scale,
+                                               int anti_sign, int8_t* out_q, void* out_nvfp4, void* sfa, void* stream);
+/* reference: add_pos_gelu_quantize_nvfp4 src/cuda_kernels.cu:4088-4126 (kernel :2260-2349) */
+int bnf4_add_pos_gelu_quantize_nvfp4(const float* in, const float* pos_t, int hidden, int batch, float act_scale,
+                                     int8_t* out_q, void* out_nvfp4, void* sfa, void* stream);
+/* reference: activation_quantize_nvfp4 src/cuda_kernels.cu:4128-4160 (kernel :1783-1878) */
+int bnf4_activation_quantize_nvfp4(const float* in, int rows, int cols_in, int cols_out, int activation, int8_t* out_q,
+                                   void* out_nvfp4, void* sfa, void* stream);
+/* reference: gelu_quantize_nvfp4 src/cuda_kernels.cu:4162-4194 (kernel :2500-2589) */
+int bnf4_gelu_quantize_nvfp4(const float* in, int rows, int cols_in, int cols_out, float act_scale, int8_t* out_q,
+                             void* out_nvfp4, void* sfa, void* stream);
+/* reference: absmean_norm_q_nvfp4 src/cuda_kernels.cu:4196-4215 (kernel :2928-3031) */
+int bnf4_absmean_norm_q_nvfp4(const int8_t* in, int hidden, int batch, int cols_out, float scale, int8_t* out_q,
+                              void* out_nvfp4, void* sfa, void* stream);
+/* reference: add_scaled_to_int8_absmean_norm_q_nvfp4 src/cuda_kernels.cu:4217-4238 (kernel :3033-3143) */
+int bnf4_add_scaled_to_int8_absmean_norm_q_nvfp4(int8_t* inout, const float* in, int hidden, int batch, int cols_out,
+                                                 float add_scale, float norm_scale, int8_t* out_q, void* out_nvfp4,
+                                                 void* sfa, void* stream);
+
+/* Generic row quantiser with population addressing and rank-r projections (no reference counterpart;
+ * it is what the batched population driver uses). front_end: see BNF4_FE_*. */
+#define BNF4_FE_INT8 0
+#define BNF4_FE_WQKV 1
+#define BNF4_FE_EMBED_DENSE 2
+#define BNF4_FE_EMBED_LOWRANK 3
+#define BNF4_FE_POS_GELU 4
+#define BNF4_FE_POS_GELU_ABSMEAN 5
+#define BNF4_FE_ACT 6
+#define BNF4_FE_ABSMEAN 7
+#define BNF4_FE_ADD_ABSMEAN 8
+
+typedef struct bnf4_rowquant_desc {
+    int rows, cols_in, cols_out;
+    /* row -> member = row / rows_per_member -> pair = member / 2, sign + for even members, - for odd.
+     * rows_per_member == 0: a single member whose sign is anti_fixed. */
+    int rows_per_member;
+    int anti_fixed;
+    float sigma;  /* perturbation magnitude (0 disables noise) */
+    float c_rank; /* rank-r normalisation constant sqrt(3/8)/sqrt(rank) */
+    const int8_t* in_i8;
+    const float* in_f32;
+    int ld_in;
+    int8_t* inout_i8; /* int8 residual stream [rows][cols_in] */
+    const int8_t *wq, *wk, *wv, *wb;
+    float q_scale, k_scale, v_scale, b_scale;
+    const uint8_t* tokens;
+    int token_stride;
+    int row_mod; /* token row = row % row_mod (0: row) */
+    const int8_t* emb_w;
+    const int8_t* emb_noise; /* [pair][V][H] */
+    const int8_t* embA;      /* [pair][V][rank] */
+    const int8_t* embB;      /* [pair][H][rank] */
+    long long embA_pair_stride, embB_pair_stride;
+    int rank;
+    const float* pos;         /* [pos rows][H] */
+    const int8_t* pos_noise;  /* [pair][pos rows][H] or NULL */
+    int pos_mod;              /* positional row = row_in_member % pos_mod (0: row 0) */
+    long long noise_pair_stride;
+    int act_mode; /* 0 none, 1 relu, 2 tanh(x/127)*127, 3 gelu(x)*act_scale */
+    float act_scale, add_scale, norm_scale;
+    int8_t* out_q; /* optional int8 copy */
+    int ld_q;
+    uint8_t* out_codes;
+    uint8_t* out_sf;
+    /* t_out[row][v] = sum_k q[row][k] * tvec[pair][v][k], exact int32 */
+    const int8_t* tvec;
+    long long tvec_pair_stride;
+    int nvec;
+    int32_t* t_out;
+    int vec_ok, vec_ok_q; /* set by the library */
+} bnf4_rowquant_desc;
+
+int bnf4_rowquant(int front_end, const bnf4_rowquant_desc* desc, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Block-scaled FP4 GEMM (tcgen05).  A [M][K] and B [N][K] are K-major packed e2m1, k % 64 == 0.
+ * ------------------------------------------------------------------------------------------- */
+/* reference: gemm_ternary_f_nvfp4 src/cuda_kernels.cu:4342-4473.  D = alpha*A*B^T + beta*C, fp32 row-major [m][n]. */
+int bnf4_gemm_ternary_f_nvfp4(const void* a, const void* b, const void* sfa, const void* sfb, int m, int n, int k,
+                              float alpha, float beta, const float* c, float* d, void* stream);
+/* reference: gemm_ternary_f_nvfp4_gelu_i8 src/cuda_kernels.cu:4475-4607.  D8 = clip8(rint(gelu(alpha*A*B^T + beta*C) * act_scale)). */
+int bnf4_gemm_ternary_f_nvfp4_gelu_i8(const void* a, const void* b, const void* sfa, const void* sfb, int m, int n,
+                                      int k, float alpha, float beta, const float* c, float act_scale, int8_t* d,
+                                      void* stream);
+/* reference: nvfp4_prepare_gemm src/cuda_kernels.cu:3902-4011 (plan warm-up; here: argument validation only). */
+int bnf4_nvfp4_prepare_gemm(const void* a, const void* b, const void* sfa, const void* sfb, int m, int n, int k,
+                            float alpha, float beta, const float* c, float* d, void* stream);
+
+#define BNF4_EPI_F32 0
+#define BNF4_EPI_GELU_I8 1
+#define BNF4_EPI_GELU_FP4 2
+
+/* Full form: strides, fused epilogues and the rank-r perturbation
+ *   D += s_member * sum_r t[m][g*rank + r] * A_pair[n][r]
+ * (math of the reference's lora kernels, src/cuda_kernels.cu:370-410, 1271-1305, which its driver never calls). */
+typedef struct bnf4_gemm_desc {
+    const void* a;
+    const void* b;
+    const void* sfa;
+    const void* sfb;
+    int m, n, k;
+    float alpha, beta;
+    const float* c;
+    int ldc;
+    float* d;
+    int ldd;
+    int epilogue;
+    float act_scale;
+    int8_t* d_i8;
+    int ld_i8;
+    uint8_t* d_codes; /* BNF4_EPI_GELU_FP4: codes [M][N/2] and scale atoms for (M,N) */
+    uint8_t* d_sf;
+    int rank;            /* 0 disables the perturbation; at most 4 */
+    int rows_per_member; /* member = row / rows_per_member (0: one member, positive sign) */
+    const int32_t* lora_t; /* [M][t_stride] */
+    int t_stride;
+    const int8_t* lora_A; /* [pair][N][rank] */
+    long long lora_A_pair_stride;
+    float lora_scale; /* magnitude; the member's sign is applied by the kernel */
+    int group_cols;   /* columns per stacked group (0: one group); group g reads t[g*rank ..] */
+    const int8_t* next_tvec; /* BNF4_EPI_GELU_FP4: [pair][next_nvec][N] */
+    long long next_tvec_pair_stride;
+    int next_nvec;
+    int32_t* next_t; /* [M][next_nvec], zeroed by the caller; accumulated with integer atomics */
+} bnf4_gemm_desc;
+
+int bnf4_gemm_nvfp4_ex(const bnf4_gemm_desc* desc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BNF4_H_ */
