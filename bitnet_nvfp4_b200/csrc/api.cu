@@ -1,10 +1,13 @@
 // extern "C" surface of libbnf4: library state, size helpers, quantisers and GEMM entry points.
 // Each function mirrors the argument meaning of the reference function named in include/bnf4.h.
 
+#include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -195,6 +198,43 @@ int bnf4_nvfp4_prepare_gemm(const void* a, const void* b, const void* sfa, const
                             float /*alpha*/, float /*beta*/, const float* /*c*/, float* d, void* /*stream*/) {
     if (!a || !b || !sfa || !sfb || !d) return set_error(BNF4_ERR_INVALID, "nvfp4_prepare_gemm: null operand");
     if (m <= 0 || n <= 0 || k <= 0 || (k % 64) != 0) return set_error(BNF4_ERR_INVALID, "nvfp4_prepare_gemm: unsupported shape %dx%dx%d", m, n, k);
+    return BNF4_OK;
+}
+
+// Host function (reference: shape_pair_weights src/train_efla_lm.cpp:3898-3952). Ties in the rank sort are
+// broken by index so that every rank of a data-parallel job shapes identically.
+int bnf4_shape_pair_weights(float* w, int n, int mode, float clip) {
+    if (n <= 0) return BNF4_OK;
+    if (!w) return set_error(BNF4_ERR_INVALID, "shape_pair_weights: null pointer");
+    if (mode == 2) {
+        for (int i = 0; i < n; ++i) w[i] = w[i] > 0.0f ? 1.0f : (w[i] < 0.0f ? -1.0f : 0.0f);
+        return BNF4_OK;
+    }
+    if (mode == 0) {
+        std::vector<int> order(n);
+        for (int i = 0; i < n; ++i) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return w[a] < w[b]; });
+        std::vector<float> ranked(n);
+        if (n == 1) ranked[0] = 0.0f;
+        else
+            for (int r = 0; r < n; ++r) ranked[order[r]] = static_cast<float>(r) / static_cast<float>(n - 1) - 0.5f;
+        for (int i = 0; i < n; ++i) w[i] = ranked[i];
+    } else if (mode != 1) {
+        return set_error(BNF4_ERR_INVALID, "shape_pair_weights: unknown mode %d", mode);
+    }
+    float mean = 0.0f;
+    for (int i = 0; i < n; ++i) mean += w[i];
+    mean /= static_cast<float>(n);
+    float var = 0.0f;
+    for (int i = 0; i < n; ++i) var += (w[i] - mean) * (w[i] - mean);
+    var /= static_cast<float>(n);
+    const float stdv = std::sqrt(var) + 1e-6f;
+    for (int i = 0; i < n; ++i) {
+        float d = (w[i] - mean) / stdv;
+        if (d > clip) d = clip;
+        if (d < -clip) d = -clip;
+        w[i] = d;
+    }
     return BNF4_OK;
 }
 

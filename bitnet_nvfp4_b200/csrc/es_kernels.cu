@@ -1,0 +1,473 @@
+// Cross-entropy fitness, counter-hash noise and the ES weight update (bandwidth / integer-pipe kernels).
+//
+// Reference semantics restated here (file:line in the reference project):
+//   cross entropy          src/efla_lm_kernels.cu:252-311
+//   noise fill             src/efla_lm_kernels.cu:73-86, 352-385
+//   pair seeds             src/efla_lm_kernels.cu:1844-1852
+//   Z and sum of squares   src/efla_lm_kernels.cu:1854-1890
+//   inv_rms                src/efla_lm_kernels.cu:2003-2021
+//   shadow update          src/efla_lm_kernels.cu:1892-1922
+// All reductions run in a fixed order so that every rank of a data-parallel job computes identical bits
+// (the reference uses unordered float atomics).
+
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bnf4 {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// Cross entropy. One warp per row; lane l holds logits l, l+32, ...
+// ------------------------------------------------------------------------------------------------
+constexpr int kCeMaxPerLane = 32;  // vocab <= 1024
+
+__device__ __forceinline__ float ce_row_loss(const float* lg, const float* bias, const float* noise_f, const int8_t* noise_i,
+                                             float bns, int vocab, int y, int lane) {
+    float v[kCeMaxPerLane];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kCeMaxPerLane; ++j) {
+        const int i = lane + 32 * j;
+        if (i < vocab) {
+            float x = lg[i];
+            if (bias != nullptr) x += bias[i];
+            if (noise_f != nullptr) x = fmaf(bns, noise_f[i], x);
+            if (noise_i != nullptr) x = fmaf(bns, static_cast<float>(noise_i[i]), x);
+            v[j] = x;
+            mx = fmaxf(mx, x);
+        } else {
+            v[j] = -INFINITY;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kCeMaxPerLane; ++j) {
+        const int i = lane + 32 * j;
+        if (i < vocab) sum += expf(v[j] - mx);
+    }
+    sum = warp_sum_f(sum);
+    // the target's value lives in lane y%32, slot y/32
+    float vy = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kCeMaxPerLane; ++j)
+        if (j == (y >> 5)) vy = v[j];
+    vy = __shfl_sync(0xffffffffu, vy, y & 31);
+    return -(vy - mx - logf(sum + 1e-9f));
+}
+
+// API form: a single CTA sums the rows of one token step in a fixed order and adds the total to *loss_accum.
+__global__ void __launch_bounds__(256) ce_step_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                      const float* __restrict__ bias_noise, float bns,
+                                                      const uint8_t* __restrict__ targets_t, int token_stride, int vocab, int batch,
+                                                      float* loss_accum) {
+    __shared__ float part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float acc = 0.0f;
+    for (int b = warp; b < batch; b += 8) {
+        const int y = static_cast<int>(targets_t[static_cast<size_t>(b) * token_stride]);
+        acc += ce_row_loss(logits + static_cast<size_t>(b) * vocab, bias, bias_noise, nullptr, bns, vocab, y, lane);
+    }
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < 8; ++w) t += part[w];
+        loss_accum[0] += t;
+    }
+}
+
+// Population form: grid (16 chunks, members). partial[member*16 + chunk] = sum of the chunk's row losses.
+constexpr int kCeChunks = 16;
+__global__ void __launch_bounds__(256) ce_population_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                                            const int8_t* __restrict__ bias_noise, float sigma,
+                                                            const uint8_t* __restrict__ targets, int vocab, int rows_per_member,
+                                                            float* __restrict__ partial) {
+    __shared__ float part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int member = blockIdx.y, chunk = blockIdx.x;
+    const int per = (rows_per_member + kCeChunks - 1) / kCeChunks;
+    const int r0 = chunk * per, r1 = min(rows_per_member, r0 + per);
+    const float bns = (member & 1) ? -sigma : sigma;
+    const int8_t* nz = bias_noise != nullptr ? bias_noise + static_cast<size_t>(member >> 1) * vocab : nullptr;
+    float acc = 0.0f;
+    for (int r = r0 + warp; r < r1; r += 8) {
+        const size_t row = static_cast<size_t>(member) * rows_per_member + r;
+        acc += ce_row_loss(logits + row * ld, bias, nullptr, nz, bns, vocab, static_cast<int>(targets[r]), lane);
+    }
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < 8; ++w) t += part[w];
+        partial[member * kCeChunks + chunk] = t;
+    }
+}
+
+__global__ void ce_finalize_kernel(const float* __restrict__ partial, int members, int rows_per_member, float* __restrict__ loss_mean) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= members) return;
+    double t = 0.0;
+    for (int c = 0; c < kCeChunks; ++c) t += static_cast<double>(partial[m * kCeChunks + c]);
+    loss_mean[m] = static_cast<float>(t / static_cast<double>(rows_per_member));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Noise
+// ------------------------------------------------------------------------------------------------
+__global__ void fill_noise_kernel(int8_t* __restrict__ out, size_t n, uint64_t seed, int use_clt, int clt_k) {
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx < n) out[idx] = static_cast<int8_t>(noise_hash(seed, idx, use_clt != 0, clt_k));
+}
+__global__ void fill_noise_batched_kernel(const bnf4_noise_desc* __restrict__ descs, int num_desc, int use_clt, int clt_k) {
+    const int di = blockIdx.y;
+    if (di >= num_desc) return;
+    const bnf4_noise_desc d = descs[di];
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx < d.n) d.out[idx] = static_cast<int8_t>(noise_hash(d.seed, idx, use_clt != 0, clt_k));
+}
+__global__ void fill_float_noise_kernel(float* __restrict__ out, int n, uint64_t seed, int use_clt, int clt_k) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) out[idx] = static_cast<float>(noise_hash(seed, static_cast<uint64_t>(idx), use_clt != 0, clt_k));
+}
+__global__ void pair_seeds_kernel(uint64_t base_seed, uint64_t epoch, int pairs, uint64_t* __restrict__ out) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < pairs) out[p] = mix_u64(base_seed, mix_u64(epoch, static_cast<uint64_t>(p)));
+}
+
+// ------------------------------------------------------------------------------------------------
+// ES update
+// ------------------------------------------------------------------------------------------------
+__global__ void init_shadow_kernel(const int8_t* __restrict__ w, float* __restrict__ shadow, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) shadow[i] = static_cast<float>(w[i]);
+}
+
+// Z for the dense (full-matrix noise) form; 256 threads per block, one element each.
+__global__ void __launch_bounds__(256) z_dense_kernel(const float* __restrict__ pair_weights, const uint64_t* __restrict__ pair_seeds,
+                                                      uint64_t salt, int pairs, int n, int use_clt, int clt_k, float* __restrict__ Z) {
+    extern __shared__ uint8_t zsm[];
+    uint64_t* seeds = reinterpret_cast<uint64_t*>(zsm);
+    float* wts = reinterpret_cast<float*>(zsm + sizeof(uint64_t) * 256);
+    const int idx = blockIdx.x * 256 + threadIdx.x;
+    float z = 0.0f;
+    for (int p0 = 0; p0 < pairs; p0 += 256) {
+        __syncthreads();
+        if (p0 + threadIdx.x < pairs) {
+            seeds[threadIdx.x] = mix_u64(pair_seeds[p0 + threadIdx.x], salt);
+            wts[threadIdx.x] = pair_weights[p0 + threadIdx.x];
+        }
+        __syncthreads();
+        const int cnt = min(256, pairs - p0);
+        if (idx < n) {
+            for (int p = 0; p < cnt; ++p) {
+                const float w = wts[p];
+                if (w == 0.0f) continue;
+                z = fmaf(w, static_cast<float>(noise_hash(seeds[p], static_cast<uint64_t>(idx), use_clt != 0, clt_k)), z);
+            }
+        }
+    }
+    if (idx < n) Z[idx] = z;
+}
+
+// Z for the rank-r form. Block = 16 rows x 64 columns of one matrix, 256 threads, 4 columns per thread.
+__global__ void __launch_bounds__(256) z_lowrank_kernel(const float* __restrict__ pair_weights, const int8_t* __restrict__ A,
+                                                        long long A_ps, const int8_t* __restrict__ B, long long B_ps, int pairs,
+                                                        int rows, int cols, int rank, float cscale, float* __restrict__ Z) {
+    constexpr int PC = 32;  // pairs per shared-memory chunk
+    __shared__ int8_t a_sh[PC][16][4];
+    __shared__ __align__(4) int8_t b_sh[PC][4][64];
+    __shared__ float w_sh[PC];
+    const int tr = threadIdx.x >> 4;        // 0..15 row in tile
+    const int tc = (threadIdx.x & 15) * 4;  // column group in tile
+    const int i = blockIdx.y * 16 + tr;
+    const int j0 = blockIdx.x * 64 + tc;
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p0 = 0; p0 < pairs; p0 += PC) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < PC * 16 * 4; e += 256) {
+            const int pp = e / 64, rr = (e / 4) % 16, r = e % 4;
+            const int gi = blockIdx.y * 16 + rr;
+            int8_t v = 0;
+            if (p0 + pp < pairs && gi < rows && r < rank) v = A[static_cast<size_t>(p0 + pp) * A_ps + static_cast<size_t>(gi) * rank + r];
+            a_sh[pp][rr][r] = v;
+        }
+        for (int e = threadIdx.x; e < PC * 4 * 64; e += 256) {
+            const int pp = e / 256, r = (e / 64) % 4, c = e % 64;
+            const int gj = blockIdx.x * 64 + c;
+            int8_t v = 0;
+            if (p0 + pp < pairs && gj < cols && r < rank) v = B[static_cast<size_t>(p0 + pp) * B_ps + static_cast<size_t>(r) * cols + gj];
+            b_sh[pp][r][c] = v;
+        }
+        if (threadIdx.x < PC) w_sh[threadIdx.x] = (p0 + threadIdx.x < pairs) ? pair_weights[p0 + threadIdx.x] : 0.0f;
+        __syncthreads();
+        const int cnt = min(PC, pairs - p0);
+        for (int pp = 0; pp < cnt; ++pp) {
+            const float w = w_sh[pp];
+            int e[4] = {0, 0, 0, 0};
+            for (int r = 0; r < rank; ++r) {
+                const int a = a_sh[pp][tr][r];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) e[c] += a * static_cast<int>(b_sh[pp][r][tc + c]);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) z[c] = fmaf(w, static_cast<float>(e[c]), z[c]);
+        }
+    }
+    if (i < rows) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (j0 + c < cols) Z[static_cast<size_t>(i) * cols + j0 + c] = __fmul_rn(cscale, z[c]);
+    }
+}
+
+// Sum of squares, stage 1: block b reduces Z[256b .. 256b+255] with the reference's shared-memory tree.
+__global__ void __launch_bounds__(256) sumsq_blocks_kernel(const float* __restrict__ Z, int n, float* __restrict__ partial) {
+    __shared__ float sh[256];
+    const int idx = blockIdx.x * 256 + threadIdx.x;
+    const float z = idx < n ? Z[idx] : 0.0f;
+    sh[threadIdx.x] = __fmul_rn(z, z);
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partial[blockIdx.x] = sh[0];
+}
+// stage 2: one warp adds the block partials in double (lane-contiguous ranges, then lanes in order) and
+// accumulates into *sumsq.
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int nblocks, float* sumsq) {
+    __shared__ double lane_sum[32];
+    const int lane = threadIdx.x;
+    const int per = (nblocks + 31) / 32;
+    double t = 0.0;
+    for (int b = lane * per; b < min(nblocks, (lane + 1) * per); ++b) t += static_cast<double>(partial[b]);
+    lane_sum[lane] = t;
+    __syncwarp();
+    if (lane == 0) {
+        double tot = 0.0;
+        for (int l = 0; l < 32; ++l) tot += lane_sum[l];
+        sumsq[0] += static_cast<float>(tot);
+    }
+}
+
+__global__ void inv_rms_kernel(const float* __restrict__ sumsq, float* __restrict__ rms_ema, int use_adaptive, float beta, float eps,
+                               int n, float* __restrict__ inv_rms_out) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    float inv = 1.0f;
+    if (use_adaptive) {
+        const float ms = __fdiv_rn(sumsq[0], static_cast<float>(n));
+        float ema = rms_ema[0];
+        if (ema == 0.0f) ema = ms;
+        ema = fmaf(beta, ema, __fmul_rn(1.0f - beta, ms));
+        rms_ema[0] = ema;
+        inv = __fdiv_rn(1.0f, __fsqrt_rn(ema + eps));
+    }
+    inv_rms_out[0] = inv;
+}
+
+__global__ void update_shadow_kernel(int8_t* __restrict__ w, float* __restrict__ shadow, const float* __restrict__ Z, int n,
+                                     const float* __restrict__ inv_rms_dev, float inv_rms_host, float lr, float thresh) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float inv = inv_rms_dev != nullptr ? inv_rms_dev[0] : inv_rms_host;
+    const float g = __fmul_rn(inv, Z[i]);
+    if (fabsf(g) < thresh) return;
+    const float s = fmaf(lr, g, shadow[i]);
+    shadow[i] = s;
+    w[i] = static_cast<int8_t>(clip_ternary(__float2int_rn(s)));
+}
+
+__global__ void update_vector_kernel(float* __restrict__ v, const float* __restrict__ Z, int n, const float* __restrict__ inv_rms,
+                                     float lr, float thresh) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = __fmul_rn(inv_rms[0], Z[i]);
+    if (fabsf(g) < thresh) return;
+    v[i] = fmaf(lr, g, v[i]);
+}
+
+__global__ void add_scaled_kernel(float* __restrict__ out, const float* __restrict__ noise, int n, float scale) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = fmaf(scale, noise[i], out[i]);
+}
+
+// library-owned scratch for the block partials of sum(Z^2), one per device
+struct Scratch {
+    float* ptr = nullptr;
+    size_t floats = 0;
+};
+std::mutex g_scratch_mu;
+Scratch g_scratch[64];
+
+int get_scratch(size_t floats, float** out) {
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return set_error(BNF4_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    Scratch& s = g_scratch[dev];
+    if (s.floats < floats) {
+        // stream-ordered users of the old buffer may still be running: synchronise before freeing it
+        if (s.ptr != nullptr) {
+            rc = check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+            if (rc) return rc;
+            cudaFree(s.ptr);
+            s.ptr = nullptr;
+            s.floats = 0;
+        }
+        const size_t want = floats < 65536 ? 65536 : floats;
+        rc = check_cuda(cudaMalloc(&s.ptr, want * sizeof(float)), "cudaMalloc(sumsq scratch)");
+        if (rc) return rc;
+        s.floats = want;
+    }
+    *out = s.ptr;
+    return BNF4_OK;
+}
+
+int sumsq_into(const float* Z, int n, float* sumsq, cudaStream_t st) {
+    const int nblocks = (n + 255) / 256;
+    float* partial = nullptr;
+    int rc = get_scratch(static_cast<size_t>(nblocks), &partial);
+    if (rc) return rc;
+    sumsq_blocks_kernel<<<nblocks, 256, 0, st>>>(Z, n, partial);
+    rc = check_launch("sumsq_blocks_kernel");
+    if (rc) return rc;
+    sumsq_final_kernel<<<1, 32, 0, st>>>(partial, nblocks, sumsq);
+    return check_launch("sumsq_final_kernel");
+}
+
+}  // namespace
+
+int sumsq_with_scratch(const float* Z, int n, float* partial, float* sumsq, cudaStream_t st) {
+    const int nblocks = (n + 255) / 256;
+    sumsq_blocks_kernel<<<nblocks, 256, 0, st>>>(Z, n, partial);
+    int rc = check_launch("sumsq_blocks_kernel");
+    if (rc) return rc;
+    sumsq_final_kernel<<<1, 32, 0, st>>>(partial, nblocks, sumsq);
+    return check_launch("sumsq_final_kernel");
+}
+
+}  // namespace bnf4
+
+using namespace bnf4;
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+int bnf4_cross_entropy_loss(const float* logits, const float* bias, const float* bias_noise, float bias_noise_scale,
+                            const uint8_t* targets_t, int token_stride, int vocab, int batch, float* loss_accum, void* stream) {
+    if (batch <= 0) return BNF4_OK;
+    if (!logits || !targets_t || !loss_accum) return set_error(BNF4_ERR_INVALID, "cross_entropy_loss: null pointer");
+    if (vocab <= 0 || vocab > 32 * kCeMaxPerLane) return set_error(BNF4_ERR_INVALID, "cross_entropy_loss: vocab=%d outside [1,%d]", vocab, 32 * kCeMaxPerLane);
+    ce_step_kernel<<<1, 256, 0, S(stream)>>>(logits, bias, bias_noise, bias_noise_scale, targets_t, token_stride, vocab, batch, loss_accum);
+    return check_launch("ce_step_kernel");
+}
+
+int bnf4_cross_entropy_population(const float* logits, int ld, const float* bias, const int8_t* bias_noise, float sigma,
+                                  const uint8_t* targets, int vocab, int members, int rows_per_member, float* partial,
+                                  float* loss_mean, void* stream) {
+    if (members <= 0 || rows_per_member <= 0) return BNF4_OK;
+    if (!logits || !targets || !partial || !loss_mean) return set_error(BNF4_ERR_INVALID, "cross_entropy_population: null pointer");
+    if (vocab <= 0 || vocab > 32 * kCeMaxPerLane) return set_error(BNF4_ERR_INVALID, "cross_entropy_population: vocab=%d", vocab);
+    if (members > 65535) return set_error(BNF4_ERR_INVALID, "cross_entropy_population: at most 65535 members per call");
+    ce_population_kernel<<<dim3(kCeChunks, members), 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
+    int rc = check_launch("ce_population_kernel");
+    if (rc) return rc;
+    ce_finalize_kernel<<<(members + 127) / 128, 128, 0, S(stream)>>>(partial, members, rows_per_member, loss_mean);
+    return check_launch("ce_finalize_kernel");
+}
+
+int bnf4_fill_ternary_noise(int8_t* out, size_t n, uint64_t seed, int use_clt, int clt_k, void* stream) {
+    if (n == 0) return BNF4_OK;
+    if (!out) return set_error(BNF4_ERR_INVALID, "fill_ternary_noise: null pointer");
+    fill_noise_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, S(stream)>>>(out, n, seed, use_clt, clt_k);
+    return check_launch("fill_noise_kernel");
+}
+
+int bnf4_fill_ternary_noise_batched(const bnf4_noise_desc* descs, int num_desc, int max_blocks, int use_clt, int clt_k, void* stream) {
+    if (num_desc <= 0 || max_blocks <= 0) return BNF4_OK;
+    if (!descs) return set_error(BNF4_ERR_INVALID, "fill_ternary_noise_batched: null pointer");
+    fill_noise_batched_kernel<<<dim3(max_blocks, num_desc), 256, 0, S(stream)>>>(descs, num_desc, use_clt, clt_k);
+    return check_launch("fill_noise_batched_kernel");
+}
+
+int bnf4_fill_float_noise(float* out, int n, uint64_t seed, int use_clt, int clt_k, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    fill_float_noise_kernel<<<(n + 255) / 256, 256, 0, S(stream)>>>(out, n, seed, use_clt, clt_k);
+    return check_launch("fill_float_noise_kernel");
+}
+
+int bnf4_init_shadow_from_weights(const int8_t* w, float* shadow, int n, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    init_shadow_kernel<<<(n + 255) / 256, 256, 0, S(stream)>>>(w, shadow, n);
+    return check_launch("init_shadow_kernel");
+}
+
+int bnf4_fill_pair_seeds(uint64_t base_seed, uint64_t epoch, int pairs, uint64_t* out, void* stream) {
+    if (pairs <= 0) return BNF4_OK;
+    pair_seeds_kernel<<<(pairs + 255) / 256, 256, 0, S(stream)>>>(base_seed, epoch, pairs, out);
+    return check_launch("pair_seeds_kernel");
+}
+
+int bnf4_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int n, int use_clt,
+                         int clt_k, float* Z, float* sumsq, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    if (!pair_weights || !pair_seeds || !Z || !sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq: null pointer");
+    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), S(stream)>>>(pair_weights, pair_seeds, salt, pairs, n, use_clt, clt_k, Z);
+    const int rc = check_launch("z_dense_kernel");
+    if (rc) return rc;
+    return sumsq_into(Z, n, sumsq, S(stream));
+}
+
+int bnf4_compute_z_sumsq_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
+                                 long long B_pair_stride, int pairs, int rows, int cols, int rank, float cscale, float* Z,
+                                 float* sumsq, void* stream) {
+    if (rows <= 0 || cols <= 0) return BNF4_OK;
+    if (!pair_weights || !A || !B || !Z || !sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: null pointer");
+    if (rank < 1 || rank > 4) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: rank=%d outside [1,4]", rank);
+    const dim3 grid((cols + 63) / 64, (rows + 15) / 16);
+    z_lowrank_kernel<<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, rank, cscale, Z);
+    const int rc = check_launch("z_lowrank_kernel");
+    if (rc) return rc;
+    return sumsq_into(Z, rows * cols, sumsq, S(stream));
+}
+
+int bnf4_update_inv_rms(const float* sumsq, float* rms_ema, int use_adaptive, float adaptive_beta, float adaptive_eps, int n,
+                        float* inv_rms, void* stream) {
+    if (!sumsq || !rms_ema || !inv_rms) return set_error(BNF4_ERR_INVALID, "update_inv_rms: null pointer");
+    inv_rms_kernel<<<1, 1, 0, S(stream)>>>(sumsq, rms_ema, use_adaptive, adaptive_beta, adaptive_eps, n, inv_rms);
+    return check_launch("inv_rms_kernel");
+}
+
+int bnf4_update_shadow_ternary_device(int8_t* w, float* shadow, const float* Z, int n, const float* inv_rms, float lr,
+                                      float thresh, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    if (!inv_rms) return set_error(BNF4_ERR_INVALID, "update_shadow_ternary_device: null inv_rms");
+    update_shadow_kernel<<<(n + 255) / 256, 256, 0, S(stream)>>>(w, shadow, Z, n, inv_rms, 0.0f, lr, thresh);
+    return check_launch("update_shadow_kernel");
+}
+
+int bnf4_update_shadow_ternary(int8_t* w, float* shadow, const float* Z, int n, float inv_rms, float lr, float thresh, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    update_shadow_kernel<<<(n + 255) / 256, 256, 0, S(stream)>>>(w, shadow, Z, n, nullptr, inv_rms, lr, thresh);
+    return check_launch("update_shadow_kernel");
+}
+
+int bnf4_update_vector_device(float* v, const float* Z, int n, const float* inv_rms, float lr, float thresh, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    update_vector_kernel<<<(n + 255) / 256, 256, 0, S(stream)>>>(v, Z, n, inv_rms, lr, thresh);
+    return check_launch("update_vector_kernel");
+}
+
+int bnf4_add_scaled(float* out, const float* noise, int n, float scale, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    add_scaled_kernel<<<(n + 255) / 256, 256, 0, S(stream)>>>(out, noise, n, scale);
+    return check_launch("add_scaled_kernel");
+}
+
+}  // extern "C"

@@ -45,6 +45,10 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream);
 int gemm_nvfp4_device_error(cudaStream_t stream, int* out_code);
 extern int g_gemm_allow_tma_store;
 
+// EFLA recurrence (efla.cu). Parameter block = the public bnf4_efla_desc.
+using EflaParams = bnf4_efla_desc;
+int efla_launch(const EflaParams& p, cudaStream_t stream);
+
 void count_launch();
 
 }  // namespace bnf4

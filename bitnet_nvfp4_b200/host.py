@@ -154,3 +154,119 @@ def gemm_nvfp4_ex(**kw):
     for k, v in kw.items():
         setattr(g, k, _p(v) if isinstance(v, torch.Tensor) else v)
     _l.check(_l.load().bnf4_gemm_nvfp4_ex(C.byref(g), _stream()))
+
+
+# ------------------------------------------------------------------------------------------ ternary GEMM / rank-r helpers
+def gemm_ternary_f(x, w, scale_x, out_scale):
+    batch, cols = x.shape
+    rows = w.shape[0]
+    out = torch.empty((batch, rows), dtype=torch.float32, device=x.device)
+    _l.check(_l.load().bnf4_gemm_ternary_f(_p(x), _p(w), _p(scale_x), rows, cols, batch, out_scale, _p(out), _stream()))
+    return out
+
+
+def lora_compute_t(x, B, rank):
+    batch, cols = x.shape
+    t = torch.empty((batch, rank), dtype=torch.int32, device=x.device)
+    _l.check(_l.load().bnf4_lora_compute_t(_p(x), _p(B), cols, batch, rank, _p(t), _stream()))
+    return t
+
+
+def lora_add(t, A, rows, scale, out):
+    batch, rank = t.shape
+    _l.check(_l.load().bnf4_lora_add(_p(t), _p(A), rows, batch, rank, scale, _p(out), _stream()))
+    return out
+
+
+def split_qkvb_fused(qkv, hidden, beta_bias):
+    batch, fused_cols = qkv.shape
+    q, k, v = (torch.empty((batch, hidden), dtype=torch.float32, device=qkv.device) for _ in range(3))
+    beta = torch.empty(batch, dtype=torch.float32, device=qkv.device)
+    _l.check(_l.load().bnf4_split_qkvb_fused(_p(qkv), batch, hidden, fused_cols, _p(q), _p(k), _p(v), _p(beta), beta_bias,
+                                             _stream()))
+    return q, k, v, beta
+
+
+# ------------------------------------------------------------------------------------------ EFLA
+def efla_scan(**kw):
+    """Whole-sequence scan / generic recurrence (bnf4_efla_scan); keyword names are the fields of bnf4_efla_desc."""
+    d = _l.EflaDesc()
+    for k, v in kw.items():
+        setattr(d, k, _p(v) if isinstance(v, torch.Tensor) else v)
+    _l.check(_l.load().bnf4_efla_scan(C.byref(d), _stream()))
+
+
+def efla_step_half_qkv_fused(S, qkv, fused_cols, beta_bias, hidden, batch, method, eps):
+    out = torch.empty((batch, hidden), dtype=torch.float32, device=qkv.device)
+    _l.check(_l.load().bnf4_efla_step_half_qkv_fused(_p(S), _p(qkv), fused_cols, beta_bias, hidden, batch, method, eps, _p(out),
+                                                     _stream()))
+    return out
+
+
+def efla_step_qkv_fused(S, qkv, fused_cols, beta_bias, hidden, batch, method, eps):
+    out = torch.empty((batch, hidden), dtype=torch.float32, device=qkv.device)
+    _l.check(_l.load().bnf4_efla_step_qkv_fused(_p(S), _p(qkv), fused_cols, beta_bias, hidden, batch, method, eps, _p(out),
+                                                _stream()))
+    return out
+
+
+# ------------------------------------------------------------------------------------------ loss / noise / update
+def cross_entropy_loss(logits, bias, bias_noise, bias_noise_scale, targets_t, token_stride, loss_accum):
+    batch, vocab = logits.shape
+    _l.check(_l.load().bnf4_cross_entropy_loss(_p(logits), _p(bias), _p(bias_noise), bias_noise_scale, _p(targets_t),
+                                               token_stride, vocab, batch, _p(loss_accum), _stream()))
+
+
+def cross_entropy_population(logits, ld, bias, bias_noise_i8, sigma, targets, vocab, members, rows_per_member):
+    partial = torch.empty(members * 16, dtype=torch.float32, device=logits.device)
+    loss = torch.empty(members, dtype=torch.float32, device=logits.device)
+    _l.check(_l.load().bnf4_cross_entropy_population(_p(logits), ld, _p(bias), _p(bias_noise_i8), sigma, _p(targets), vocab,
+                                                     members, rows_per_member, _p(partial), _p(loss), _stream()))
+    return loss
+
+
+def fill_ternary_noise(n, seed, use_clt=True, clt_k=4, device="cuda"):
+    out = torch.empty(n, dtype=torch.int8, device=device)
+    _l.check(_l.load().bnf4_fill_ternary_noise(_p(out), n, seed, int(use_clt), clt_k, _stream()))
+    return out
+
+
+def fill_pair_seeds(base_seed, epoch, pairs, device="cuda"):
+    out = torch.empty(pairs, dtype=torch.int64, device=device)
+    _l.check(_l.load().bnf4_fill_pair_seeds(base_seed, epoch, pairs, _p(out), _stream()))
+    return out
+
+
+def compute_z_sumsq(pair_weights, pair_seeds, salt, n, use_clt=True, clt_k=4):
+    Z = torch.empty(n, dtype=torch.float32, device=pair_weights.device)
+    sumsq = torch.zeros(1, dtype=torch.float32, device=pair_weights.device)
+    _l.check(_l.load().bnf4_compute_z_sumsq(_p(pair_weights), _p(pair_seeds), salt, pair_weights.numel(), n, int(use_clt),
+                                            clt_k, _p(Z), _p(sumsq), _stream()))
+    return Z, sumsq
+
+
+def compute_z_sumsq_lowrank(pair_weights, A, B, rows, cols, rank, cscale):
+    pairs = pair_weights.numel()
+    Z = torch.empty(rows * cols, dtype=torch.float32, device=pair_weights.device)
+    sumsq = torch.zeros(1, dtype=torch.float32, device=pair_weights.device)
+    _l.check(_l.load().bnf4_compute_z_sumsq_lowrank(_p(pair_weights), _p(A), rows * rank, _p(B), rank * cols, pairs, rows, cols,
+                                                    rank, cscale, _p(Z), _p(sumsq), _stream()))
+    return Z, sumsq
+
+
+def update_inv_rms(sumsq, rms_ema, use_adaptive, beta, eps, n):
+    inv = torch.empty(1, dtype=torch.float32, device=sumsq.device)
+    _l.check(_l.load().bnf4_update_inv_rms(_p(sumsq), _p(rms_ema), int(use_adaptive), beta, eps, n, _p(inv), _stream()))
+    return inv
+
+
+def update_shadow_ternary_device(w, shadow, Z, inv_rms, lr, thresh):
+    _l.check(_l.load().bnf4_update_shadow_ternary_device(_p(w), _p(shadow), _p(Z), Z.numel(), _p(inv_rms), lr, thresh, _stream()))
+
+
+def shape_pair_weights(w_host, mode=0, clip=3.0):
+    """Host-side fitness shaping on a float32 numpy array (in place)."""
+    import numpy as np
+    assert w_host.dtype == np.float32 and w_host.flags["C_CONTIGUOUS"]
+    _l.check(_l.load().bnf4_shape_pair_weights(w_host.ctypes.data, w_host.size, mode, clip))
+    return w_host

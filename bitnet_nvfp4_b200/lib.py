@@ -50,7 +50,27 @@ class GemmDesc(C.Structure):
     ]
 
 
+class EflaDesc(C.Structure):
+    """bnf4_efla_desc"""
+
+    _fields_ = [
+        ("state", c_void_p), ("state_fp16", c_int),
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("beta_raw", c_void_p),
+        ("ld_qkv", c_int), ("ld_beta", c_int),
+        ("beta_bias", c_float), ("beta_bias_seq", c_void_p), ("seqs_per_bias", c_int),
+        ("hidden", c_int), ("heads", c_int), ("seqs", c_ll), ("T", c_int), ("method", c_int), ("eps", c_float),
+        ("out", c_void_p), ("ld_out", c_int), ("force_generic", c_int),
+    ]
+
+
+class NoiseDesc(C.Structure):
+    """bnf4_noise_desc"""
+
+    _fields_ = [("out", c_void_p), ("n", c_size_t), ("seed", C.c_uint64)]
+
+
 _I8P = c_void_p  # device pointers travel as integers
+c_u64 = C.c_uint64
 
 _PROTOS = {
     # name: (restype, argtypes)
@@ -84,6 +104,36 @@ _PROTOS = {
                                                   c_float, c_void_p, c_float, _I8P, c_void_p]),
     "bnf4_nvfp4_prepare_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
                                         c_void_p, c_void_p, c_void_p]),
+    "bnf4_gemm_ternary_f": (c_int, [_I8P, _I8P, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "bnf4_lora_compute_t": (c_int, [_I8P, _I8P, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "bnf4_lora_add": (c_int, [c_void_p, _I8P, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "bnf4_split_qkvb_fused": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                      c_void_p]),
+    "bnf4_efla_scan": (c_int, [C.POINTER(EflaDesc), c_void_p]),
+    "bnf4_efla_step_half_qkv_fused": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p,
+                                              c_void_p]),
+    "bnf4_efla_step_qkv_fused": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_float, c_void_p,
+                                         c_void_p]),
+    "bnf4_efla_step": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
+                               c_float, c_void_p, c_void_p]),
+    "bnf4_cross_entropy_loss": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p,
+                                        c_void_p]),
+    "bnf4_cross_entropy_population": (c_int, [c_void_p, c_int, c_void_p, _I8P, c_float, c_void_p, c_int, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p]),
+    "bnf4_fill_ternary_noise": (c_int, [_I8P, c_size_t, c_u64, c_int, c_int, c_void_p]),
+    "bnf4_fill_ternary_noise_batched": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "bnf4_fill_float_noise": (c_int, [c_void_p, c_int, c_u64, c_int, c_int, c_void_p]),
+    "bnf4_init_shadow_from_weights": (c_int, [_I8P, c_void_p, c_int, c_void_p]),
+    "bnf4_fill_pair_seeds": (c_int, [c_u64, c_u64, c_int, c_void_p, c_void_p]),
+    "bnf4_compute_z_sumsq": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "bnf4_compute_z_sumsq_lowrank": (c_int, [c_void_p, _I8P, c_ll, _I8P, c_ll, c_int, c_int, c_int, c_int, c_float,
+                                             c_void_p, c_void_p, c_void_p]),
+    "bnf4_update_inv_rms": (c_int, [c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p]),
+    "bnf4_update_shadow_ternary_device": (c_int, [_I8P, c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p]),
+    "bnf4_update_shadow_ternary": (c_int, [_I8P, c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p]),
+    "bnf4_update_vector_device": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p]),
+    "bnf4_add_scaled": (c_int, [c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "bnf4_shape_pair_weights": (c_int, [c_void_p, c_int, c_int, c_float]),
 }
 
 

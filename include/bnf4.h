@@ -199,6 +199,130 @@ typedef struct bnf4_gemm_desc {
 
 int bnf4_gemm_nvfp4_ex(const bnf4_gemm_desc* desc, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Exact-integer ternary GEMM (the reference's non-NVFP4 fallback).
+ * reference: gemm_ternary_f src/cuda_kernels.cu:3725-3739 (kernels :740-762, :163-192).
+ * out[b,i] = out_scale * sum_g scale_x[g] * (int32 sum over the g-th group of 256 columns of x[b,:]*w[i,:]);
+ * scale_x == NULL means all ones. x [batch][cols] int8, w [rows][cols] int8, out [batch][rows] fp32.
+ * ------------------------------------------------------------------------------------------- */
+int bnf4_gemm_ternary_f(const int8_t* x, const int8_t* w, const float* scale_x, int rows, int cols, int batch,
+                        float out_scale, float* out, void* stream);
+/* reference: lora_compute_t src/cuda_kernels.cu:5003-5012 (kernel :370-390). t[b,r] = sum_j x[b,j]*B[j,r], B [cols][rank]. */
+int bnf4_lora_compute_t(const int8_t* x, const int8_t* B, int cols, int batch, int rank, int32_t* t, void* stream);
+/* reference: lora_add src/cuda_kernels.cu:5014-5024 (kernel :392-410). out[b,i] += scale * sum_r t[b,r]*A[i,r]. */
+int bnf4_lora_add(const int32_t* t, const int8_t* A, int rows, int batch, int rank, float scale, float* out, void* stream);
+/* reference: split_qkvb_fused src/cuda_kernels.cu:4308-4340 (kernels :2856-2926). */
+int bnf4_split_qkvb_fused(const float* in, int batch, int hidden, int fused_cols, float* q, float* k, float* v,
+                          float* beta, float beta_bias, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * EFLA / DeltaNet linear-attention recurrence. State stays on chip for all T steps of a call.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct bnf4_efla_desc {
+    void* state;    /* optional HBM state [seqs][heads][hd][hd]; loaded before and stored after the T steps.
+                       NULL: zero initial state, final state discarded (whole-sequence scan). */
+    int state_fp16; /* 1: state is rounded to fp16 after every step (the reference default); 0: fp32 state */
+    const float* q; /* row r = seq*T + t at q + r*ld_qkv; head h at column h*hd (likewise k, v) */
+    const float* k;
+    const float* v;
+    const float* beta_raw; /* row r at beta_raw + r*ld_beta */
+    int ld_qkv, ld_beta;
+    float beta_bias;            /* used when beta_bias_seq == NULL */
+    const float* beta_bias_seq; /* bias of sequence s = beta_bias_seq[s / seqs_per_bias] */
+    int seqs_per_bias;
+    int hidden, heads;
+    long long seqs;
+    int T;
+    int method; /* 0 DeltaNet, 1 EFLA */
+    float eps;
+    float* out; /* row r at out + r*ld_out */
+    int ld_out;
+    int force_generic; /* 1: never take the head_dim-64 register kernel (for testing) */
+} bnf4_efla_desc;
+
+int bnf4_efla_scan(const bnf4_efla_desc* desc, void* stream);
+/* reference: efla_step_half_qkv_fused src/efla_lm_kernels.cu:2367-2447 (6 kernels; one here). The scratch
+ * pointers of the reference signature are accepted and ignored. heads = 1. */
+int bnf4_efla_step_half_qkv_fused(void* S_half, const float* qkv, int fused_cols, float beta_bias, int hidden,
+                                  int batch, int method, float eps, float* out, void* stream);
+/* reference: efla_step_qkv_fused src/efla_lm_kernels.cu:2181-2221 (fp32 state). */
+int bnf4_efla_step_qkv_fused(float* S, const float* qkv, int fused_cols, float beta_bias, int hidden, int batch,
+                             int method, float eps, float* out, void* stream);
+/* reference: efla_step / efla_step_half / efla_step_fused / efla_step_fused_half
+ * src/efla_lm_kernels.cu:2134-2179, 2223-2365, 2449-2483 (separate q, k, v [batch][hidden], beta_raw [batch]). */
+int bnf4_efla_step(void* S, int state_fp16, const float* q, const float* k, const float* v, const float* beta_raw,
+                   float beta_bias, int hidden, int batch, int method, float eps, float* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Cross-entropy fitness.
+ * ------------------------------------------------------------------------------------------- */
+/* reference: cross_entropy_loss src/efla_lm_kernels.cu:2509-2523 (kernel :252-311). Adds the summed loss of
+ * `batch` rows to *loss_accum. The sum is formed in a fixed order (the reference uses float atomics). */
+int bnf4_cross_entropy_loss(const float* logits, const float* bias, const float* bias_noise, float bias_noise_scale,
+                            const uint8_t* targets_t, int token_stride, int vocab, int batch, float* loss_accum,
+                            void* stream);
+/* Population form: logits [members*rows_per_member][ld]; targets [rows_per_member] shared by all members;
+ * bias_noise int8 [pair][vocab] (pair = member/2, sign by parity, magnitude sigma).
+ * loss_mean[member] = mean over the member's rows. partial: scratch of members*16 floats. */
+int bnf4_cross_entropy_population(const float* logits, int ld, const float* bias, const int8_t* bias_noise,
+                                  float sigma, const uint8_t* targets, int vocab, int members, int rows_per_member,
+                                  float* partial, float* loss_mean, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Noise generation (counter hash; bit-exact with the reference's host and device generators).
+ * ------------------------------------------------------------------------------------------- */
+/* reference: fill_ternary_noise src/efla_lm_kernels.cu:2525-2535 (kernel :352-360) */
+int bnf4_fill_ternary_noise(int8_t* out, size_t n, uint64_t seed, int use_clt, int clt_k, void* stream);
+/* reference: struct NoiseDesc src/efla_lm_kernels.h:306-310 */
+typedef struct bnf4_noise_desc {
+    int8_t* out;
+    size_t n;
+    uint64_t seed;
+} bnf4_noise_desc;
+/* reference: fill_ternary_noise_batched src/efla_lm_kernels.cu:2537-2550 (kernel :362-374); descs is a device array */
+int bnf4_fill_ternary_noise_batched(const bnf4_noise_desc* descs, int num_desc, int max_blocks, int use_clt, int clt_k,
+                                    void* stream);
+/* reference: fill_float_noise src/efla_lm_kernels.cu:2552-2562 (kernel :376-385) */
+int bnf4_fill_float_noise(float* out, int n, uint64_t seed, int use_clt, int clt_k, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * ES update.
+ * ------------------------------------------------------------------------------------------- */
+/* reference: init_shadow_from_weights src/efla_lm_kernels.cu:2023-2030 (kernel :1836-1842) */
+int bnf4_init_shadow_from_weights(const int8_t* w, float* shadow, int n, void* stream);
+/* reference: fill_pair_seeds src/efla_lm_kernels.cu:2032-2040 (kernel :1844-1852) */
+int bnf4_fill_pair_seeds(uint64_t base_seed, uint64_t epoch, int pairs, uint64_t* out, void* stream);
+/* reference: compute_z_sumsq src/efla_lm_kernels.cu:2042-2059 (kernel :1854-1890).
+ * Z[i] = sum_p w_p * noise(mix(seed_p, salt), i) (p ascending, fused multiply-add); sum(Z^2) is ADDED to *sumsq.
+ * The sum of squares is reduced in a fixed order (per-256 tree, then block partials in double). Uses a
+ * library-owned scratch buffer for the block partials (allocated with cudaMalloc on first use and grown on demand). */
+int bnf4_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int n,
+                         int use_clt, int clt_k, float* Z, float* sumsq, void* stream);
+/* Rank-r form: Z[i*cols+j] = cscale * sum_p w_p * sum_r A[p][i][r]*B[p][r][j] with A [pairs][rows][rank] and
+ * B [pairs][rank][cols] int8 (the same factor buffers the forward pass uses). */
+int bnf4_compute_z_sumsq_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
+                                 long long B_pair_stride, int pairs, int rows, int cols, int rank, float cscale,
+                                 float* Z, float* sumsq, void* stream);
+/* reference: update_inv_rms src/efla_lm_kernels.cu:2061-2073 (kernel :2003-2021). inv_rms = 1/sqrt(ema+eps)
+ * evaluated with IEEE sqrt and divide (the reference's rsqrtf is within 2 ulp of it). */
+int bnf4_update_inv_rms(const float* sumsq, float* rms_ema, int use_adaptive, float adaptive_beta, float adaptive_eps,
+                        int n, float* inv_rms, void* stream);
+/* reference: update_shadow_ternary_device src/efla_lm_kernels.cu:2088-2099 (kernel :1908-1922) */
+int bnf4_update_shadow_ternary_device(int8_t* w, float* shadow, const float* Z, int n, const float* inv_rms, float lr,
+                                      float thresh, void* stream);
+/* reference: update_shadow_ternary src/efla_lm_kernels.cu:2075-2086 (kernel :1892-1906) */
+int bnf4_update_shadow_ternary(int8_t* w, float* shadow, const float* Z, int n, float inv_rms, float lr, float thresh,
+                               void* stream);
+/* Device twin of the reference's host update_vector (plain branch), src/train_efla_lm.cpp:4085-4189:
+ * v[i] += lr * g where g = inv_rms * Z[i], skipped when |g| < thresh. */
+int bnf4_update_vector_device(float* v, const float* Z, int n, const float* inv_rms, float lr, float thresh,
+                              void* stream);
+/* reference: add_scaled src/efla_lm_kernels.cu:1769-1779 (out[i] += scale * noise[i]) */
+int bnf4_add_scaled(float* out, const float* noise, int n, float scale, void* stream);
+/* Centered-rank / z-score / sign shaping of the pair fitness vector on the host (pure function, no GPU):
+ * reference shape_pair_weights src/train_efla_lm.cpp:3898-3952; ties broken by index. mode 0/1/2. */
+int bnf4_shape_pair_weights(float* h_w, int n, int mode, float clip);
+
 #ifdef __cplusplus
 }
 #endif
