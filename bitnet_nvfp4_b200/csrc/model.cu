@@ -1,0 +1,528 @@
+// Population driver: layer-major, wave-batched evaluation of perturbed members and the ES update.
+//
+// Host-side re-design of the reference's CudaEflaLm::evaluate_loss (src/train_efla_lm.cpp:2117-3431), the
+// per-pair seed derivation of eval_worker (:5344-5468), DeviceWeights / quantize_nvfp4_base_weights (:439-651,
+// 1207-1310) and gpu_update_matrix (:4304-4358). The op order inside a layer is the reference's; the loop
+// order is inverted (layers outside, tokens inside) which changes no value because only the recurrent state
+// couples time steps.
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bnf4 {
+
+namespace {
+
+constexpr float kCRankBase = 0.6123724356957945f;  // sqrt(3/8)
+
+// One entry of the per-step noise table: dst[pair][...] filled from the counter hash.
+struct GenDesc {
+    int8_t* dst;
+    long long pair_stride;
+    uint64_t salt;    // mixed with the pair seed
+    uint64_t factor;  // 0: plain vector, else sub-stream (kFactorA / kFactorB) of the matrix seed
+    int n_major;      // rows (A), columns (B) or vector length
+    int rank;         // 1 for plain vectors
+    int transposed;   // store element (major, r) at r*n_major + major instead of major*rank + r
+};
+
+__global__ void gen_noise_kernel(const GenDesc* __restrict__ descs, const uint64_t* __restrict__ pair_seeds, int use_clt, int clt_k) {
+    const GenDesc d = descs[blockIdx.y];
+    const int pair = blockIdx.z;
+    const long long n = static_cast<long long>(d.n_major) * d.rank;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    uint64_t seed = mix_u64(pair_seeds[pair], d.salt);
+    if (d.factor != 0) seed = mix_u64(seed, d.factor);
+    const int v = noise_hash(seed, static_cast<uint64_t>(idx), use_clt != 0, clt_k);
+    long long o = idx;
+    if (d.transposed) {
+        const long long major = idx / d.rank, r = idx - major * d.rank;
+        o = r * d.n_major + major;
+    }
+    d.dst[static_cast<size_t>(pair) * d.pair_stride + o] = static_cast<int8_t>(v);
+}
+
+// beta_bias_eff[l][member] = beta_bias[l] + ns(member) * noise[pair][l]   (reference: src/train_efla_lm.cpp:2912-2917)
+__global__ void beta_bias_kernel(const float* __restrict__ beta_bias, const int8_t* __restrict__ noise, int layers, int members,
+                                 float sigma, float* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= layers * members) return;
+    const int l = i / members, m = i - l * members;
+    const float ns = (m & 1) ? -sigma : sigma;
+    const float nz = sigma != 0.0f ? static_cast<float>(noise[static_cast<size_t>(m >> 1) * layers + l]) : 0.0f;
+    out[i] = fmaf(ns, nz, beta_bias[l]);
+}
+
+struct Model {
+    bnf4_model_cfg cfg;
+    int V, H, F, L, T, B, R, FC, r, hd;
+    float s_h, s_f, sigma, c_r;
+    int W;          // members per wave
+    long long M;    // rows per wave
+    size_t device_bytes = 0;
+    std::vector<void*> allocs;
+
+    // weights
+    int8_t *emb, *win, *wq, *wk, *wv, *wbeta, *ff1, *ff2, *head;
+    float *head_bias, *beta_bias, *pos;
+    float *sh_emb, *sh_win, *sh_wq, *sh_wk, *sh_wv, *sh_wbeta, *sh_ff1, *sh_ff2, *sh_head;  // fp32 shadows
+    float* rms_ema;  // [27 matrices + 3 vectors]
+    // NVFP4 copies of the base weights
+    uint8_t *q_win, *sfq_win, *q_head, *sfq_head;
+    std::vector<uint8_t*> q_qkv, sfq_qkv, q_ff1, sfq_ff1, q_ff2, sfq_ff2;
+    // tokens
+    uint8_t *tokens, *targets;
+    // per-step noise (all pairs)
+    uint64_t* pair_seeds;
+    int pairs_step = 0;
+    int8_t *embA, *embB, *A_win, *tB_win, *A_head, *tB_head, *pos_noise, *hb_noise, *bb_noise;
+    std::vector<int8_t*> A_qkv, tB_qkv, A_ff1, tB_ff1, A_ff2, tB_ff2;
+    GenDesc* gen_descs;
+    int num_gen = 0;
+    int gen_max_n = 0;
+    // wave buffers
+    int8_t* x_q;
+    uint8_t *a_h, *sf_h, *a_f, *sf_f;
+    float *qkv, *y, *bb_eff, *ce_partial, *losses;
+    int32_t *t_a, *t_f;
+    // update scratch
+    float *Z, *sumsq, *inv_rms;
+    int launches_per_wave = 0;
+
+    template <typename Tp>
+    int alloc(Tp** p, size_t count, bool zero = true) {
+        void* ptr = nullptr;
+        const size_t bytes = ((count * sizeof(Tp) + 255) / 256) * 256;
+        int rc = check_cuda(cudaMalloc(&ptr, bytes), "cudaMalloc(model)");
+        if (rc) return rc;
+        allocs.push_back(ptr);
+        device_bytes += bytes;
+        if (zero) {
+            rc = check_cuda(cudaMemset(ptr, 0, bytes), "cudaMemset(model)");
+            if (rc) return rc;
+        }
+        *p = static_cast<Tp*>(ptr);
+        return BNF4_OK;
+    }
+};
+
+#define TRY(expr)              \
+    do {                       \
+        const int rc_ = (expr); \
+        if (rc_) return rc_;   \
+    } while (0)
+
+int quantize_base(Model& m, cudaStream_t st) {
+    auto plain = [&](const int8_t* w, int rows, int cols, uint8_t* codes, uint8_t* sf) {
+        bnf4_rowquant_desc p = {};
+        p.rows = rows; p.cols_in = cols; p.cols_out = cols; p.in_i8 = w; p.ld_in = cols; p.out_codes = codes; p.out_sf = sf;
+        return rowquant_dispatch(FE_INT8, p, st);
+    };
+    TRY(plain(m.win, m.H, m.H, m.q_win, m.sfq_win));
+    TRY(plain(m.head, m.V, m.H, m.q_head, m.sfq_head));
+    const size_t hh = static_cast<size_t>(m.H) * m.H, hf = static_cast<size_t>(m.H) * m.F;
+    for (int l = 0; l < m.L; ++l) {
+        bnf4_rowquant_desc p = {};
+        p.rows = 3 * m.H + 1; p.cols_in = m.H; p.cols_out = m.H;
+        p.wq = m.wq + l * hh; p.wk = m.wk + l * hh; p.wv = m.wv + l * hh; p.wb = m.wbeta + static_cast<size_t>(l) * m.H;
+        p.q_scale = p.k_scale = p.v_scale = p.b_scale = m.s_h;
+        p.out_codes = m.q_qkv[l]; p.out_sf = m.sfq_qkv[l];
+        TRY(rowquant_dispatch(FE_WQKV, p, st));
+        TRY(plain(m.ff1 + l * hf, m.F, m.H, m.q_ff1[l], m.sfq_ff1[l]));
+        TRY(plain(m.ff2 + l * hf, m.H, m.F, m.q_ff2[l], m.sfq_ff2[l]));
+    }
+    return BNF4_OK;
+}
+
+// One wave: members [0, nm) of the wave correspond to pairs [p0, p0 + nm/2). sigma == 0 evaluates the base model.
+int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStream_t st) {
+    const int H = m.H, F = m.F, L = m.L, V = m.V, R = m.R, FC = m.FC, r = m.r;
+    const int rows = nm * R;
+    const bool pert = sigma != 0.0f;
+    const int rank = pert ? r : 0;
+    const size_t P0 = static_cast<size_t>(p0);
+    int launches = 0;
+
+    {   // per-member beta bias for every layer
+        const int n = L * nm;
+        beta_bias_kernel<<<(n + 127) / 128, 128, 0, st>>>(m.beta_bias, m.bb_noise + P0 * L, L, nm, sigma, m.bb_eff);
+        TRY(check_launch("beta_bias_kernel"));
+        ++launches;
+    }
+    {   // embedding -> a_h, t for win
+        bnf4_rowquant_desc p = {};
+        p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma; p.c_rank = m.c_r;
+        p.tokens = m.tokens; p.token_stride = 1; p.row_mod = R; p.emb_w = m.emb;
+        p.embA = m.embA + P0 * V * r; p.embB = m.embB + P0 * H * r; p.embA_pair_stride = static_cast<long long>(V) * r;
+        p.embB_pair_stride = static_cast<long long>(H) * r; p.rank = r;
+        p.out_codes = m.a_h; p.out_sf = m.sf_h;
+        if (pert) { p.tvec = m.tB_win + P0 * H * r; p.tvec_pair_stride = static_cast<long long>(H) * r; p.nvec = r; p.t_out = m.t_a; }
+        TRY(rowquant_dispatch(FE_EMBED_LOWRANK, p, st));
+        ++launches;
+    }
+    auto gemm = [&](const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, int n, int k, float alpha, float* d,
+                    int ldd, const int8_t* A, long long A_stride, const int32_t* t, int t_stride, float out_scale, int group_cols) {
+        bnf4_gemm_desc g = {};
+        g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.m = rows; g.n = n; g.k = k; g.alpha = alpha; g.d = d; g.ldd = ldd;
+        g.epilogue = EPI_F32; g.rank = rank; g.rows_per_member = R; g.lora_t = t; g.t_stride = t_stride; g.lora_A = A;
+        g.lora_A_pair_stride = A_stride; g.lora_scale = (sigma * out_scale) * m.c_r; g.group_cols = group_cols;
+        return gemm_nvfp4_launch(g, st);
+    };
+    // input projection -> y
+    TRY(gemm(m.a_h, m.sf_h, m.q_win, m.sfq_win, H, H, m.s_h, m.y, H, m.A_win + P0 * H * r, static_cast<long long>(H) * r, m.t_a, r,
+             m.s_h, 0));
+    ++launches;
+    {   // + pos, GELU -> residual stream x_q; abs-mean norm -> a_h; t for qkv[0]
+        bnf4_rowquant_desc p = {};
+        p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
+        p.in_f32 = m.y; p.ld_in = H; p.inout_i8 = m.x_q; p.pos = m.pos; p.pos_mod = m.T;
+        p.pos_noise = pert ? m.pos_noise + P0 * m.T * H : nullptr; p.noise_pair_stride = static_cast<long long>(m.T) * H;
+        p.act_scale = m.cfg.act_scale; p.norm_scale = m.cfg.ln_scale; p.out_codes = m.a_h; p.out_sf = m.sf_h;
+        if (pert) { p.tvec = m.tB_qkv[0] + P0 * 4 * r * H; p.tvec_pair_stride = static_cast<long long>(4) * r * H; p.nvec = 4 * r; p.t_out = m.t_a; }
+        TRY(rowquant_dispatch(FE_POS_GELU_ABSMEAN, p, st));
+        ++launches;
+    }
+    for (int l = 0; l < L; ++l) {
+        // fused QKV(+beta) projection -> qkv [rows][FC]; out_scale is folded into the weight scales (alpha = 1)
+        TRY(gemm(m.a_h, m.sf_h, m.q_qkv[l], m.sfq_qkv[l], 3 * H + 1, H, 1.0f, m.qkv, FC, m.A_qkv[l] + P0 * (3 * H + 1) * r,
+                 static_cast<long long>(3 * H + 1) * r, m.t_a, 4 * r, m.s_h, H));
+        ++launches;
+        {   // recurrence over the whole sequence -> y
+            bnf4_efla_desc e = {};
+            e.state = nullptr; e.state_fp16 = 1; e.q = m.qkv; e.k = m.qkv + H; e.v = m.qkv + 2 * H; e.beta_raw = m.qkv + 3 * H;
+            e.ld_qkv = FC; e.ld_beta = FC; e.beta_bias_seq = m.bb_eff + static_cast<size_t>(l) * nm; e.seqs_per_bias = m.B;
+            e.hidden = H; e.heads = m.cfg.heads; e.seqs = static_cast<long long>(nm) * m.B; e.T = m.T; e.method = m.cfg.method;
+            e.eps = m.cfg.eps; e.out = m.y; e.ld_out = H;
+            // the generic kernel addresses sequences with blockIdx.z: split large waves
+            if (m.hd == 64) {
+                TRY(efla_launch(e, st));
+                ++launches;
+            } else {
+                for (long long s0 = 0; s0 < e.seqs; s0 += 32768) {
+                    bnf4_efla_desc ee = e;
+                    const long long cnt = std::min<long long>(32768, e.seqs - s0);
+                    const size_t ro = static_cast<size_t>(s0) * m.T;
+                    ee.q = e.q + ro * FC; ee.k = e.k + ro * FC; ee.v = e.v + ro * FC; ee.beta_raw = e.beta_raw + ro * FC;
+                    ee.out = e.out + ro * H; ee.seqs = cnt;
+                    if ((s0 % m.B) != 0) return set_error(BNF4_ERR_INVALID, "efla split not aligned to batch");
+                    ee.beta_bias_seq = e.beta_bias_seq + s0 / m.B;
+                    TRY(efla_launch(ee, st));
+                    ++launches;
+                }
+            }
+        }
+        {   // residual add + abs-mean norm -> a_h; t for ff1
+            bnf4_rowquant_desc p = {};
+            p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
+            p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.add_scale = m.cfg.residual_scale; p.norm_scale = m.cfg.ln_scale;
+            p.out_codes = m.a_h; p.out_sf = m.sf_h;
+            if (pert) { p.tvec = m.tB_ff1[l] + P0 * r * H; p.tvec_pair_stride = static_cast<long long>(r) * H; p.nvec = r; p.t_out = m.t_a; }
+            TRY(rowquant_dispatch(FE_ADD_ABSMEAN, p, st));
+            ++launches;
+        }
+        {   // ff1 with GELU -> int8 -> FP4 epilogue, projections for ff2
+            if (pert) TRY(check_cuda(cudaMemsetAsync(m.t_f, 0, static_cast<size_t>(rows) * r * sizeof(int32_t), st), "cudaMemsetAsync(t_f)"));
+            bnf4_gemm_desc g = {};
+            g.a = m.a_h; g.b = m.q_ff1[l]; g.sfa = m.sf_h; g.sfb = m.sfq_ff1[l]; g.m = rows; g.n = F; g.k = H; g.alpha = m.s_h;
+            g.epilogue = EPI_GELU_FP4; g.act_scale = m.cfg.mlp_act_scale; g.d_codes = m.a_f; g.d_sf = m.sf_f;
+            g.rank = rank; g.rows_per_member = R; g.lora_t = m.t_a; g.t_stride = r; g.lora_A = m.A_ff1[l] + P0 * F * r;
+            g.lora_A_pair_stride = static_cast<long long>(F) * r; g.lora_scale = (sigma * m.s_h) * m.c_r;
+            if (pert) { g.next_tvec = m.tB_ff2[l] + P0 * r * F; g.next_tvec_pair_stride = static_cast<long long>(r) * F; g.next_nvec = r; g.next_t = m.t_f; }
+            TRY(gemm_nvfp4_launch(g, st));
+            ++launches;
+        }
+        // ff2 -> y
+        TRY(gemm(m.a_f, m.sf_f, m.q_ff2[l], m.sfq_ff2[l], H, F, m.s_f, m.y, H, m.A_ff2[l] + P0 * H * r, static_cast<long long>(H) * r, m.t_f,
+                 r, m.s_f, 0));
+        ++launches;
+        {   // residual add + abs-mean norm -> a_h; t for the next layer's qkv or the head
+            const bool last = (l == L - 1);
+            bnf4_rowquant_desc p = {};
+            p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
+            p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.add_scale = m.cfg.mlp_residual_scale; p.norm_scale = m.cfg.ln_scale;
+            p.out_codes = m.a_h; p.out_sf = m.sf_h;
+            if (pert) {
+                if (last) { p.tvec = m.tB_head + P0 * r * H; p.tvec_pair_stride = static_cast<long long>(r) * H; p.nvec = r; }
+                else { p.tvec = m.tB_qkv[l + 1] + P0 * 4 * r * H; p.tvec_pair_stride = static_cast<long long>(4) * r * H; p.nvec = 4 * r; }
+                p.t_out = m.t_a;
+            }
+            TRY(rowquant_dispatch(FE_ADD_ABSMEAN, p, st));
+            ++launches;
+        }
+    }
+    // head -> logits (in the qkv buffer, leading dimension V), cross-entropy per member
+    TRY(gemm(m.a_h, m.sf_h, m.q_head, m.sfq_head, V, H, m.s_h, m.qkv, V, m.A_head + P0 * V * r, static_cast<long long>(V) * r, m.t_a, r, m.s_h, 0));
+    ++launches;
+    TRY(bnf4_cross_entropy_population(m.qkv, V, m.head_bias, pert ? m.hb_noise + P0 * V : nullptr, sigma, m.targets, V, nm, R, m.ce_partial,
+                                      losses_out, st));
+    launches += 2;
+    m.launches_per_wave = launches;
+    return BNF4_OK;
+}
+
+}  // namespace
+}  // namespace bnf4
+
+using namespace bnf4;
+static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
+static inline Model* M(void* h) { return static_cast<Model*>(h); }
+
+extern "C" {
+
+int bnf4_model_destroy(void* handle) {
+    if (!handle) return BNF4_OK;
+    Model* m = M(handle);
+    cudaDeviceSynchronize();
+    for (void* p : m->allocs) cudaFree(p);
+    delete m;
+    return BNF4_OK;
+}
+
+int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
+    if (!cfg || !handle) return set_error(BNF4_ERR_INVALID, "model_create: null argument");
+    *handle = nullptr;
+    if (cfg->vocab <= 0 || cfg->vocab > 1024) return set_error(BNF4_ERR_INVALID, "model_create: vocab=%d outside [1,1024]", cfg->vocab);
+    if (cfg->hidden <= 0 || (cfg->hidden % 64) != 0) return set_error(BNF4_ERR_INVALID, "model_create: hidden=%d must be a multiple of 64", cfg->hidden);
+    if (cfg->layers <= 0 || cfg->mlp_mult <= 0 || cfg->seq <= 0 || cfg->batch <= 0) return set_error(BNF4_ERR_INVALID, "model_create: bad shape");
+    if (cfg->heads <= 0 || (cfg->hidden % cfg->heads) != 0 || ((cfg->hidden / cfg->heads) % 32) != 0)
+        return set_error(BNF4_ERR_INVALID, "model_create: heads=%d needs head_dim %% 32 == 0", cfg->heads);
+    if (cfg->rank < 1 || cfg->rank > 4) return set_error(BNF4_ERR_INVALID, "model_create: rank=%d outside [1,4]", cfg->rank);
+    if (cfg->sigma_shift < 0 || cfg->sigma_shift > 30) return set_error(BNF4_ERR_INVALID, "model_create: sigma_shift");
+    if (cfg->max_pairs <= 0) return set_error(BNF4_ERR_INVALID, "model_create: max_pairs");
+    if (static_cast<long long>(cfg->hidden) * cfg->mlp_mult > 4096) return set_error(BNF4_ERR_INVALID, "model_create: mlp width above 4096");
+
+    Model* m = new Model;
+    m->cfg = *cfg;
+    m->V = cfg->vocab; m->H = cfg->hidden; m->F = cfg->hidden * cfg->mlp_mult; m->L = cfg->layers; m->T = cfg->seq; m->B = cfg->batch;
+    m->R = m->B * m->T; m->FC = (3 * m->H + 1 + 31) & ~31; m->r = cfg->rank; m->hd = m->H / cfg->heads;
+    m->s_h = 1.0f / std::sqrt(static_cast<float>(m->H));
+    m->s_f = 1.0f / std::sqrt(static_cast<float>(m->F));
+    m->sigma = 1.0f / static_cast<float>(1 << cfg->sigma_shift);
+    m->c_r = kCRankBase / std::sqrt(static_cast<float>(m->r));
+    int W = cfg->wave_members > 0 ? cfg->wave_members : 16;
+    W = std::min(W, 2 * cfg->max_pairs);
+    W = std::max(2, W & ~1);
+    m->W = W;
+    m->M = static_cast<long long>(W) * m->R;
+    if (m->M > 0x7fffffffLL / 8) { delete m; return set_error(BNF4_ERR_INVALID, "model_create: wave of %d members is too large", W); }
+
+    const int V = m->V, H = m->H, F = m->F, L = m->L, T = m->T, r = m->r, P = cfg->max_pairs;
+    const size_t hh = static_cast<size_t>(H) * H, hf = static_cast<size_t>(H) * F;
+    int rc = 0;
+#define A_(ptr, count) if (!rc) rc = m->alloc(&m->ptr, (count))
+    A_(emb, static_cast<size_t>(V) * H); A_(win, hh); A_(wq, L * hh); A_(wk, L * hh); A_(wv, L * hh); A_(wbeta, static_cast<size_t>(L) * H);
+    A_(ff1, L * hf); A_(ff2, L * hf); A_(head, static_cast<size_t>(V) * H);
+    A_(head_bias, V); A_(beta_bias, L); A_(pos, static_cast<size_t>(T) * H);
+    A_(sh_emb, static_cast<size_t>(V) * H); A_(sh_win, hh); A_(sh_wq, L * hh); A_(sh_wk, L * hh); A_(sh_wv, L * hh);
+    A_(sh_wbeta, static_cast<size_t>(L) * H); A_(sh_ff1, L * hf); A_(sh_ff2, L * hf); A_(sh_head, static_cast<size_t>(V) * H);
+    A_(rms_ema, 3 + 6 * static_cast<size_t>(L) + 3);
+    A_(q_win, hh / 2); A_(sfq_win, sf_bytes(H, H)); A_(q_head, static_cast<size_t>(V) * H / 2); A_(sfq_head, sf_bytes(V, H));
+    m->q_qkv.resize(L); m->sfq_qkv.resize(L); m->q_ff1.resize(L); m->sfq_ff1.resize(L); m->q_ff2.resize(L); m->sfq_ff2.resize(L);
+    m->A_qkv.resize(L); m->tB_qkv.resize(L); m->A_ff1.resize(L); m->tB_ff1.resize(L); m->A_ff2.resize(L); m->tB_ff2.resize(L);
+    for (int l = 0; l < L && !rc; ++l) {
+        A_(q_qkv[l], static_cast<size_t>(m->FC) * H / 2); A_(sfq_qkv[l], sf_bytes(m->FC, H));
+        A_(q_ff1[l], hf / 2); A_(sfq_ff1[l], sf_bytes(F, H)); A_(q_ff2[l], hf / 2); A_(sfq_ff2[l], sf_bytes(H, F));
+        A_(A_qkv[l], static_cast<size_t>(P) * (3 * H + 1) * r); A_(tB_qkv[l], static_cast<size_t>(P) * 4 * r * H);
+        A_(A_ff1[l], static_cast<size_t>(P) * F * r); A_(tB_ff1[l], static_cast<size_t>(P) * r * H);
+        A_(A_ff2[l], static_cast<size_t>(P) * H * r); A_(tB_ff2[l], static_cast<size_t>(P) * r * F);
+    }
+    A_(tokens, m->R); A_(targets, m->R);
+    A_(pair_seeds, P);
+    A_(embA, static_cast<size_t>(P) * V * r); A_(embB, static_cast<size_t>(P) * H * r);
+    A_(A_win, static_cast<size_t>(P) * H * r); A_(tB_win, static_cast<size_t>(P) * H * r);
+    A_(A_head, static_cast<size_t>(P) * V * r); A_(tB_head, static_cast<size_t>(P) * H * r);
+    A_(pos_noise, static_cast<size_t>(P) * T * H); A_(hb_noise, static_cast<size_t>(P) * V); A_(bb_noise, static_cast<size_t>(P) * L);
+    const size_t Mr = static_cast<size_t>(m->M);
+    A_(x_q, Mr * H); A_(a_h, Mr * H / 2); A_(sf_h, sf_bytes(static_cast<int>(Mr), H)); A_(a_f, Mr * F / 2); A_(sf_f, sf_bytes(static_cast<int>(Mr), F));
+    A_(qkv, Mr * m->FC); A_(y, Mr * H); A_(bb_eff, static_cast<size_t>(L) * W); A_(ce_partial, static_cast<size_t>(W) * 16); A_(losses, W);
+    A_(t_a, Mr * 4 * r); A_(t_f, Mr * r);
+    A_(Z, std::max(hf, static_cast<size_t>(T) * H)); A_(sumsq, 1); A_(inv_rms, 1);
+#undef A_
+    if (rc) { bnf4_model_destroy(m); return rc; }
+
+    // noise table
+    std::vector<GenDesc> gd;
+    auto factor_pair = [&](int8_t* A, long long A_stride, long long A_off, int rows, int8_t* Bt, long long B_stride, long long B_off, int cols,
+                           uint64_t salt) {
+        gd.push_back({A + A_off, A_stride, salt, kFactorA, rows, r, 0});
+        gd.push_back({Bt + B_off, B_stride, salt, kFactorB, cols, r, 1});
+    };
+    factor_pair(m->embA, static_cast<long long>(V) * r, 0, V, m->embB, static_cast<long long>(H) * r, 0, H, kSaltEmb);
+    factor_pair(m->A_win, static_cast<long long>(H) * r, 0, H, m->tB_win, static_cast<long long>(H) * r, 0, H, kSaltWin);
+    factor_pair(m->A_head, static_cast<long long>(V) * r, 0, V, m->tB_head, static_cast<long long>(H) * r, 0, H, kSaltHead);
+    for (int l = 0; l < L; ++l) {
+        const uint64_t lu = static_cast<uint64_t>(l);
+        const uint64_t gs[4] = {mix_u64(lu, kSaltWq), mix_u64(lu, kSaltWk), mix_u64(lu, kSaltWv), mix_u64(lu, kSaltWbeta)};
+        const int grows[4] = {H, H, H, 1};
+        for (int g = 0; g < 4; ++g)
+            factor_pair(m->A_qkv[l], static_cast<long long>(3 * H + 1) * r, static_cast<long long>(g) * H * r, grows[g], m->tB_qkv[l],
+                        static_cast<long long>(4) * r * H, static_cast<long long>(g) * r * H, H, gs[g]);
+        factor_pair(m->A_ff1[l], static_cast<long long>(F) * r, 0, F, m->tB_ff1[l], static_cast<long long>(r) * H, 0, H, mix_u64(lu, kSaltFf1));
+        factor_pair(m->A_ff2[l], static_cast<long long>(H) * r, 0, H, m->tB_ff2[l], static_cast<long long>(r) * F, 0, F, mix_u64(lu, kSaltFf2));
+    }
+    gd.push_back({m->pos_noise, static_cast<long long>(T) * H, kSaltPos, 0, T * H, 1, 0});
+    gd.push_back({m->hb_noise, V, kSaltHeadBias, 0, V, 1, 0});
+    gd.push_back({m->bb_noise, L, kSaltBetaBias, 0, L, 1, 0});
+    m->num_gen = static_cast<int>(gd.size());
+    for (const GenDesc& d : gd) m->gen_max_n = std::max(m->gen_max_n, d.n_major * d.rank);
+    rc = m->alloc(&m->gen_descs, gd.size());
+    if (!rc) rc = check_cuda(cudaMemcpy(m->gen_descs, gd.data(), gd.size() * sizeof(GenDesc), cudaMemcpyHostToDevice), "cudaMemcpy(gen_descs)");
+    if (rc) { bnf4_model_destroy(m); return rc; }
+    *handle = m;
+    return BNF4_OK;
+}
+
+size_t bnf4_model_device_bytes(void* handle) { return handle ? M(handle)->device_bytes : 0; }
+int bnf4_model_launches_per_wave(void* handle) { return handle ? M(handle)->launches_per_wave : 0; }
+
+int bnf4_model_set_weights(void* handle, const bnf4_model_weights* w) {
+    if (!handle || !w) return set_error(BNF4_ERR_INVALID, "model_set_weights: null argument");
+    Model& m = *M(handle);
+    const size_t vh = static_cast<size_t>(m.V) * m.H, hh = static_cast<size_t>(m.H) * m.H, hf = static_cast<size_t>(m.H) * m.F;
+    struct Item { void* d; const void* h; size_t bytes; float* shadow; size_t n; };
+    const Item items[] = {
+        {m.emb, w->emb, vh, m.sh_emb, vh}, {m.win, w->win, hh, m.sh_win, hh}, {m.wq, w->wq, m.L * hh, m.sh_wq, m.L * hh},
+        {m.wk, w->wk, m.L * hh, m.sh_wk, m.L * hh}, {m.wv, w->wv, m.L * hh, m.sh_wv, m.L * hh},
+        {m.wbeta, w->wbeta, static_cast<size_t>(m.L) * m.H, m.sh_wbeta, static_cast<size_t>(m.L) * m.H},
+        {m.ff1, w->ff1, m.L * hf, m.sh_ff1, m.L * hf}, {m.ff2, w->ff2, m.L * hf, m.sh_ff2, m.L * hf}, {m.head, w->head, vh, m.sh_head, vh},
+        {m.head_bias, w->head_bias, m.V * sizeof(float), nullptr, 0}, {m.beta_bias, w->beta_bias, m.L * sizeof(float), nullptr, 0},
+        {m.pos, w->pos, static_cast<size_t>(m.T) * m.H * sizeof(float), nullptr, 0}};
+    for (const Item& it : items) {
+        if (!it.h) return set_error(BNF4_ERR_INVALID, "model_set_weights: null weight array");
+        TRY(check_cuda(cudaMemcpy(it.d, it.h, it.bytes, cudaMemcpyHostToDevice), "cudaMemcpy(weights)"));
+        if (it.shadow) TRY(bnf4_init_shadow_from_weights(static_cast<const int8_t*>(it.d), it.shadow, static_cast<int>(it.n), nullptr));
+    }
+    TRY(check_cuda(cudaMemset(m.rms_ema, 0, (6 + 6 * static_cast<size_t>(m.L)) * sizeof(float)), "cudaMemset(rms_ema)"));
+    TRY(quantize_base(m, nullptr));
+    return check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+}
+
+int bnf4_model_get_weights(void* handle, bnf4_model_weights* w) {
+    if (!handle || !w) return set_error(BNF4_ERR_INVALID, "model_get_weights: null argument");
+    Model& m = *M(handle);
+    TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    const size_t vh = static_cast<size_t>(m.V) * m.H, hh = static_cast<size_t>(m.H) * m.H, hf = static_cast<size_t>(m.H) * m.F;
+    struct Item { const void* d; void* h; size_t bytes; };
+    const Item items[] = {{m.emb, w->emb, vh}, {m.win, w->win, hh}, {m.wq, w->wq, m.L * hh}, {m.wk, w->wk, m.L * hh}, {m.wv, w->wv, m.L * hh},
+                          {m.wbeta, w->wbeta, static_cast<size_t>(m.L) * m.H}, {m.ff1, w->ff1, m.L * hf}, {m.ff2, w->ff2, m.L * hf},
+                          {m.head, w->head, vh}, {m.head_bias, w->head_bias, m.V * sizeof(float)}, {m.beta_bias, w->beta_bias, m.L * sizeof(float)},
+                          {m.pos, w->pos, static_cast<size_t>(m.T) * m.H * sizeof(float)}};
+    for (const Item& it : items)
+        if (it.h) TRY(check_cuda(cudaMemcpy(it.h, it.d, it.bytes, cudaMemcpyDeviceToHost), "cudaMemcpy(weights)"));
+    return BNF4_OK;
+}
+
+int bnf4_model_set_tokens(void* handle, const uint8_t* tokens, const uint8_t* targets, int on_device, void* stream) {
+    if (!handle || !tokens || !targets) return set_error(BNF4_ERR_INVALID, "model_set_tokens: null argument");
+    Model& m = *M(handle);
+    const cudaMemcpyKind kind = on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+    TRY(check_cuda(cudaMemcpyAsync(m.tokens, tokens, m.R, kind, S(stream)), "cudaMemcpyAsync(tokens)"));
+    return check_cuda(cudaMemcpyAsync(m.targets, targets, m.R, kind, S(stream)), "cudaMemcpyAsync(targets)");
+}
+
+int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pairs, void* stream) {
+    if (!handle) return set_error(BNF4_ERR_INVALID, "model_prepare_step: null handle");
+    Model& m = *M(handle);
+    if (pairs <= 0 || pairs > m.cfg.max_pairs) return set_error(BNF4_ERR_INVALID, "model_prepare_step: pairs=%d outside [1,%d]", pairs, m.cfg.max_pairs);
+    if (pairs > 65535) return set_error(BNF4_ERR_INVALID, "model_prepare_step: at most 65535 pairs");
+    m.pairs_step = pairs;
+    TRY(bnf4_fill_pair_seeds(seed, epoch, pairs, m.pair_seeds, stream));
+    const dim3 grid((m.gen_max_n + 255) / 256, m.num_gen, pairs);
+    gen_noise_kernel<<<grid, 256, 0, S(stream)>>>(m.gen_descs, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
+    return check_launch("gen_noise_kernel");
+}
+
+int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* losses, void* stream) {
+    if (!handle || !losses) return set_error(BNF4_ERR_INVALID, "model_eval_pairs: null argument");
+    Model& m = *M(handle);
+    if (pair_begin < 0 || pair_count < 0 || pair_begin + pair_count > m.pairs_step)
+        return set_error(BNF4_ERR_INVALID, "model_eval_pairs: pairs [%d,%d) outside the prepared step of %d pairs", pair_begin, pair_begin + pair_count, m.pairs_step);
+    const int wave_pairs = m.W / 2;
+    for (int p = 0; p < pair_count; p += wave_pairs) {
+        const int np = std::min(wave_pairs, pair_count - p);
+        TRY(run_wave(m, pair_begin + p, 2 * np, m.sigma, losses + 2 * static_cast<size_t>(p), S(stream)));
+    }
+    return BNF4_OK;
+}
+
+int bnf4_model_eval_base(void* handle, float* loss, void* stream) {
+    if (!handle || !loss) return set_error(BNF4_ERR_INVALID, "model_eval_base: null argument");
+    Model& m = *M(handle);
+    TRY(run_wave(m, 0, 2, 0.0f, m.losses, S(stream)));
+    return check_cuda(cudaMemcpyAsync(loss, m.losses, sizeof(float), cudaMemcpyDeviceToDevice, S(stream)), "cudaMemcpyAsync(loss)");
+}
+
+int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update_cfg* u, void* stream) {
+    if (!handle || !pair_weights || !u) return set_error(BNF4_ERR_INVALID, "model_update: null argument");
+    Model& m = *M(handle);
+    const int P = m.pairs_step;
+    if (P <= 0) return set_error(BNF4_ERR_INVALID, "model_update: no prepared step");
+    cudaStream_t st = S(stream);
+    const int V = m.V, H = m.H, F = m.F, L = m.L, r = m.r;
+    const float thresh = u->thresh * std::sqrt(static_cast<float>(P));
+    int slot = 0;
+    auto matrix = [&](int8_t* w, float* shadow, const int8_t* A, long long A_stride, const int8_t* Bt, long long B_stride, int rows, int cols) {
+        float* ema = m.rms_ema + (slot++);
+        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
+        TRY(bnf4_compute_z_sumsq_lowrank(pair_weights, A, A_stride, Bt, B_stride, P, rows, cols, r, m.c_r, m.Z, m.sumsq, st));
+        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, rows * cols, m.inv_rms, st));
+        return bnf4_update_shadow_ternary_device(w, shadow, m.Z, rows * cols, m.inv_rms, u->lr, thresh, st);
+    };
+    const size_t hh = static_cast<size_t>(H) * H, hf = static_cast<size_t>(H) * F;
+    TRY(matrix(m.emb, m.sh_emb, m.embA, static_cast<long long>(V) * r, m.embB, static_cast<long long>(H) * r, V, H));
+    TRY(matrix(m.win, m.sh_win, m.A_win, static_cast<long long>(H) * r, m.tB_win, static_cast<long long>(H) * r, H, H));
+    for (int l = 0; l < L; ++l) {
+        const long long As = static_cast<long long>(3 * H + 1) * r, Bs = static_cast<long long>(4) * r * H;
+        int8_t* ws[4] = {m.wq + l * hh, m.wk + l * hh, m.wv + l * hh, m.wbeta + static_cast<size_t>(l) * H};
+        float* ss[4] = {m.sh_wq + l * hh, m.sh_wk + l * hh, m.sh_wv + l * hh, m.sh_wbeta + static_cast<size_t>(l) * H};
+        const int grows[4] = {H, H, H, 1};
+        for (int g = 0; g < 4; ++g)
+            TRY(matrix(ws[g], ss[g], m.A_qkv[l] + static_cast<size_t>(g) * H * r, As, m.tB_qkv[l] + static_cast<size_t>(g) * r * H, Bs, grows[g], H));
+        TRY(matrix(m.ff1 + l * hf, m.sh_ff1 + l * hf, m.A_ff1[l], static_cast<long long>(F) * r, m.tB_ff1[l], static_cast<long long>(r) * H, F, H));
+        TRY(matrix(m.ff2 + l * hf, m.sh_ff2 + l * hf, m.A_ff2[l], static_cast<long long>(H) * r, m.tB_ff2[l], static_cast<long long>(r) * F, H, F));
+    }
+    TRY(matrix(m.head, m.sh_head, m.A_head, static_cast<long long>(V) * r, m.tB_head, static_cast<long long>(H) * r, V, H));
+    // fp32 vectors (reference: update_vector on the host, src/train_efla_lm.cpp:5648-5657)
+    auto vec = [&](float* v, int n, uint64_t salt) {
+        float* ema = m.rms_ema + (slot++);
+        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
+        TRY(bnf4_compute_z_sumsq(pair_weights, m.pair_seeds, salt, P, n, m.cfg.use_clt, m.cfg.clt_k, m.Z, m.sumsq, st));
+        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
+        return bnf4_update_vector_device(v, m.Z, n, m.inv_rms, u->lr, thresh, st);
+    };
+    TRY(vec(m.head_bias, V, kSaltHeadBias));
+    TRY(vec(m.beta_bias, L, kSaltBetaBias));
+    if (u->train_pos) TRY(vec(m.pos, m.T * H, kSaltPos));
+    return quantize_base(m, st);
+}
+
+int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes) {
+    if (!handle || !name || !h_dst) return set_error(BNF4_ERR_INVALID, "model_read_buffer: null argument");
+    Model& m = *M(handle);
+    const size_t Mr = static_cast<size_t>(m.M);
+    const std::string n(name);
+    const void* src = nullptr;
+    size_t size = 0;
+    if (n == "x_q") { src = m.x_q; size = Mr * m.H; }
+    else if (n == "a_h") { src = m.a_h; size = Mr * m.H / 2; }
+    else if (n == "sf_h") { src = m.sf_h; size = sf_bytes(static_cast<int>(Mr), m.H); }
+    else if (n == "a_f") { src = m.a_f; size = Mr * m.F / 2; }
+    else if (n == "sf_f") { src = m.sf_f; size = sf_bytes(static_cast<int>(Mr), m.F); }
+    else if (n == "qkv") { src = m.qkv; size = Mr * m.FC * sizeof(float); }
+    else if (n == "y") { src = m.y; size = Mr * m.H * sizeof(float); }
+    else if (n == "t_a") { src = m.t_a; size = Mr * 4 * m.r * sizeof(int32_t); }
+    else if (n == "t_f") { src = m.t_f; size = Mr * m.r * sizeof(int32_t); }
+    else if (n == "losses") { src = m.losses; size = m.W * sizeof(float); }
+    else return set_error(BNF4_ERR_INVALID, "model_read_buffer: unknown buffer '%s'", name);
+    TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    return check_cuda(cudaMemcpy(h_dst, src, std::min(bytes, size), cudaMemcpyDeviceToHost), "cudaMemcpy(read_buffer)");
+}
+
+}  // extern "C"

@@ -86,9 +86,9 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p) {
                 } else {
                     if (ns != 0.0f) {
                         const int8_t* A = p.embA + static_cast<size_t>(pair) * p.embA_pair_stride + static_cast<size_t>(tok) * p.rank;
-                        const int8_t* B = p.embB + static_cast<size_t>(pair) * p.embB_pair_stride + static_cast<size_t>(j) * p.rank;
+                        const int8_t* B = p.embB + static_cast<size_t>(pair) * p.embB_pair_stride + j;  // [rank][H]
                         int pert = 0;
-                        for (int r = 0; r < p.rank; ++r) pert += static_cast<int>(A[r]) * static_cast<int>(B[r]);
+                        for (int r = 0; r < p.rank; ++r) pert += static_cast<int>(A[r]) * static_cast<int>(B[static_cast<size_t>(r) * p.cols_in]);
                         f = fmaf(ns * p.c_rank, static_cast<float>(pert), f);
                     }
                 }

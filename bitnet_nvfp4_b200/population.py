@@ -1,0 +1,196 @@
+"""Population-evaluation ES step on one GPU: binding of the bnf4_model_* entry points (include/bnf4.h).
+
+Mirrors, at the granularity of one ES step, what the reference's train_efla_lm does per epoch
+(src/train_efla_lm.cpp:5255-5657): derive pair seeds, evaluate every antithetic pair, shape the fitness,
+update the weights. The work is done by libbnf4.so; this module only moves pointers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, asdict
+
+import numpy as np
+import torch
+
+from . import lib as _l
+
+c_int, c_float, c_void_p = C.c_int, C.c_float, C.c_void_p
+
+
+class ModelCfg(C.Structure):
+    """bnf4_model_cfg"""
+
+    _fields_ = [(n, c_int) for n in "vocab hidden layers mlp_mult seq batch heads rank sigma_shift use_clt clt_k method".split()] + \
+               [(n, c_float) for n in "act_scale mlp_act_scale ln_scale residual_scale mlp_residual_scale eps".split()] + \
+               [("max_pairs", c_int), ("wave_members", c_int)]
+
+
+class ModelWeights(C.Structure):
+    """bnf4_model_weights (host pointers)"""
+
+    _fields_ = [(n, c_void_p) for n in "emb win wq wk wv wbeta ff1 ff2 head head_bias beta_bias pos".split()]
+
+
+class UpdateCfg(C.Structure):
+    """bnf4_update_cfg"""
+
+    _fields_ = [("lr", c_float), ("thresh", c_float), ("use_adaptive", c_int), ("adaptive_beta", c_float),
+                ("adaptive_eps", c_float), ("train_pos", c_int)]
+
+
+_l.register({
+    "bnf4_model_create": (c_int, [C.POINTER(ModelCfg), C.POINTER(c_void_p)]),
+    "bnf4_model_destroy": (c_int, [c_void_p]),
+    "bnf4_model_device_bytes": (C.c_size_t, [c_void_p]),
+    "bnf4_model_set_weights": (c_int, [c_void_p, C.POINTER(ModelWeights)]),
+    "bnf4_model_get_weights": (c_int, [c_void_p, C.POINTER(ModelWeights)]),
+    "bnf4_model_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "bnf4_model_prepare_step": (c_int, [c_void_p, C.c_uint64, C.c_uint64, c_int, c_void_p]),
+    "bnf4_model_eval_pairs": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "bnf4_model_eval_base": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "bnf4_model_update": (c_int, [c_void_p, c_void_p, C.POINTER(UpdateCfg), c_void_p]),
+    "bnf4_model_read_buffer": (c_int, [c_void_p, C.c_char_p, c_void_p, C.c_size_t]),
+    "bnf4_model_launches_per_wave": (c_int, [c_void_p]),
+})
+
+WEIGHT_NAMES = "emb win wq wk wv wbeta ff1 ff2 head head_bias beta_bias pos".split()
+
+
+@dataclass
+class Config:
+    """Defaults are the reference's (TrainConfig, src/train_efla_lm.cpp:186-300) except heads and rank, which follow
+    the benchmark configuration (8 heads of 64, rank-1 perturbations)."""
+    vocab: int = 256
+    hidden: int = 512
+    layers: int = 4
+    mlp_mult: int = 2
+    seq: int = 128
+    batch: int = 32
+    heads: int = 8
+    rank: int = 1
+    sigma_shift: int = 3
+    use_clt: int = 1
+    clt_k: int = 4
+    method: int = 1
+    act_scale: float = 0.8
+    mlp_act_scale: float = 1.0
+    ln_scale: float = 1.0
+    residual_scale: float = 1.0
+    mlp_residual_scale: float = 1.0
+    eps: float = 1e-6
+    max_pairs: int = 1024
+    wave_members: int = 0
+
+    def weight_shapes(self) -> dict:
+        V, H, L, F, T = self.vocab, self.hidden, self.layers, self.hidden * self.mlp_mult, self.seq
+        return {"emb": (V, H), "win": (H, H), "wq": (L, H, H), "wk": (L, H, H), "wv": (L, H, H), "wbeta": (L, H),
+                "ff1": (L, F, H), "ff2": (L, H, F), "head": (V, H), "head_bias": (V,), "beta_bias": (L,), "pos": (T, H)}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class PopulationModel:
+    def __init__(self, cfg: Config):
+        self.cfg = cfg
+        self.lib = _l.load()
+        self._c = ModelCfg(**asdict(cfg))
+        self.h = c_void_p()
+        _l.check(self.lib.bnf4_model_create(C.byref(self._c), C.byref(self.h)))
+        self.pairs = 0
+
+    def close(self):
+        if self.h:
+            self.lib.bnf4_model_destroy(self.h)
+            self.h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def device_bytes(self) -> int:
+        return self.lib.bnf4_model_device_bytes(self.h)
+
+    @property
+    def launches_per_wave(self) -> int:
+        return self.lib.bnf4_model_launches_per_wave(self.h)
+
+    def _weights_struct(self, arrays: dict) -> ModelWeights:
+        return ModelWeights(*[arrays[n].ctypes.data for n in WEIGHT_NAMES])
+
+    def set_weights(self, weights: dict):
+        shapes = self.cfg.weight_shapes()
+        arrays = {}
+        for n in WEIGHT_NAMES:
+            dt = np.float32 if n in ("head_bias", "beta_bias", "pos") else np.int8
+            a = np.ascontiguousarray(weights[n], dtype=dt)
+            assert a.shape == shapes[n], (n, a.shape, shapes[n])
+            arrays[n] = a
+        _l.check(self.lib.bnf4_model_set_weights(self.h, C.byref(self._weights_struct(arrays))))
+
+    def get_weights(self) -> dict:
+        shapes = self.cfg.weight_shapes()
+        arrays = {n: np.zeros(shapes[n], np.float32 if n in ("head_bias", "beta_bias", "pos") else np.int8) for n in WEIGHT_NAMES}
+        _l.check(self.lib.bnf4_model_get_weights(self.h, C.byref(self._weights_struct(arrays))))
+        return arrays
+
+    def set_tokens(self, tokens, targets):
+        """tokens/targets: uint8 [B][T], torch CUDA tensors or (pinned) host tensors / numpy arrays."""
+        def ptr(x):
+            if isinstance(x, torch.Tensor):
+                assert x.dtype == torch.uint8 and x.is_contiguous()
+                return x.data_ptr(), x.is_cuda
+            x = np.ascontiguousarray(x, np.uint8)
+            self._keep = getattr(self, "_keep", []) + [x]
+            return x.ctypes.data, False
+        (pt, dt), (pg, dg) = ptr(tokens), ptr(targets)
+        assert dt == dg
+        _l.check(self.lib.bnf4_model_set_tokens(self.h, pt, pg, int(dt), _stream()))
+        if not dt:
+            torch.cuda.current_stream().synchronize()
+            self._keep = []
+
+    def prepare_step(self, seed: int, epoch: int, pairs: int):
+        _l.check(self.lib.bnf4_model_prepare_step(self.h, seed, epoch, pairs, _stream()))
+        self.pairs = pairs
+
+    def eval_pairs(self, pair_begin: int, pair_count: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Returns a float32 CUDA tensor [2*pair_count]: (loss+, loss-) per pair."""
+        if out is None:
+            out = torch.empty(2 * pair_count, dtype=torch.float32, device="cuda")
+        _l.check(self.lib.bnf4_model_eval_pairs(self.h, pair_begin, pair_count, out.data_ptr(), _stream()))
+        return out
+
+    def eval_base(self) -> torch.Tensor:
+        out = torch.empty(1, dtype=torch.float32, device="cuda")
+        _l.check(self.lib.bnf4_model_eval_base(self.h, out.data_ptr(), _stream()))
+        return out
+
+    def update(self, pair_weights: torch.Tensor, lr=0.8, thresh=0.008, use_adaptive=True, adaptive_beta=0.95, adaptive_eps=1e-3,
+               train_pos=True):
+        assert pair_weights.is_cuda and pair_weights.dtype == torch.float32 and pair_weights.numel() == self.pairs
+        u = UpdateCfg(lr, thresh, int(use_adaptive), adaptive_beta, adaptive_eps, int(train_pos))
+        _l.check(self.lib.bnf4_model_update(self.h, pair_weights.data_ptr(), C.byref(u), _stream()))
+
+    def read_buffer(self, name: str, dtype, count: int) -> np.ndarray:
+        out = np.zeros(count, dtype)
+        _l.check(self.lib.bnf4_model_read_buffer(self.h, name.encode(), out.ctypes.data, out.nbytes))
+        return out
+
+
+def fitness_from_losses(losses: torch.Tensor) -> torch.Tensor:
+    """f_p = -(loss+ - loss-)  (reference: src/train_efla_lm.cpp:5466)."""
+    l2 = losses.view(-1, 2)
+    return -(l2[:, 0] - l2[:, 1])
+
+
+def shape_fitness(fitness: torch.Tensor, mode: int = 0, clip: float = 3.0) -> torch.Tensor:
+    """Centered-rank shaping on the host (2 KB round trip), returned as a CUDA tensor."""
+    from . import host
+    w = fitness.detach().to("cpu", torch.float32).contiguous().numpy().copy()
+    host.shape_pair_weights(w, mode, clip)
+    return torch.from_numpy(w).to(fitness.device)

@@ -122,7 +122,7 @@ typedef struct bnf4_rowquant_desc {
     const int8_t* emb_w;
     const int8_t* emb_noise; /* [pair][V][H] */
     const int8_t* embA;      /* [pair][V][rank] */
-    const int8_t* embB;      /* [pair][H][rank] */
+    const int8_t* embB;      /* [pair][rank][H] */
     long long embA_pair_stride, embB_pair_stride;
     int rank;
     const float* pos;         /* [pos rows][H] */
@@ -322,6 +322,90 @@ int bnf4_add_scaled(float* out, const float* noise, int n, float scale, void* st
 /* Centered-rank / z-score / sign shaping of the pair fitness vector on the host (pure function, no GPU):
  * reference shape_pair_weights src/train_efla_lm.cpp:3898-3952; ties broken by index. mode 0/1/2. */
 int bnf4_shape_pair_weights(float* h_w, int n, int mode, float clip);
+
+/* ---------------------------------------------------------------------------------------------
+ * Population driver: the B200-native re-design of CudaEflaLm::evaluate_loss + eval_worker + gpu_update_matrix
+ * (reference: src/train_efla_lm.cpp:2117-3431, 5344-5468, 4304-4358).
+ *
+ * The reference evaluates one member at a time, token by token (M = batch rows per GEMM, ~8.7k launches and
+ * one blocking sync per member). Here a wave of members is evaluated layer by layer: every GEMM of a layer
+ * covers all tokens of all members of the wave (M = members * batch * seq rows), the recurrent state stays on
+ * chip for the whole sequence, and the per-member perturbation is the rank-r form fused into the GEMM
+ * epilogue. Row r of a wave buffer is (member, b, t) = (r / (B*T), (r / T) % B, r % T).
+ * Members 2p and 2p+1 are the + and - evaluations of antithetic pair p.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct bnf4_model_cfg {
+    int vocab;        /* 256 */
+    int hidden;       /* H, multiple of 64 */
+    int layers;       /* L */
+    int mlp_mult;     /* F = mlp_mult * H */
+    int seq;          /* T */
+    int batch;        /* B */
+    int heads;        /* head_dim = H / heads; 1 reproduces the reference */
+    int rank;         /* rank of the per-member perturbation, 1..4 */
+    int sigma_shift;  /* sigma = 2^-sigma_shift */
+    int use_clt;
+    int clt_k;
+    int method;       /* 0 DeltaNet, 1 EFLA */
+    float act_scale, mlp_act_scale, ln_scale, residual_scale, mlp_residual_scale, eps;
+    int max_pairs;    /* pairs per ES step (population / 2) */
+    int wave_members; /* members evaluated per wave (even); 0 = library default */
+} bnf4_model_cfg;
+
+/* Host-side weight set (reference: EflaLmWeights src/train_efla_lm.cpp:419-431 plus the positional table). */
+typedef struct bnf4_model_weights {
+    int8_t* emb;      /* [V][H] */
+    int8_t* win;      /* [H][H] */
+    int8_t* wq;       /* [L][H][H] */
+    int8_t* wk;       /* [L][H][H] */
+    int8_t* wv;       /* [L][H][H] */
+    int8_t* wbeta;    /* [L][H] */
+    int8_t* ff1;      /* [L][F][H] */
+    int8_t* ff2;      /* [L][H][F] */
+    int8_t* head;     /* [V][H] */
+    float* head_bias; /* [V] */
+    float* beta_bias; /* [L] */
+    float* pos;       /* [T][H] */
+} bnf4_model_weights;
+
+typedef struct bnf4_update_cfg {
+    float lr;
+    float thresh;        /* the update is skipped where |inv_rms * Z| < thresh * sqrt(pairs) */
+    int use_adaptive;    /* RMS-EMA normalisation */
+    float adaptive_beta; /* 0.95 */
+    float adaptive_eps;  /* 1e-3 */
+    int train_pos;       /* also update the positional table */
+} bnf4_update_cfg;
+
+/* Allocates every device buffer of the model on the current device (cudaMalloc). */
+int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle);
+int bnf4_model_destroy(void* handle);
+/* Bytes of device memory held by the model. */
+size_t bnf4_model_device_bytes(void* handle);
+/* h_w: host arrays. Uploads, resets the fp32 shadow weights to the int8 values (reference: init_shadow_from_weights),
+ * clears the RMS-EMA state and quantises the base weights to NVFP4. Synchronises. */
+int bnf4_model_set_weights(void* handle, const bnf4_model_weights* h_w);
+/* Copies the current int8 weights / fp32 vectors (and optionally the shadow weights) back to host arrays. Synchronises. */
+int bnf4_model_get_weights(void* handle, bnf4_model_weights* h_w);
+/* tokens / targets: uint8 [B][T] (device pointers when on_device != 0, else host). */
+int bnf4_model_set_tokens(void* handle, const uint8_t* tokens, const uint8_t* targets, int on_device, void* stream);
+/* Derives pair seeds (mix(seed, mix(epoch, p))) and generates every per-pair noise vector of the step:
+ * rank-r factors of all 27 matrices, positional / head-bias / beta-bias noise. pairs <= cfg.max_pairs. */
+int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pairs, void* stream);
+/* Evaluates pairs [pair_begin, pair_begin + pair_count): losses[2*i], losses[2*i+1] = mean cross-entropy of the
+ * + and - member of pair pair_begin + i. Device output. */
+int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* losses, void* stream);
+/* Mean cross-entropy of the unperturbed model on the current tokens (device output, 1 float). */
+int bnf4_model_eval_base(void* handle, float* loss, void* stream);
+/* pair_weights: shaped fitness of ALL pairs of the step (device, `pairs` floats as passed to prepare_step).
+ * Applies the ES update to all ternary matrices and fp32 vectors and re-quantises the base weights.
+ * Deterministic: every rank that calls it with the same inputs ends with identical bits. */
+int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update_cfg* ucfg, void* stream);
+/* Debug/verification access to an internal wave buffer by name ("x_q", "a_h", "sf_h", "a_f", "sf_f", "qkv", "y",
+ * "t_a", "t_f", "losses"): copies min(bytes, size) bytes to host. Synchronises. */
+int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes);
+/* Kernels launched by one bnf4_model_eval_pairs wave and by one bnf4_model_update (for accounting). */
+int bnf4_model_launches_per_wave(void* handle);
 
 #ifdef __cplusplus
 }

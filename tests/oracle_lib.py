@@ -236,6 +236,14 @@ def update_shadow_ternary(w, shadow, Z, inv_rms, lr, thresh):
     lib().orc_update_shadow_ternary(P(w), P(shadow), P(Z), len(Z), cf(inv_rms), cf(lr), cf(thresh))
 
 
+def update_vector(v, pair_weights, pair_seeds, salt, rms_ema, use_adaptive, beta, eps, lr, thresh, use_clt=True, clt_k=4):
+    """In-place plain update of a float vector; returns the new rms_ema."""
+    ema = C.c_float(rms_ema)
+    lib().orc_update_vector(P(v), len(v), P(pair_weights), P(pair_seeds), cu64(salt), len(pair_weights), int(use_clt), clt_k,
+                            C.byref(ema), int(use_adaptive), cf(beta), cf(eps), cf(lr), cf(thresh))
+    return ema.value
+
+
 class OracleModel:
     """One member's forward on the CPU (oracle/model.cpp)."""
 

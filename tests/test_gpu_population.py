@@ -1,0 +1,147 @@
+"""GPU parity of the population driver (bnf4_model_*) against the CPU oracle's member forward and ES update.
+
+Bars: per-member mean cross-entropy within 1e-4 relative of the oracle; after an update driven by the
+oracle's own fitness vector the int8 weights are bit-identical to the oracle's.
+"""
+import numpy as np
+import pytest
+
+import oracle_lib as orc
+
+pytestmark = pytest.mark.gpu
+
+SALT = dict(emb=0x111111, win=0x222222, wq=0x333333, wk=0x444444, wv=0x555555, wbeta=0x666666, ff1=0x999999, ff2=0xAAAAAA,
+            head=0x777777, head_bias=0x888888, beta_bias=0x9999999, pos=0xBEEFF00D)
+
+
+def make(cfg_kw):
+    import torch
+    from bitnet_nvfp4_b200 import population, synth
+    assert torch.cuda.is_available()
+    cfg = population.Config(**cfg_kw)
+    w = synth.init_weights(cfg)
+    corpus = synth.zipf_corpus(1 << 16, 1.1, 123)
+    tok, tgt = synth.sample_batch(corpus, cfg.batch, cfg.seq, 123)
+    model = population.PopulationModel(cfg)
+    model.set_weights(w)
+    model.set_tokens(tok, tgt)
+    return cfg, w, tok, tgt, model
+
+
+def oracle_cfg(cfg):
+    return dict(vocab=cfg.vocab, hidden=cfg.hidden, layers=cfg.layers, mlp_mult=cfg.mlp_mult, seq=cfg.seq, batch=cfg.batch,
+                heads=cfg.heads, rank=cfg.rank, sigma_shift=cfg.sigma_shift, use_clt=cfg.use_clt, clt_k=cfg.clt_k, method=cfg.method,
+                act_scale=cfg.act_scale, mlp_act_scale=cfg.mlp_act_scale, ln_scale=cfg.ln_scale, residual_scale=cfg.residual_scale,
+                mlp_residual_scale=cfg.mlp_residual_scale, eps=cfg.eps)
+
+
+@pytest.mark.parametrize("cfg_kw", [
+    dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=4, wave_members=4),
+    dict(hidden=128, layers=2, seq=32, batch=8, heads=1, rank=2, max_pairs=3, wave_members=2),
+    dict(hidden=256, layers=1, seq=16, batch=8, heads=4, rank=4, max_pairs=2, wave_members=4),
+    dict(hidden=512, layers=4, seq=128, batch=32, heads=8, rank=1, max_pairs=2, wave_members=4),
+])
+def test_member_losses_match_oracle(cfg_kw):
+    from bitnet_nvfp4_b200 import host
+    cfg, w, tok, tgt, model = make(cfg_kw)
+    seed, epoch, pairs = 1, 5, cfg.max_pairs
+    model.prepare_step(seed, epoch, pairs)
+    losses = model.eval_pairs(0, pairs).cpu().numpy()
+    base = model.eval_base().item()
+    assert host.device_error() == 0
+    om = orc.OracleModel(oracle_cfg(cfg), w)
+    ref_base = om.forward(tok, tgt, 0, 0)
+    assert abs(base - ref_base) <= 1e-4 * abs(ref_base)
+    for p in range(pairs):
+        ps = orc.mix(seed, orc.mix(epoch, p))
+        for s, anti in enumerate((1, -1)):
+            ref = om.forward(tok, tgt, ps, anti)
+            got = losses[2 * p + s]
+            assert abs(got - ref) <= 1e-4 * abs(ref), (p, anti, got, ref)
+    # antithetic members differ from each other and from the base model
+    assert np.abs(losses[0::2] - losses[1::2]).min() > 0
+
+
+def test_wave_split_is_invisible():
+    """The same pairs evaluated in waves of 2 or of 8 members give identical losses."""
+    kw = dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=6)
+    _, _, _, _, m2 = make(dict(kw, wave_members=2))
+    _, _, _, _, m8 = make(dict(kw, wave_members=8))
+    for m in (m2, m8):
+        m.prepare_step(3, 0, 6)
+    a = m2.eval_pairs(0, 6).cpu().numpy()
+    b = m8.eval_pairs(0, 6).cpu().numpy()
+    c = m8.eval_pairs(2, 3).cpu().numpy()  # a slice, as a data-parallel rank would evaluate it
+    assert np.array_equal(a, b)
+    assert np.array_equal(c, b[4:10])
+
+
+def test_residual_stream_taps_match_oracle():
+    """Layer-by-layer localisation: the int8 residual stream of member 0 after the last layer."""
+    cfg, w, tok, tgt, model = make(dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=1, wave_members=2))
+    model.prepare_step(1, 0, 1)
+    model.eval_pairs(0, 1)
+    R, H, L = cfg.batch * cfg.seq, cfg.hidden, cfg.layers
+    xq = model.read_buffer("x_q", np.int8, 2 * R * H).reshape(2, R, H)
+    om = orc.OracleModel(oracle_cfg(cfg), w)
+    for s, anti in enumerate((1, -1)):
+        taps = dict(x_q=np.zeros((L, R, H), np.int8))
+        om.forward(tok, tgt, orc.mix(1, orc.mix(0, 0)), anti, taps)
+        diff = np.abs(xq[s].astype(int) - taps["x_q"][-1].astype(int))
+        # int8 values downstream of float GEMMs and tanhf: a step of one on a small fraction of elements
+        assert diff.max() <= 2 and (diff != 0).mean() <= 2e-2
+
+
+def test_update_bit_exact_given_fitness():
+    """ES update (rank-r Z, RMS-EMA, gated round-clip, vectors) against the oracle, two consecutive steps."""
+    import torch
+    from bitnet_nvfp4_b200 import host
+    cfg, w, tok, tgt, model = make(dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=2, max_pairs=24, wave_members=8))
+    rng = np.random.default_rng(7)
+    V, H, L, F, T, r = cfg.vocab, cfg.hidden, cfg.layers, cfg.hidden * cfg.mlp_mult, cfg.seq, cfg.rank
+    ref = {k: v.copy() for k, v in w.items()}
+    shadow = {k: v.astype(np.float32) for k, v in ref.items() if v.dtype == np.int8}
+    ema = {}
+    cs = host.c_rank(r)
+    lr, th = 0.8, 0.008
+    for epoch in range(2):
+        pairs = 24
+        model.prepare_step(1, epoch, pairs)
+        pw = orc.shape_pair_weights(rng.standard_normal(pairs).astype(np.float32))
+        model.update(torch.from_numpy(pw).cuda(), lr=lr, thresh=th)
+        seeds = orc.fill_pair_seeds(1, epoch, pairs)
+        thresh = float(np.float32(th) * np.sqrt(np.float32(pairs)))
+
+        def upd_matrix(name, sub, salt, rows, cols):
+            wv = ref[name] if sub is None else ref[name][sub]
+            sv = shadow[name] if sub is None else shadow[name][sub]
+            Z, ss = orc.compute_z_sumsq_lowrank(pw, seeds, salt, rows, cols, r, cs)
+            inv, ema[(name, sub)] = orc.update_inv_rms(ss, ema.get((name, sub), 0.0), True, 0.95, 1e-3, rows * cols)
+            wf, sf = wv.reshape(-1), sv.reshape(-1)
+            orc.update_shadow_ternary(wf, sf, Z, inv, lr, thresh)
+
+        upd_matrix("emb", None, SALT["emb"], V, H)
+        upd_matrix("win", None, SALT["win"], H, H)
+        for l in range(L):
+            upd_matrix("wq", l, orc.mix(l, SALT["wq"]), H, H)
+            upd_matrix("wk", l, orc.mix(l, SALT["wk"]), H, H)
+            upd_matrix("wv", l, orc.mix(l, SALT["wv"]), H, H)
+            upd_matrix("wbeta", l, orc.mix(l, SALT["wbeta"]), 1, H)
+            upd_matrix("ff1", l, orc.mix(l, SALT["ff1"]), F, H)
+            upd_matrix("ff2", l, orc.mix(l, SALT["ff2"]), H, F)
+        upd_matrix("head", None, SALT["head"], V, H)
+        for name, n in (("head_bias", V), ("beta_bias", L), ("pos", T * H)):
+            v = ref[name].reshape(-1)
+            ema[name] = orc.update_vector(v, pw, seeds, SALT[name], ema.get(name, 0.0), True, 0.95, 1e-3, lr, thresh)
+        got = model.get_weights()
+        for name in ("emb", "win", "wq", "wk", "wv", "wbeta", "ff1", "ff2", "head"):
+            assert np.array_equal(got[name], ref[name]), name
+        for name in ("head_bias", "beta_bias", "pos"):
+            assert np.array_equal(got[name], ref[name]), name
+    changed = sum(int((got[n] != w[n]).sum()) for n in ("emb", "win", "wq", "ff1", "head"))
+    assert changed > 0
+    # the re-quantised base weights are used by the next evaluation
+    model.prepare_step(1, 2, 2)
+    l_after = model.eval_base().item()
+    om = orc.OracleModel(oracle_cfg(cfg), ref)
+    assert abs(l_after - om.forward(tok, tgt, 0, 0)) <= 1e-4 * abs(l_after)

@@ -106,7 +106,7 @@ def test_embedding_lowrank_population(H):
     sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
     tout = torch.zeros((rows, 3), dtype=torch.int32, device="cuda")
     H.rowquant(H.FE_EMBED_LOWRANK, rows=rows, cols_in=hid, cols_out=hid, rows_per_member=R, sigma=sigma, c_rank=cr,
-               tokens=dev(toks), token_stride=1, row_mod=R, emb_w=dev(emb), embA=dev(A), embB=dev(Bm),
+               tokens=dev(toks), token_stride=1, row_mod=R, emb_w=dev(emb), embA=dev(A), embB=dev(Bm.transpose(0, 2, 1)),
                embA_pair_stride=V * rank, embB_pair_stride=hid * rank, rank=rank, out_q=q, ld_q=hid, out_codes=codes,
                out_sf=sf, tvec=dev(tvec), tvec_pair_stride=3 * hid, nvec=3, t_out=tout)
     qs, ts = [], []
