@@ -21,6 +21,15 @@ namespace {
 
 constexpr float kCRankBase = 0.6123724356957945f;  // sqrt(3/8)
 
+// Kernel classes for the optional timing breakdown (bnf4_model_get_timing).
+enum KernelClass : int {
+    KC_GEN_NOISE = 0, KC_BETA_BIAS, KC_EMBED, KC_GEMM_WIN, KC_POS_GELU_NORM, KC_GEMM_QKV, KC_EFLA, KC_ADD_NORM, KC_GEMM_FF1,
+    KC_GEMM_FF2, KC_GEMM_HEAD, KC_CROSS_ENTROPY, KC_UPDATE_Z, KC_UPDATE_APPLY, KC_REQUANTIZE, kNumClasses
+};
+const char* const kClassNames[kNumClasses] = {"gen_noise", "beta_bias", "embed_quant", "gemm_win", "pos_gelu_norm_quant", "gemm_qkv",
+                                              "efla_scan", "add_norm_quant", "gemm_ff1_gelu_fp4", "gemm_ff2", "gemm_head",
+                                              "cross_entropy", "update_z_sumsq", "update_apply", "requantize_weights"};
+
 // One entry of the per-step noise table: dst[pair][...] filled from the counter hash.
 struct GenDesc {
     int8_t* dst;
@@ -96,6 +105,21 @@ struct Model {
     float *Z, *sumsq, *inv_rms;
     int launches_per_wave = 0;
 
+    // optional per-kernel-class timing with CUDA events on the launching stream
+    bool timing = false;
+    struct Span { int cls; cudaEvent_t a, b; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> free_events;
+    double class_ms[kNumClasses] = {};
+    long long class_launches[kNumClasses] = {};
+
+    cudaEvent_t get_event() {
+        if (!free_events.empty()) { cudaEvent_t e = free_events.back(); free_events.pop_back(); return e; }
+        cudaEvent_t e = nullptr;
+        cudaEventCreate(&e);
+        return e;
+    }
+
     template <typename Tp>
     int alloc(Tp** p, size_t count, bool zero = true) {
         void* ptr = nullptr;
@@ -110,6 +134,25 @@ struct Model {
         }
         *p = static_cast<Tp*>(ptr);
         return BNF4_OK;
+    }
+};
+
+// Records an event pair around the launches issued while it is alive (only when timing is on).
+struct TimedScope {
+    Model& m;
+    cudaStream_t st;
+    int cls, n;
+    cudaEvent_t a = nullptr;
+    TimedScope(Model& m_, int cls_, cudaStream_t st_, int n_ = 1) : m(m_), st(st_), cls(cls_), n(n_) {
+        if (m.timing) { a = m.get_event(); cudaEventRecord(a, st); }
+    }
+    ~TimedScope() {
+        if (m.timing) {
+            cudaEvent_t b = m.get_event();
+            cudaEventRecord(b, st);
+            m.spans.push_back({cls, a, b});
+            m.class_launches[cls] += n;
+        }
     }
 };
 
@@ -152,11 +195,13 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
 
     {   // per-member beta bias for every layer
         const int n = L * nm;
+        TimedScope ts(m, KC_BETA_BIAS, st);
         beta_bias_kernel<<<(n + 127) / 128, 128, 0, st>>>(m.beta_bias, m.bb_noise + P0 * L, L, nm, sigma, m.bb_eff);
         TRY(check_launch("beta_bias_kernel"));
         ++launches;
     }
     {   // embedding -> a_h, t for win
+        TimedScope ts(m, KC_EMBED, st);
         bnf4_rowquant_desc p = {};
         p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma; p.c_rank = m.c_r;
         p.tokens = m.tokens; p.token_stride = 1; p.row_mod = R; p.emb_w = m.emb;
@@ -167,8 +212,9 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
         TRY(rowquant_dispatch(FE_EMBED_LOWRANK, p, st));
         ++launches;
     }
-    auto gemm = [&](const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, int n, int k, float alpha, float* d,
+    auto gemm = [&](int cls, const uint8_t* a, const uint8_t* sfa, const uint8_t* b, const uint8_t* sfb, int n, int k, float alpha, float* d,
                     int ldd, const int8_t* A, long long A_stride, const int32_t* t, int t_stride, float out_scale, int group_cols) {
+        TimedScope ts(m, cls, st);
         bnf4_gemm_desc g = {};
         g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.m = rows; g.n = n; g.k = k; g.alpha = alpha; g.d = d; g.ldd = ldd;
         g.epilogue = EPI_F32; g.rank = rank; g.rows_per_member = R; g.lora_t = t; g.t_stride = t_stride; g.lora_A = A;
@@ -176,10 +222,11 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
         return gemm_nvfp4_launch(g, st);
     };
     // input projection -> y
-    TRY(gemm(m.a_h, m.sf_h, m.q_win, m.sfq_win, H, H, m.s_h, m.y, H, m.A_win + P0 * H * r, static_cast<long long>(H) * r, m.t_a, r,
+    TRY(gemm(KC_GEMM_WIN, m.a_h, m.sf_h, m.q_win, m.sfq_win, H, H, m.s_h, m.y, H, m.A_win + P0 * H * r, static_cast<long long>(H) * r, m.t_a, r,
              m.s_h, 0));
     ++launches;
     {   // + pos, GELU -> residual stream x_q; abs-mean norm -> a_h; t for qkv[0]
+        TimedScope ts(m, KC_POS_GELU_NORM, st);
         bnf4_rowquant_desc p = {};
         p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
         p.in_f32 = m.y; p.ld_in = H; p.inout_i8 = m.x_q; p.pos = m.pos; p.pos_mod = m.T;
@@ -191,10 +238,11 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
     }
     for (int l = 0; l < L; ++l) {
         // fused QKV(+beta) projection -> qkv [rows][FC]; out_scale is folded into the weight scales (alpha = 1)
-        TRY(gemm(m.a_h, m.sf_h, m.q_qkv[l], m.sfq_qkv[l], 3 * H + 1, H, 1.0f, m.qkv, FC, m.A_qkv[l] + P0 * (3 * H + 1) * r,
+        TRY(gemm(KC_GEMM_QKV, m.a_h, m.sf_h, m.q_qkv[l], m.sfq_qkv[l], 3 * H + 1, H, 1.0f, m.qkv, FC, m.A_qkv[l] + P0 * (3 * H + 1) * r,
                  static_cast<long long>(3 * H + 1) * r, m.t_a, 4 * r, m.s_h, H));
         ++launches;
         {   // recurrence over the whole sequence -> y
+            TimedScope ts(m, KC_EFLA, st);
             bnf4_efla_desc e = {};
             e.state = nullptr; e.state_fp16 = 1; e.q = m.qkv; e.k = m.qkv + H; e.v = m.qkv + 2 * H; e.beta_raw = m.qkv + 3 * H;
             e.ld_qkv = FC; e.ld_beta = FC; e.beta_bias_seq = m.bb_eff + static_cast<size_t>(l) * nm; e.seqs_per_bias = m.B;
@@ -219,6 +267,7 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
             }
         }
         {   // residual add + abs-mean norm -> a_h; t for ff1
+            TimedScope ts(m, KC_ADD_NORM, st);
             bnf4_rowquant_desc p = {};
             p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
             p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.add_scale = m.cfg.residual_scale; p.norm_scale = m.cfg.ln_scale;
@@ -228,6 +277,7 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
             ++launches;
         }
         {   // ff1 with GELU -> int8 -> FP4 epilogue, projections for ff2
+            TimedScope ts(m, KC_GEMM_FF1, st);
             if (pert) TRY(check_cuda(cudaMemsetAsync(m.t_f, 0, static_cast<size_t>(rows) * r * sizeof(int32_t), st), "cudaMemsetAsync(t_f)"));
             bnf4_gemm_desc g = {};
             g.a = m.a_h; g.b = m.q_ff1[l]; g.sfa = m.sf_h; g.sfb = m.sfq_ff1[l]; g.m = rows; g.n = F; g.k = H; g.alpha = m.s_h;
@@ -239,11 +289,12 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
             ++launches;
         }
         // ff2 -> y
-        TRY(gemm(m.a_f, m.sf_f, m.q_ff2[l], m.sfq_ff2[l], H, F, m.s_f, m.y, H, m.A_ff2[l] + P0 * H * r, static_cast<long long>(H) * r, m.t_f,
+        TRY(gemm(KC_GEMM_FF2, m.a_f, m.sf_f, m.q_ff2[l], m.sfq_ff2[l], H, F, m.s_f, m.y, H, m.A_ff2[l] + P0 * H * r, static_cast<long long>(H) * r, m.t_f,
                  r, m.s_f, 0));
         ++launches;
         {   // residual add + abs-mean norm -> a_h; t for the next layer's qkv or the head
             const bool last = (l == L - 1);
+            TimedScope ts(m, KC_ADD_NORM, st);
             bnf4_rowquant_desc p = {};
             p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
             p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.add_scale = m.cfg.mlp_residual_scale; p.norm_scale = m.cfg.ln_scale;
@@ -258,8 +309,9 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
         }
     }
     // head -> logits (in the qkv buffer, leading dimension V), cross-entropy per member
-    TRY(gemm(m.a_h, m.sf_h, m.q_head, m.sfq_head, V, H, m.s_h, m.qkv, V, m.A_head + P0 * V * r, static_cast<long long>(V) * r, m.t_a, r, m.s_h, 0));
+    TRY(gemm(KC_GEMM_HEAD, m.a_h, m.sf_h, m.q_head, m.sfq_head, V, H, m.s_h, m.qkv, V, m.A_head + P0 * V * r, static_cast<long long>(V) * r, m.t_a, r, m.s_h, 0));
     ++launches;
+    TimedScope ts_ce(m, KC_CROSS_ENTROPY, st, 2);
     TRY(bnf4_cross_entropy_population(m.qkv, V, m.head_bias, pert ? m.hb_noise + P0 * V : nullptr, sigma, m.targets, V, nm, R, m.ce_partial,
                                       losses_out, st));
     launches += 2;
@@ -435,6 +487,7 @@ int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pai
     m.pairs_step = pairs;
     TRY(bnf4_fill_pair_seeds(seed, epoch, pairs, m.pair_seeds, stream));
     const dim3 grid((m.gen_max_n + 255) / 256, m.num_gen, pairs);
+    TimedScope ts(m, KC_GEN_NOISE, S(stream), 2);
     gen_noise_kernel<<<grid, 256, 0, S(stream)>>>(m.gen_descs, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
     return check_launch("gen_noise_kernel");
 }
@@ -471,7 +524,11 @@ int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update
     auto matrix = [&](int8_t* w, float* shadow, const int8_t* A, long long A_stride, const int8_t* Bt, long long B_stride, int rows, int cols) {
         float* ema = m.rms_ema + (slot++);
         TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
-        TRY(bnf4_compute_z_sumsq_lowrank(pair_weights, A, A_stride, Bt, B_stride, P, rows, cols, r, m.c_r, m.Z, m.sumsq, st));
+        {
+            TimedScope ts(m, KC_UPDATE_Z, st, 3);
+            TRY(bnf4_compute_z_sumsq_lowrank(pair_weights, A, A_stride, Bt, B_stride, P, rows, cols, r, m.c_r, m.Z, m.sumsq, st));
+        }
+        TimedScope ts2(m, KC_UPDATE_APPLY, st, 2);
         TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, rows * cols, m.inv_rms, st));
         return bnf4_update_shadow_ternary_device(w, shadow, m.Z, rows * cols, m.inv_rms, u->lr, thresh, st);
     };
@@ -493,6 +550,7 @@ int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update
     auto vec = [&](float* v, int n, uint64_t salt) {
         float* ema = m.rms_ema + (slot++);
         TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
+        TimedScope ts(m, KC_UPDATE_Z, st, 5);
         TRY(bnf4_compute_z_sumsq(pair_weights, m.pair_seeds, salt, P, n, m.cfg.use_clt, m.cfg.clt_k, m.Z, m.sumsq, st));
         TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
         return bnf4_update_vector_device(v, m.Z, n, m.inv_rms, u->lr, thresh, st);
@@ -500,7 +558,36 @@ int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update
     TRY(vec(m.head_bias, V, kSaltHeadBias));
     TRY(vec(m.beta_bias, L, kSaltBetaBias));
     if (u->train_pos) TRY(vec(m.pos, m.T * H, kSaltPos));
+    TimedScope ts(m, KC_REQUANTIZE, st, 2 + 3 * L);
     return quantize_base(m, st);
+}
+
+int bnf4_model_set_timing(void* handle, int enable) {
+    if (!handle) return set_error(BNF4_ERR_INVALID, "model_set_timing: null handle");
+    Model& m = *M(handle);
+    m.timing = enable != 0;
+    for (int c = 0; c < kNumClasses; ++c) { m.class_ms[c] = 0.0; m.class_launches[c] = 0; }
+    for (auto& sp : m.spans) { m.free_events.push_back(sp.a); m.free_events.push_back(sp.b); }
+    m.spans.clear();
+    return BNF4_OK;
+}
+
+int bnf4_model_num_kernel_classes(void) { return kNumClasses; }
+const char* bnf4_model_kernel_class_name(int cls) { return (cls >= 0 && cls < kNumClasses) ? kClassNames[cls] : ""; }
+
+int bnf4_model_get_timing(void* handle, double* ms, long long* launches, int n) {
+    if (!handle || !ms || !launches) return set_error(BNF4_ERR_INVALID, "model_get_timing: null argument");
+    Model& m = *M(handle);
+    TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    for (auto& sp : m.spans) {
+        float t = 0.0f;
+        if (cudaEventElapsedTime(&t, sp.a, sp.b) == cudaSuccess) m.class_ms[sp.cls] += t;
+        m.free_events.push_back(sp.a);
+        m.free_events.push_back(sp.b);
+    }
+    m.spans.clear();
+    for (int c = 0; c < n && c < kNumClasses; ++c) { ms[c] = m.class_ms[c]; launches[c] = m.class_launches[c]; }
+    return BNF4_OK;
 }
 
 int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes) {

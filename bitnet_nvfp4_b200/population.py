@@ -51,6 +51,10 @@ _l.register({
     "bnf4_model_update": (c_int, [c_void_p, c_void_p, C.POINTER(UpdateCfg), c_void_p]),
     "bnf4_model_read_buffer": (c_int, [c_void_p, C.c_char_p, c_void_p, C.c_size_t]),
     "bnf4_model_launches_per_wave": (c_int, [c_void_p]),
+    "bnf4_model_set_timing": (c_int, [c_void_p, c_int]),
+    "bnf4_model_num_kernel_classes": (c_int, []),
+    "bnf4_model_kernel_class_name": (C.c_char_p, [c_int]),
+    "bnf4_model_get_timing": (c_int, [c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_longlong), c_int]),
 })
 
 WEIGHT_NAMES = "emb win wq wk wv wbeta ff1 ff2 head head_bias beta_bias pos".split()
@@ -150,7 +154,8 @@ class PopulationModel:
         (pt, dt), (pg, dg) = ptr(tokens), ptr(targets)
         assert dt == dg
         _l.check(self.lib.bnf4_model_set_tokens(self.h, pt, pg, int(dt), _stream()))
-        if not dt:
+        if getattr(self, "_keep", None):
+            # numpy inputs were copied to temporaries: wait for the H2D copies before releasing them
             torch.cuda.current_stream().synchronize()
             self._keep = []
 
@@ -175,6 +180,17 @@ class PopulationModel:
         assert pair_weights.is_cuda and pair_weights.dtype == torch.float32 and pair_weights.numel() == self.pairs
         u = UpdateCfg(lr, thresh, int(use_adaptive), adaptive_beta, adaptive_eps, int(train_pos))
         _l.check(self.lib.bnf4_model_update(self.h, pair_weights.data_ptr(), C.byref(u), _stream()))
+
+    def set_timing(self, enable: bool):
+        _l.check(self.lib.bnf4_model_set_timing(self.h, int(enable)))
+
+    def get_timing(self) -> dict:
+        """{kernel class: (milliseconds, launches)} accumulated since set_timing(True). Synchronises."""
+        n = self.lib.bnf4_model_num_kernel_classes()
+        ms = (C.c_double * n)()
+        cnt = (C.c_longlong * n)()
+        _l.check(self.lib.bnf4_model_get_timing(self.h, ms, cnt, n))
+        return {self.lib.bnf4_model_kernel_class_name(i).decode(): (ms[i], cnt[i]) for i in range(n)}
 
     def read_buffer(self, name: str, dtype, count: int) -> np.ndarray:
         out = np.zeros(count, dtype)

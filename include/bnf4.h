@@ -404,8 +404,15 @@ int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update
 /* Debug/verification access to an internal wave buffer by name ("x_q", "a_h", "sf_h", "a_f", "sf_f", "qkv", "y",
  * "t_a", "t_f", "losses"): copies min(bytes, size) bytes to host. Synchronises. */
 int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes);
-/* Kernels launched by one bnf4_model_eval_pairs wave and by one bnf4_model_update (for accounting). */
+/* Kernels launched by the last bnf4_model_eval_pairs wave (for accounting). */
 int bnf4_model_launches_per_wave(void* handle);
+/* Optional timing breakdown: when enabled, the driver brackets every kernel class with CUDA events on the launching
+ * stream. bnf4_model_get_timing synchronises and returns accumulated milliseconds and launches per class since the
+ * last bnf4_model_set_timing call. */
+int bnf4_model_set_timing(void* handle, int enable);
+int bnf4_model_num_kernel_classes(void);
+const char* bnf4_model_kernel_class_name(int cls);
+int bnf4_model_get_timing(void* handle, double* ms, long long* launches, int n);
 
 #ifdef __cplusplus
 }
