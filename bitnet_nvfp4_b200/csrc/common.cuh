@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 
+#include <cmath>
 #include <cstddef>
 #include <cstdint>
 
@@ -81,6 +82,19 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     const float c = 0.7978845608028654f;
     const float x3 = x * x * x;
     return 0.5f * x * (1.0f + tanhf(c * fmaf(0.044715f, x3, x)));
+}
+
+// gelu_tanh(x) * act_scale for values that are about to be rounded to an integer: a fast evaluation
+// (x * sigmoid(2u) with the hardware exponential, absolute error far below 1e-3) decides every case except
+// those within 1e-3 of a rounding boundary, which are re-evaluated with the tanhf form. The integer obtained
+// after rounding is therefore the one the tanhf form gives.
+__device__ __forceinline__ float gelu_scaled(float x, float act_scale) {
+    const float c = 0.7978845608028654f;
+    const float u = c * fmaf(0.044715f, x * x * x, x);
+    float f = __fdividef(x, 1.0f + __expf(-2.0f * u)) * act_scale;
+    const float d = fabsf(f - rintf(f));
+    if (fabsf(d - 0.5f) < 1e-3f * fmaxf(1.0f, fabsf(f)) || !(fabsf(f) < 1e6f)) f = gelu_tanh(x) * act_scale;
+    return f;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -178,6 +192,56 @@ __device__ __forceinline__ void quant_block16(const int (&w)[4], float row_scale
     }
     code_lo = lo;
     code_hi = hi;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Table-driven block quantiser. For int8 inputs both outputs depend only on (amax, |v|):
+//   scale byte = sf_lut[amax],  code(v) = code_lut[amax][|v|] | sign(v) << 3
+// with exactly the arithmetic of quant_block16 (amax/6 -> ue4m3, v/scale -> e2m1, IEEE division).
+// The table (16 KiB + 128 B, built on the host by get_quant_lut()) lives in global memory and is read
+// through the L1: the 16 values of a block share one amax, i.e. one 128-byte row.
+// ---------------------------------------------------------------------------------------------
+constexpr int kQuantLutCodeBytes = 128 * 128;
+constexpr int kQuantLutBytes = kQuantLutCodeBytes + 128;
+// Device pointer to the table of the current device (allocated and filled on first use); nullptr + error on failure.
+const uint8_t* get_quant_lut();
+
+__device__ __forceinline__ void quant_block16_lut(const int (&w)[4], const uint8_t* __restrict__ lut, uint32_t& sf_byte,
+                                                  uint32_t& code_lo, uint32_t& code_hi) {
+    int a[16];
+    int amax = 0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const int v = static_cast<int>(static_cast<int8_t>((w[e >> 2] >> (8 * (e & 3))) & 0xff));
+        a[e] = v;
+        amax = max(amax, abs(v));
+    }
+    amax = min(amax, 127);
+    sf_byte = __ldg(lut + kQuantLutCodeBytes + amax);
+    const uint8_t* row = lut + amax * 128;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+        const uint32_t c = static_cast<uint32_t>(__ldg(row + min(abs(a[e]), 127))) | (a[e] < 0 ? 8u : 0u);
+        if (e < 8) lo |= c << (4 * e);
+        else hi |= c << (4 * (e - 8));
+    }
+    code_lo = lo;
+    code_hi = hi;
+}
+
+// Host twin of ue4m3_encode (used to build the table).
+inline uint32_t ue4m3_encode_host(float x) {
+    if (!(x > 0.0f)) return 0u;
+    if (x >= 448.0f) return 0x7eu;
+    if (x < 0.015625f) return static_cast<uint32_t>(nearbyintf(x * 512.0f));
+    int e;
+    const float m = frexpf(x, &e) * 2.0f;  // [1,2)
+    e -= 1;
+    int q = static_cast<int>(nearbyintf((m - 1.0f) * 8.0f));
+    if (q == 8) { q = 0; e += 1; }
+    const uint32_t code = (static_cast<uint32_t>(e + 7) << 3) | static_cast<uint32_t>(q);
+    return code > 0x7eu ? 0x7eu : code;
 }
 
 __device__ __forceinline__ int pack4_i8(int a, int b, int c, int d) {

@@ -7,12 +7,12 @@
 // gemm_ternary_f_nvfp4_gelu_i8 (reference: src/cuda_kernels.cu:3145-3310, 4342-4607) and fuses the
 // rank-r term of gemm_lora_f_kernel (reference: src/cuda_kernels.cu:1271-1305) into the tile epilogue.
 //
-// Structure of one CTA (one 128 x 128 output tile, 192 threads):
+// Structure of one CTA (one 128 x 128 output tile, 320 threads):
 //   warp 0      producer: TMA tiles of A and B (128 rows x 128 bytes = 256 K-elements, 128B swizzle) and
 //               bulk copies of the matching scale-factor atoms into a ring of shared-memory stages
 //   warp 1      owns TMEM; per stage copies the scale atoms to TMEM (tcgen05.cp 32x128b.warpx4) and issues
 //               tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x N128 x K64) accumulating fp32 in TMEM
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (one TMEM lane quadrant per warp), apply
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (two warps per TMEM lane quadrant, 64 columns each), apply
 //               alpha/beta/rank-r/GELU, and store (TMA store through swizzled staging, or direct)
 // Two CTAs fit per SM (shared memory and 256 TMEM columns each), so one tile's epilogue overlaps the
 // next tile's loads and MMAs. Every mbarrier wait is bounded: on expiry the kernel records an error
@@ -35,9 +35,9 @@ constexpr int kStages = 2;
 constexpr int kStageABytes = BM * 128;
 constexpr int kStageBBytes = BN * 128;
 constexpr int kStageSfBytes = 4 * 512;  // four 128-row x 64-K atoms
-constexpr int kEpiWarps = 4;
+constexpr int kEpiWarps = 8;
 constexpr int kEpiBufBytes = 32 * 32 * 4;  // one 32 x 32 fp32 box
-constexpr int kThreads = 192;
+constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr int kTmemCols = 256;      // 128 accumulator + kStages * 32 scale columns, rounded to a power of two
 constexpr int kAccCol = 0;
 constexpr int kSfCol = 128;
@@ -47,7 +47,8 @@ constexpr int kSmemB = kSmemA + kStages * kStageABytes;
 constexpr int kSmemSfa = kSmemB + kStages * kStageBBytes;
 constexpr int kSmemSfb = kSmemSfa + kStages * kStageSfBytes;
 constexpr int kSmemEpi = kSmemSfb + kStages * kStageSfBytes;
-constexpr int kSmemBar = kSmemEpi + kEpiWarps * 2 * kEpiBufBytes;
+constexpr int kSmemLora = kSmemEpi + kEpiWarps * kEpiBufBytes;  // [4][BN] int8
+constexpr int kSmemBar = kSmemLora + 4 * BN;
 constexpr int kSmemTotal = kSmemBar + 128;
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
 
@@ -174,6 +175,7 @@ struct KernelArgs {
     GemmParams p;
     int use_tma_store;
     int k_atoms;  // scale atoms along K
+    const uint8_t* lut;  // table of the block quantiser (EPI_GELU_FP4)
     int n_tiles;  // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile (N fastest: CTAs that share A rows run together)
 };
 
@@ -266,16 +268,16 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
             if (ok) tc_commit(bar_accum);     // accumulator complete
         }
     } else {
-        // ------------------------------ epilogue ------------------------------
+        // ------------------------------ epilogue (8 warps: two per TMEM lane quadrant) ------------------------------
+        const int ew = warp - 2;                // 0..7
         const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+        const int half = ew >> 2;               // which 64-column half of the tile this warp handles
         const int row_in_tile = q * 32 + lane;
         const long long row = static_cast<long long>(m0) + row_in_tile;
         const bool row_ok = row < p.m;
-        bool ok = mbar_wait(bar_accum, 0, 3);
-        ok = __all_sync(0xffffffffu, ok);
-        tc_fence_after();
 
-        // per-row perturbation context
+        // Per-row perturbation context; stage the A factor of this tile's columns in shared memory when every
+        // row of the tile belongs to the same pair (always the case when rows_per_member is a multiple of 128).
         int pair = 0;
         float lsign = 0.0f;
         if (p.rank > 0 && row_ok) {
@@ -283,14 +285,36 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
             pair = member >> 1;
             lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
         }
+        bool a_staged = false;
+        int8_t* loraA_sh = reinterpret_cast<int8_t*>(smem_gen + kSmemLora);  // [4][BN]
+        if (p.rank > 0) {
+            const long long last_row = min(static_cast<long long>(p.m), static_cast<long long>(m0) + BM) - 1;
+            const int pair_first = p.rows_per_member > 0 ? static_cast<int>(m0 / p.rows_per_member) >> 1 : 0;
+            const int pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / p.rows_per_member) >> 1 : 0;
+            a_staged = (pair_first == pair_last);
+            if (a_staged) {
+                const int8_t* Ag = p.lora_A + static_cast<size_t>(pair_first) * p.lora_A_pair_stride;
+                for (int idx = ew * 32 + lane; idx < p.rank * BN; idx += kEpiWarps * 32) {
+                    const int r = idx / BN, cidx = idx - r * BN;
+                    const int n = n0 + cidx;
+                    loraA_sh[r * BN + cidx] = (n < p.n) ? Ag[static_cast<size_t>(n) * p.rank + r] : static_cast<int8_t>(0);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+        }
+
+        bool ok = mbar_wait(bar_accum, 0, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
         int next_acc[4] = {0, 0, 0, 0};
 
-        const uint32_t epi_buf0 = smem_base + kSmemEpi + (warp - 2) * 2 * kEpiBufBytes;
-        uint8_t* epi_gen0 = smem_gen + kSmemEpi + (warp - 2) * 2 * kEpiBufBytes;
+        const uint32_t epi_buf = smem_base + kSmemEpi + ew * kEpiBufBytes;
+        uint8_t* epi_gen = smem_gen + kSmemEpi + ew * kEpiBufBytes;
 
         if (ok) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int cc = 0; cc < 2; ++cc) {
+                const int c = half * 2 + cc;
                 const int col0 = n0 + c * 32;
                 if (col0 >= p.n) break;  // warp-uniform
                 uint32_t acc[32];
@@ -308,34 +332,43 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
                 }
                 if (p.rank > 0 && row_ok) {
                     const int g = p.group_cols > 0 ? (col0 / p.group_cols) : 0;
-                    int tr[4] = {0, 0, 0, 0};
-                    for (int r = 0; r < p.rank; ++r) tr[r] = p.lora_t[static_cast<size_t>(row) * p.t_stride + g * p.rank + r];
-                    const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank;
+                    int pert[32];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (col0 + j < p.n) {
-                            int pert = 0;
-                            for (int r = 0; r < p.rank; ++r) pert += tr[r] * static_cast<int>(Ap[j * p.rank + r]);
-                            v[j] = fmaf(lsign, static_cast<float>(pert), v[j]);
+                    for (int j = 0; j < 32; ++j) pert[j] = 0;
+                    for (int r = 0; r < p.rank; ++r) {
+                        const int tr = p.lora_t[static_cast<size_t>(row) * p.t_stride + g * p.rank + r];
+                        if (a_staged) {
+                            const int4* ap = reinterpret_cast<const int4*>(loraA_sh + r * BN + c * 32);
+                            const int4 a0 = ap[0], a1 = ap[1];
+                            const int aw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                pert[j] += tr * static_cast<int>(static_cast<int8_t>((aw[j >> 2] >> (8 * (j & 3))) & 0xff));
+                        } else {
+                            const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank + r;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.n) pert[j] += tr * static_cast<int>(Ap[static_cast<size_t>(j) * p.rank]);
                         }
                     }
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = fmaf(lsign, static_cast<float>(pert[j]), v[j]);
                 }
 
                 if constexpr (EPI == EPI_F32) {
                     if (args.use_tma_store) {
                         // stage the 32x32 box in 128B-swizzled shared memory, then one TMA store (clips at M and N)
-                        const int buf = c & 1;
-                        if (c >= 2) {
-                            if (lane == 0) bulk_wait_read<1>();
+                        if (cc > 0) {
+                            if (lane == 0) bulk_wait_read<0>();
                             __syncwarp();
                         }
-                        float4* dst = reinterpret_cast<float4*>(epi_gen0 + buf * kEpiBufBytes + lane * 128);
+                        float4* dst = reinterpret_cast<float4*>(epi_gen + lane * 128);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_store_2d(&map_d, epi_buf0 + buf * kEpiBufBytes, col0, m0 + q * 32);
+                            tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
                             bulk_commit();
                         }
                     } else if (row_ok) {
@@ -352,12 +385,15 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
                     }
                 } else {
                     // GELU -> int8 (reference: src/cuda_kernels.cu:3178-3194; tanh-form GELU, clip to +-127)
-                    int qv[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) qv[j] = (col0 + j < p.n) ? clip_int8(rint_to_int(gelu_tanh(v[j]) * p.act_scale)) : 0;
                     int w[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) w[j] = pack4_i8(qv[4 * j], qv[4 * j + 1], qv[4 * j + 2], qv[4 * j + 3]);
+                    for (int j = 0; j < 8; ++j) {
+                        int qv[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            qv[u] = (col0 + 4 * j + u < p.n) ? clip_int8(rint_to_int(gelu_scaled(v[4 * j + u], p.act_scale))) : 0;
+                        w[j] = pack4_i8(qv[0], qv[1], qv[2], qv[3]);
+                    }
                     if (row_ok && p.d_i8 != nullptr) {
                         int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
                         if (((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && col0 + 32 <= p.n) {
@@ -366,7 +402,7 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.n) drow[j] = static_cast<int8_t>(qv[j]);
+                                if (col0 + j < p.n) drow[j] = static_cast<int8_t>((w[j >> 2] >> (8 * (j & 3))) & 0xff);
                         }
                     }
                     if constexpr (EPI == EPI_GELU_FP4) {
@@ -374,8 +410,8 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
                             const int wa[4] = {w[0], w[1], w[2], w[3]};
                             const int wb[4] = {w[4], w[5], w[6], w[7]};
                             uint32_t s0, s1, lo0, hi0, lo1, hi1;
-                            quant_block16(wa, 1.0f, false, s0, lo0, hi0);
-                            quant_block16(wb, 1.0f, false, s1, lo1, hi1);
+                            quant_block16_lut(wa, args.lut, s0, lo0, hi0);
+                            quant_block16_lut(wb, args.lut, s1, lo1, hi1);
                             *reinterpret_cast<uint4*>(p.d_codes + (static_cast<size_t>(row) * p.n + col0) / 2) = make_uint4(lo0, hi0, lo1, hi1);
                             const int kb = col0 >> 4;
                             *reinterpret_cast<uint16_t*>(p.d_sf + sf_offset(static_cast<int>(row), kb, sf_k_atoms(p.n))) =
@@ -384,7 +420,7 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
                                 const int8_t* tv = p.next_tvec + static_cast<size_t>(pair) * p.next_tvec_pair_stride + col0;
                                 for (int vv = 0; vv < p.next_nvec; ++vv) {
                                     const int4* bv = reinterpret_cast<const int4*>(tv + static_cast<size_t>(vv) * p.n);
-                                    const int4 b0 = bv[0], b1 = bv[1];
+                                    const int4 b0 = __ldg(bv), b1 = __ldg(bv + 1);
                                     int a = next_acc[vv];
                                     a = __dp4a(w[0], b0.x, a); a = __dp4a(w[1], b0.y, a); a = __dp4a(w[2], b0.z, a); a = __dp4a(w[3], b0.w, a);
                                     a = __dp4a(w[4], b1.x, a); a = __dp4a(w[5], b1.y, a); a = __dp4a(w[6], b1.z, a); a = __dp4a(w[7], b1.w, a);
@@ -500,6 +536,11 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     KernelArgs args;
     args.p = p;
     args.k_atoms = sf_k_atoms(p.k);
+    args.lut = nullptr;
+    if (p.epilogue == EPI_GELU_FP4) {
+        args.lut = get_quant_lut();
+        if (args.lut == nullptr) return BNF4_ERR_CUDA;
+    }
     args.use_tma_store = 0;
     if (p.epilogue == EPI_F32 && (reinterpret_cast<uintptr_t>(p.d) & 15) == 0 && (p.ldd % 4) == 0 && p.ldd >= p.n) {
         rc = make_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.d, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.m),

@@ -28,7 +28,7 @@ namespace {
 constexpr int kMaxBlocksPerLane = 8;  // rows of up to 32*8*16 = 4096 columns
 
 template <int FE, int NB>
-__global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p) {
+__global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
     const int warps_per_cta = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p) {
                     float x = f[e];
                     if (p.act_mode == 1) x = x < 0.0f ? 0.0f : x;
                     else if (p.act_mode == 2) x = tanhf(__fdiv_rn(x, 127.0f)) * 127.0f;
-                    else if (p.act_mode == 3) x = gelu_tanh(x) * p.act_scale;
+                    else if (p.act_mode == 3) x = gelu_scaled(x, p.act_scale);
                     vals[e] = (k0 + e < p.cols_in) ? clip_int8(rint_to_int(x)) : 0;
                 }
             } else {
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p) {
                 for (int e = 0; e < 16; ++e) {
                     float pv = pos[k0 + e];
                     if (pn != nullptr) pv = fmaf(ns, static_cast<float>(pn[k0 + e]), pv);
-                    const float x = gelu_tanh(f[e] + pv) * p.act_scale;
+                    const float x = gelu_scaled(f[e] + pv, p.act_scale);
                     vals[e] = clip_int8(rint_to_int(x));
                 }
             }
@@ -214,7 +214,8 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p) {
         }
         uint32_t sfb = 0, lo = 0, hi = 0;
         if (active) {
-            quant_block16(w, row_scale, FE == FE_WQKV, sfb, lo, hi);
+            if constexpr (FE == FE_WQKV) quant_block16(w, row_scale, true, sfb, lo, hi);
+            else quant_block16_lut(w, lut, sfb, lo, hi);
             *reinterpret_cast<uint2*>(p.out_codes + (static_cast<size_t>(row) * p.cols_out + k0) / 2) = make_uint2(lo, hi);
         }
         // four neighbouring lanes hold the four scale bytes of one 32-bit word of the atom layout
@@ -264,10 +265,12 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
     const int warps = 8;
     const unsigned ctas = static_cast<unsigned>((static_cast<long long>(p.rows) + warps - 1) / warps);
     const int nblk = p.cols_out >> 4;
-    if (nblk <= 32) rowquant_kernel<FE, 1><<<ctas, warps * 32, 0, stream>>>(p);
-    else if (nblk <= 64) rowquant_kernel<FE, 2><<<ctas, warps * 32, 0, stream>>>(p);
-    else if (nblk <= 128) rowquant_kernel<FE, 4><<<ctas, warps * 32, 0, stream>>>(p);
-    else rowquant_kernel<FE, 8><<<ctas, warps * 32, 0, stream>>>(p);
+    const uint8_t* lut = get_quant_lut();
+    if (lut == nullptr) return BNF4_ERR_CUDA;
+    if (nblk <= 32) rowquant_kernel<FE, 1><<<ctas, warps * 32, 0, stream>>>(p, lut);
+    else if (nblk <= 64) rowquant_kernel<FE, 2><<<ctas, warps * 32, 0, stream>>>(p, lut);
+    else if (nblk <= 128) rowquant_kernel<FE, 4><<<ctas, warps * 32, 0, stream>>>(p, lut);
+    else rowquant_kernel<FE, 8><<<ctas, warps * 32, 0, stream>>>(p, lut);
     return check_launch("rowquant_kernel");
 }
 
