@@ -203,22 +203,16 @@ def main():
     tok_h = torch.from_numpy(tok).pin_memory()
     tgt_h = torch.from_numpy(tgt).pin_memory()
     model.set_tokens(tok_d, tgt_d)
-    losses_mine = torch.empty(2 * my_pairs, dtype=torch.float32, device="cuda")
-    losses_all = torch.empty(2 * pairs_total, dtype=torch.float32, device="cuda") if world > 1 else losses_mine
+    losses_all = torch.empty(2 * pairs_total, dtype=torch.float32, device="cuda")
     losses_host = torch.empty(2 * pairs_total, dtype=torch.float32).pin_memory()
 
     def step(epoch: int, from_host: bool):
         if from_host:
             model.set_tokens(tok_h, tgt_h)            # H2D of the step's inputs (pinned host memory)
-        model.prepare_step(1, epoch, pairs_total)
-        model.eval_pairs(my_begin, my_pairs, losses_mine)
-        if world > 1:
-            dist.all_gather_into_tensor(losses_all, losses_mine)
-        fit = population.fitness_from_losses(losses_all)
-        w = population.shape_fitness(fit)             # 4 KB to the host and back (rank shaping, as in the reference)
-        model.update(w, lr=0.8, thresh=0.008)
+        # evaluate this rank's pairs, all-gather the losses (NCCL), shape (4 KB host round trip, as the reference), update
+        losses = population.es_step(model, 1, epoch, pairs_total, rank, world, lr=0.8, thresh=0.008, losses_out=losses_all)
         if from_host:
-            losses_host.copy_(losses_all, non_blocking=True)  # D2H of the step's result
+            losses_host.copy_(losses, non_blocking=True)  # D2H of the step's result
 
     def barrier():
         if world > 1:

@@ -57,6 +57,11 @@ int bnf4_set_option(const char* name, int value) {
         g_gemm_allow_tma_store = value;
         return BNF4_OK;
     }
+    if (name && std::strcmp(name, "efla_cols_per_lane") == 0) {
+        if (value != 1 && value != 2) return set_error(BNF4_ERR_INVALID, "efla_cols_per_lane must be 1 or 2");
+        g_efla_cols_per_lane = value;
+        return BNF4_OK;
+    }
     return set_error(BNF4_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
 }
 

@@ -97,6 +97,25 @@ __device__ __forceinline__ float gelu_scaled(float x, float act_scale) {
     return f;
 }
 
+// clip8(rint(gelu_tanh(x) * act_scale)) with one MUFU: tanh.approx (relative error <= 2^-11) decides every case
+// whose distance to a rounding boundary exceeds its error bound; the rest (a fraction of a percent) is re-evaluated
+// with the tanhf form, so the integer is the one the tanhf form gives. Rounding uses the 1.5*2^23 trick.
+__device__ __forceinline__ int gelu_q8(float x, float act_scale) {
+    const float c = 0.7978845608028654f;
+    const float u = c * fmaf(0.044715f, x * x * x, x);
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
+    const float hx = 0.5f * x;
+    const float f = fmaf(hx, th, hx) * act_scale;
+    const float margin = fmaf(fabsf(hx * act_scale), 5.2e-4f, 1e-5f);
+    const float t = f + 12582912.0f;
+    const float r = t - 12582912.0f;
+    int q;
+    if (fabsf(fabsf(f - r) - 0.5f) > margin && fabsf(f) < 1000.0f) q = __float_as_int(t) - 0x4B400000;
+    else q = __float2int_rn(gelu_tanh(x) * act_scale);
+    return clip_int8(q);
+}
+
 // ---------------------------------------------------------------------------------------------
 // NVFP4 number formats.
 //   e2m1: magnitudes {0,.5,1,1.5,2,3,4,6}, bit 3 = sign, round-to-nearest-even, saturating.
@@ -206,23 +225,21 @@ constexpr int kQuantLutBytes = kQuantLutCodeBytes + 128;
 // Device pointer to the table of the current device (allocated and filled on first use); nullptr + error on failure.
 const uint8_t* get_quant_lut();
 
-__device__ __forceinline__ void quant_block16_lut(const int (&w)[4], const uint8_t* __restrict__ lut, uint32_t& sf_byte,
+__device__ __forceinline__ void quant_block16_lut(const int (&a)[16], const uint8_t* __restrict__ lut, uint32_t& sf_byte,
                                                   uint32_t& code_lo, uint32_t& code_hi) {
-    int a[16];
+    int mag[16];
     int amax = 0;
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
-        const int v = static_cast<int>(static_cast<int8_t>((w[e >> 2] >> (8 * (e & 3))) & 0xff));
-        a[e] = v;
-        amax = max(amax, abs(v));
+        mag[e] = min(abs(a[e]), 127);  // -128 is treated as -127 (the reference never produces it: values are clipped to +-127)
+        amax = max(amax, mag[e]);
     }
-    amax = min(amax, 127);
     sf_byte = __ldg(lut + kQuantLutCodeBytes + amax);
     const uint8_t* row = lut + amax * 128;
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int e = 0; e < 16; ++e) {
-        const uint32_t c = static_cast<uint32_t>(__ldg(row + min(abs(a[e]), 127))) | (a[e] < 0 ? 8u : 0u);
+        const uint32_t c = static_cast<uint32_t>(__ldg(row + mag[e])) | ((static_cast<uint32_t>(a[e]) >> 28) & 8u);
         if (e < 8) lo |= c << (4 * e);
         else hi |= c << (4 * (e - 8));
     }

@@ -115,19 +115,28 @@ __global__ void efla_generic_kernel(const EflaParams p) {
 // ------------------------------------------------------------------------------------------------
 constexpr int kScanWarps = 4;
 
-__global__ void __launch_bounds__(kScanWarps * 32, 2) efla_scan64_kernel(const EflaParams p) {
-    constexpr int HD = 64;
+// NCOL = 2: one warp per (sequence, head), lane owns columns lane and lane+32 (128 state registers).
+// NCOL = 1: two warps per (sequence, head), lane owns one column (64 state registers, twice the warps per SM).
+// The state is held as float2 pairs over adjacent rows (d, d+1) so that the three multiply-adds per state element
+// (k.S, the rank-1 update, S.q^) issue as packed fma.rn.f32x2 instructions.
+template <int NCOL>
+__global__ void __launch_bounds__(kScanWarps * 32, NCOL == 1 ? 4 : 2) efla_scan64_kernel(const EflaParams p) {
+    constexpr int HD = 64, HP = HD / 2;
     __shared__ __align__(16) float sh[kScanWarps][3][HD];  // k, q^, alpha*k per warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long unit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;  // (sequence, head)
+    const long long wunit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;
+    const long long unit = NCOL == 1 ? (wunit >> 1) : wunit;  // (sequence, head)
+    const int colbase = NCOL == 1 ? static_cast<int>(wunit & 1) * 32 : 0;
     if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
     const long long seq = unit / p.heads;
     const int h = static_cast<int>(unit - seq * p.heads);
     const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
 
-    float S0[HD], S1[HD];
+    float2 S[NCOL][HP];  // S[c][j] = (S[2j][col c], S[2j+1][col c])
 #pragma unroll
-    for (int d = 0; d < HD; ++d) { S0[d] = 0.0f; S1[d] = 0.0f; }
+    for (int c = 0; c < NCOL; ++c)
+#pragma unroll
+        for (int j = 0; j < HP; ++j) S[c][j] = make_float2(0.0f, 0.0f);
 
     const size_t row0 = static_cast<size_t>(seq) * p.T;
     const float* qb = p.q + row0 * p.ld_qkv + h * HD;
@@ -136,20 +145,27 @@ __global__ void __launch_bounds__(kScanWarps * 32, 2) efla_scan64_kernel(const E
     const float* bb = p.beta_raw + row0 * p.ld_beta;
     float* ob = p.out + row0 * p.ld_out + h * HD;
 
-    // prefetch token 0
-    float q0 = qb[lane], q1 = qb[lane + 32], k0 = kb[lane], k1 = kb[lane + 32], v0 = vb[lane], v1 = vb[lane + 32], br = bb[0];
+    // prefetch token 0 (q and k: all 64 elements across the warp; v: this lane's columns)
+    float q0 = qb[lane], q1 = qb[lane + 32], k0 = kb[lane], k1 = kb[lane + 32], br = bb[0];
+    float vv[NCOL];
+#pragma unroll
+    for (int c = 0; c < NCOL; ++c) vv[c] = vb[colbase + lane + 32 * c];
 
     float* k_s = sh[warp][0];
     float* q_s = sh[warp][1];
     float* a_s = sh[warp][2];
 
     for (int t = 0; t < p.T; ++t) {
-        const float cq0 = q0, cq1 = q1, ck0 = k0, ck1 = k1, cv0 = v0, cv1 = v1, cbr = br;
+        const float cq0 = q0, cq1 = q1, ck0 = k0, ck1 = k1, cbr = br;
+        float cv[NCOL];
+#pragma unroll
+        for (int c = 0; c < NCOL; ++c) cv[c] = vv[c];
         if (t + 1 < p.T) {
             const size_t o = static_cast<size_t>(t + 1) * p.ld_qkv;
             q0 = qb[o + lane]; q1 = qb[o + lane + 32];
             k0 = kb[o + lane]; k1 = kb[o + lane + 32];
-            v0 = vb[o + lane]; v1 = vb[o + lane + 32];
+#pragma unroll
+            for (int c = 0; c < NCOL; ++c) vv[c] = vb[o + colbase + lane + 32 * c];
             br = bb[static_cast<size_t>(t + 1) * p.ld_beta];
         }
         const float qss = warp_sum_f(fmaf(cq0, cq0, cq1 * cq1));
@@ -167,43 +183,55 @@ __global__ void __launch_bounds__(kScanWarps * 32, 2) efla_scan64_kernel(const E
         a_s[lane] = alpha * (ck0 * kscale); a_s[lane + 32] = alpha * (ck1 * kscale);
         __syncwarp();
 
-        // kS for this lane's two columns, four partial sums per column
-        float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+        // kS for this lane's columns: two packed partial sums per column (even / odd rows twice over)
+        float2 acc[NCOL][2];
 #pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            const float4 kk = *reinterpret_cast<const float4*>(k_s + d);
-            a0[0] = fmaf(kk.x, S0[d], a0[0]); a1[0] = fmaf(kk.x, S1[d], a1[0]);
-            a0[1] = fmaf(kk.y, S0[d + 1], a0[1]); a1[1] = fmaf(kk.y, S1[d + 1], a1[1]);
-            a0[2] = fmaf(kk.z, S0[d + 2], a0[2]); a1[2] = fmaf(kk.z, S1[d + 2], a1[2]);
-            a0[3] = fmaf(kk.w, S0[d + 3], a0[3]); a1[3] = fmaf(kk.w, S1[d + 3], a1[3]);
-        }
-        const float diff0 = cv0 - ((a0[0] + a0[1]) + (a0[2] + a0[3]));
-        const float diff1 = cv1 - ((a1[0] + a1[1]) + (a1[2] + a1[3]));
-
-        // state update (rounded to fp16 every step) fused with the readout of the updated state
-        float y0[4] = {0.f, 0.f, 0.f, 0.f}, y1[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < NCOL; ++c) acc[c][0] = acc[c][1] = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int d = 0; d < HD; d += 4) {
-            const float4 ak = *reinterpret_cast<const float4*>(a_s + d);
-            const float4 qq = *reinterpret_cast<const float4*>(q_s + d);
-            const float akv[4] = {ak.x, ak.y, ak.z, ak.w};
-            const float qv[4] = {qq.x, qq.y, qq.z, qq.w};
+        for (int j = 0; j < HP; j += 2) {
+            const float4 kk = *reinterpret_cast<const float4*>(k_s + 2 * j);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const __half2 hh = __floats2half2_rn(fmaf(akv[u], diff0, S0[d + u]), fmaf(akv[u], diff1, S1[d + u]));
-                const float2 ff = __half22float2(hh);
-                S0[d + u] = ff.x;
-                S1[d + u] = ff.y;
-                y0[u] = fmaf(ff.x, qv[u], y0[u]);
-                y1[u] = fmaf(ff.y, qv[u], y1[u]);
+            for (int c = 0; c < NCOL; ++c) {
+                acc[c][0] = __ffma2_rn(make_float2(kk.x, kk.y), S[c][j], acc[c][0]);
+                acc[c][1] = __ffma2_rn(make_float2(kk.z, kk.w), S[c][j + 1], acc[c][1]);
             }
         }
-        ob[static_cast<size_t>(t) * p.ld_out + lane] = (y0[0] + y0[1]) + (y0[2] + y0[3]);
-        ob[static_cast<size_t>(t) * p.ld_out + lane + 32] = (y1[0] + y1[1]) + (y1[2] + y1[3]);
+        float2 diff2[NCOL];
+#pragma unroll
+        for (int c = 0; c < NCOL; ++c) {
+            const float d = cv[c] - ((acc[c][0].x + acc[c][0].y) + (acc[c][1].x + acc[c][1].y));
+            diff2[c] = make_float2(d, d);
+        }
+
+        // state update (rounded to fp16 every step) fused with the readout of the updated state
+        float2 y[NCOL][2];
+#pragma unroll
+        for (int c = 0; c < NCOL; ++c) y[c][0] = y[c][1] = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int j = 0; j < HP; j += 2) {
+            const float4 ak = *reinterpret_cast<const float4*>(a_s + 2 * j);
+            const float4 qq = *reinterpret_cast<const float4*>(q_s + 2 * j);
+#pragma unroll
+            for (int c = 0; c < NCOL; ++c) {
+                const float2 s0 = __ffma2_rn(make_float2(ak.x, ak.y), diff2[c], S[c][j]);
+                const float2 s1 = __ffma2_rn(make_float2(ak.z, ak.w), diff2[c], S[c][j + 1]);
+                const float2 r0 = __half22float2(__floats2half2_rn(s0.x, s0.y));
+                const float2 r1 = __half22float2(__floats2half2_rn(s1.x, s1.y));
+                S[c][j] = r0;
+                S[c][j + 1] = r1;
+                y[c][0] = __ffma2_rn(r0, make_float2(qq.x, qq.y), y[c][0]);
+                y[c][1] = __ffma2_rn(r1, make_float2(qq.z, qq.w), y[c][1]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < NCOL; ++c)
+            ob[static_cast<size_t>(t) * p.ld_out + colbase + lane + 32 * c] = (y[c][0].x + y[c][0].y) + (y[c][1].x + y[c][1].y);
     }
 }
 
 }  // namespace
+
+int g_efla_cols_per_lane = 2;  // host toggle (option "efla_cols_per_lane")
 
 int efla_launch(const EflaParams& p, cudaStream_t stream) {
     if (p.seqs <= 0 || p.T <= 0) return BNF4_OK;
@@ -212,8 +240,13 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
     const int hd = p.hidden / p.heads;
     if (p.state == nullptr && p.state_fp16 && hd == 64 && !p.force_generic) {
         const long long units = p.seqs * static_cast<long long>(p.heads);
-        const long long ctas = (units + kScanWarps - 1) / kScanWarps;
-        efla_scan64_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
+        if (g_efla_cols_per_lane == 2) {
+            const long long ctas = (units + kScanWarps - 1) / kScanWarps;
+            efla_scan64_kernel<2><<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
+        } else {
+            const long long ctas = (2 * units + kScanWarps - 1) / kScanWarps;
+            efla_scan64_kernel<1><<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
+        }
         return check_launch("efla_scan64_kernel");
     }
     if ((hd % 32) != 0) return set_error(BNF4_ERR_INVALID, "efla: head_dim=%d must be a multiple of 32", hd);

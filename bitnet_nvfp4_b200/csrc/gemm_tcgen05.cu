@@ -7,18 +7,20 @@
 // gemm_ternary_f_nvfp4_gelu_i8 (reference: src/cuda_kernels.cu:3145-3310, 4342-4607) and fuses the
 // rank-r term of gemm_lora_f_kernel (reference: src/cuda_kernels.cu:1271-1305) into the tile epilogue.
 //
-// Structure of one CTA (one 128 x 128 output tile, 320 threads):
+// Structure of one CTA (128 x 128 output tiles, 576 threads):
 //   warp 0      producer: TMA tiles of A and B (128 rows x 128 bytes = 256 K-elements, 128B swizzle) and
 //               bulk copies of the matching scale-factor atoms into a ring of shared-memory stages
 //   warp 1      owns TMEM; per stage copies the scale atoms to TMEM (tcgen05.cp 32x128b.warpx4) and issues
 //               tcgen05.mma.kind::mxf4nvf4.block_scale (M128 x N128 x K64) accumulating fp32 in TMEM
-//   warps 2..9  epilogue: tcgen05.ld the accumulator (two warps per TMEM lane quadrant, 64 columns each), apply
+//   warps 2..17 epilogue: tcgen05.ld the accumulator (four warps per TMEM lane quadrant, 32 columns each), apply
 //               alpha/beta/rank-r/GELU, and store (TMA store through swizzled staging, or direct)
-// Two CTAs fit per SM (shared memory and 256 TMEM columns each), so one tile's epilogue overlaps the
-// next tile's loads and MMAs. Every mbarrier wait is bounded: on expiry the kernel records an error
+// The kernel is persistent (one CTA per SM, tiles assigned round-robin): the producer runs up to four k-blocks
+// ahead, and two TMEM accumulators let the MMAs of tile i+1 overlap the epilogue of tile i. Every mbarrier wait is bounded: on expiry the kernel records an error
 // word, leaves its role loop, frees TMEM and returns.
 
 #include <cuda.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -31,24 +33,24 @@ constexpr int BM = 128;             // tile rows
 constexpr int BN = 128;             // tile columns
 constexpr int BK = 256;             // K elements per stage (128 bytes of packed e2m1 per row)
 constexpr int UMMA_K = 64;          // K elements per tcgen05.mma
-constexpr int kStages = 2;
+constexpr int kStages = 4;
 constexpr int kStageABytes = BM * 128;
 constexpr int kStageBBytes = BN * 128;
 constexpr int kStageSfBytes = 4 * 512;  // four 128-row x 64-K atoms
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;
 constexpr int kEpiBufBytes = 32 * 32 * 4;  // one 32 x 32 fp32 box
 constexpr int kThreads = 64 + kEpiWarps * 32;
-constexpr int kTmemCols = 256;      // 128 accumulator + kStages * 32 scale columns, rounded to a power of two
+constexpr int kTmemCols = 512;      // two 128-column accumulators + kStages * 32 scale columns, rounded to a power of two
 constexpr int kAccCol = 0;
-constexpr int kSfCol = 128;
+constexpr int kSfCol = 256;
 
 constexpr int kSmemA = 0;
 constexpr int kSmemB = kSmemA + kStages * kStageABytes;
 constexpr int kSmemSfa = kSmemB + kStages * kStageBBytes;
 constexpr int kSmemSfb = kSmemSfa + kStages * kStageSfBytes;
 constexpr int kSmemEpi = kSmemSfb + kStages * kStageSfBytes;
-constexpr int kSmemLora = kSmemEpi + kEpiWarps * kEpiBufBytes;  // [4][BN] int8
-constexpr int kSmemBar = kSmemLora + 4 * BN;
+constexpr int kSmemLora = kSmemEpi + kEpiWarps * kEpiBufBytes;
+constexpr int kSmemBar = kSmemLora + 2 * 4 * BN * 4;  // two buffers of [4][BN] floats
 constexpr int kSmemTotal = kSmemBar + 128;
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
 
@@ -176,14 +178,23 @@ struct KernelArgs {
     int use_tma_store;
     int k_atoms;  // scale atoms along K
     const uint8_t* lut;  // table of the block quantiser (EPI_GELU_FP4)
+    int total_tiles;
     int n_tiles;  // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile (N fastest: CTAs that share A rows run together)
 };
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent kernel: one CTA per SM walks the tile list (tile = m_tile * n_tiles + n_tile, N fastest so that
+// CTAs working at the same time share rows of A through L2). Three roles run concurrently on different tiles:
+// the producer prefetches operands up to kStages k-blocks ahead, the MMA warp fills one of two TMEM
+// accumulators while the sixteen epilogue warps drain the other one.
 template <int EPI>
-__global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                              const __grid_constant__ CUtensorMap map_b,
-                                                              const __grid_constant__ CUtensorMap map_d,
-                                                              const KernelArgs args) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                 const __grid_constant__ CUtensorMap map_b,
+                                                                 const __grid_constant__ CUtensorMap map_d,
+                                                                 const KernelArgs args) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -191,22 +202,25 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
     const GemmParams& p = args.p;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n_tile = static_cast<int>(blockIdx.x % args.n_tiles), m_tile = static_cast<int>(blockIdx.x / args.n_tiles);
-    const int m0 = m_tile * BM, n0 = n_tile * BN;
     const int num_ks = (p.k + BK - 1) / BK;
+    const int total_tiles = args.total_tiles;
 
-    const uint32_t bar_full = smem_base + kSmemBar;          // kStages x 8 bytes
-    const uint32_t bar_empty = bar_full + 8 * kStages;       // kStages x 8 bytes
-    const uint32_t bar_accum = bar_empty + 8 * kStages;      // 8 bytes
-    const uint32_t tmem_slot = bar_accum + 8;                // 4 bytes
-    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBar + 16 * kStages + 8);
+    const uint32_t bar_full = smem_base + kSmemBar;               // kStages x 8 bytes
+    const uint32_t bar_empty = bar_full + 8 * kStages;            // kStages x 8 bytes
+    const uint32_t bar_acc_full = bar_empty + 8 * kStages;        // 2 x 8 bytes
+    const uint32_t bar_acc_empty = bar_acc_full + 16;             // 2 x 8 bytes
+    const uint32_t tmem_slot = bar_acc_empty + 16;                // 4 bytes
+    volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBar + 16 * kStages + 32);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        mbar_init(bar_accum, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);
+            mbar_init(bar_acc_empty + 8 * b, kEpiWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -221,226 +235,248 @@ __global__ void __launch_bounds__(kThreads) gemm_nvfp4_kernel(const __grid_const
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
-            const uint8_t* sfa_tile = static_cast<const uint8_t*>(p.sfa) + static_cast<size_t>(m_tile) * args.k_atoms * 512;
-            const uint8_t* sfb_tile = static_cast<const uint8_t*>(p.sfb) + static_cast<size_t>(n_tile) * args.k_atoms * 512;
-            for (int ks = 0; ks < num_ks; ++ks) {
-                const int s = ks % kStages;
-                if (ks >= kStages) {
-                    if (!mbar_wait(bar_empty + 8 * s, ((ks / kStages) - 1) & 1, 1)) break;
+            int kc = 0;  // k-block counter across tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int n_tile = tile % args.n_tiles, m_tile = tile / args.n_tiles;
+                const uint8_t* sfa_tile = static_cast<const uint8_t*>(p.sfa) + static_cast<size_t>(m_tile) * args.k_atoms * 512;
+                const uint8_t* sfb_tile = static_cast<const uint8_t*>(p.sfb) + static_cast<size_t>(n_tile) * args.k_atoms * 512;
+                for (int ks = 0; ks < num_ks; ++ks, ++kc) {
+                    const int s = kc % kStages, use = kc / kStages;
+                    if (use >= 1) {
+                        ok = mbar_wait(bar_empty + 8 * s, (use - 1) & 1, 1);
+                        if (!ok) break;
+                    }
+                    const int atoms = min(4, args.k_atoms - ks * 4);
+                    const uint32_t sf_bytes_stage = static_cast<uint32_t>(atoms) * 512u;
+                    const uint32_t bar = bar_full + 8 * s;
+                    mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
+                    tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, m_tile * BM, bar);
+                    tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, n_tile * BN, bar);
+                    bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
+                    bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
                 }
-                const int atoms = min(4, args.k_atoms - ks * 4);
-                const uint32_t sf_bytes_stage = static_cast<uint32_t>(atoms) * 512u;
-                const uint32_t bar = bar_full + 8 * s;
-                mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
-                tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, m0, bar);
-                tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, n0, bar);
-                bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
-                bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
+            int kc = 0, it = 0;
             bool ok = true;
-            for (int ks = 0; ks < num_ks && ok; ++ks) {
-                const int s = ks % kStages;
-                ok = mbar_wait(bar_full + 8 * s, (ks / kStages) & 1, 2);
-                if (!ok) break;
-                tc_fence_after();
-                const int nk = min(4, (p.k - ks * BK) / UMMA_K);
-                const uint32_t sfa_s = smem_base + kSmemSfa + s * kStageSfBytes;
-                const uint32_t sfb_s = smem_base + kSmemSfb + s * kStageSfBytes;
-                const uint32_t t_sfa = tmem_base + kSfCol + s * 32;
-                const uint32_t t_sfb = t_sfa + 16;
-                for (int j = 0; j < nk; ++j) {
-                    tc_cp_sf(t_sfa + 4 * j, smem_desc(sfa_s + 512 * j, 0, 128, kLayoutNone));
-                    tc_cp_sf(t_sfb + 4 * j, smem_desc(sfb_s + 512 * j, 0, 128, kLayoutNone));
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                if (it >= 2) {  // the epilogue must have drained this accumulator (tile it-2)
+                    ok = mbar_wait(bar_acc_empty + 8 * buf, ((it >> 1) - 1) & 1, 4);
+                    if (!ok) break;
+                    tc_fence_after();
                 }
-                const uint32_t a_s = smem_base + kSmemA + s * kStageABytes;
-                const uint32_t b_s = smem_base + kSmemB + s * kStageBBytes;
-                for (int j = 0; j < nk; ++j) {
-                    const uint64_t adesc = smem_desc(a_s + 32 * j, 16, 1024, kLayoutSw128);
-                    const uint64_t bdesc = smem_desc(b_s + 32 * j, 16, 1024, kLayoutSw128);
-                    tc_mma_nvf4(tmem_base + kAccCol, adesc, bdesc, kIdesc, t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
+                const uint32_t acc_col = tmem_base + kAccCol + buf * BN;
+                for (int ks = 0; ks < num_ks; ++ks, ++kc) {
+                    const int s = kc % kStages, use = kc / kStages;
+                    ok = mbar_wait(bar_full + 8 * s, use & 1, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const int nk = min(4, (p.k - ks * BK) / UMMA_K);
+                    const uint32_t sfa_s = smem_base + kSmemSfa + s * kStageSfBytes;
+                    const uint32_t sfb_s = smem_base + kSmemSfb + s * kStageSfBytes;
+                    const uint32_t t_sfa = tmem_base + kSfCol + s * 32;
+                    const uint32_t t_sfb = t_sfa + 16;
+                    for (int j = 0; j < nk; ++j) {
+                        tc_cp_sf(t_sfa + 4 * j, smem_desc(sfa_s + 512 * j, 0, 128, kLayoutNone));
+                        tc_cp_sf(t_sfb + 4 * j, smem_desc(sfb_s + 512 * j, 0, 128, kLayoutNone));
+                    }
+                    const uint32_t a_s = smem_base + kSmemA + s * kStageABytes;
+                    const uint32_t b_s = smem_base + kSmemB + s * kStageBBytes;
+                    for (int j = 0; j < nk; ++j) {
+                        const uint64_t adesc = smem_desc(a_s + 32 * j, 16, 1024, kLayoutSw128);
+                        const uint64_t bdesc = smem_desc(b_s + 32 * j, 16, 1024, kLayoutSw128);
+                        tc_mma_nvf4(acc_col, adesc, bdesc, kIdesc, t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * s);  // frees this smem stage once the MMAs above have read it
                 }
-                tc_commit(bar_empty + 8 * s);  // frees this smem stage once the MMAs above have read it
+                if (ok) tc_commit(bar_acc_full + 8 * buf);  // accumulator of this tile complete
             }
-            if (ok) tc_commit(bar_accum);     // accumulator complete
         }
     } else {
-        // ------------------------------ epilogue (8 warps: two per TMEM lane quadrant) ------------------------------
-        const int ew = warp - 2;                // 0..7
-        const int q = warp & 3;                 // TMEM lane quadrant this warp may access
-        const int half = ew >> 2;               // which 64-column half of the tile this warp handles
-        const int row_in_tile = q * 32 + lane;
-        const long long row = static_cast<long long>(m0) + row_in_tile;
-        const bool row_ok = row < p.m;
-
-        // Per-row perturbation context; stage the A factor of this tile's columns in shared memory when every
-        // row of the tile belongs to the same pair (always the case when rows_per_member is a multiple of 128).
-        int pair = 0;
-        float lsign = 0.0f;
-        if (p.rank > 0 && row_ok) {
-            const int member = p.rows_per_member > 0 ? static_cast<int>(row / p.rows_per_member) : 0;
-            pair = member >> 1;
-            lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
-        }
-        bool a_staged = false;
-        int8_t* loraA_sh = reinterpret_cast<int8_t*>(smem_gen + kSmemLora);  // [4][BN]
-        if (p.rank > 0) {
-            const long long last_row = min(static_cast<long long>(p.m), static_cast<long long>(m0) + BM) - 1;
-            const int pair_first = p.rows_per_member > 0 ? static_cast<int>(m0 / p.rows_per_member) >> 1 : 0;
-            const int pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / p.rows_per_member) >> 1 : 0;
-            a_staged = (pair_first == pair_last);
-            if (a_staged) {
-                const int8_t* Ag = p.lora_A + static_cast<size_t>(pair_first) * p.lora_A_pair_stride;
-                for (int idx = ew * 32 + lane; idx < p.rank * BN; idx += kEpiWarps * 32) {
-                    const int r = idx / BN, cidx = idx - r * BN;
-                    const int n = n0 + cidx;
-                    loraA_sh[r * BN + cidx] = (n < p.n) ? Ag[static_cast<size_t>(n) * p.rank + r] : static_cast<int8_t>(0);
-                }
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
-        }
-
-        bool ok = mbar_wait(bar_accum, 0, 3);
-        ok = __all_sync(0xffffffffu, ok);
-        tc_fence_after();
-        int next_acc[4] = {0, 0, 0, 0};
-
+        // ------------------------------ epilogue: 16 warps, four per TMEM lane quadrant, 32 columns each ------------------------------
+        const int ew = warp - 2;   // 0..15
+        const int q = warp & 3;    // TMEM lane quadrant this warp may access
+        const int c = ew >> 2;     // 32-column chunk of the tile handled by this warp
         const uint32_t epi_buf = smem_base + kSmemEpi + ew * kEpiBufBytes;
         uint8_t* epi_gen = smem_gen + kSmemEpi + ew * kEpiBufBytes;
+        bool ok = true;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            const int n_tile = tile % args.n_tiles, m_tile = tile / args.n_tiles;
+            const int m0 = m_tile * BM, n0 = n_tile * BN;
+            const int row_in_tile = q * 32 + lane;
+            const long long row = static_cast<long long>(m0) + row_in_tile;
+            const bool row_ok = row < p.m;
+            const int col0 = n0 + c * 32;
+            const bool chunk_ok = col0 < p.n;  // warp-uniform
 
-        if (ok) {
-#pragma unroll 1
-            for (int cc = 0; cc < 2; ++cc) {
-                const int c = half * 2 + cc;
-                const int col0 = n0 + c * 32;
-                if (col0 >= p.n) break;  // warp-uniform
-                uint32_t acc[32];
-                tmem_ld32(tmem_base + kAccCol + (static_cast<uint32_t>(q * 32) << 16) + c * 32, acc);
-                tmem_ld_wait();
-
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(p.alpha, __uint_as_float(acc[j]));
-                if (p.beta != 0.0f && row_ok) {
-                    const float* crow = p.c + static_cast<size_t>(row) * p.ldc + col0;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.n) v[j] = fmaf(p.beta, crow[j], v[j]);
-                }
-                if (p.rank > 0 && row_ok) {
-                    const int g = p.group_cols > 0 ? (col0 / p.group_cols) : 0;
-                    int pert[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) pert[j] = 0;
-                    for (int r = 0; r < p.rank; ++r) {
-                        const int tr = p.lora_t[static_cast<size_t>(row) * p.t_stride + g * p.rank + r];
-                        if (a_staged) {
-                            const int4* ap = reinterpret_cast<const int4*>(loraA_sh + r * BN + c * 32);
-                            const int4 a0 = ap[0], a1 = ap[1];
-                            const int aw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                pert[j] += tr * static_cast<int>(static_cast<int8_t>((aw[j >> 2] >> (8 * (j & 3))) & 0xff));
-                        } else {
-                            const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank + r;
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.n) pert[j] += tr * static_cast<int>(Ap[static_cast<size_t>(j) * p.rank]);
-                        }
+            // Perturbation context of this row; stage the A factor of the tile's columns in shared memory when all
+            // rows of the tile belong to one pair (always true when rows_per_member is a multiple of 128).
+            int pair = 0;
+            float lsign = 0.0f;
+            float tr[4] = {0.f, 0.f, 0.f, 0.f};
+            bool a_staged = false;
+            float* loraA_sh = reinterpret_cast<float*>(smem_gen + kSmemLora + buf * 4 * BN * 4);  // [4][BN]
+            if (p.rank > 0) {
+                if (row_ok) {
+                    const int member = p.rows_per_member > 0 ? static_cast<int>(row / p.rows_per_member) : 0;
+                    pair = member >> 1;
+                    lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
+                    if (chunk_ok) {
+                        const int g = p.group_cols > 0 ? (col0 / p.group_cols) : 0;
+                        for (int r = 0; r < p.rank; ++r) tr[r] = static_cast<float>(__ldg(p.lora_t + static_cast<size_t>(row) * p.t_stride + g * p.rank + r));
                     }
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = fmaf(lsign, static_cast<float>(pert[j]), v[j]);
                 }
+                const long long last_row = min(static_cast<long long>(p.m), static_cast<long long>(m0) + BM) - 1;
+                const int pair_first = p.rows_per_member > 0 ? static_cast<int>(m0 / p.rows_per_member) >> 1 : 0;
+                const int pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / p.rows_per_member) >> 1 : 0;
+                a_staged = (pair_first == pair_last);
+                if (a_staged) {
+                    const int8_t* Ag = p.lora_A + static_cast<size_t>(pair_first) * p.lora_A_pair_stride;
+                    for (int idx = ew * 32 + lane; idx < p.rank * BN; idx += kEpiWarps * 32) {
+                        const int r = idx / BN, cidx = idx - r * BN;
+                        const int n = n0 + cidx;
+                        loraA_sh[r * BN + cidx] = (n < p.n) ? static_cast<float>(__ldg(Ag + static_cast<size_t>(n) * p.rank + r)) : 0.0f;
+                    }
+                }
+                // double-buffered by tile parity: one barrier per tile orders writers before readers
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+            }
 
-                if constexpr (EPI == EPI_F32) {
-                    if (args.use_tma_store) {
-                        // stage the 32x32 box in 128B-swizzled shared memory, then one TMA store (clips at M and N)
-                        if (cc > 0) {
-                            if (lane == 0) bulk_wait_read<0>();
-                            __syncwarp();
-                        }
-                        float4* dst = reinterpret_cast<float4*>(epi_gen + lane * 128);
+            ok = mbar_wait(bar_acc_full + 8 * buf, (it >> 1) & 1, 3);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+
+            uint32_t acc[32];
+            tmem_ld32(tmem_base + kAccCol + buf * BN + (static_cast<uint32_t>(q * 32) << 16) + c * 32, acc);
+            tmem_ld_wait();
+            // this warp no longer needs the accumulator: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+            if (!chunk_ok) continue;
+
+            float v[32];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        fence_async_smem();
+            for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(p.alpha, __uint_as_float(acc[j]));
+            if (p.beta != 0.0f && row_ok) {
+                const float* crow = p.c + static_cast<size_t>(row) * p.ldc + col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) v[j] = fmaf(p.beta, crow[j], v[j]);
+            }
+            if (p.rank > 0 && row_ok) {
+                // sum_r t[r]*A[n][r] is an integer below 2^24: float products and sums are exact
+                float pert[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) pert[j] = 0.0f;
+                for (int r = 0; r < p.rank; ++r) {
+                    if (a_staged) {
+                        const float4* ap = reinterpret_cast<const float4*>(loraA_sh + r * BN + c * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 a4 = ap[j];
+                            pert[4 * j + 0] = fmaf(tr[r], a4.x, pert[4 * j + 0]);
+                            pert[4 * j + 1] = fmaf(tr[r], a4.y, pert[4 * j + 1]);
+                            pert[4 * j + 2] = fmaf(tr[r], a4.z, pert[4 * j + 2]);
+                            pert[4 * j + 3] = fmaf(tr[r], a4.w, pert[4 * j + 3]);
+                        }
+                    } else {
+                        const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank + r;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) pert[j] = fmaf(tr[r], static_cast<float>(Ap[static_cast<size_t>(j) * p.rank]), pert[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = fmaf(lsign, pert[j], v[j]);
+            }
+
+            if constexpr (EPI == EPI_F32) {
+                if (args.use_tma_store) {
+                    // stage the 32x32 box in 128B-swizzled shared memory, then one TMA store (clips at M and N)
+                    if (it > 0) {
+                        if (lane == 0) bulk_wait_read<0>();
                         __syncwarp();
-                        if (lane == 0) {
-                            tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
-                            bulk_commit();
-                        }
-                    } else if (row_ok) {
-                        float* drow = p.d + static_cast<size_t>(row) * p.ldd + col0;
-                        const bool vec = ((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && (col0 + 32 <= p.n);
-                        if (vec) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(drow)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.n) drow[j] = v[j];
-                        }
                     }
-                } else {
-                    // GELU -> int8 (reference: src/cuda_kernels.cu:3178-3194; tanh-form GELU, clip to +-127)
-                    int w[8];
+                    float4* dst = reinterpret_cast<float4*>(epi_gen + lane * 128);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        int qv[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            qv[u] = (col0 + 4 * j + u < p.n) ? clip_int8(rint_to_int(gelu_scaled(v[4 * j + u], p.act_scale))) : 0;
-                        w[j] = pack4_i8(qv[0], qv[1], qv[2], qv[3]);
+                    for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
+                        bulk_commit();
                     }
-                    if (row_ok && p.d_i8 != nullptr) {
-                        int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
-                        if (((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && col0 + 32 <= p.n) {
-                            reinterpret_cast<int4*>(drow)[0] = make_int4(w[0], w[1], w[2], w[3]);
-                            reinterpret_cast<int4*>(drow)[1] = make_int4(w[4], w[5], w[6], w[7]);
-                        } else {
+                } else if (row_ok) {
+                    float* drow = p.d + static_cast<size_t>(row) * p.ldd + col0;
+                    const bool vec = ((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && (col0 + 32 <= p.n);
+                    if (vec) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.n) drow[j] = static_cast<int8_t>((w[j >> 2] >> (8 * (j & 3))) & 0xff);
-                        }
+                        for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(drow)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) drow[j] = v[j];
                     }
-                    if constexpr (EPI == EPI_GELU_FP4) {
-                        if (row_ok) {
-                            const int wa[4] = {w[0], w[1], w[2], w[3]};
-                            const int wb[4] = {w[4], w[5], w[6], w[7]};
-                            uint32_t s0, s1, lo0, hi0, lo1, hi1;
-                            quant_block16_lut(wa, args.lut, s0, lo0, hi0);
-                            quant_block16_lut(wb, args.lut, s1, lo1, hi1);
-                            *reinterpret_cast<uint4*>(p.d_codes + (static_cast<size_t>(row) * p.n + col0) / 2) = make_uint4(lo0, hi0, lo1, hi1);
-                            const int kb = col0 >> 4;
-                            *reinterpret_cast<uint16_t*>(p.d_sf + sf_offset(static_cast<int>(row), kb, sf_k_atoms(p.n))) =
-                                static_cast<uint16_t>(s0 | (s1 << 8));
-                            if (p.next_nvec > 0) {
-                                const int8_t* tv = p.next_tvec + static_cast<size_t>(pair) * p.next_tvec_pair_stride + col0;
-                                for (int vv = 0; vv < p.next_nvec; ++vv) {
-                                    const int4* bv = reinterpret_cast<const int4*>(tv + static_cast<size_t>(vv) * p.n);
-                                    const int4 b0 = __ldg(bv), b1 = __ldg(bv + 1);
-                                    int a = next_acc[vv];
-                                    a = __dp4a(w[0], b0.x, a); a = __dp4a(w[1], b0.y, a); a = __dp4a(w[2], b0.z, a); a = __dp4a(w[3], b0.w, a);
-                                    a = __dp4a(w[4], b1.x, a); a = __dp4a(w[5], b1.y, a); a = __dp4a(w[6], b1.z, a); a = __dp4a(w[7], b1.w, a);
-                                    next_acc[vv] = a;
-                                }
+                }
+            } else {
+                // GELU -> int8 (reference: src/cuda_kernels.cu:3178-3194; tanh-form GELU, clip to +-127)
+                int qv[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) qv[j] = (col0 + j < p.n) ? gelu_q8(v[j], p.act_scale) : 0;
+                int w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w[j] = pack4_i8(qv[4 * j], qv[4 * j + 1], qv[4 * j + 2], qv[4 * j + 3]);
+                if (row_ok && p.d_i8 != nullptr) {
+                    int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
+                    if (((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && col0 + 32 <= p.n) {
+                        reinterpret_cast<int4*>(drow)[0] = make_int4(w[0], w[1], w[2], w[3]);
+                        reinterpret_cast<int4*>(drow)[1] = make_int4(w[4], w[5], w[6], w[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) drow[j] = static_cast<int8_t>((w[j >> 2] >> (8 * (j & 3))) & 0xff);
+                    }
+                }
+                if constexpr (EPI == EPI_GELU_FP4) {
+                    if (row_ok) {
+                        int qa[16], qb[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) { qa[j] = qv[j]; qb[j] = qv[16 + j]; }
+                        uint32_t s0, s1, lo0, hi0, lo1, hi1;
+                        quant_block16_lut(qa, args.lut, s0, lo0, hi0);
+                        quant_block16_lut(qb, args.lut, s1, lo1, hi1);
+                        *reinterpret_cast<uint4*>(p.d_codes + (static_cast<size_t>(row) * p.n + col0) / 2) = make_uint4(lo0, hi0, lo1, hi1);
+                        const int kb = col0 >> 4;
+                        *reinterpret_cast<uint16_t*>(p.d_sf + sf_offset(static_cast<int>(row), kb, sf_k_atoms(p.n))) =
+                            static_cast<uint16_t>(s0 | (s1 << 8));
+                        if (p.next_nvec > 0) {
+                            const int8_t* tv = p.next_tvec + static_cast<size_t>(pair) * p.next_tvec_pair_stride + col0;
+                            for (int vv = 0; vv < p.next_nvec; ++vv) {
+                                const int4* bv = reinterpret_cast<const int4*>(tv + static_cast<size_t>(vv) * p.n);
+                                const int4 b0 = __ldg(bv), b1 = __ldg(bv + 1);
+                                int a = 0;
+                                a = __dp4a(w[0], b0.x, a); a = __dp4a(w[1], b0.y, a); a = __dp4a(w[2], b0.z, a); a = __dp4a(w[3], b0.w, a);
+                                a = __dp4a(w[4], b1.x, a); a = __dp4a(w[5], b1.y, a); a = __dp4a(w[6], b1.z, a); a = __dp4a(w[7], b1.w, a);
+                                atomicAdd(p.next_t + static_cast<size_t>(row) * p.next_nvec + vv, a);
                             }
                         }
                     }
                 }
             }
-            if constexpr (EPI == EPI_F32) {
-                if (args.use_tma_store) {
-                    if (lane == 0) bulk_wait_read<0>();
-                    __syncwarp();
-                }
-            }
-            if constexpr (EPI == EPI_GELU_FP4) {
-                if (row_ok && p.next_nvec > 0) {
-                    for (int vv = 0; vv < p.next_nvec; ++vv) atomicAdd(p.next_t + static_cast<size_t>(row) * p.next_nvec + vv, next_acc[vv]);
-                }
+        }
+        if constexpr (EPI == EPI_F32) {
+            if (args.use_tma_store) {
+                if (lane == 0) bulk_wait_read<0>();
+                __syncwarp();
             }
         }
     }
@@ -553,7 +589,13 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     args.n_tiles = (p.n + BN - 1) / BN;
     const long long tiles = static_cast<long long>(args.n_tiles) * ((p.m + BM - 1) / BM);
     if (tiles > 0x7fffffffLL) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: too many tiles");
-    const dim3 grid(static_cast<unsigned>(tiles), 1, 1);
+    args.total_tiles = static_cast<int>(tiles);
+    int dev = 0, sms = 0;
+    rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+    if (rc) return rc;
+    const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
     switch (p.epilogue) {
         case EPI_F32: return launch_t<EPI_F32>(ma, mb, md, args, grid, stream);
         case EPI_GELU_I8: return launch_t<EPI_GELU_I8>(ma, mb, md, args, grid, stream);

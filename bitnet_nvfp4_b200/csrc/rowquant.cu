@@ -113,8 +113,10 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
                     float x = f[e];
                     if (p.act_mode == 1) x = x < 0.0f ? 0.0f : x;
                     else if (p.act_mode == 2) x = tanhf(__fdiv_rn(x, 127.0f)) * 127.0f;
-                    else if (p.act_mode == 3) x = gelu_scaled(x, p.act_scale);
-                    vals[e] = (k0 + e < p.cols_in) ? clip_int8(rint_to_int(x)) : 0;
+                    int qx;
+                    if (p.act_mode == 3) qx = gelu_q8(x, p.act_scale);
+                    else qx = clip_int8(rint_to_int(x));
+                    vals[e] = (k0 + e < p.cols_in) ? qx : 0;
                 }
             } else {
                 const int prow = p.pos_mod > 0 ? (row_in_member % p.pos_mod) : 0;
@@ -126,8 +128,7 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
                 for (int e = 0; e < 16; ++e) {
                     float pv = pos[k0 + e];
                     if (pn != nullptr) pv = fmaf(ns, static_cast<float>(pn[k0 + e]), pv);
-                    const float x = gelu_scaled(f[e] + pv, p.act_scale);
-                    vals[e] = clip_int8(rint_to_int(x));
+                    vals[e] = gelu_q8(f[e] + pv, p.act_scale);
                 }
             }
         } else if constexpr (FE == FE_ADD_ABSMEAN) {
@@ -180,6 +181,9 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
         if (!__any_sync(0xffffffffu, active)) continue;
         const int k0 = kb << 4;
         int w[4] = {0, 0, 0, 0};
+        int qi[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) qi[e] = 0;
         if (active) {
             if constexpr (FE == FE_POS_GELU_ABSMEAN) {
                 // residual stream = the pre-norm values
@@ -188,15 +192,14 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
             }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                int b[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     int v = static_cast<int>(static_cast<int8_t>((xw[i][q] >> (8 * j)) & 0xff));
                     if constexpr (FE == FE_ABSMEAN || FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN)
                         v = clip_int8(rint_to_int(__fmul_rn(static_cast<float>(v), inv)));
-                    b[j] = v;
+                    qi[4 * q + j] = v;
                 }
-                w[q] = pack4_i8(b[0], b[1], b[2], b[3]);
+                w[q] = pack4_i8(qi[4 * q], qi[4 * q + 1], qi[4 * q + 2], qi[4 * q + 3]);
             }
             if (p.out_q != nullptr) {
                 int8_t* dst = p.out_q + static_cast<size_t>(row) * p.ld_q + k0;
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
         uint32_t sfb = 0, lo = 0, hi = 0;
         if (active) {
             if constexpr (FE == FE_WQKV) quant_block16(w, row_scale, true, sfb, lo, hi);
-            else quant_block16_lut(w, lut, sfb, lo, hi);
+            else quant_block16_lut(qi, lut, sfb, lo, hi);
             *reinterpret_cast<uint2*>(p.out_codes + (static_cast<size_t>(row) * p.cols_out + k0) / 2) = make_uint2(lo, hi);
         }
         // four neighbouring lanes hold the four scale bytes of one 32-bit word of the atom layout

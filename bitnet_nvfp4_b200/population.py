@@ -198,6 +198,42 @@ class PopulationModel:
         return out
 
 
+def shard_pairs(pairs_total: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous pair range [begin, begin + count) evaluated by `rank` (reference: eval_ranges,
+    src/train_efla_lm.cpp:5067-5077). Both members of a pair stay on one rank."""
+    base, rem = divmod(pairs_total, world)
+    begin = rank * base + min(rank, rem)
+    return begin, base + (1 if rank < rem else 0)
+
+
+def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world: int = 1, group=None, lr: float = 0.8,
+            thresh: float = 0.008, fitness_mode: int = 0, fitness_clip: float = 3.0, losses_out: torch.Tensor | None = None,
+            **update_kw) -> torch.Tensor:
+    """One ES step on this rank: evaluate this rank's pairs, all-gather the per-member losses over `group`
+    (torch.distributed), shape the fitness and apply the identical deterministic update on every rank.
+    `model` is a PopulationModel (or any object with prepare_step / eval_pairs / update). Returns all 2*pairs_total losses."""
+    import torch.distributed as dist
+    begin, count = shard_pairs(pairs_total, rank, world)
+    model.prepare_step(seed, epoch, pairs_total)
+    mine = model.eval_pairs(begin, count)
+    if world > 1:
+        if pairs_total % world == 0:
+            losses = losses_out if losses_out is not None else torch.empty(2 * pairs_total, dtype=mine.dtype, device=mine.device)
+            dist.all_gather_into_tensor(losses, mine, group=group)
+        else:  # ragged shards: gather with padding
+            cap = 2 * (pairs_total // world + 1)
+            padded = torch.zeros(cap, dtype=mine.dtype, device=mine.device)
+            padded[: mine.numel()] = mine
+            parts = [torch.empty_like(padded) for _ in range(world)]
+            dist.all_gather(parts, padded, group=group)
+            losses = torch.cat([parts[r][: 2 * shard_pairs(pairs_total, r, world)[1]] for r in range(world)])
+    else:
+        losses = mine
+    weights = shape_fitness(fitness_from_losses(losses), fitness_mode, fitness_clip)
+    model.update(weights, lr=lr, thresh=thresh, **update_kw)
+    return losses
+
+
 def fitness_from_losses(losses: torch.Tensor) -> torch.Tensor:
     """f_p = -(loss+ - loss-)  (reference: src/train_efla_lm.cpp:5466)."""
     l2 = losses.view(-1, 2)
