@@ -261,7 +261,7 @@ def main():
 
     # ------------------------------------------------------------------ roofline of the dominant kernel class
     peaks, peak_src = load_peaks()
-    wave_members = min(cfg.wave_members or 16, 2 * my_pairs)
+    wave_members = min(cfg.wave_members or 64, 2 * my_pairs)
     work = algorithmic_work(cfg, wave_members)
     kernels = []
     for name, (ms, cnt) in timing.items():

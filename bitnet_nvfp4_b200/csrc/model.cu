@@ -358,7 +358,7 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     m->s_f = 1.0f / std::sqrt(static_cast<float>(m->F));
     m->sigma = 1.0f / static_cast<float>(1 << cfg->sigma_shift);
     m->c_r = kCRankBase / std::sqrt(static_cast<float>(m->r));
-    int W = cfg->wave_members > 0 ? cfg->wave_members : 16;
+    int W = cfg->wave_members > 0 ? cfg->wave_members : 64;
     W = std::min(W, 2 * cfg->max_pairs);
     W = std::max(2, W & ~1);
     m->W = W;
