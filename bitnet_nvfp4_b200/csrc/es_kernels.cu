@@ -471,3 +471,65 @@ int bnf4_add_scaled(float* out, const float* noise, int n, float scale, void* st
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// bnf4_compute_z_sumsq_static: the dense Z / sum-of-squares step with no allocation of any kind.
+//
+// bnf4_compute_z_sumsq keeps its block partials in a buffer the library obtains from cudaMalloc the first time
+// it is needed on a device and replaces by a larger one when a longer vector arrives. Some hosts cannot accept
+// that: a trainer whose own allocator has already reserved the whole of HBM (a library cudaMalloc then fails
+// although the job has memory to spare), a serving loop in which the implicit device-wide synchronisation of
+// cudaMalloc / cudaFree stalls every other stream, or a process that must keep a fixed, auditable device
+// footprint. For them the partials live in the array below, which is part of the loaded module image: it exists
+// as soon as the library is loaded on a device and is never resized or released.
+//
+// Capacity: kStaticPartials block partials of 256 elements each, i.e. n <= 67,108,864 (an 8192 x 8192 matrix);
+// longer vectors are refused with BNF4_ERR_INVALID and nothing is launched.
+// ---------------------------------------------------------------------------------------------------
+static constexpr int kStaticPartials = 262144;  // 1 MiB of device memory per device
+static constexpr long long kStaticMaxN = 256LL * kStaticPartials;
+static __device__ __align__(256) float g_static_partials[kStaticPartials];
+
+namespace {
+std::mutex g_static_mu;
+float* g_static_ptr[64] = {};  // device address of g_static_partials, per device ordinal; filled on first use
+
+// Resolves the device address of the array for the CURRENT device (each device holds its own copy of a
+// __device__ variable). Host code never uses the array's name as an address: only the pointer obtained here
+// is handed to kernels.
+int static_partials(float** out) {
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return set_error(BNF4_ERR_INVALID, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+        float* ptr = nullptr;
+        rc = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_partials), "cudaGetSymbolAddress(static partials)");
+        if (rc) return rc;
+        if (ptr == nullptr) return set_error(BNF4_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return BNF4_OK;
+}
+}  // namespace
+
+extern "C" int bnf4_compute_z_sumsq_static(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int n,
+                                           int use_clt, int clt_k, float* Z, float* sumsq, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    if (!pair_weights || !pair_seeds || !Z || !sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_static: null pointer");
+    if (static_cast<long long>(n) > kStaticMaxN)
+        return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_static: n=%d exceeds the built-in scratch capacity of %lld elements; "
+                         "use bnf4_compute_z_sumsq or split the vector", n, kStaticMaxN);
+    float* partial = nullptr;
+    int rc = static_partials(&partial);
+    if (rc) return rc;
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), st>>>(pair_weights, pair_seeds, salt, pairs, n, use_clt, clt_k, Z);
+    rc = check_launch("z_dense_kernel");
+    if (rc) return rc;
+    // Every partial the final kernel reads (indices 0 .. ceil(n/256)-1) is written by the block kernel of this same
+    // call first, so stale contents left by an earlier call are never observed and nothing needs clearing.
+    return sumsq_with_scratch(Z, n, partial, sumsq, st);
+}

@@ -126,6 +126,7 @@ _PROTOS = {
     "bnf4_init_shadow_from_weights": (c_int, [_I8P, c_void_p, c_int, c_void_p]),
     "bnf4_fill_pair_seeds": (c_int, [c_u64, c_u64, c_int, c_void_p, c_void_p]),
     "bnf4_compute_z_sumsq": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "bnf4_compute_z_sumsq_static": (c_int, [c_void_p, c_void_p, c_u64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "bnf4_compute_z_sumsq_lowrank": (c_int, [c_void_p, _I8P, c_ll, _I8P, c_ll, c_int, c_int, c_int, c_int, c_float,
                                              c_void_p, c_void_p, c_void_p]),
     "bnf4_update_inv_rms": (c_int, [c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p]),

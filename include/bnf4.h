@@ -298,6 +298,21 @@ int bnf4_fill_pair_seeds(uint64_t base_seed, uint64_t epoch, int pairs, uint64_t
  * library-owned scratch buffer for the block partials (allocated with cudaMalloc on first use and grown on demand). */
 int bnf4_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int n,
                          int use_clt, int clt_k, float* Z, float* sumsq, void* stream);
+/* No counterpart in the reference. Same arguments, arithmetic and result as bnf4_compute_z_sumsq, for callers that
+ * cannot let a library allocate device memory: a host whose own allocator has reserved all of HBM (a library
+ * cudaMalloc would fail), a loop that cannot afford the device-wide synchronisation cudaMalloc/cudaFree imply, or a
+ * process held to a fixed device footprint. This entry point calls no allocator at all (no cudaMalloc, no cudaFree,
+ * no pool or library routine that allocates); the caller still supplies every input and output buffer, and the block
+ * partials of sum(Z^2) go to a 1 MiB array built into the library's device image.
+ *   - Limit: n <= 67,108,864 elements (262,144 partials of 256 elements). Larger n returns BNF4_ERR_INVALID and
+ *     launches nothing.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and caches it; make that first call during set-up, before any stream capture begins.
+ *   - The array is one per device and shared by every call, on every stream and host thread; it keeps whatever the
+ *     last call left. Each call overwrites every partial it later reads, so nothing has to be cleared, but two calls
+ *     that may overlap in time (different streams, or different threads without ordering) race on it: order them. */
+int bnf4_compute_z_sumsq_static(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int n,
+                                int use_clt, int clt_k, float* Z, float* sumsq, void* stream);
 /* Rank-r form: Z[i*cols+j] = cscale * sum_p w_p * sum_r A[p][i][r]*B[p][r][j] with A [pairs][rows][rank] and
  * B [pairs][rank][cols] int8 (the same factor buffers the forward pass uses). */
 int bnf4_compute_z_sumsq_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
