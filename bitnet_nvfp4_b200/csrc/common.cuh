@@ -97,23 +97,39 @@ __device__ __forceinline__ float gelu_scaled(float x, float act_scale) {
     return f;
 }
 
-// clip8(rint(gelu_tanh(x) * act_scale)) with one MUFU: tanh.approx (relative error <= 2^-11) decides every case
-// whose distance to a rounding boundary exceeds its error bound; the rest (a fraction of a percent) is re-evaluated
-// with the tanhf form, so the integer is the one the tanhf form gives. Rounding uses the 1.5*2^23 trick.
+// clip8(rint(gelu_tanh(x) * act_scale)) without tanhf on the common path.
+//   gelu_tanh(x) = 0.5 x (1 + tanh u) = x - x / (1 + e^(2u)),   u = c (x + 0.044715 x^3)
+// evaluated with ex2.approx and rcp.approx (absolute error below 1e-6 |x act_scale|). The value is clamped to
+// +-127, rounded with the 1.5*2^23 trick and returned still biased: q = float_as_int(t) - kRoundBiasBits, and the low
+// byte of float_as_int(t) is q as an int8. `ok` is cleared when the value lies within twice the error bound of a
+// rounding boundary; the caller then takes gelu_q8_exact, so the integer is always the one the tanhf form gives.
+constexpr float kRoundBias = 12582912.0f;      // 1.5 * 2^23
+constexpr int kRoundBiasBits = 0x4B400000;     // its bit pattern
+__device__ __forceinline__ float gelu_q8_fast(float x, float act_scale, bool& ok, float& clamped) {
+    const float kB = 2.0f * 0.7978845608028654f * 1.4426950408889634f;  // 2 c log2(e)
+    const float kA = kB * 0.044715f;
+    const float u2 = x * fmaf(x * x, kA, kB);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u2));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.0f));
+    const float xs = x * act_scale;
+    const float f = fmaf(-xs, r, xs);
+    const float fc = fminf(fmaxf(f, -127.0f), 127.0f);
+    const float t = fc + kRoundBias;
+    const float d = fabsf(fc - (t - kRoundBias)) - 0.5f;
+    ok = ok && (fabsf(d) > fmaf(fabsf(xs), 2e-6f, 2e-6f));
+    clamped = fc;
+    return t;
+}
+__device__ __forceinline__ int gelu_q8_exact(float x, float act_scale) {
+    return clip_int8(__float2int_rn(gelu_tanh(x) * act_scale));
+}
 __device__ __forceinline__ int gelu_q8(float x, float act_scale) {
-    const float c = 0.7978845608028654f;
-    const float u = c * fmaf(0.044715f, x * x * x, x);
-    float th;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
-    const float hx = 0.5f * x;
-    const float f = fmaf(hx, th, hx) * act_scale;
-    const float margin = fmaf(fabsf(hx * act_scale), 5.2e-4f, 1e-5f);
-    const float t = f + 12582912.0f;
-    const float r = t - 12582912.0f;
-    int q;
-    if (fabsf(fabsf(f - r) - 0.5f) > margin && fabsf(f) < 1000.0f) q = __float_as_int(t) - 0x4B400000;
-    else q = __float2int_rn(gelu_tanh(x) * act_scale);
-    return clip_int8(q);
+    bool ok = true;
+    float fc;
+    const float t = gelu_q8_fast(x, act_scale, ok, fc);
+    if (ok) return __float_as_int(t) - kRoundBiasBits;
+    return gelu_q8_exact(x, act_scale);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -221,7 +237,14 @@ __device__ __forceinline__ void quant_block16(const int (&w)[4], float row_scale
 // through the L1: the 16 values of a block share one amax, i.e. one 128-byte row.
 // ---------------------------------------------------------------------------------------------
 constexpr int kQuantLutCodeBytes = 128 * 128;
-constexpr int kQuantLutBytes = kQuantLutCodeBytes + 128;
+// A second form of the same table follows the first one, meant to be copied to shared memory: rows of
+// kQuantLutSignedStride bytes indexed by v + 128 (v = -127..127) that already carry the sign bit, then the 128 scale
+// bytes again. The stride of 260 bytes spreads the rows of neighbouring amax values over different banks.
+constexpr int kQuantLutSignedOffset = kQuantLutCodeBytes + 128;
+constexpr int kQuantLutSignedStride = 260;
+constexpr int kQuantLutSignedSfOffset = 128 * kQuantLutSignedStride;            // relative to the signed block
+constexpr int kQuantLutSignedBytes = kQuantLutSignedSfOffset + 128;             // 33408, a multiple of 16
+constexpr int kQuantLutBytes = kQuantLutSignedOffset + kQuantLutSignedBytes;
 // Device pointer to the table of the current device (allocated and filled on first use); nullptr + error on failure.
 const uint8_t* get_quant_lut();
 

@@ -50,7 +50,7 @@ constexpr int kSmemSfa = kSmemB + kStages * kStageBBytes;
 constexpr int kSmemSfb = kSmemSfa + kStages * kStageSfBytes;
 constexpr int kSmemEpi = kSmemSfb + kStages * kStageSfBytes;
 constexpr int kSmemLora = kSmemEpi + kEpiWarps * kEpiBufBytes;
-constexpr int kSmemBar = kSmemLora + 2 * 4 * BN * 4;  // two buffers of [4][BN] floats
+constexpr int kSmemBar = kSmemLora + kEpiWarps * 4 * 32 * 4;  // per epilogue warp: [4][32] floats of the pair's A factor
 constexpr int kSmemTotal = kSmemBar + 128;
 constexpr int kSmemAlloc = kSmemTotal + 1024;  // slack for manual 1024-byte alignment
 
@@ -154,6 +154,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading byte
@@ -176,6 +181,7 @@ constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >
 struct KernelArgs {
     GemmParams p;
     int use_tma_store;
+    int timing_aid;  // results invalid; after the first kStages k-blocks: bit 0 no B loads, bit 1 no A loads, bit 2 no scale copies, bit 3 no MMAs
     int k_atoms;  // scale atoms along K
     const uint8_t* lut;  // table of the block quantiser (EPI_GELU_FP4)
     int total_tiles;
@@ -250,9 +256,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     const int atoms = min(4, args.k_atoms - ks * 4);
                     const uint32_t sf_bytes_stage = static_cast<uint32_t>(atoms) * 512u;
                     const uint32_t bar = bar_full + 8 * s;
-                    mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
-                    tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, m_tile * BM, bar);
-                    tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, n_tile * BN, bar);
+                    const bool load_a = !((args.timing_aid & 2) && kc >= kStages), load_b = !((args.timing_aid & 1) && kc >= kStages);
+                    mbar_expect_tx(bar, (load_a ? kStageABytes : 0) + (load_b ? kStageBBytes : 0) + 2 * sf_bytes_stage);
+                    if (load_a) tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, m_tile * BM, bar);
+                    if (load_b) tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, n_tile * BN, bar);
                     bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
                     bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
                 }
@@ -281,13 +288,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     const uint32_t sfb_s = smem_base + kSmemSfb + s * kStageSfBytes;
                     const uint32_t t_sfa = tmem_base + kSfCol + s * 32;
                     const uint32_t t_sfb = t_sfa + 16;
-                    for (int j = 0; j < nk; ++j) {
-                        tc_cp_sf(t_sfa + 4 * j, smem_desc(sfa_s + 512 * j, 0, 128, kLayoutNone));
-                        tc_cp_sf(t_sfb + 4 * j, smem_desc(sfb_s + 512 * j, 0, 128, kLayoutNone));
+                    if (!((args.timing_aid & 4) && kc >= kStages)) {
+                        for (int j = 0; j < nk; ++j) {
+                            tc_cp_sf(t_sfa + 4 * j, smem_desc(sfa_s + 512 * j, 0, 128, kLayoutNone));
+                            tc_cp_sf(t_sfb + 4 * j, smem_desc(sfb_s + 512 * j, 0, 128, kLayoutNone));
+                        }
                     }
                     const uint32_t a_s = smem_base + kSmemA + s * kStageABytes;
                     const uint32_t b_s = smem_base + kSmemB + s * kStageBBytes;
                     for (int j = 0; j < nk; ++j) {
+                        if ((args.timing_aid & 8) && kc >= kStages) break;
                         const uint64_t adesc = smem_desc(a_s + 32 * j, 16, 1024, kLayoutSw128);
                         const uint64_t bdesc = smem_desc(b_s + 32 * j, 16, 1024, kLayoutSw128);
                         tc_mma_nvf4(acc_col, adesc, bdesc, kIdesc, t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
@@ -306,47 +316,85 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         uint8_t* epi_gen = smem_gen + kSmemEpi + ew * kEpiBufBytes;
         bool ok = true;
         int it = 0;
+        if constexpr (EPI == EPI_GELU_FP4) {
+            // The block quantiser's table (signed form, 33 KB) lives in the staging area the fp32 epilogue would use.
+            const int4* src = reinterpret_cast<const int4*>(args.lut + kQuantLutSignedOffset);
+            int4* dst = reinterpret_cast<int4*>(smem_gen + kSmemEpi);
+            for (int i = ew * 32 + lane; i < kQuantLutSignedBytes / 16; i += kEpiWarps * 32) dst[i] = __ldg(src + i);
+            asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+        }
+        // Perturbation context of one tile: this thread's row (projections t, sign, pair) and, when all rows of the tile
+        // belong to one pair (always true when rows_per_member is a multiple of 128), this thread's element of the
+        // pair's A factor for the tile's columns. It is fetched one tile ahead so that the global-load latency hides
+        // behind the previous tile's epilogue.
+        struct LoraCtx {
+            int pair;
+            float lsign;
+            int tr[4];    // raw integers: converted to float only when the tile is processed, so that nothing waits
+            int aval[4];  // on these loads earlier;  aval[r] = A[pair][col0 + lane][r]
+            bool a_staged;
+        };
+        const int row_in_tile = q * 32 + lane;
+        auto fetch_ctx = [&](int tile_, LoraCtx& cx) {
+            cx.pair = 0;
+            cx.lsign = 0.0f;
+            cx.tr[0] = cx.tr[1] = cx.tr[2] = cx.tr[3] = 0;
+            cx.aval[0] = cx.aval[1] = cx.aval[2] = cx.aval[3] = 0;
+            cx.a_staged = false;
+            if (p.rank <= 0 || tile_ >= total_tiles) return;
+            const int n_tile_ = tile_ % args.n_tiles, m_tile_ = tile_ / args.n_tiles;
+            const int m0_ = m_tile_ * BM, n0_ = n_tile_ * BN;
+            const long long row_ = static_cast<long long>(m0_) + row_in_tile;
+            const int col0_ = n0_ + c * 32;
+            if (row_ < p.m) {
+                // rows fit 31 bits (p.m is an int): 32-bit divisions
+                const int member = p.rows_per_member > 0 ? static_cast<int>(static_cast<unsigned>(row_) / static_cast<unsigned>(p.rows_per_member)) : 0;
+                cx.pair = member >> 1;
+                cx.lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
+                if (col0_ < p.n) {
+                    const int g = p.group_cols > 0 ? (col0_ / p.group_cols) : 0;
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (r < p.rank) cx.tr[r] = __ldg(p.lora_t + static_cast<size_t>(row_) * p.t_stride + g * p.rank + r);
+                }
+            }
+            const unsigned last_row = static_cast<unsigned>(min(static_cast<long long>(p.m), static_cast<long long>(m0_) + BM) - 1);
+            const int pair_first = p.rows_per_member > 0 ? static_cast<int>(static_cast<unsigned>(m0_) / static_cast<unsigned>(p.rows_per_member)) >> 1 : 0;
+            const int pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / static_cast<unsigned>(p.rows_per_member)) >> 1 : 0;
+            cx.a_staged = (pair_first == pair_last);
+            const int n = col0_ + lane;
+            if (cx.a_staged && n < p.n) {
+                const int8_t* Ag = p.lora_A + static_cast<size_t>(pair_first) * p.lora_A_pair_stride + static_cast<size_t>(n) * p.rank;
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (r < p.rank) cx.aval[r] = __ldg(Ag + r);
+            }
+        };
+        LoraCtx nxt;
+        fetch_ctx(blockIdx.x, nxt);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
             const int n_tile = tile % args.n_tiles, m_tile = tile / args.n_tiles;
             const int m0 = m_tile * BM, n0 = n_tile * BN;
-            const int row_in_tile = q * 32 + lane;
             const long long row = static_cast<long long>(m0) + row_in_tile;
             const bool row_ok = row < p.m;
             const int col0 = n0 + c * 32;
             const bool chunk_ok = col0 < p.n;  // warp-uniform
 
-            // Perturbation context of this row; stage the A factor of the tile's columns in shared memory when all
-            // rows of the tile belong to one pair (always true when rows_per_member is a multiple of 128).
-            int pair = 0;
-            float lsign = 0.0f;
-            float tr[4] = {0.f, 0.f, 0.f, 0.f};
-            bool a_staged = false;
-            float* loraA_sh = reinterpret_cast<float*>(smem_gen + kSmemLora + buf * 4 * BN * 4);  // [4][BN]
+            const int pair = nxt.pair;
+            const float lsign = nxt.lsign;
+            const float tr[4] = {static_cast<float>(nxt.tr[0]), static_cast<float>(nxt.tr[1]), static_cast<float>(nxt.tr[2]), static_cast<float>(nxt.tr[3])};
+            const bool a_staged = nxt.a_staged;
+            float* loraA_sh = reinterpret_cast<float*>(smem_gen + kSmemLora) + ew * 4 * 32;  // this warp's [4][32]
             if (p.rank > 0) {
-                if (row_ok) {
-                    const int member = p.rows_per_member > 0 ? static_cast<int>(row / p.rows_per_member) : 0;
-                    pair = member >> 1;
-                    lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
-                    if (chunk_ok) {
-                        const int g = p.group_cols > 0 ? (col0 / p.group_cols) : 0;
-                        for (int r = 0; r < p.rank; ++r) tr[r] = static_cast<float>(__ldg(p.lora_t + static_cast<size_t>(row) * p.t_stride + g * p.rank + r));
-                    }
-                }
-                const long long last_row = min(static_cast<long long>(p.m), static_cast<long long>(m0) + BM) - 1;
-                const int pair_first = p.rows_per_member > 0 ? static_cast<int>(m0 / p.rows_per_member) >> 1 : 0;
-                const int pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / p.rows_per_member) >> 1 : 0;
-                a_staged = (pair_first == pair_last);
+                __syncwarp();  // the previous tile's reads are done
                 if (a_staged) {
-                    const int8_t* Ag = p.lora_A + static_cast<size_t>(pair_first) * p.lora_A_pair_stride;
-                    for (int idx = ew * 32 + lane; idx < p.rank * BN; idx += kEpiWarps * 32) {
-                        const int r = idx / BN, cidx = idx - r * BN;
-                        const int n = n0 + cidx;
-                        loraA_sh[r * BN + cidx] = (n < p.n) ? static_cast<float>(__ldg(Ag + static_cast<size_t>(n) * p.rank + r)) : 0.0f;
-                    }
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (r < p.rank) loraA_sh[r * 32 + lane] = static_cast<float>(nxt.aval[r]);
                 }
-                // double-buffered by tile parity: one barrier per tile orders writers before readers
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+                __syncwarp();
+                fetch_ctx(tile + gridDim.x, nxt);
             }
 
             ok = mbar_wait(bar_acc_full + 8 * buf, (it >> 1) & 1, 3);
@@ -374,33 +422,52 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             }
             if (p.rank > 0 && row_ok) {
                 // sum_r t[r]*A[n][r] is an integer below 2^24: float products and sums are exact
-                float pert[32];
+                if (a_staged && p.rank == 1) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) pert[j] = 0.0f;
-                for (int r = 0; r < p.rank; ++r) {
-                    if (a_staged) {
-                        const float4* ap = reinterpret_cast<const float4*>(loraA_sh + r * BN + c * 32);
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 a4 = *reinterpret_cast<const float4*>(loraA_sh + 4 * j);
+                        v[4 * j + 0] = fmaf(lsign, __fmul_rn(tr[0], a4.x), v[4 * j + 0]);
+                        v[4 * j + 1] = fmaf(lsign, __fmul_rn(tr[0], a4.y), v[4 * j + 1]);
+                        v[4 * j + 2] = fmaf(lsign, __fmul_rn(tr[0], a4.z), v[4 * j + 2]);
+                        v[4 * j + 3] = fmaf(lsign, __fmul_rn(tr[0], a4.w), v[4 * j + 3]);
+                    }
+                } else if (a_staged) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 a4 = ap[j];
-                            pert[4 * j + 0] = fmaf(tr[r], a4.x, pert[4 * j + 0]);
-                            pert[4 * j + 1] = fmaf(tr[r], a4.y, pert[4 * j + 1]);
-                            pert[4 * j + 2] = fmaf(tr[r], a4.z, pert[4 * j + 2]);
-                            pert[4 * j + 3] = fmaf(tr[r], a4.w, pert[4 * j + 3]);
+                    for (int j = 0; j < 8; ++j) {
+                        float4 pert = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        for (int r = 0; r < p.rank; ++r) {
+                            const float trr = r == 0 ? tr[0] : (r == 1 ? tr[1] : (r == 2 ? tr[2] : tr[3]));
+                            const float4 a4 = *reinterpret_cast<const float4*>(loraA_sh + r * 32 + 4 * j);
+                            pert.x = fmaf(trr, a4.x, pert.x);
+                            pert.y = fmaf(trr, a4.y, pert.y);
+                            pert.z = fmaf(trr, a4.z, pert.z);
+                            pert.w = fmaf(trr, a4.w, pert.w);
                         }
-                    } else {
-                        const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank + r;
+                        v[4 * j + 0] = fmaf(lsign, pert.x, v[4 * j + 0]);
+                        v[4 * j + 1] = fmaf(lsign, pert.y, v[4 * j + 1]);
+                        v[4 * j + 2] = fmaf(lsign, pert.z, v[4 * j + 2]);
+                        v[4 * j + 3] = fmaf(lsign, pert.w, v[4 * j + 3]);
+                    }
+                } else {
+                    const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * p.rank;
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) pert[j] = fmaf(tr[r], static_cast<float>(Ap[static_cast<size_t>(j) * p.rank]), pert[j]);
+                    for (int j = 0; j < 32; ++j) {
+                        if (col0 + j < p.n) {
+                            float pert = 0.0f;
+#pragma unroll
+                            for (int r = 0; r < 4; ++r)
+                                if (r < p.rank) pert = fmaf(tr[r], static_cast<float>(Ap[static_cast<size_t>(j) * p.rank + r]), pert);
+                            v[j] = fmaf(lsign, pert, v[j]);
+                        }
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = fmaf(lsign, pert[j], v[j]);
             }
 
             if constexpr (EPI == EPI_F32) {
-                if (args.use_tma_store) {
+                if (args.use_tma_store == 3) {
+                    // timing aid: the tile is computed but not written
+                    if (v[0] == 123456.789f && v[31] == 9.87654321f) p.d[0] = v[5];
+                } else if (args.use_tma_store) {
                     // stage the 32x32 box in 128B-swizzled shared memory, then one TMA store (clips at M and N)
                     if (it > 0) {
                         if (lane == 0) bulk_wait_read<0>();
@@ -411,7 +478,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
+                    if (lane == 0 && args.use_tma_store == 1) {
                         tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
                         bulk_commit();
                     }
@@ -429,12 +496,32 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
             } else {
                 // GELU -> int8 (reference: src/cuda_kernels.cu:3178-3194; tanh-form GELU, clip to +-127)
-                int qv[32];
+                if (col0 + 32 > p.n) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) qv[j] = (col0 + j < p.n) ? gelu_q8(v[j], p.act_scale) : 0;
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j >= p.n) v[j] = 0.0f;  // gelu(0) = 0
+                }
+                float tb[32];  // rounded values still biased by 1.5 * 2^23: the low byte of the bit pattern is the int8
+                float am[2] = {0.0f, 0.0f};  // max |value| of the two 16-element scale blocks
                 int w[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) w[j] = pack4_i8(qv[4 * j], qv[4 * j + 1], qv[4 * j + 2], qv[4 * j + 3]);
+                for (int g = 0; g < 8; ++g) {
+                    bool fast_ok = true;
+                    float fc[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) tb[4 * g + e] = gelu_q8_fast(v[4 * g + e], p.act_scale, fast_ok, fc[e]);
+                    if (!fast_ok) {  // some value too close to a rounding boundary: redo the four with the tanhf form
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int qe = gelu_q8_exact(v[4 * g + e], p.act_scale);
+                            tb[4 * g + e] = __int_as_float(qe + kRoundBiasBits);
+                            fc[e] = static_cast<float>(qe);
+                        }
+                    }
+                    am[g >> 2] = fmaxf(fmaxf(am[g >> 2], fmaxf(fabsf(fc[0]), fabsf(fc[1]))), fmaxf(fabsf(fc[2]), fabsf(fc[3])));
+                    w[g] = static_cast<int>(__byte_perm(__byte_perm(__float_as_uint(tb[4 * g]), __float_as_uint(tb[4 * g + 1]), 0x0040),
+                                                        __byte_perm(__float_as_uint(tb[4 * g + 2]), __float_as_uint(tb[4 * g + 3]), 0x0040), 0x5410));
+                }
                 if (row_ok && p.d_i8 != nullptr) {
                     int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
                     if (((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && col0 + 32 <= p.n) {
@@ -448,12 +535,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
                 if constexpr (EPI == EPI_GELU_FP4) {
                     if (row_ok) {
-                        int qa[16], qb[16];
+                        // code(v) = table[amax][v + 128] and scale byte = table_sf[amax], addressed straight from the biased
+                        // bit patterns: bits(t) - kRoundBiasBits is the integer.
+                        const uint32_t lut_s = smem_base + kSmemEpi;
+                        const uint32_t kBias = static_cast<uint32_t>(kRoundBiasBits);
+                        const uint32_t row_c = lut_s + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
+                        const uint32_t sf_c = lut_s + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
+                        uint32_t sfv[2], codes[4];
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) { qa[j] = qv[j]; qb[j] = qv[16 + j]; }
-                        uint32_t s0, s1, lo0, hi0, lo1, hi1;
-                        quant_block16_lut(qa, args.lut, s0, lo0, hi0);
-                        quant_block16_lut(qb, args.lut, s1, lo1, hi1);
+                        for (int blk = 0; blk < 2; ++blk) {
+                            const uint32_t ab = __float_as_uint(am[blk] + kRoundBias);
+                            sfv[blk] = lds_u8(ab + sf_c);
+                            const uint32_t rowbase = ab * static_cast<uint32_t>(kQuantLutSignedStride) + row_c;
+                            uint32_t lo = 0, hi = 0;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                lo |= lds_u8(__float_as_uint(tb[16 * blk + e]) + rowbase) << (4 * e);
+                                hi |= lds_u8(__float_as_uint(tb[16 * blk + 8 + e]) + rowbase) << (4 * e);
+                            }
+                            codes[2 * blk] = lo;
+                            codes[2 * blk + 1] = hi;
+                        }
+                        const uint32_t s0 = sfv[0], s1 = sfv[1], lo0 = codes[0], hi0 = codes[1], lo1 = codes[2], hi1 = codes[3];
                         *reinterpret_cast<uint4*>(p.d_codes + (static_cast<size_t>(row) * p.n + col0) / 2) = make_uint4(lo0, hi0, lo1, hi1);
                         const int kb = col0 >> 4;
                         *reinterpret_cast<uint16_t*>(p.d_sf + sf_offset(static_cast<int>(row), kb, sf_k_atoms(p.n))) =
@@ -578,11 +681,12 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
         if (args.lut == nullptr) return BNF4_ERR_CUDA;
     }
     args.use_tma_store = 0;
+    args.timing_aid = g_gemm_allow_tma_store >> 2;
     if (p.epilogue == EPI_F32 && (reinterpret_cast<uintptr_t>(p.d) & 15) == 0 && (p.ldd % 4) == 0 && p.ldd >= p.n) {
         rc = make_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.d, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.m),
                          static_cast<uint64_t>(p.ldd) * 4, 32, 32, "D");
         if (rc) return rc;
-        args.use_tma_store = g_gemm_allow_tma_store ? 1 : 0;
+        args.use_tma_store = g_gemm_allow_tma_store & 3;  // 0 direct stores, 1 TMA stores; 2 / 3 are timing aids (no output written)
     } else {
         md = ma;  // unused
     }

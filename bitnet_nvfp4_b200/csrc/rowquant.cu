@@ -35,8 +35,10 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
     if (row >= p.rows) return;
 
     const int nblk = p.cols_out >> 4;
-    const int member = p.rows_per_member > 0 ? static_cast<int>(row / p.rows_per_member) : 0;
-    const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row % p.rows_per_member) : static_cast<int>(row);
+    // rows fit 31 bits (p.rows is an int): one 32-bit division instead of a 64-bit division and remainder
+    const unsigned urow = static_cast<unsigned>(row);
+    const int member = p.rows_per_member > 0 ? static_cast<int>(urow / static_cast<unsigned>(p.rows_per_member)) : 0;
+    const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(urow - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
     const int pair = member >> 1;
     const float ns = p.rows_per_member > 0 ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
 
@@ -71,7 +73,7 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
                 for (int e = 0; e < 16; ++e) vals[e] = (k0 + e < p.cols_in) ? static_cast<int>(src[k0 + e]) : 0;
             }
         } else if constexpr (FE == FE_EMBED_DENSE || FE == FE_EMBED_LOWRANK) {
-            const int trow = p.row_mod > 0 ? static_cast<int>(row % p.row_mod) : static_cast<int>(row);
+            const int trow = p.row_mod > 0 ? static_cast<int>(urow % static_cast<unsigned>(p.row_mod)) : static_cast<int>(row);
             const int tok = static_cast<int>(p.tokens[static_cast<size_t>(trow) * p.token_stride]);
             const int8_t* e_w = p.emb_w + static_cast<size_t>(tok) * p.cols_in;
 #pragma unroll

@@ -1,6 +1,6 @@
 """Single-kernel micro-benchmarks of libbnf4 (CUDA-event timing; also the small cases used for ncu captures).
 
-    python -m bitnet_nvfp4_b200.microbench gemm  [--m 65536] [--variants plain,lora,direct,gelu,gelufp4] [--iters 5]
+    python -m bitnet_nvfp4_b200.microbench gemm  [--m 65536] [--variants plain,lora,direct,gelu,gelufp4,aid<N>] [--iters 5]
     python -m bitnet_nvfp4_b200.microbench efla  [--seqs 2048] [--iters 3]
     python -m bitnet_nvfp4_b200.microbench rowquant [--rows 65536] [--iters 5]
     python -m bitnet_nvfp4_b200.microbench sweep            # perturbed-GEMM sweep M x (K = N) with FP4 utilisation
@@ -77,6 +77,10 @@ def bench_gemm(m, variants, iters):
                 lib.load().bnf4_set_option(b"gemm_tma_store", 0)
                 H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32)
                 lib.load().bnf4_set_option(b"gemm_tma_store", 1)
+            elif v.startswith("aid"):  # aid<store mode + 4 * timing-aid bits>, e.g. aid15 = no A/B loads, no store
+                lib.load().bnf4_set_option(b"gemm_tma_store", int(v[3:]))
+                H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32)
+                lib.load().bnf4_set_option(b"gemm_tma_store", 1)
             elif v == "lora":
                 H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32, **lora)
             elif v == "gelu":
@@ -88,7 +92,7 @@ def bench_gemm(m, variants, iters):
                 raise SystemExit(f"unknown variant {v}")
 
         ms = _time(run, iters)
-        out_bytes = m * n * (4 if v in ("plain", "direct", "lora") else (1 if v == "gelu" else 0.5625))
+        out_bytes = m * n * (4 if v in ("plain", "direct", "lora") or v.startswith("aid") else (1 if v == "gelu" else 0.5625))
         print(f"gemm {v:8s} M={m} N={n} K={k}: {ms:.4f} ms  {2 * m * n * k / ms / 1e9:8.1f} TFLOP/s  output {out_bytes / ms / 1e6:7.1f} GB/s")
     assert H.device_error() == 0
 
