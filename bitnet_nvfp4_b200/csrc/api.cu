@@ -62,6 +62,10 @@ int bnf4_set_option(const char* name, int value) {
         g_efla_cols_per_lane = value;
         return BNF4_OK;
     }
+    if (name && std::strcmp(name, "efla_mma") == 0) {
+        g_efla_mma = value ? 1 : 0;
+        return BNF4_OK;
+    }
     return set_error(BNF4_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
 }
 

@@ -229,9 +229,222 @@ __global__ void __launch_bounds__(kScanWarps * 32, NCOL == 1 ? 4 : 2) efla_scan6
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Tensor-core form of the scan kernel (head_dim 64, fp16-rounded state, zero initial state).
+//
+// The state is exactly representable in fp16 (it is rounded to fp16 every token), so it lives in registers ONLY as
+// packed halves, laid out as the A fragments of mma.sync.m16n8k16 with A[n][d] = S[d,n]. Per token and per 16 x 16
+// tile of the state:
+//   1. update:   S32 = S16 * I + (alpha k) diff^T      two m16n8k8 MMAs against an 8 x 8 identity; the rank-1 term,
+//                computed with packed fp32 multiplies, enters as the fp32 accumulator C, so the tensor core performs the
+//                fp16 -> fp32 widening and the addition in one step;
+//   2. rounding: S16' = fp16_rn(S32)                   packed conversions, which directly produce the next A fragment;
+//   3. readout:  D += S16' * B                          one m16n8k16 MMA with B[d][j] = { q^ hi, q^ mid 2^11, k' hi,
+//                k' mid 2^11, 0, 0, 0, 0 }: columns 0-1 give y_t = S'^T q^_t, columns 2-3 give k'.S' of the NEXT token.
+// x = hi + mid is the two-term fp16 split of an fp32 value (hi = fp16(x), mid = fp16((x - hi) 2^11) / 2^11, error
+// <= 2^-24 |x|), so every product is exact in fp32. Compared with the multiply-add kernels the deviations are the
+// order/rounding of fp32 accumulation inside the tensor core and one extra fp32 rounding of (alpha k)*diff before
+// the addition; both are far below the fp16 rounding of the state that follows.
+//
+// Fragment coordinates (g = lane / 4, tq = lane % 4): for n-tile mt and d-tile ks the lane holds S[d][n] for
+// n = 16 mt + g + {0, 8} and d = 16 ks + 2 tq + {0, 1, 8, 9}.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int scan_perm(int d) {
+    // position of element d in the per-lane-contiguous order [tq][ks][{0, 1, 8, 9}]
+    const int ks = d >> 4, r = d & 15;
+    return ((r & 7) >> 1) * 16 + ks * 4 + ((r & 1) | ((r >> 3) << 1));
+}
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// d (in place) += a (16 x 8) * b (8 x 8)
+__device__ __forceinline__ void mma_f16_1688(float& d0, float& d1, float& d2, float& d3, uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
+        : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3)
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 hv = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&hv);
+}
+
+constexpr int kScanRing = 4;             // tokens of q/k/v/beta in flight per warp
+constexpr int kScanSlotFloats = 3 * 64 + 4;  // q[64], k[64], v[64], beta (+ padding to 16 bytes)
+constexpr int kScanMmaCtasPerSm = 3;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan64_mma_kernel(const EflaParams p) {
+    constexpr int HD = 64;
+    __shared__ __align__(16) float in_sh[kScanWarps][kScanRing][kScanSlotFloats];  // ring of raw inputs per warp
+    __shared__ __align__(16) float a_sh[kScanWarps][2][HD];                        // alpha * k of a token, permuted
+    __shared__ __align__(16) __half b_sh[kScanWarps][2][4][HD];                    // q^ hi, q^ mid, k hi, k mid, permuted
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long unit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;  // (sequence, head)
+    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
+    const long long seq = unit / p.heads;
+    const int h = static_cast<int>(unit - seq * p.heads);
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
+    const int g = lane >> 2, tq = lane & 3;
+
+    uint32_t Sh[4][4][4];  // [mt][ks][i]: the A fragment (i = 0: n = g, d pair 2tq; 1: n = g + 8; 2: n = g, d pair 2tq + 8; 3: n = g + 8)
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
+    // 8 x 8 identity as a B fragment: this lane holds rows 2tq, 2tq + 1 of column g
+    const uint32_t ident = pack_half2(2 * tq == g ? 1.0f : 0.0f, 2 * tq + 1 == g ? 1.0f : 0.0f);
+
+    const size_t row0 = static_cast<size_t>(seq) * p.T;
+    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
+    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
+    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
+    const float* bb = p.beta_raw + row0 * p.ld_beta;
+    float* ob = p.out + row0 * p.ld_out + h * HD;
+    const int po0 = scan_perm(lane), po1 = scan_perm(lane + 32);
+
+    // asynchronous copy of one token's inputs into its ring slot (every lane commits a group, empty or not)
+    auto issue = [&](int tok) {
+        if (tok < p.T) {
+            float* slot = in_sh[warp][tok % kScanRing];
+            const size_t o = static_cast<size_t>(tok) * p.ld_qkv;
+            const int l16 = lane & 15;
+            cp_async16(slot + (lane < 16 ? 0 : HD) + 4 * l16, (lane < 16 ? qb : kb) + o + 4 * l16);
+            if (lane < 16) cp_async16(slot + 2 * HD + 4 * l16, vb + o + 4 * l16);
+            else if (lane == 16) cp_async4(slot + 3 * HD, bb + static_cast<size_t>(tok) * p.ld_beta);
+        }
+        cp_async_commit();
+    };
+
+    // per-token vectors from a ring slot: the lane prepares elements d = lane and lane + 32
+    auto prepare = [&](const float* slot, int buf) {
+        const float rq0 = slot[lane], rq1 = slot[lane + 32], rk0 = slot[HD + lane], rk1 = slot[HD + lane + 32], rbr = slot[3 * HD];
+        const float qss = warp_sum_f(fmaf(rq0, rq0, rq1 * rq1));
+        const float kss = warp_sum_f(fmaf(rk0, rk0, rk1 * rk1));
+        const float q_inv = rsqrtf(qss + p.eps);
+        const float lambda = kss < p.eps ? p.eps : kss;
+        const float beta = sigmoidf_dev(rbr + beta_bias);
+        float alpha, kscale = 1.0f;
+        if (p.method == 0) { alpha = beta; kscale = rsqrtf(lambda + p.eps); }
+        else alpha = -expm1f(-(beta * lambda)) / (lambda + p.eps);
+        const float kn0 = rk0 * kscale, kn1 = rk1 * kscale, qn0 = rq0 * q_inv, qn1 = rq1 * q_inv;
+        a_sh[warp][buf][po0] = alpha * kn0;
+        a_sh[warp][buf][po1] = alpha * kn1;
+        // two-term fp16 splits with packed conversions
+        const __half2 qh = __floats2half2_rn(qn0, qn1), kh = __floats2half2_rn(kn0, kn1);
+        const float2 qhf = __half22float2(qh), khf = __half22float2(kh);
+        const __half2 qm = __floats2half2_rn((qn0 - qhf.x) * 2048.0f, (qn1 - qhf.y) * 2048.0f);
+        const __half2 km = __floats2half2_rn((kn0 - khf.x) * 2048.0f, (kn1 - khf.y) * 2048.0f);
+        b_sh[warp][buf][0][po0] = __low2half(qh);
+        b_sh[warp][buf][0][po1] = __high2half(qh);
+        b_sh[warp][buf][1][po0] = __low2half(qm);
+        b_sh[warp][buf][1][po1] = __high2half(qm);
+        b_sh[warp][buf][2][po0] = __low2half(kh);
+        b_sh[warp][buf][2][po1] = __high2half(kh);
+        b_sh[warp][buf][3][po0] = __low2half(km);
+        b_sh[warp][buf][3][po1] = __high2half(km);
+    };
+
+    float kS[4][2];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) kS[mt][0] = kS[mt][1] = 0.0f;  // zero initial state
+#pragma unroll
+    for (int i = 0; i < kScanRing - 1; ++i) issue(i);
+    cp_async_wait<kScanRing - 2>();  // token 0 has landed
+    __syncwarp();
+    prepare(in_sh[warp][0], 0);
+
+    for (int t = 0; t < p.T; ++t) {
+        const int cur = t & 1, nxt = cur ^ 1;
+        __syncwarp();  // everyone is done with ring slot (t - 1) % kScanRing and with buffer nxt (token t - 1)
+        issue(t + kScanRing - 1);
+        cp_async_wait<kScanRing - 2>();  // tokens <= t + 1 have landed
+        __syncwarp();
+        const float* vslot = in_sh[warp][t % kScanRing] + 2 * HD;
+        float2 diff2[4][2];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float d = vslot[16 * mt + 8 * hh + g] - kS[mt][hh];
+                diff2[mt][hh] = make_float2(d, d);
+            }
+        if (t + 1 < p.T) prepare(in_sh[warp][(t + 1) % kScanRing], nxt);
+        __syncwarp();
+
+        // per d-tile operands: alpha*k pairs (update) and the B fragment: columns 0,1 = q^ of token t, 2,3 = k of token t+1
+        const float* a_src = &a_sh[warp][cur][tq * 16];
+        const __half* b_src = &b_sh[warp][g < 2 ? cur : nxt][g & 3][tq * 16];
+        float D[4][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) D[mt][0] = D[mt][1] = D[mt][2] = D[mt][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const float4 av = *reinterpret_cast<const float4*>(a_src + ks * 4);
+            uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
+            if (g >= 4) bf = make_uint2(0u, 0u);
+            const float2 alo = make_float2(av.x, av.y), ahi = make_float2(av.z, av.w);
+            // the four n-tiles are independent: issue each stage for all of them so that MMA latency overlaps
+            float cs[4][8];
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                // rank-1 term for the lane's elements: (d pair) x (n = g, g + 8)
+                const float2 c0 = __fmul2_rn(alo, diff2[mt][0]), c1 = __fmul2_rn(alo, diff2[mt][1]);
+                const float2 c2 = __fmul2_rn(ahi, diff2[mt][0]), c3 = __fmul2_rn(ahi, diff2[mt][1]);
+                cs[mt][0] = c0.x; cs[mt][1] = c0.y; cs[mt][2] = c1.x; cs[mt][3] = c1.y;
+                cs[mt][4] = c2.x; cs[mt][5] = c2.y; cs[mt][6] = c3.x; cs[mt][7] = c3.y;
+            }
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                mma_f16_1688(cs[mt][0], cs[mt][1], cs[mt][2], cs[mt][3], Sh[mt][ks][0], Sh[mt][ks][1], ident);  // d pair 2tq
+                mma_f16_1688(cs[mt][4], cs[mt][5], cs[mt][6], cs[mt][7], Sh[mt][ks][2], Sh[mt][ks][3], ident);  // d pair 2tq + 8
+            }
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                Sh[mt][ks][0] = pack_half2(cs[mt][0], cs[mt][1]);  // the state is rounded to fp16 every token
+                Sh[mt][ks][1] = pack_half2(cs[mt][2], cs[mt][3]);
+                Sh[mt][ks][2] = pack_half2(cs[mt][4], cs[mt][5]);
+                Sh[mt][ks][3] = pack_half2(cs[mt][6], cs[mt][7]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+                mma_f16_16816(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
+        }
+
+        // column pair of this lane: tq = 0 -> (q^ hi, q^ mid): y of token t;  tq = 1 -> (k hi, k mid): k.S of token t + 1
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const float r0 = fmaf(D[mt][1], 1.0f / 2048.0f, D[mt][0]);  // n = 16 mt + g
+            const float r1 = fmaf(D[mt][3], 1.0f / 2048.0f, D[mt][2]);  // n = 16 mt + g + 8
+            if (tq == 0) {
+                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + g] = r0;
+                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + 8 + g] = r1;
+            }
+            kS[mt][0] = __shfl_sync(0xffffffffu, r0, (lane & ~3) | 1);
+            kS[mt][1] = __shfl_sync(0xffffffffu, r1, (lane & ~3) | 1);
+        }
+    }
+    cp_async_wait<0>();
+}
+
 }  // namespace
 
 int g_efla_cols_per_lane = 2;  // host toggle (option "efla_cols_per_lane")
+int g_efla_mma = 1;            // host toggle (option "efla_mma"): 1 = tensor-core scan kernel, 0 = multiply-add scan kernel
 
 int efla_launch(const EflaParams& p, cudaStream_t stream) {
     if (p.seqs <= 0 || p.T <= 0) return BNF4_OK;
@@ -240,6 +453,13 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
     const int hd = p.hidden / p.heads;
     if (p.state == nullptr && p.state_fp16 && hd == 64 && !p.force_generic) {
         const long long units = p.seqs * static_cast<long long>(p.heads);
+        const bool aligned = ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0 &&
+                             (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
+        if (g_efla_mma && aligned) {
+            const long long ctas = (units + kScanWarps - 1) / kScanWarps;
+            efla_scan64_mma_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
+            return check_launch("efla_scan64_mma_kernel");
+        }
         if (g_efla_cols_per_lane == 2) {
             const long long ctas = (units + kScanWarps - 1) / kScanWarps;
             efla_scan64_kernel<2><<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);

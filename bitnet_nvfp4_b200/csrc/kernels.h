@@ -49,6 +49,7 @@ extern int g_gemm_allow_tma_store;
 using EflaParams = bnf4_efla_desc;
 int efla_launch(const EflaParams& p, cudaStream_t stream);
 extern int g_efla_cols_per_lane;
+extern int g_efla_mma;
 
 void count_launch();
 

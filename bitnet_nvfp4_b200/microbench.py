@@ -1,7 +1,7 @@
 """Single-kernel micro-benchmarks of libbnf4 (CUDA-event timing; also the small cases used for ncu captures).
 
     python -m bitnet_nvfp4_b200.microbench gemm  [--m 65536] [--variants plain,lora,direct,gelu,gelufp4,aid<N>] [--iters 5]
-    python -m bitnet_nvfp4_b200.microbench efla  [--seqs 2048] [--iters 3]
+    python -m bitnet_nvfp4_b200.microbench efla  [--seqs 2048] [--iters 3] [--mma 0|1]
     python -m bitnet_nvfp4_b200.microbench rowquant [--rows 65536] [--iters 5]
     python -m bitnet_nvfp4_b200.microbench sweep            # perturbed-GEMM sweep M x (K = N) with FP4 utilisation
 
@@ -118,8 +118,9 @@ def bench_sweep(iters):
     assert H.device_error() == 0
 
 
-def bench_efla(seqs, iters):
+def bench_efla(seqs, iters, mma=1):
     T, hidden, heads, fc = 128, 512, 8, 1568
+    lib.load().bnf4_set_option(b"efla_mma", mma)
     qkv = torch.randn(seqs * T, fc, device="cuda") * 0.3
     out = torch.empty(seqs * T, hidden, device="cuda")
     bb = torch.full((seqs // 32 + 1,), -2.0, device="cuda")
@@ -131,7 +132,7 @@ def bench_efla(seqs, iters):
 
     ms = _time(run, iters, warm=2)
     rows = seqs * T
-    print(f"efla_scan seqs={seqs} T={T} heads={heads}x64: {ms:.4f} ms  {rows * ((3 * hidden + 1) * 4 + 4 * hidden) / ms / 1e6:7.1f} GB/s algorithmic  "
+    print(f"efla_scan ({'tensor-core' if mma else 'multiply-add'} kernel) seqs={seqs} T={T} heads={heads}x64: {ms:.4f} ms  {rows * ((3 * hidden + 1) * 4 + 4 * hidden) / ms / 1e6:7.1f} GB/s algorithmic  "
           f"{rows * heads / ms / 1e3:7.1f} M head-steps/s")
 
 
@@ -160,13 +161,14 @@ def main():
     ap.add_argument("--seqs", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--mma", type=int, default=1, help="efla: 1 = tensor-core scan kernel, 0 = multiply-add scan kernel")
     a = ap.parse_args()
     if a.what == "gemm":
         bench_gemm(a.m, a.variants.split(","), a.iters)
     elif a.what == "sweep":
         bench_sweep(a.iters)
     elif a.what == "efla":
-        bench_efla(a.seqs, a.iters)
+        bench_efla(a.seqs, a.iters, a.mma)
     else:
         bench_rowquant(a.rows, a.iters)
 

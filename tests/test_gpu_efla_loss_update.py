@@ -101,6 +101,33 @@ def test_efla_scan_whole_sequence(H, hidden, heads, seqs, T, force_generic):
     assert np.abs(got - ref).max() <= 3e-3 * np.abs(ref).max()
 
 
+def test_efla_scan_tensor_core_kernel_agrees_with_multiply_add_kernel(H):
+    """The two register-state scan kernels (tensor-core and packed multiply-add) implement the same recurrence; they differ
+    in fp32 summation order only, which shows up as rare one-ulp flips of the fp16 state. Both must sit within the
+    oracle tolerance of each other, and the bulk of the outputs must agree to fp32 summation accuracy."""
+    import torch
+    from bitnet_nvfp4_b200 import lib
+    rng = np.random.default_rng(99)
+    hidden, heads, seqs, T = 512, 8, 16, 128
+    fc = (3 * hidden + 1 + 31) & ~31
+    qd = dev(make_qkv(rng, seqs * T, hidden, fc, 0.3))
+    outs = []
+    try:
+        for mma in (1, 0):
+            assert lib.load().bnf4_set_option(b"efla_mma", mma) == 0
+            out = torch.empty((seqs * T, hidden), dtype=torch.float32, device="cuda")
+            H.efla_scan(state=None, state_fp16=1, q=qd, k=qd[:, hidden:], v=qd[:, 2 * hidden:], beta_raw=qd[:, 3 * hidden:], ld_qkv=fc,
+                        ld_beta=fc, beta_bias=-2.0, seqs_per_bias=1, hidden=hidden, heads=heads, seqs=seqs, T=T, method=1, eps=1e-6,
+                        out=out, ld_out=hidden)
+            outs.append(out.cpu().numpy())
+    finally:
+        lib.load().bnf4_set_option(b"efla_mma", 1)
+    a, b = outs
+    scale = np.abs(b).max()
+    assert np.abs(a - b).max() <= 3e-3 * scale
+    assert np.median(np.abs(a - b)) <= 1e-5 * scale
+
+
 # ---------------------------------------------------------------------------------------------- cross entropy
 def test_cross_entropy_step_api(H):
     import torch
