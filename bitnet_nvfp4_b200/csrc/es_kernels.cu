@@ -108,6 +108,86 @@ __global__ void __launch_bounds__(256) ce_population_kernel(const float* __restr
     }
 }
 
+// Streaming form of the same reduction for 16-byte aligned rows and vocab % 4 == 0: lane l owns the float4 groups
+// l, l + 32, ... of a row (NV4 groups), the member's bias and noise stay in registers for all rows, and RPI rows are in
+// flight per warp so that the load latency of one row hides behind the reductions of the others. The warps walk the
+// rows in the same order and add the row losses in the same order as ce_population_kernel.
+template <int NV4, int RPI>
+__global__ void __launch_bounds__(256) ce_population_vec_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                                                const int8_t* __restrict__ bias_noise, float sigma,
+                                                                const uint8_t* __restrict__ targets, int vocab, int rows_per_member,
+                                                                float* __restrict__ partial) {
+    __shared__ float part[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int member = blockIdx.y, chunk = blockIdx.x;
+    const int per = (rows_per_member + kCeChunks - 1) / kCeChunks;
+    const int r0 = chunk * per, r1 = min(rows_per_member, r0 + per);
+    const float bns = (member & 1) ? -sigma : sigma;
+    const int groups = vocab >> 2;
+    float4 bv[NV4], nv[NV4];
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) {
+        const int gi = lane + 32 * j;
+        bv[j] = nv[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (gi < groups) {
+            if (bias != nullptr) bv[j] = *reinterpret_cast<const float4*>(bias + 4 * gi);
+            if (bias_noise != nullptr) {
+                const char4 c = *reinterpret_cast<const char4*>(bias_noise + static_cast<size_t>(member >> 1) * vocab + 4 * gi);
+                nv[j] = make_float4(static_cast<float>(c.x), static_cast<float>(c.y), static_cast<float>(c.z), static_cast<float>(c.w));
+            }
+        }
+    }
+    float acc = 0.0f;
+    for (int rb = r0 + warp; rb < r1; rb += 8 * RPI) {
+        float4 x[RPI][NV4];
+        int y[RPI];
+#pragma unroll
+        for (int i = 0; i < RPI; ++i) {
+            const int r = rb + 8 * i;
+            y[i] = r < r1 ? static_cast<int>(targets[r]) : 0;
+            const float* lg = logits + (static_cast<size_t>(member) * rows_per_member + min(r, r1 - 1)) * ld;
+#pragma unroll
+            for (int j = 0; j < NV4; ++j) {
+                const int gi = lane + 32 * j;
+                x[i][j] = gi < groups ? __ldcs(reinterpret_cast<const float4*>(lg) + gi) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < RPI; ++i) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < NV4; ++j) {
+                if (lane + 32 * j < groups) {  // (x + bias) + bns * noise, like the scalar kernel (zero bias / noise when absent)
+                    x[i][j].x = fmaf(bns, nv[j].x, x[i][j].x + bv[j].x);
+                    x[i][j].y = fmaf(bns, nv[j].y, x[i][j].y + bv[j].y);
+                    x[i][j].z = fmaf(bns, nv[j].z, x[i][j].z + bv[j].z);
+                    x[i][j].w = fmaf(bns, nv[j].w, x[i][j].w + bv[j].w);
+                }
+                mx = fmaxf(fmaxf(mx, fmaxf(x[i][j].x, x[i][j].y)), fmaxf(x[i][j].z, x[i][j].w));
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NV4; ++j) sum += (expf(x[i][j].x - mx) + expf(x[i][j].y - mx)) + (expf(x[i][j].z - mx) + expf(x[i][j].w - mx));
+            sum = warp_sum_f(sum);
+            // the target's logit is re-read (one broadcast load per row) and perturbed with the same two operations
+            const int r = min(rb + 8 * i, r1 - 1);
+            float vy = logits[(static_cast<size_t>(member) * rows_per_member + r) * ld + y[i]];
+            if (bias != nullptr) vy += bias[y[i]];
+            if (bias_noise != nullptr) vy = fmaf(bns, static_cast<float>(bias_noise[static_cast<size_t>(member >> 1) * vocab + y[i]]), vy);
+            if (rb + 8 * i < r1) acc += -(vy - mx - logf(sum + 1e-9f));
+        }
+    }
+    if (lane == 0) part[warp] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < 8; ++w) t += part[w];
+        partial[member * kCeChunks + chunk] = t;
+    }
+}
+
 __global__ void ce_finalize_kernel(const float* __restrict__ partial, int members, int rows_per_member, float* __restrict__ loss_mean) {
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     if (m >= members) return;
@@ -375,7 +455,19 @@ int bnf4_cross_entropy_population(const float* logits, int ld, const float* bias
     if (!logits || !targets || !partial || !loss_mean) return set_error(BNF4_ERR_INVALID, "cross_entropy_population: null pointer");
     if (vocab <= 0 || vocab > 32 * kCeMaxPerLane) return set_error(BNF4_ERR_INVALID, "cross_entropy_population: vocab=%d", vocab);
     if (members > 65535) return set_error(BNF4_ERR_INVALID, "cross_entropy_population: at most 65535 members per call");
-    ce_population_kernel<<<dim3(kCeChunks, members), 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
+    const dim3 grid(kCeChunks, members);
+    const bool vec = (vocab % 4) == 0 && (ld % 4) == 0 && ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(bias_noise) & 3) == 0;
+    if (vec && vocab <= 128)
+        ce_population_vec_kernel<1, 4><<<grid, 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
+    else if (vec && vocab <= 256)
+        ce_population_vec_kernel<2, 4><<<grid, 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
+    else if (vec && vocab <= 512)
+        ce_population_vec_kernel<4, 2><<<grid, 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
+    else if (vec)
+        ce_population_vec_kernel<8, 1><<<grid, 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
+    else
+        ce_population_kernel<<<grid, 256, 0, S(stream)>>>(logits, ld, bias, bias_noise, sigma, targets, vocab, rows_per_member, partial);
     int rc = check_launch("ce_population_kernel");
     if (rc) return rc;
     ce_finalize_kernel<<<(members + 127) / 128, 128, 0, S(stream)>>>(partial, members, rows_per_member, loss_mean);
