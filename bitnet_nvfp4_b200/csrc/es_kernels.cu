@@ -254,13 +254,17 @@ __global__ void __launch_bounds__(256) z_dense_kernel(const float* __restrict__ 
     if (idx < n) Z[idx] = z;
 }
 
-// Z for the rank-r form. Block = 16 rows x 64 columns of one matrix, 256 threads, 4 columns per thread.
+// Rank-r form of Z: Z[i][j] = cscale * sum_p w_p * (sum_r A[p][i][r] * B[p][r][j]), pairs in ascending order with one fused
+// multiply-add per pair (reference: src/efla_lm_kernels.cu:1854-1890 applied to the factored noise). The inner sum is a
+// small integer, so it is formed exactly in fp32 from factors converted once while they are staged in shared memory.
+// Tile: 16 rows x 64 columns per CTA, 4 columns per thread, 32 pairs per shared-memory chunk.
+template <int RANK>
 __global__ void __launch_bounds__(256) z_lowrank_kernel(const float* __restrict__ pair_weights, const int8_t* __restrict__ A,
                                                         long long A_ps, const int8_t* __restrict__ B, long long B_ps, int pairs,
-                                                        int rows, int cols, int rank, float cscale, float* __restrict__ Z) {
+                                                        int rows, int cols, float cscale, float* __restrict__ Z) {
     constexpr int PC = 32;  // pairs per shared-memory chunk
-    __shared__ int8_t a_sh[PC][16][4];
-    __shared__ __align__(4) int8_t b_sh[PC][4][64];
+    __shared__ float a_sh[PC][16][RANK];
+    __shared__ __align__(16) float b_sh[PC][RANK][64];
     __shared__ float w_sh[PC];
     const int tr = threadIdx.x >> 4;        // 0..15 row in tile
     const int tc = (threadIdx.x & 15) * 4;  // column group in tile
@@ -269,33 +273,38 @@ __global__ void __launch_bounds__(256) z_lowrank_kernel(const float* __restrict_
     float z[4] = {0.f, 0.f, 0.f, 0.f};
     for (int p0 = 0; p0 < pairs; p0 += PC) {
         __syncthreads();
-        for (int e = threadIdx.x; e < PC * 16 * 4; e += 256) {
-            const int pp = e / 64, rr = (e / 4) % 16, r = e % 4;
-            const int gi = blockIdx.y * 16 + rr;
-            int8_t v = 0;
-            if (p0 + pp < pairs && gi < rows && r < rank) v = A[static_cast<size_t>(p0 + pp) * A_ps + static_cast<size_t>(gi) * rank + r];
-            a_sh[pp][rr][r] = v;
+        for (int e = threadIdx.x; e < PC * 16 * RANK; e += 256) {
+            const int pp = e / (16 * RANK), rem = e - pp * 16 * RANK;  // rem = row * RANK + r: contiguous in A
+            const int gi = blockIdx.y * 16 + rem / RANK;
+            float v = 0.0f;
+            if (p0 + pp < pairs && gi < rows) v = static_cast<float>(A[static_cast<size_t>(p0 + pp) * A_ps + static_cast<size_t>(blockIdx.y) * 16 * RANK + rem]);
+            (&a_sh[pp][0][0])[rem] = v;
         }
-        for (int e = threadIdx.x; e < PC * 4 * 64; e += 256) {
-            const int pp = e / 256, r = (e / 64) % 4, c = e % 64;
+        for (int e = threadIdx.x; e < PC * RANK * 64; e += 256) {
+            const int pp = e / (RANK * 64), rem = e - pp * RANK * 64, r = rem >> 6, c = rem & 63;
             const int gj = blockIdx.x * 64 + c;
-            int8_t v = 0;
-            if (p0 + pp < pairs && gj < cols && r < rank) v = B[static_cast<size_t>(p0 + pp) * B_ps + static_cast<size_t>(r) * cols + gj];
+            float v = 0.0f;
+            if (p0 + pp < pairs && gj < cols) v = static_cast<float>(B[static_cast<size_t>(p0 + pp) * B_ps + static_cast<size_t>(r) * cols + gj]);
             b_sh[pp][r][c] = v;
         }
         if (threadIdx.x < PC) w_sh[threadIdx.x] = (p0 + threadIdx.x < pairs) ? pair_weights[p0 + threadIdx.x] : 0.0f;
         __syncthreads();
         const int cnt = min(PC, pairs - p0);
+#pragma unroll 4
         for (int pp = 0; pp < cnt; ++pp) {
             const float w = w_sh[pp];
-            int e[4] = {0, 0, 0, 0};
-            for (int r = 0; r < rank; ++r) {
-                const int a = a_sh[pp][tr][r];
+            float e[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) e[c] += a * static_cast<int>(b_sh[pp][r][tc + c]);
+            for (int r = 0; r < RANK; ++r) {
+                const float a = a_sh[pp][tr][r];
+                const float4 b4 = *reinterpret_cast<const float4*>(&b_sh[pp][r][tc]);
+                e[0] = fmaf(a, b4.x, e[0]);  // exact: small integers
+                e[1] = fmaf(a, b4.y, e[1]);
+                e[2] = fmaf(a, b4.z, e[2]);
+                e[3] = fmaf(a, b4.w, e[3]);
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) z[c] = fmaf(w, static_cast<float>(e[c]), z[c]);
+            for (int c = 0; c < 4; ++c) z[c] = fmaf(w, e[c], z[c]);
         }
     }
     if (i < rows) {
@@ -523,7 +532,12 @@ int bnf4_compute_z_sumsq_lowrank(const float* pair_weights, const int8_t* A, lon
     if (!pair_weights || !A || !B || !Z || !sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: null pointer");
     if (rank < 1 || rank > 4) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: rank=%d outside [1,4]", rank);
     const dim3 grid((cols + 63) / 64, (rows + 15) / 16);
-    z_lowrank_kernel<<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, rank, cscale, Z);
+    switch (rank) {
+        case 1: z_lowrank_kernel<1><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
+        case 2: z_lowrank_kernel<2><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
+        case 3: z_lowrank_kernel<3><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
+        default: z_lowrank_kernel<4><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
+    }
     const int rc = check_launch("z_lowrank_kernel");
     if (rc) return rc;
     return sumsq_into(Z, rows * cols, sumsq, S(stream));

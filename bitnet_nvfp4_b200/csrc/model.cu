@@ -41,11 +41,14 @@ struct GenDesc {
     int transposed;   // store element (major, r) at r*n_major + major instead of major*rank + r
 };
 
-__global__ void gen_noise_kernel(const GenDesc* __restrict__ descs, const uint64_t* __restrict__ pair_seeds, int use_clt, int clt_k) {
-    const GenDesc d = descs[blockIdx.y];
-    const int pair = blockIdx.z;
+// block_map[b] = (descriptor << 20) | block within that descriptor: every launched block has work.
+__global__ void gen_noise_kernel(const GenDesc* __restrict__ descs, const uint32_t* __restrict__ block_map,
+                                 const uint64_t* __restrict__ pair_seeds, int use_clt, int clt_k) {
+    const uint32_t bm = block_map[blockIdx.x];
+    const GenDesc d = descs[bm >> 20];
+    const int pair = blockIdx.y;
     const long long n = static_cast<long long>(d.n_major) * d.rank;
-    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long idx = static_cast<long long>(bm & 0xfffffu) * blockDim.x + threadIdx.x;
     if (idx >= n) return;
     uint64_t seed = mix_u64(pair_seeds[pair], d.salt);
     if (d.factor != 0) seed = mix_u64(seed, d.factor);
@@ -94,8 +97,9 @@ struct Model {
     int8_t *embA, *embB, *A_win, *tB_win, *A_head, *tB_head, *pos_noise, *hb_noise, *bb_noise;
     std::vector<int8_t*> A_qkv, tB_qkv, A_ff1, tB_ff1, A_ff2, tB_ff2;
     GenDesc* gen_descs;
+    uint32_t* gen_block_map;
     int num_gen = 0;
-    int gen_max_n = 0;
+    int gen_blocks = 0;
     // wave buffers
     int8_t* x_q;
     uint8_t *a_h, *sf_h, *a_f, *sf_f;
@@ -348,7 +352,8 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     if (cfg->rank < 1 || cfg->rank > 4) return set_error(BNF4_ERR_INVALID, "model_create: rank=%d outside [1,4]", cfg->rank);
     if (cfg->sigma_shift < 0 || cfg->sigma_shift > 30) return set_error(BNF4_ERR_INVALID, "model_create: sigma_shift");
     if (cfg->max_pairs <= 0) return set_error(BNF4_ERR_INVALID, "model_create: max_pairs");
-    if (static_cast<long long>(cfg->hidden) * cfg->mlp_mult > 4096) return set_error(BNF4_ERR_INVALID, "model_create: mlp width above 4096");
+    if (cfg->hidden > 4096) return set_error(BNF4_ERR_INVALID, "model_create: hidden above 4096");
+    if (static_cast<long long>(cfg->hidden) * cfg->mlp_mult > 8192) return set_error(BNF4_ERR_INVALID, "model_create: mlp width above 8192");
 
     Model* m = new Model;
     m->cfg = *cfg;
@@ -423,9 +428,17 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     gd.push_back({m->hb_noise, V, kSaltHeadBias, 0, V, 1, 0});
     gd.push_back({m->bb_noise, L, kSaltBetaBias, 0, L, 1, 0});
     m->num_gen = static_cast<int>(gd.size());
-    for (const GenDesc& d : gd) m->gen_max_n = std::max(m->gen_max_n, d.n_major * d.rank);
+    std::vector<uint32_t> bmap;
+    for (size_t i = 0; i < gd.size(); ++i) {
+        const long long nb = (static_cast<long long>(gd[i].n_major) * gd[i].rank + 255) / 256;
+        if (nb > 0xfffff || i > 0xfff) { bnf4_model_destroy(m); return set_error(BNF4_ERR_INVALID, "model_create: noise table too large"); }
+        for (long long b = 0; b < nb; ++b) bmap.push_back(static_cast<uint32_t>(i << 20) | static_cast<uint32_t>(b));
+    }
+    m->gen_blocks = static_cast<int>(bmap.size());
     rc = m->alloc(&m->gen_descs, gd.size());
     if (!rc) rc = check_cuda(cudaMemcpy(m->gen_descs, gd.data(), gd.size() * sizeof(GenDesc), cudaMemcpyHostToDevice), "cudaMemcpy(gen_descs)");
+    if (!rc) rc = m->alloc(&m->gen_block_map, bmap.size());
+    if (!rc) rc = check_cuda(cudaMemcpy(m->gen_block_map, bmap.data(), bmap.size() * sizeof(uint32_t), cudaMemcpyHostToDevice), "cudaMemcpy(gen_block_map)");
     if (rc) { bnf4_model_destroy(m); return rc; }
     *handle = m;
     return BNF4_OK;
@@ -486,9 +499,9 @@ int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pai
     if (pairs > 65535) return set_error(BNF4_ERR_INVALID, "model_prepare_step: at most 65535 pairs");
     m.pairs_step = pairs;
     TRY(bnf4_fill_pair_seeds(seed, epoch, pairs, m.pair_seeds, stream));
-    const dim3 grid((m.gen_max_n + 255) / 256, m.num_gen, pairs);
+    const dim3 grid(m.gen_blocks, pairs);
     TimedScope ts(m, KC_GEN_NOISE, S(stream), 2);
-    gen_noise_kernel<<<grid, 256, 0, S(stream)>>>(m.gen_descs, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
+    gen_noise_kernel<<<grid, 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
     return check_launch("gen_noise_kernel");
 }
 

@@ -25,7 +25,8 @@ namespace bnf4 {
 
 namespace {
 
-constexpr int kMaxBlocksPerLane = 8;  // rows of up to 32*8*16 = 4096 columns
+constexpr int kMaxBlocksPerLane = 8;        // rows of up to 32*8*16 = 4096 columns ...
+constexpr int kMaxBlocksPerLaneInt8 = 16;  // ... and 8192 for plain int8 rows (weight matrices of wide MLPs)
 
 template <int FE, int NB>
 __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
@@ -262,7 +263,8 @@ template <int FE>
 int launch(const RowQuantParams& p, cudaStream_t stream) {
     if (p.rows <= 0 || p.cols_out <= 0) return BNF4_OK;
     if ((p.cols_out & 15) != 0) return set_error(BNF4_ERR_INVALID, "rowquant: cols_out=%d must be a multiple of 16", p.cols_out);
-    if (p.cols_out > 32 * 16 * kMaxBlocksPerLane) return set_error(BNF4_ERR_INVALID, "rowquant: cols_out=%d exceeds %d", p.cols_out, 32 * 16 * kMaxBlocksPerLane);
+    constexpr int max_cols = 32 * 16 * (FE == FE_INT8 ? kMaxBlocksPerLaneInt8 : kMaxBlocksPerLane);
+    if (p.cols_out > max_cols) return set_error(BNF4_ERR_INVALID, "rowquant: cols_out=%d exceeds %d", p.cols_out, max_cols);
     if (p.nvec > kMaxTVec) return set_error(BNF4_ERR_INVALID, "rowquant: nvec=%d exceeds %d", p.nvec, kMaxTVec);
     if (p.out_codes == nullptr || p.out_sf == nullptr) return set_error(BNF4_ERR_INVALID, "rowquant: null output");
     if ((reinterpret_cast<uintptr_t>(p.out_codes) & 7) || (reinterpret_cast<uintptr_t>(p.out_sf) & 3))
@@ -275,7 +277,10 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
     if (nblk <= 32) rowquant_kernel<FE, 1><<<ctas, warps * 32, 0, stream>>>(p, lut);
     else if (nblk <= 64) rowquant_kernel<FE, 2><<<ctas, warps * 32, 0, stream>>>(p, lut);
     else if (nblk <= 128) rowquant_kernel<FE, 4><<<ctas, warps * 32, 0, stream>>>(p, lut);
-    else rowquant_kernel<FE, 8><<<ctas, warps * 32, 0, stream>>>(p, lut);
+    else if (nblk <= 256) rowquant_kernel<FE, 8><<<ctas, warps * 32, 0, stream>>>(p, lut);
+    else {
+        if constexpr (FE == FE_INT8) rowquant_kernel<FE, 16><<<ctas, warps * 32, 0, stream>>>(p, lut);
+    }
     return check_launch("rowquant_kernel");
 }
 

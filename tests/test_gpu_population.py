@@ -40,6 +40,8 @@ def oracle_cfg(cfg):
     dict(hidden=128, layers=2, seq=32, batch=8, heads=1, rank=2, max_pairs=3, wave_members=2),
     dict(hidden=256, layers=1, seq=16, batch=8, heads=4, rank=4, max_pairs=2, wave_members=4),
     dict(hidden=512, layers=4, seq=128, batch=32, heads=8, rank=1, max_pairs=2, wave_members=4),
+    # widths of the scaled-up stress workload (hidden 2048, 32 heads of 64, MLP 8192, rank 4), one layer, short sequences
+    dict(hidden=2048, layers=1, mlp_mult=4, seq=16, batch=2, heads=32, rank=4, max_pairs=1, wave_members=2),
 ])
 def test_member_losses_match_oracle(cfg_kw):
     from bitnet_nvfp4_b200 import host
