@@ -18,6 +18,8 @@
 //   abs-mean norm              src/cuda_kernels.cu:2928-3031
 //   residual add + norm        src/cuda_kernels.cu:3033-3143
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -259,6 +261,291 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Float-domain fast path for the three front-ends the population forward runs once or twice per layer
+// (embedding + rank-r noise, + pos / GELU / abs-mean norm, residual add + abs-mean norm).
+//
+// Same results as rowquant_kernel, fewer and cheaper instructions: int8 values travel as exact small integers in
+// fp32 ("v"), or biased by 1.5 * 2^23 ("t = v + M", whose low byte is the int8), so that
+//   * bytes become floats with one byte-permute and one subtraction, and floats become bytes with a byte-permute;
+//   * rint() is an addition of M (round-to-nearest-even, like cvt.rni), clip8(rint(x)) = rint(clamp(x, +-127));
+//   * the block maximum is a float max, and the code / scale-byte tables are addressed by bit patterns;
+// and the table lives in shared memory, loaded once by a persistent CTA that then walks rows with a grid stride.
+// Requirements (checked by the host; otherwise rowquant_kernel runs): 16-byte aligned rows, cols_in == cols_out <= 2048.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+// four signed bytes -> four floats
+__device__ __forceinline__ void bytes4_to_float(uint32_t w, float* out) {
+    const uint32_t u = w ^ 0x80808080u;  // byte + 128 as an unsigned byte
+    const float off = kRoundBias + 128.0f;
+    out[0] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7650)) - off;
+    out[1] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7651)) - off;
+    out[2] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7652)) - off;
+    out[3] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7653)) - off;
+}
+// low bytes of four biased floats -> one word
+__device__ __forceinline__ uint32_t biased4_to_bytes(float a, float b, float c, float d) {
+    return __byte_perm(__byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040), __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040), 0x5410);
+}
+
+// Element ownership as in rowquant_kernel: lane l owns the 16-element scale blocks l, l + 32, ... (NB of them).
+template <int FE, int NB>
+__global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowquant_fast_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
+    __shared__ __align__(16) uint8_t lut_s[kQuantLutSignedBytes];
+    {
+        const int4* src = reinterpret_cast<const int4*>(lut + kQuantLutSignedOffset);
+        int4* dst = reinterpret_cast<int4*>(lut_s);
+        for (int i = threadIdx.x; i < kQuantLutSignedBytes / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+    __syncthreads();
+    const uint32_t lut_a = static_cast<uint32_t>(__cvta_generic_to_shared(lut_s));
+    const uint32_t kBias = static_cast<uint32_t>(kRoundBiasBits);
+    const uint32_t row_c = lut_a + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
+    const uint32_t sf_c = lut_a + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
+    const float M = kRoundBias;
+    constexpr bool kNorm = (FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN);
+
+    const int lane = threadIdx.x & 31;
+    const int nblk = p.cols_out >> 4;
+    const int k_atoms = sf_k_atoms(p.cols_out);
+    const unsigned rows = static_cast<unsigned>(p.rows);
+    for (unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8u) {
+        const int member = p.rows_per_member > 0 ? static_cast<int>(row / static_cast<unsigned>(p.rows_per_member)) : 0;
+        const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
+        const int pair = member >> 1;
+        const float ns = p.rows_per_member > 0 ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
+
+        // ---------------- stage 1: integer values of the row as floats ----------------
+        float vf[NB][16];
+        float sum_abs = 0.0f;
+        int tok = 0;
+        float a_r[4] = {0.f, 0.f, 0.f, 0.f};
+        if constexpr (FE == FE_EMBED_LOWRANK) {
+            const int trow = p.row_mod > 0 ? static_cast<int>(row % static_cast<unsigned>(p.row_mod)) : static_cast<int>(row);
+            tok = static_cast<int>(p.tokens[static_cast<size_t>(trow) * p.token_stride]);
+            if (ns != 0.0f) {
+                const int8_t* A = p.embA + static_cast<size_t>(pair) * p.embA_pair_stride + static_cast<size_t>(tok) * p.rank;
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (r < p.rank) a_r[r] = static_cast<float>(A[r]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int kb = lane + 32 * i;
+            const int k0 = kb << 4;
+            if (kb >= nblk) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) vf[i][e] = 0.0f;
+                continue;
+            }
+            if constexpr (FE == FE_ADD_ABSMEAN) {
+                int8_t* xr = p.inout_i8 + static_cast<size_t>(row) * p.cols_in;
+                const float* yr = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
+                const int4 raw = *reinterpret_cast<const int4*>(xr + k0);
+                const uint32_t rw[4] = {static_cast<uint32_t>(raw.x), static_cast<uint32_t>(raw.y), static_cast<uint32_t>(raw.z), static_cast<uint32_t>(raw.w)};
+                float4 y4[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) y4[q] = __ldcs(reinterpret_cast<const float4*>(yr + k0 + 4 * q));
+                uint32_t upd[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float yy[4] = {y4[q].x, y4[q].y, y4[q].z, y4[q].w};
+                    float oldf[4], tb[4];
+                    bytes4_to_float(rw[q], oldf);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        // old + rint(y * add_scale), clipped to +-127, all on biased floats
+                        const float t_r = __fmul_rn(yy[j], p.add_scale) + M;
+                        tb[j] = fminf(fmaxf(t_r + oldf[j], M - 127.0f), M + 127.0f);
+                        vf[i][4 * q + j] = tb[j] - M;
+                        sum_abs += fabsf(vf[i][4 * q + j]);
+                    }
+                    upd[q] = biased4_to_bytes(tb[0], tb[1], tb[2], tb[3]);
+                }
+                *reinterpret_cast<int4*>(xr + k0) = make_int4(static_cast<int>(upd[0]), static_cast<int>(upd[1]), static_cast<int>(upd[2]), static_cast<int>(upd[3]));
+            } else if constexpr (FE == FE_POS_GELU_ABSMEAN) {
+                const float* src = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
+                const int prow = p.pos_mod > 0 ? (row_in_member % p.pos_mod) : 0;
+                const float* pos = p.pos + static_cast<size_t>(prow) * p.cols_in;
+                uint32_t pw[4] = {0x0u, 0x0u, 0x0u, 0x0u};
+                const bool has_pn = p.pos_noise != nullptr;
+                if (has_pn) {
+                    const int4 pn = *reinterpret_cast<const int4*>(p.pos_noise + static_cast<size_t>(pair) * p.noise_pair_stride + static_cast<size_t>(prow) * p.cols_in + k0);
+                    pw[0] = static_cast<uint32_t>(pn.x); pw[1] = static_cast<uint32_t>(pn.y); pw[2] = static_cast<uint32_t>(pn.z); pw[3] = static_cast<uint32_t>(pn.w);
+                }
+                float4 f4[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) f4[q] = __ldcs(reinterpret_cast<const float4*>(src + k0 + 4 * q));
+                uint32_t resid[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 p4 = *reinterpret_cast<const float4*>(pos + k0 + 4 * q);
+                    const float ff[4] = {f4[q].x, f4[q].y, f4[q].z, f4[q].w};
+                    float pv[4] = {p4.x, p4.y, p4.z, p4.w};
+                    if (has_pn) {
+                        float pnf[4];
+                        bytes4_to_float(pw[q], pnf);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) pv[j] = fmaf(ns, pnf[j], pv[j]);
+                    }
+                    float x[4], tb[4], fc[4];
+                    bool fast_ok = true;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        x[j] = ff[j] + pv[j];
+                        tb[j] = gelu_q8_fast(x[j], p.act_scale, fast_ok, fc[j]);
+                    }
+                    if (!fast_ok) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tb[j] = __int_as_float(gelu_q8_exact(x[j], p.act_scale) + kRoundBiasBits);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        vf[i][4 * q + j] = tb[j] - M;
+                        sum_abs += fabsf(vf[i][4 * q + j]);
+                    }
+                    resid[q] = biased4_to_bytes(tb[0], tb[1], tb[2], tb[3]);
+                }
+                // residual stream = the pre-norm values
+                *reinterpret_cast<int4*>(p.inout_i8 + static_cast<size_t>(row) * p.cols_in + k0) =
+                    make_int4(static_cast<int>(resid[0]), static_cast<int>(resid[1]), static_cast<int>(resid[2]), static_cast<int>(resid[3]));
+            } else {  // FE_EMBED_LOWRANK
+                const int4 ew = *reinterpret_cast<const int4*>(p.emb_w + static_cast<size_t>(tok) * p.cols_in + k0);
+                const uint32_t eww[4] = {static_cast<uint32_t>(ew.x), static_cast<uint32_t>(ew.y), static_cast<uint32_t>(ew.z), static_cast<uint32_t>(ew.w)};
+                float pert[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) pert[e] = 0.0f;
+                if (ns != 0.0f) {
+                    const int8_t* B = p.embB + static_cast<size_t>(pair) * p.embB_pair_stride + k0;  // [rank][H]
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (r < p.rank) {
+                            const int4 bw = *reinterpret_cast<const int4*>(B + static_cast<size_t>(r) * p.cols_in);
+                            const uint32_t bww[4] = {static_cast<uint32_t>(bw.x), static_cast<uint32_t>(bw.y), static_cast<uint32_t>(bw.z), static_cast<uint32_t>(bw.w)};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                float bf[4];
+                                bytes4_to_float(bww[q], bf);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) pert[4 * q + j] = fmaf(a_r[r], bf[j], pert[4 * q + j]);  // exact: small integers
+                            }
+                        }
+                    }
+                }
+                const float nsc = ns * p.c_rank;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float wf[4];
+                    bytes4_to_float(eww[q], wf);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float f = ns != 0.0f ? fmaf(nsc, pert[4 * q + j], wf[j]) : wf[j];
+                        vf[i][4 * q + j] = (fminf(fmaxf(f, -127.0f), 127.0f) + M) - M;  // clip8(rint(f))
+                    }
+                }
+            }
+        }
+
+        // ---------------- stage 2: abs-mean normalisation (integer-exact row sum) ----------------
+        float inv = 1.0f;
+        if constexpr (kNorm) {
+            const int total = __reduce_add_sync(0xffffffffu, __float2int_rn(sum_abs));
+            float abs_mean = __fdiv_rn(static_cast<float>(total), static_cast<float>(p.cols_in));
+            if (abs_mean < 1.0f) abs_mean = 1.0f;
+            inv = __fdiv_rn(p.norm_scale, abs_mean);
+        }
+
+        // ---------------- stage 3: int8 copy, codes, scales, rank-r projections ----------------
+        int tacc[kMaxTVec];
+#pragma unroll
+        for (int v = 0; v < kMaxTVec; ++v) tacc[v] = 0;
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int kb = lane + 32 * i;
+            const bool active = kb < nblk;
+            if (!__any_sync(0xffffffffu, active)) continue;
+            const int k0 = kb << 4;
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            uint32_t sfb = 0;
+            if (active) {
+                float tq[16];
+                float am = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    float n = vf[i][e];
+                    if constexpr (kNorm) n = fminf(fmaxf(__fmul_rn(n, inv), -127.0f), 127.0f);
+                    am = fmaxf(am, fabsf(n));
+                    tq[e] = n + M;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) w[q] = biased4_to_bytes(tq[4 * q], tq[4 * q + 1], tq[4 * q + 2], tq[4 * q + 3]);
+                if (p.out_q != nullptr)
+                    *reinterpret_cast<int4*>(p.out_q + static_cast<size_t>(row) * p.ld_q + k0) =
+                        make_int4(static_cast<int>(w[0]), static_cast<int>(w[1]), static_cast<int>(w[2]), static_cast<int>(w[3]));
+                const uint32_t ab = __float_as_uint(am + M);
+                sfb = lds_u8(ab + sf_c);
+                const uint32_t rowbase = ab * static_cast<uint32_t>(kQuantLutSignedStride) + row_c;
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    lo |= lds_u8(__float_as_uint(tq[e]) + rowbase) << (4 * e);
+                    hi |= lds_u8(__float_as_uint(tq[8 + e]) + rowbase) << (4 * e);
+                }
+                *reinterpret_cast<uint2*>(p.out_codes + (static_cast<size_t>(row) * p.cols_out + k0) / 2) = make_uint2(lo, hi);
+            }
+            // four neighbouring lanes hold the four scale bytes of one 32-bit word of the atom layout
+            const int base_lane = lane & ~3;
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) word |= (__shfl_sync(0xffffffffu, sfb, base_lane + j) & 0xffu) << (8 * j);
+            if (active && (lane & 3) == 0)
+                *reinterpret_cast<uint32_t*>(p.out_sf + sf_offset(static_cast<int>(row), kb, k_atoms)) = word;
+
+            if (p.nvec > 0 && active) {
+                const int8_t* tv = p.tvec + static_cast<size_t>(pair) * p.tvec_pair_stride + k0;
+#pragma unroll
+                for (int vg = 0; vg < kMaxTVec / 4; ++vg) {
+                    if (4 * vg < p.nvec) {  // warp-uniform; projections come in groups of four or fewer
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int v = 4 * vg + j;
+                            if (v < p.nvec) {
+                                const int4 bv = *reinterpret_cast<const int4*>(tv + static_cast<size_t>(v) * p.cols_out);
+                                int a = tacc[v];
+                                a = __dp4a(static_cast<int>(w[0]), bv.x, a);
+                                a = __dp4a(static_cast<int>(w[1]), bv.y, a);
+                                a = __dp4a(static_cast<int>(w[2]), bv.z, a);
+                                a = __dp4a(static_cast<int>(w[3]), bv.w, a);
+                                tacc[v] = a;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (p.nvec > 0) {
+#pragma unroll
+            for (int vg = 0; vg < kMaxTVec / 4; ++vg) {
+                if (4 * vg < p.nvec) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int v = 4 * vg + j;
+                        if (v < p.nvec) {
+                            const int tot = __reduce_add_sync(0xffffffffu, tacc[v]);
+                            if (lane == 0) p.t_out[static_cast<size_t>(row) * p.nvec + v] = tot;
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int FE>
 int launch(const RowQuantParams& p, cudaStream_t stream) {
     if (p.rows <= 0 || p.cols_out <= 0) return BNF4_OK;
@@ -274,6 +561,35 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
     const int nblk = p.cols_out >> 4;
     const uint8_t* lut = get_quant_lut();
     if (lut == nullptr) return BNF4_ERR_CUDA;
+    if constexpr (FE == FE_EMBED_LOWRANK || FE == FE_POS_GELU_ABSMEAN || FE == FE_ADD_ABSMEAN) {
+        auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        bool fast = p.cols_in == p.cols_out && nblk <= 128 && (p.out_q == nullptr || p.vec_ok_q) && al16(p.inout_i8 ? p.inout_i8 : nullptr);
+        if (FE == FE_ADD_ABSMEAN) fast = fast && al16(p.in_f32) && (p.ld_in % 4) == 0;
+        if (FE == FE_POS_GELU_ABSMEAN)
+            fast = fast && p.vec_ok && al16(p.pos) && (p.pos_noise == nullptr || (al16(p.pos_noise) && (p.noise_pair_stride % 16) == 0));
+        if (FE == FE_EMBED_LOWRANK)
+            fast = fast && al16(p.emb_w) && p.rank >= 0 && p.rank <= 4 && (p.sigma == 0.0f || (al16(p.embB) && (p.embB_pair_stride % 16) == 0));
+        if (fast) {
+            int dev = 0, sms = 0;
+            int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+            if (!rc) rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+            if (rc) return rc;
+            // persistent CTAs: exactly as many as are resident at once (each holds a 33 KB copy of the table)
+            auto run = [&](auto kernel) -> int {
+                int per_sm = 0;
+                int rc2 = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, warps * 32, 0), "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+                if (rc2) return rc2;
+                const unsigned grid = std::min(ctas, static_cast<unsigned>(sms) * static_cast<unsigned>(std::max(per_sm, 1)));
+                kernel<<<grid, warps * 32, 0, stream>>>(p, lut);
+                return BNF4_OK;
+            };
+            if (nblk <= 32) rc = run(rowquant_fast_kernel<FE, 1>);
+            else if (nblk <= 64) rc = run(rowquant_fast_kernel<FE, 2>);
+            else rc = run(rowquant_fast_kernel<FE, 4>);
+            if (rc) return rc;
+            return check_launch("rowquant_fast_kernel");
+        }
+    }
     if (nblk <= 32) rowquant_kernel<FE, 1><<<ctas, warps * 32, 0, stream>>>(p, lut);
     else if (nblk <= 64) rowquant_kernel<FE, 2><<<ctas, warps * 32, 0, stream>>>(p, lut);
     else if (nblk <= 128) rowquant_kernel<FE, 4><<<ctas, warps * 32, 0, stream>>>(p, lut);
