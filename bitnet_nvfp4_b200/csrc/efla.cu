@@ -250,11 +250,8 @@ __global__ void __launch_bounds__(kScanWarps * 32, NCOL == 1 ? 4 : 2) efla_scan6
 // Fragment coordinates (g = lane / 4, tq = lane % 4): for n-tile mt and d-tile ks the lane holds S[d][n] for
 // n = 16 mt + g + {0, 8} and d = 16 ks + 2 tq + {0, 1, 8, 9}.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ int scan_perm(int d) {
-    // position of element d in the per-lane-contiguous order [tq][ks][{0, 1, 8, 9}]
-    const int ks = d >> 4, r = d & 15;
-    return ((r & 7) >> 1) * 16 + ks * 4 + ((r & 1) | ((r >> 3) << 1));
-}
+// Shared-memory order of a 64-vector ("permuted"): element d sits at ((d % 8) / 2) * 16 + (d / 16) * 4 + (d % 2) + 2 * ((d / 8) % 2),
+// so that the 16 values a lane needs (d = 16 ks + 2 tq + {0, 1, 8, 9}, ks = 0..3) are contiguous at tq * 16.
 
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -272,9 +269,13 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&hv);
 }
 
-constexpr int kScanRing = 4;             // tokens of q/k/v/beta in flight per warp
+constexpr int kScanRing = 12;                // ring of raw q/k/v/beta per warp: three groups of four tokens
 constexpr int kScanSlotFloats = 3 * 64 + 4;  // q[64], k[64], v[64], beta (+ padding to 16 bytes)
+constexpr int kScanVecBufs = 8;              // prepared vectors per warp: two groups of four tokens
 constexpr int kScanMmaCtasPerSm = 3;
+// dynamic shared memory per warp: ring, alpha*k (fp32), and the four fp16 columns q^ hi, q^ mid, k hi, k mid
+constexpr int kScanWarpSmemBytes = kScanRing * kScanSlotFloats * 4 + kScanVecBufs * 64 * 4 + kScanVecBufs * 4 * 64 * 2;
+constexpr int kScanMmaSmemBytes = kScanWarps * kScanWarpSmemBytes;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
@@ -288,10 +289,11 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 __global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan64_mma_kernel(const EflaParams p) {
     constexpr int HD = 64;
-    __shared__ __align__(16) float in_sh[kScanWarps][kScanRing][kScanSlotFloats];  // ring of raw inputs per warp
-    __shared__ __align__(16) float a_sh[kScanWarps][2][HD];                        // alpha * k of a token, permuted
-    __shared__ __align__(16) __half b_sh[kScanWarps][2][4][HD];                    // q^ hi, q^ mid, k hi, k mid, permuted
+    extern __shared__ __align__(16) uint8_t scan_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* in_sh = reinterpret_cast<float*>(scan_smem + warp * kScanWarpSmemBytes);  // [kScanRing][kScanSlotFloats]
+    float* a_sh = in_sh + kScanRing * kScanSlotFloats;                               // [kScanVecBufs][64]   alpha * k, permuted
+    __half* b_sh = reinterpret_cast<__half*>(a_sh + kScanVecBufs * HD);              // [kScanVecBufs][4][64] q^ hi, q^ mid, k hi, k mid, permuted
     const long long unit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;  // (sequence, head)
     if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
     const long long seq = unit / p.heads;
@@ -315,66 +317,93 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan6
     const float* vb = p.v + row0 * p.ld_qkv + h * HD;
     const float* bb = p.beta_raw + row0 * p.ld_beta;
     float* ob = p.out + row0 * p.ld_out + h * HD;
-    const int po0 = scan_perm(lane), po1 = scan_perm(lane + 32);
 
-    // asynchronous copy of one token's inputs into its ring slot (every lane commits a group, empty or not)
-    auto issue = [&](int tok) {
-        if (tok < p.T) {
-            float* slot = in_sh[warp][tok % kScanRing];
-            const size_t o = static_cast<size_t>(tok) * p.ld_qkv;
-            const int l16 = lane & 15;
-            cp_async16(slot + (lane < 16 ? 0 : HD) + 4 * l16, (lane < 16 ? qb : kb) + o + 4 * l16);
-            if (lane < 16) cp_async16(slot + 2 * HD + 4 * l16, vb + o + 4 * l16);
-            else if (lane == 16) cp_async4(slot + 3 * HD, bb + static_cast<size_t>(tok) * p.ld_beta);
+    // asynchronous copy of four tokens' inputs (one group) into their ring slots; every lane commits one group, empty or not
+    auto issue_group = [&](int tok0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int tok = tok0 + j;
+            if (tok < p.T) {
+                float* slot = in_sh + (tok % kScanRing) * kScanSlotFloats;
+                const size_t o = static_cast<size_t>(tok) * p.ld_qkv;
+                const int l16 = lane & 15;
+                cp_async16(slot + (lane < 16 ? 0 : HD) + 4 * l16, (lane < 16 ? qb : kb) + o + 4 * l16);
+                if (lane < 16) cp_async16(slot + 2 * HD + 4 * l16, vb + o + 4 * l16);
+                else if (lane == 16) cp_async4(slot + 3 * HD, bb + static_cast<size_t>(tok) * p.ld_beta);
+            }
         }
         cp_async_commit();
     };
 
-    // per-token vectors from a ring slot: the lane prepares elements d = lane and lane + 32
-    auto prepare = [&](const float* slot, int buf) {
-        const float rq0 = slot[lane], rq1 = slot[lane + 32], rk0 = slot[HD + lane], rk1 = slot[HD + lane + 32], rbr = slot[3 * HD];
-        const float qss = warp_sum_f(fmaf(rq0, rq0, rq1 * rq1));
-        const float kss = warp_sum_f(fmaf(rk0, rk0, rk1 * rk1));
+    // Per-token vectors, four tokens at a time: lanes 8 j .. 8 j + 7 prepare token tok0 + j, eight elements each
+    // (d = 8 l + e), so the reductions are three shuffle levels deep and the scalar chain (sigmoid, expm1, divisions)
+    // runs once per four tokens. The permuted layout puts the element pairs (d, d + 1) next to each other, so the
+    // packed fp16 conversions are stored as they are.
+    const int pj = lane >> 3, pl = lane & 7;
+    auto prepare4 = [&](int tok0) {
+        const int tok = min(tok0 + pj, p.T - 1);  // past the end: the last token again (never used)
+        const float* slot = in_sh + (tok % kScanRing) * kScanSlotFloats;
+        const int buf = (tok0 + pj) % kScanVecBufs;
+        const float4 qa = *reinterpret_cast<const float4*>(slot + 8 * pl), qc = *reinterpret_cast<const float4*>(slot + 8 * pl + 4);
+        const float4 ka = *reinterpret_cast<const float4*>(slot + HD + 8 * pl), kc = *reinterpret_cast<const float4*>(slot + HD + 8 * pl + 4);
+        const float rbr = slot[3 * HD];
+        const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qc.x, qc.y, qc.z, qc.w};
+        const float kv[8] = {ka.x, ka.y, ka.z, ka.w, kc.x, kc.y, kc.z, kc.w};
+        float qss = 0.0f, kss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { qss = fmaf(qv[e], qv[e], qss); kss = fmaf(kv[e], kv[e], kss); }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            qss += __shfl_xor_sync(0xffffffffu, qss, o);
+            kss += __shfl_xor_sync(0xffffffffu, kss, o);
+        }
         const float q_inv = rsqrtf(qss + p.eps);
         const float lambda = kss < p.eps ? p.eps : kss;
         const float beta = sigmoidf_dev(rbr + beta_bias);
         float alpha, kscale = 1.0f;
         if (p.method == 0) { alpha = beta; kscale = rsqrtf(lambda + p.eps); }
         else alpha = -expm1f(-(beta * lambda)) / (lambda + p.eps);
-        const float kn0 = rk0 * kscale, kn1 = rk1 * kscale, qn0 = rq0 * q_inv, qn1 = rq1 * q_inv;
-        a_sh[warp][buf][po0] = alpha * kn0;
-        a_sh[warp][buf][po1] = alpha * kn1;
-        // two-term fp16 splits with packed conversions
-        const __half2 qh = __floats2half2_rn(qn0, qn1), kh = __floats2half2_rn(kn0, kn1);
-        const float2 qhf = __half22float2(qh), khf = __half22float2(kh);
-        const __half2 qm = __floats2half2_rn((qn0 - qhf.x) * 2048.0f, (qn1 - qhf.y) * 2048.0f);
-        const __half2 km = __floats2half2_rn((kn0 - khf.x) * 2048.0f, (kn1 - khf.y) * 2048.0f);
-        b_sh[warp][buf][0][po0] = __low2half(qh);
-        b_sh[warp][buf][0][po1] = __high2half(qh);
-        b_sh[warp][buf][1][po0] = __low2half(qm);
-        b_sh[warp][buf][1][po1] = __high2half(qm);
-        b_sh[warp][buf][2][po0] = __low2half(kh);
-        b_sh[warp][buf][2][po1] = __high2half(kh);
-        b_sh[warp][buf][3][po0] = __low2half(km);
-        b_sh[warp][buf][3][po1] = __high2half(km);
+        // element d = 8 pl + e sits at (e / 2) * 16 + (pl / 2) * 4 + (e % 2) + 2 * (pl % 2) of the permuted order
+        const int pbase = (pl >> 1) * 4 + 2 * (pl & 1);
+        float* a_dst = a_sh + buf * HD + pbase;
+        __half* b_dst = b_sh + buf * 4 * HD + pbase;
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+            const float kn0 = kv[2 * e2] * kscale, kn1 = kv[2 * e2 + 1] * kscale, qn0 = qv[2 * e2] * q_inv, qn1 = qv[2 * e2 + 1] * q_inv;
+            *reinterpret_cast<float2*>(a_dst + 16 * e2) = make_float2(alpha * kn0, alpha * kn1);
+            // two-term fp16 splits with packed conversions
+            const __half2 qh = __floats2half2_rn(qn0, qn1), kh = __floats2half2_rn(kn0, kn1);
+            const float2 qhf = __half22float2(qh), khf = __half22float2(kh);
+            const __half2 qm = __floats2half2_rn((qn0 - qhf.x) * 2048.0f, (qn1 - qhf.y) * 2048.0f);
+            const __half2 km = __floats2half2_rn((kn0 - khf.x) * 2048.0f, (kn1 - khf.y) * 2048.0f);
+            *reinterpret_cast<__half2*>(b_dst + 0 * HD + 16 * e2) = qh;
+            *reinterpret_cast<__half2*>(b_dst + 1 * HD + 16 * e2) = qm;
+            *reinterpret_cast<__half2*>(b_dst + 2 * HD + 16 * e2) = kh;
+            *reinterpret_cast<__half2*>(b_dst + 3 * HD + 16 * e2) = km;
+        }
     };
 
     float kS[4][2];
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt) kS[mt][0] = kS[mt][1] = 0.0f;  // zero initial state
-#pragma unroll
-    for (int i = 0; i < kScanRing - 1; ++i) issue(i);
-    cp_async_wait<kScanRing - 2>();  // token 0 has landed
+    issue_group(0);
+    issue_group(4);
+    cp_async_wait<0>();
     __syncwarp();
-    prepare(in_sh[warp][0], 0);
+    prepare4(0);
 
     for (int t = 0; t < p.T; ++t) {
-        const int cur = t & 1, nxt = cur ^ 1;
-        __syncwarp();  // everyone is done with ring slot (t - 1) % kScanRing and with buffer nxt (token t - 1)
-        issue(t + kScanRing - 1);
-        cp_async_wait<kScanRing - 2>();  // tokens <= t + 1 have landed
-        __syncwarp();
-        const float* vslot = in_sh[warp][t % kScanRing] + 2 * HD;
+        const int cur = t % kScanVecBufs, nxt = (t + 1) % kScanVecBufs;
+        if ((t & 3) == 0) {
+            // start of a group of four tokens: fetch the group after next, prepare the next one
+            __syncwarp();  // everyone is done with the ring slots and vector buffers of the previous group
+            issue_group(t + 8);
+            cp_async_wait<1>();  // everything but the newest group has landed: tokens <= t + 7
+            __syncwarp();
+            prepare4(t + 4);
+            __syncwarp();
+        }
+        const float* vslot = in_sh + (t % kScanRing) * kScanSlotFloats + 2 * HD;
         float2 diff2[4][2];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt)
@@ -383,12 +412,10 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan6
                 const float d = vslot[16 * mt + 8 * hh + g] - kS[mt][hh];
                 diff2[mt][hh] = make_float2(d, d);
             }
-        if (t + 1 < p.T) prepare(in_sh[warp][(t + 1) % kScanRing], nxt);
-        __syncwarp();
 
         // per d-tile operands: alpha*k pairs (update) and the B fragment: columns 0,1 = q^ of token t, 2,3 = k of token t+1
-        const float* a_src = &a_sh[warp][cur][tq * 16];
-        const __half* b_src = &b_sh[warp][g < 2 ? cur : nxt][g & 3][tq * 16];
+        const float* a_src = a_sh + cur * HD + tq * 16;
+        const __half* b_src = b_sh + ((g < 2 ? cur : nxt) * 4 + (g & 3)) * HD + tq * 16;
         float D[4][4];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) D[mt][0] = D[mt][1] = D[mt][2] = D[mt][3] = 0.0f;
@@ -457,7 +484,13 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
                              (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
         if (g_efla_mma && aligned) {
             const long long ctas = (units + kScanWarps - 1) / kScanWarps;
-            efla_scan64_mma_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
+            static bool configured = false;
+            if (!configured) {
+                const int rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanMmaSmemBytes), "cudaFuncSetAttribute(efla_scan64_mma_kernel)");
+                if (rc) return rc;
+                configured = true;
+            }
+            efla_scan64_mma_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScanMmaSmemBytes, stream>>>(p);
             return check_launch("efla_scan64_mma_kernel");
         }
         if (g_efla_cols_per_lane == 2) {
