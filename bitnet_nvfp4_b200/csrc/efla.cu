@@ -392,18 +392,24 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan6
     __syncwarp();
     prepare4(0);
 
-    for (int t = 0; t < p.T; ++t) {
-        const int cur = t % kScanVecBufs, nxt = (t + 1) % kScanVecBufs;
-        if ((t & 3) == 0) {
+    int rg = 0;  // ring group (four slots) that holds tokens t0 .. t0 + 3
+    for (int t0 = 0; t0 < p.T; t0 += 4) {
+        const int gb = (t0 >> 2) & 1;  // vector buffers gb * 4 .. gb * 4 + 3 hold tokens t0 .. t0 + 3
+        {
             // start of a group of four tokens: fetch the group after next, prepare the next one
             __syncwarp();  // everyone is done with the ring slots and vector buffers of the previous group
-            issue_group(t + 8);
-            cp_async_wait<1>();  // everything but the newest group has landed: tokens <= t + 7
+            issue_group(t0 + 8);
+            cp_async_wait<1>();  // everything but the newest group has landed: tokens <= t0 + 7
             __syncwarp();
-            prepare4(t + 4);
+            prepare4(t0 + 4);
             __syncwarp();
         }
-        const float* vslot = in_sh + (t % kScanRing) * kScanSlotFloats + 2 * HD;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = t0 + j;
+        if (t >= p.T) break;
+        const int cur = gb * 4 + j, nxt = j < 3 ? cur + 1 : (gb ^ 1) * 4;
+        const float* vslot = in_sh + (rg * 4 + j) * kScanSlotFloats + 2 * HD;
         float2 diff2[4][2];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt)
@@ -464,6 +470,8 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan6
             kS[mt][0] = __shfl_sync(0xffffffffu, r0, (lane & ~3) | 1);
             kS[mt][1] = __shfl_sync(0xffffffffu, r1, (lane & ~3) | 1);
         }
+      }
+        rg = rg == 2 ? 0 : rg + 1;
     }
     cp_async_wait<0>();
 }
