@@ -261,13 +261,26 @@ def main():
 
     # ------------------------------------------------------------------ roofline of the dominant kernel class
     peaks, peak_src = load_peaks()
-    wave_members = min(cfg.wave_members or 64, 2 * my_pairs)
+    wave_members = model.wave_members
     work = algorithmic_work(cfg, wave_members)
     kernels = []
+    n_waves = args.steps * ((my_pairs * 2 + wave_members - 1) // wave_members)
     for name, (ms, cnt) in timing.items():
         if cnt == 0 or ms <= 0:
             continue
         ent = {"name": name, "launch_groups_ms": ms, "launches": cnt, "share": ms / ms_total}
+        if name in work:
+            # achieved rate on algorithmic work, as a fraction of the measured peak and of the nominal one
+            # (HBM: measured copy bandwidth / nominal 8 TB/s; GEMMs: 4 x measured sustained bf16 / nominal dense FP4 9 PF)
+            bound, amount = work[name]
+            per_wave = cfg.layers if name in ("gemm_qkv", "efla_scan", "gemm_ff1_gelu_fp4", "gemm_ff2") else \
+                (2 * cfg.layers if name == "add_norm_quant" else 1)
+            rate = amount * n_waves * per_wave / (ms * 1e-3)
+            if bound == "hbm":
+                ent.update(achieved=rate / 1e9, unit="GB/s", frac_measured=rate / 1e9 / peaks["hbm_gbs"], frac_nominal=rate / 8e12)
+            else:
+                ent.update(achieved=rate / 1e12, unit="TFLOP/s", frac_measured=rate / 1e12 / (4.0 * peaks["bf16_tflops_sustained"]),
+                           frac_nominal=rate / 9e15)
         kernels.append(ent)
     kernels.sort(key=lambda e: -e["launch_groups_ms"])
     roof = None
@@ -298,6 +311,9 @@ def main():
                         "sample": f"{args.cpu_pairs} antithetic pair(s) = {2 * args.cpu_pairs} members x {cfg.batch * cfg.seq} tokens, "
                                   f"forward + loss, {sec:.1f} s of CPU work"}
 
+    # the reference's tok/s_eval excludes the update (src/train_efla_lm.cpp:5786-5792)
+    update_ms = sum(ms for name, (ms, cnt) in timing.items() if name in ("update_z_sumsq", "update_apply", "requantize_weights"))
+    tokens_per_s_eval = tokens_per_step / ((ms_total - update_ms) / args.steps * 1e-3)
     out = {
         "metric": "population tokens/s per ES step", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -306,7 +322,7 @@ def main():
                 "d2h_bytes_per_step": int(losses_host.numel() * 4)},
         "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_baseline,
         "kernels": [{k: (round(v, 4) if isinstance(v, float) else v) for k, v in e.items()} for e in kernels],
-        "device_bytes": model.device_bytes, "wave_members": wave_members,
+        "tokens_per_s_eval": tokens_per_s_eval, "device_bytes": model.device_bytes, "wave_members": wave_members,
     }
     print(json.dumps(out))
     if world > 1:

@@ -363,7 +363,11 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     m->s_f = 1.0f / std::sqrt(static_cast<float>(m->F));
     m->sigma = 1.0f / static_cast<float>(1 << cfg->sigma_shift);
     m->c_r = kCRankBase / std::sqrt(static_cast<float>(m->r));
-    int W = cfg->wave_members > 0 ? cfg->wave_members : 64;
+    // default wave: as many members as fit about 12 GB of wave buffers, at most 256 (larger waves amortise launches
+    // and tile tails; beyond 256 the gain is below 1 %)
+    const double row_bytes = m->H * (1.0 + 0.5625 + 4.0) + m->F * 0.5625 + m->FC * 4.0 + 20.0 * m->r;
+    const int w_auto = static_cast<int>(std::min(256.0, std::max(2.0, 12e9 / (row_bytes * static_cast<double>(m->R)))));
+    int W = cfg->wave_members > 0 ? cfg->wave_members : w_auto;
     W = std::min(W, 2 * cfg->max_pairs);
     W = std::max(2, W & ~1);
     m->W = W;
@@ -446,6 +450,7 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
 
 size_t bnf4_model_device_bytes(void* handle) { return handle ? M(handle)->device_bytes : 0; }
 int bnf4_model_launches_per_wave(void* handle) { return handle ? M(handle)->launches_per_wave : 0; }
+int bnf4_model_wave_members(void* handle) { return handle ? M(handle)->W : 0; }
 
 int bnf4_model_set_weights(void* handle, const bnf4_model_weights* w) {
     if (!handle || !w) return set_error(BNF4_ERR_INVALID, "model_set_weights: null argument");

@@ -51,6 +51,7 @@ _l.register({
     "bnf4_model_update": (c_int, [c_void_p, c_void_p, C.POINTER(UpdateCfg), c_void_p]),
     "bnf4_model_read_buffer": (c_int, [c_void_p, C.c_char_p, c_void_p, C.c_size_t]),
     "bnf4_model_launches_per_wave": (c_int, [c_void_p]),
+    "bnf4_model_wave_members": (c_int, [c_void_p]),
     "bnf4_model_set_timing": (c_int, [c_void_p, c_int]),
     "bnf4_model_num_kernel_classes": (c_int, []),
     "bnf4_model_kernel_class_name": (C.c_char_p, [c_int]),
@@ -122,6 +123,10 @@ class PopulationModel:
     @property
     def launches_per_wave(self) -> int:
         return self.lib.bnf4_model_launches_per_wave(self.h)
+
+    @property
+    def wave_members(self) -> int:
+        return self.lib.bnf4_model_wave_members(self.h)
 
     def _weights_struct(self, arrays: dict) -> ModelWeights:
         return ModelWeights(*[arrays[n].ctypes.data for n in WEIGHT_NAMES])

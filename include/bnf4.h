@@ -367,7 +367,7 @@ typedef struct bnf4_model_cfg {
     int method;       /* 0 DeltaNet, 1 EFLA */
     float act_scale, mlp_act_scale, ln_scale, residual_scale, mlp_residual_scale, eps;
     int max_pairs;    /* pairs per ES step (population / 2) */
-    int wave_members; /* members evaluated per wave (even); 0 = library default */
+    int wave_members; /* members evaluated per wave (even); 0 = library default: what fits ~12 GB of wave buffers, at most 256 */
 } bnf4_model_cfg;
 
 /* Host-side weight set (reference: EflaLmWeights src/train_efla_lm.cpp:419-431 plus the positional table). */
@@ -424,6 +424,8 @@ int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update
 int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes);
 /* Kernels launched by the last bnf4_model_eval_pairs wave (for accounting). */
 int bnf4_model_launches_per_wave(void* handle);
+/* Members evaluated per wave (the configured value, or the library's choice when the configuration says 0). */
+int bnf4_model_wave_members(void* handle);
 /* Optional timing breakdown: when enabled, the driver brackets every kernel class with CUDA events on the launching
  * stream. bnf4_model_get_timing synchronises and returns accumulated milliseconds and launches per class since the
  * last bnf4_model_set_timing call. */
