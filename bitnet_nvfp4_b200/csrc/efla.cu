@@ -492,11 +492,15 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
                              (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
         if (g_efla_mma && aligned) {
             const long long ctas = (units + kScanWarps - 1) / kScanWarps;
-            static bool configured = false;
-            if (!configured) {
-                const int rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanMmaSmemBytes), "cudaFuncSetAttribute(efla_scan64_mma_kernel)");
+            // function attributes are per device: set once for each device this process uses
+            static bool configured[64] = {};
+            int dev = 0;
+            int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+            if (rc) return rc;
+            if (dev < 0 || dev >= 64 || !configured[dev]) {
+                rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanMmaSmemBytes), "cudaFuncSetAttribute(efla_scan64_mma_kernel)");
                 if (rc) return rc;
-                configured = true;
+                if (dev >= 0 && dev < 64) configured[dev] = true;
             }
             efla_scan64_mma_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScanMmaSmemBytes, stream>>>(p);
             return check_launch("efla_scan64_mma_kernel");

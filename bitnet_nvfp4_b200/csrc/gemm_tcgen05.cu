@@ -630,11 +630,14 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint
 template <int EPI>
 int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const KernelArgs& args, dim3 grid,
              cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
+    // function attributes are per device: set once for each device this process uses
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError(), "cudaGetDevice");
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_nvfp4_kernel)");
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     gemm_nvfp4_kernel<EPI><<<grid, kThreads, kSmemAlloc, stream>>>(ma, mb, md, args);
     return check_launch("gemm_nvfp4_kernel");

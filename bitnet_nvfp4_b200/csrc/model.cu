@@ -337,6 +337,8 @@ int bnf4_model_destroy(void* handle) {
     Model* m = M(handle);
     cudaDeviceSynchronize();
     for (void* p : m->allocs) cudaFree(p);
+    for (cudaEvent_t e : m->free_events) cudaEventDestroy(e);
+    for (const Model::Span& sp : m->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
     delete m;
     return BNF4_OK;
 }
@@ -472,6 +474,58 @@ int bnf4_model_set_weights(void* handle, const bnf4_model_weights* w) {
     TRY(check_cuda(cudaMemset(m.rms_ema, 0, (6 + 6 * static_cast<size_t>(m.L)) * sizeof(float)), "cudaMemset(rms_ema)"));
     TRY(quantize_base(m, nullptr));
     return check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+}
+
+// Optimiser state = the fp32 shadows of the nine weight tensors (same order and sizes as bnf4_model_weights' int8 members,
+// concatenated) and the RMS-EMA scalars (6 + 6 * layers). Together with the weights it is everything a resumed run needs.
+namespace {
+struct ShadowItem { float* d; size_t n; };
+void shadow_items(Model& m, ShadowItem (&out)[9]) {
+    const size_t vh = static_cast<size_t>(m.V) * m.H, hh = static_cast<size_t>(m.H) * m.H, hf = static_cast<size_t>(m.H) * m.F;
+    const ShadowItem items[9] = {{m.sh_emb, vh}, {m.sh_win, hh}, {m.sh_wq, m.L * hh}, {m.sh_wk, m.L * hh}, {m.sh_wv, m.L * hh},
+                                 {m.sh_wbeta, static_cast<size_t>(m.L) * m.H}, {m.sh_ff1, m.L * hf}, {m.sh_ff2, m.L * hf}, {m.sh_head, vh}};
+    for (int i = 0; i < 9; ++i) out[i] = items[i];
+}
+}  // namespace
+
+int bnf4_model_optimizer_state_sizes(void* handle, size_t* shadow_floats, size_t* ema_floats) {
+    if (!handle) return set_error(BNF4_ERR_INVALID, "model_optimizer_state_sizes: null handle");
+    Model& m = *M(handle);
+    ShadowItem it[9];
+    shadow_items(m, it);
+    size_t n = 0;
+    for (const ShadowItem& x : it) n += x.n;
+    if (shadow_floats) *shadow_floats = n;
+    if (ema_floats) *ema_floats = 6 + 6 * static_cast<size_t>(m.L);
+    return BNF4_OK;
+}
+
+int bnf4_model_get_optimizer_state(void* handle, float* h_shadow, float* h_ema) {
+    if (!handle || !h_shadow || !h_ema) return set_error(BNF4_ERR_INVALID, "model_get_optimizer_state: null argument");
+    Model& m = *M(handle);
+    TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    ShadowItem it[9];
+    shadow_items(m, it);
+    size_t off = 0;
+    for (const ShadowItem& x : it) {
+        TRY(check_cuda(cudaMemcpy(h_shadow + off, x.d, x.n * sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy(shadow)"));
+        off += x.n;
+    }
+    return check_cuda(cudaMemcpy(h_ema, m.rms_ema, (6 + 6 * static_cast<size_t>(m.L)) * sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy(rms_ema)");
+}
+
+int bnf4_model_set_optimizer_state(void* handle, const float* h_shadow, const float* h_ema) {
+    if (!handle || !h_shadow || !h_ema) return set_error(BNF4_ERR_INVALID, "model_set_optimizer_state: null argument");
+    Model& m = *M(handle);
+    TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    ShadowItem it[9];
+    shadow_items(m, it);
+    size_t off = 0;
+    for (const ShadowItem& x : it) {
+        TRY(check_cuda(cudaMemcpy(x.d, h_shadow + off, x.n * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy(shadow)"));
+        off += x.n;
+    }
+    return check_cuda(cudaMemcpy(m.rms_ema, h_ema, (6 + 6 * static_cast<size_t>(m.L)) * sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy(rms_ema)");
 }
 
 int bnf4_model_get_weights(void* handle, bnf4_model_weights* w) {

@@ -52,6 +52,9 @@ _l.register({
     "bnf4_model_read_buffer": (c_int, [c_void_p, C.c_char_p, c_void_p, C.c_size_t]),
     "bnf4_model_launches_per_wave": (c_int, [c_void_p]),
     "bnf4_model_wave_members": (c_int, [c_void_p]),
+    "bnf4_model_optimizer_state_sizes": (c_int, [c_void_p, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "bnf4_model_get_optimizer_state": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "bnf4_model_set_optimizer_state": (c_int, [c_void_p, c_void_p, c_void_p]),
     "bnf4_model_set_timing": (c_int, [c_void_p, c_int]),
     "bnf4_model_num_kernel_classes": (c_int, []),
     "bnf4_model_kernel_class_name": (C.c_char_p, [c_int]),
@@ -146,6 +149,32 @@ class PopulationModel:
         arrays = {n: np.zeros(shapes[n], np.float32 if n in ("head_bias", "beta_bias", "pos") else np.int8) for n in WEIGHT_NAMES}
         _l.check(self.lib.bnf4_model_get_weights(self.h, C.byref(self._weights_struct(arrays))))
         return arrays
+
+    def get_optimizer_state(self):
+        """(shadow, ema): fp32 shadows of the nine weight tensors, concatenated, and the RMS-EMA scalars."""
+        ns, ne = C.c_size_t(0), C.c_size_t(0)
+        _l.check(self.lib.bnf4_model_optimizer_state_sizes(self.h, C.byref(ns), C.byref(ne)))
+        shadow, ema = np.zeros(ns.value, np.float32), np.zeros(ne.value, np.float32)
+        _l.check(self.lib.bnf4_model_get_optimizer_state(self.h, shadow.ctypes.data, ema.ctypes.data))
+        return shadow, ema
+
+    def set_optimizer_state(self, shadow, ema):
+        shadow, ema = np.ascontiguousarray(shadow, np.float32), np.ascontiguousarray(ema, np.float32)
+        ns, ne = C.c_size_t(0), C.c_size_t(0)
+        _l.check(self.lib.bnf4_model_optimizer_state_sizes(self.h, C.byref(ns), C.byref(ne)))
+        assert shadow.size == ns.value and ema.size == ne.value
+        _l.check(self.lib.bnf4_model_set_optimizer_state(self.h, shadow.ctypes.data, ema.ctypes.data))
+
+    def save_checkpoint(self, path, epoch: int):
+        """Everything a resumed run needs: weights, optimiser state and the epoch counter (noise is a function of seed and epoch)."""
+        shadow, ema = self.get_optimizer_state()
+        np.savez(path, epoch=np.int64(epoch), shadow=shadow, ema=ema, **self.get_weights())
+
+    def load_checkpoint(self, path) -> int:
+        z = np.load(path)
+        self.set_weights({n: z[n] for n in WEIGHT_NAMES})
+        self.set_optimizer_state(z["shadow"], z["ema"])
+        return int(z["epoch"])
 
     def set_tokens(self, tokens, targets):
         """tokens/targets: uint8 [B][T], torch CUDA tensors or (pinned) host tensors / numpy arrays."""

@@ -424,6 +424,12 @@ int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update
 int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes);
 /* Kernels launched by the last bnf4_model_eval_pairs wave (for accounting). */
 int bnf4_model_launches_per_wave(void* handle);
+/* Checkpoint / resume (the reference has none). The optimiser state is the fp32 shadows of the nine int8 weight tensors
+ * (concatenated in the member order of bnf4_model_weights) and the RMS-EMA scalars; call bnf4_model_set_weights first
+ * (it resets the state), then bnf4_model_set_optimizer_state. Host pointers; these calls synchronise the device. */
+int bnf4_model_optimizer_state_sizes(void* handle, size_t* shadow_floats, size_t* ema_floats);
+int bnf4_model_get_optimizer_state(void* handle, float* h_shadow, float* h_ema);
+int bnf4_model_set_optimizer_state(void* handle, const float* h_shadow, const float* h_ema);
 /* Members evaluated per wave (the configured value, or the library's choice when the configuration says 0). */
 int bnf4_model_wave_members(void* handle);
 /* Optional timing breakdown: when enabled, the driver brackets every kernel class with CUDA events on the launching

@@ -147,3 +147,30 @@ def test_update_bit_exact_given_fitness():
     l_after = model.eval_base().item()
     om = orc.OracleModel(oracle_cfg(cfg), ref)
     assert abs(l_after - om.forward(tok, tgt, 0, 0)) <= 1e-4 * abs(l_after)
+
+
+def test_checkpoint_resume_is_bit_identical(tmp_path):
+    """Two updates in one run == one update, checkpoint, fresh model, resume, second update (weights and optimiser state)."""
+    import torch
+    kw = dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=8, wave_members=8)
+    rng = np.random.default_rng(11)
+    pws = [orc.shape_pair_weights(rng.standard_normal(8).astype(np.float32)) for _ in range(2)]
+
+    def step(model, epoch):
+        model.prepare_step(1, epoch, 8)
+        model.update(torch.from_numpy(pws[epoch]).cuda(), lr=0.8, thresh=0.008)
+
+    _, _, _, _, a = make(kw)
+    step(a, 0)
+    a.save_checkpoint(tmp_path / "ck.npz", 1)
+    step(a, 1)
+    _, _, _, _, b = make(kw)
+    epoch = b.load_checkpoint(tmp_path / "ck.npz")
+    assert epoch == 1
+    step(b, epoch)
+    wa, wb = a.get_weights(), b.get_weights()
+    for k in wa:
+        assert np.array_equal(wa[k], wb[k]), k
+    (sa, ea), (sb, eb) = a.get_optimizer_state(), b.get_optimizer_state()
+    assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
+    assert (sa != np.round(sa)).any()  # the shadows really carry fractional state
