@@ -124,6 +124,17 @@ __device__ __forceinline__ float gelu_q8_fast(float x, float act_scale, bool& ok
 __device__ __forceinline__ int gelu_q8_exact(float x, float act_scale) {
     return clip_int8(__float2int_rn(gelu_tanh(x) * act_scale));
 }
+// Out-of-line form of the exact path for four values (the rare fallback of the unrolled epilogues: keeping the tanhf
+// code out of line keeps their instruction footprint small). Returns the biased rounded values and the integers as floats.
+static __device__ __noinline__ void gelu_q8_exact4(float x0, float x1, float x2, float x3, float act_scale, float* tb, float* fc) {
+    const float xs[4] = {x0, x1, x2, x3};
+#pragma unroll 1
+    for (int e = 0; e < 4; ++e) {
+        const int q = gelu_q8_exact(xs[e], act_scale);
+        tb[e] = __int_as_float(q + kRoundBiasBits);
+        fc[e] = static_cast<float>(q);
+    }
+}
 __device__ __forceinline__ int gelu_q8(float x, float act_scale) {
     bool ok = true;
     float fc;

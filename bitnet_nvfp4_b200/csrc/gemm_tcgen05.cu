@@ -72,14 +72,17 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One attempt: the thread may be suspended by the hardware for up to ~20 us and is woken as soon as the phase completes,
+// so a waiting role issues a handful of instructions per attempt instead of spinning through the issue slots the
+// epilogue warps need.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(20000u)
         : "memory");
     return ok != 0;
 }
@@ -511,12 +514,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
 #pragma unroll
                     for (int e = 0; e < 4; ++e) tb[4 * g + e] = gelu_q8_fast(v[4 * g + e], p.act_scale, fast_ok, fc[e]);
                     if (!fast_ok) {  // some value too close to a rounding boundary: redo the four with the tanhf form
+                        float tbx[4], fcx[4];
+                        gelu_q8_exact4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3], p.act_scale, tbx, fcx);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int qe = gelu_q8_exact(v[4 * g + e], p.act_scale);
-                            tb[4 * g + e] = __int_as_float(qe + kRoundBiasBits);
-                            fc[e] = static_cast<float>(qe);
-                        }
+                        for (int e = 0; e < 4; ++e) { tb[4 * g + e] = tbx[e]; fc[e] = fcx[e]; }
                     }
                     am[g >> 2] = fmaxf(fmaxf(am[g >> 2], fmaxf(fabsf(fc[0]), fabsf(fc[1]))), fmaxf(fabsf(fc[2]), fabsf(fc[3])));
                     w[g] = static_cast<int>(__byte_perm(__byte_perm(__float_as_uint(tb[4 * g]), __float_as_uint(tb[4 * g + 1]), 0x0040),

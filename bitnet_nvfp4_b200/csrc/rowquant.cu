@@ -401,8 +401,8 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                         tb[j] = gelu_q8_fast(x[j], p.act_scale, fast_ok, fc[j]);
                     }
                     if (!fast_ok) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) tb[j] = __int_as_float(gelu_q8_exact(x[j], p.act_scale) + kRoundBiasBits);
+                        float fcx[4];
+                        gelu_q8_exact4(x[0], x[1], x[2], x[3], p.act_scale, tb, fcx);
                     }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {

@@ -62,6 +62,14 @@ def zipf_corpus(n_bytes: int = 1 << 20, s: float = 1.1, seed: int = 123) -> np.n
     return np.minimum(np.searchsorted(cdf, u, side="right"), 255).astype(np.uint8)
 
 
+def load_corpus(path) -> np.ndarray:
+    """A real byte corpus (e.g. Tiny Shakespeare) as the reference's ByteDataset::load_file reads it (src/dataset.cpp:8-20)."""
+    data = np.fromfile(path, dtype=np.uint8)
+    if data.size < 2:
+        raise ValueError("dataset too small")
+    return data
+
+
 def sample_batch(corpus: np.ndarray, batch: int, seq: int, seed: int):
     """(tokens, targets) uint8 [batch][seq]: window starts from splitmix64(seed) % (len - seq - 1)."""
     r = splitmix64_stream(seed, batch)

@@ -3,7 +3,7 @@
 // The reference's driver translation unit (src/train_efla_lm.cpp) is #included here unmodified, from where it
 // lies, with its main() renamed; nothing of it is copied into this repository. Its file-static host functions
 // become callable through the small extern "C" surface below, which the tests use to pin the CPU oracle
-// (rng, noise hash, ternary init, fitness shaping, token cross-entropy) against the real reference code.
+// (rng, noise hash, ternary init, fitness shaping, token cross-entropy, batch sampling) against the real reference code.
 // The device entry points the driver references are resolved by libbnf4.so -- linking this file is at the
 // same time the proof that the reference driver links against the library unchanged.
 #define main ref_train_main
@@ -45,6 +45,13 @@ REF_API uint64_t ref_count_parameters(int vocab, int hidden, int layers, int mlp
     TrainConfig cfg;
     cfg.vocab = vocab; cfg.hidden = hidden; cfg.layers = layers; cfg.mlp_mult = mlp_mult; cfg.seq_len = seq; cfg.train_pos = train_pos != 0;
     return count_parameters(cfg);
+}
+// The reference's batch sampler on a corpus file (src/dataset.cpp:39-54). Returns 0 on success.
+REF_API int ref_sample_batch_packed(const char* path, int batch, int seq_len, uint64_t seed, uint8_t* inputs, uint8_t* targets) {
+    ByteDataset ds;
+    if (!ds.load_file(path)) return 1;
+    ds.sample_batch_packed(batch, seq_len, seed, inputs, targets);
+    return 0;
 }
 // The reference driver itself (argv as for its executable), running on this library's kernels.
 REF_API int ref_train(int argc, char** argv) { return ref_train_main(argc, argv); }

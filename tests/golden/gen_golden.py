@@ -112,9 +112,22 @@ def gen_ref_host():
                    for i in range(8)], np.float32)
     nparams = np.array([L.ref_count_parameters(256, 512, 4, 2, 128, 1)], np.uint64)
     fused_cols = np.array([L.ref_qkv_fused_cols_aligned(h) for h in (128, 512, 2048)], np.int32)
+    # batch sampling of the reference's ByteDataset on a seeded synthetic corpus file (a hash of the windows is stored)
+    sys.path.insert(0, str(ROOT))
+    from bitnet_nvfp4_b200 import synth
+    corpus = synth.zipf_corpus(1 << 16, 1.1, 123)
+    L.ref_sample_batch_packed.argtypes = [C.c_char_p, C.c_int, C.c_int, u64, C.c_void_p, C.c_void_p]
+    sb_tok = np.zeros((3, 32, 128), np.uint8)
+    sb_tgt = np.zeros((3, 32, 128), np.uint8)
+    sb_seed = np.array([123, 0x1234567, 2**64 - 3], np.uint64)
+    with tempfile.TemporaryDirectory() as td:
+        f = Path(td) / "corpus.bin"
+        corpus.tofile(f)
+        for i, sd in enumerate(sb_seed):
+            assert L.ref_sample_batch_packed(str(f).encode(), 32, 128, int(sd), sb_tok[i].ctypes.data, sb_tgt[i].ctypes.data) == 0
     np.savez_compressed(HERE / "ref_host.npz", mix_a=a, mix_b=b, mix=mix, sm_seed=sm_seed, sm_out=sm_out, tern_in=tern_in, tern=tern,
                         nh_seed=nh_seed, nh=nh, init=init, init_scale=init_scale, fit=fit, shaped=shaped, ce_logits=logits, ce_bias=bias,
-                        ce_noise=bnoise, ce_y=ys, ce=ce, nparams=nparams, fused_cols=fused_cols)
+                        ce_noise=bnoise, ce_y=ys, ce=ce, nparams=nparams, fused_cols=fused_cols, sb_seed=sb_seed, sb_tok=sb_tok, sb_tgt=sb_tgt)
     print("ref_host.npz", (HERE / "ref_host.npz").stat().st_size, "bytes")
 
 

@@ -231,3 +231,13 @@ def test_synthetic_tokens_are_zipf():
     assert abs(counts[0] / counts.sum() - p[0]) < 0.01 and counts[0] > counts[1] > counts[5] > counts[50]
     tok, tgt = synth.sample_batch(c, 32, 128, 123)
     assert tok.shape == (32, 128) and np.array_equal(tok[:, 1:], tgt[:, :-1])
+
+
+def test_batch_sampler_matches_reference_dataset():
+    """synth.sample_batch == the reference's ByteDataset::sample_batch_packed (src/dataset.cpp:39-54) on the same corpus bytes."""
+    from bitnet_nvfp4_b200 import synth
+    g = np.load(GOLD / "ref_host.npz")
+    corpus = synth.zipf_corpus(1 << 16, 1.1, 123)
+    for i, sd in enumerate(g["sb_seed"]):
+        tok, tgt = synth.sample_batch(corpus, 32, 128, int(sd))
+        assert np.array_equal(tok, g["sb_tok"][i]) and np.array_equal(tgt, g["sb_tgt"][i])
