@@ -100,7 +100,14 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
                 vals[e] = clip_int8(rint_to_int(f));
             }
         } else if constexpr (FE == FE_POS_GELU || FE == FE_POS_GELU_ABSMEAN || FE == FE_ACT) {
-            const float* src = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
+            size_t in_row = static_cast<size_t>(row);
+            if constexpr (FE != FE_ACT) {
+                if (p.gather_rows > 0) {  // per-member table of rows indexed by token
+                    const unsigned ti = p.row_mod > 0 ? urow % static_cast<unsigned>(p.row_mod) : urow;
+                    in_row = static_cast<size_t>(member) * p.gather_rows + p.tokens[static_cast<size_t>(ti) * p.token_stride];
+                }
+            }
+            const float* src = p.in_f32 + in_row * p.ld_in;
             float f[16];
             if (p.vec_ok && k0 + 16 <= p.cols_in) {
 #pragma unroll
@@ -369,7 +376,12 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 }
                 *reinterpret_cast<int4*>(xr + k0) = make_int4(static_cast<int>(upd[0]), static_cast<int>(upd[1]), static_cast<int>(upd[2]), static_cast<int>(upd[3]));
             } else if constexpr (FE == FE_POS_GELU_ABSMEAN) {
-                const float* src = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
+                size_t in_row = static_cast<size_t>(row);
+                if (p.gather_rows > 0) {  // per-member table of rows indexed by token
+                    const unsigned ti = p.row_mod > 0 ? row % static_cast<unsigned>(p.row_mod) : row;
+                    in_row = static_cast<size_t>(member) * p.gather_rows + p.tokens[static_cast<size_t>(ti) * p.token_stride];
+                }
+                const float* src = p.in_f32 + in_row * p.ld_in;
                 const int prow = p.pos_mod > 0 ? (row_in_member % p.pos_mod) : 0;
                 const float* pos = p.pos + static_cast<size_t>(prow) * p.cols_in;
                 uint32_t pw[4] = {0x0u, 0x0u, 0x0u, 0x0u};
@@ -626,6 +638,8 @@ int rowquant_dispatch(int fe, RowQuantParams p, cudaStream_t stream) {
         p.cols_in != p.cols_out)
         return set_error(BNF4_ERR_INVALID, "rowquant: this front-end needs cols_in == cols_out");
     if (p.nvec > 0 && !aligned16(p.tvec, p.cols_out)) return set_error(BNF4_ERR_INVALID, "rowquant: projection vectors must be 16-byte aligned");
+    if (p.gather_rows > 0 && ((fe != FE_POS_GELU && fe != FE_POS_GELU_ABSMEAN) || p.tokens == nullptr || p.rows_per_member <= 0))
+        return set_error(BNF4_ERR_INVALID, "rowquant: gather_rows needs a pos+GELU front-end, tokens and rows_per_member");
     switch (fe) {
         case FE_INT8: return launch<FE_INT8>(p, stream);
         case FE_WQKV: return launch<FE_WQKV>(p, stream);

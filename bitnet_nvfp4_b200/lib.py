@@ -31,7 +31,7 @@ class RowQuantDesc(C.Structure):
         ("act_mode", c_int), ("act_scale", c_float), ("add_scale", c_float), ("norm_scale", c_float),
         ("out_q", c_void_p), ("ld_q", c_int), ("out_codes", c_void_p), ("out_sf", c_void_p),
         ("tvec", c_void_p), ("tvec_pair_stride", c_ll), ("nvec", c_int), ("t_out", c_void_p),
-        ("vec_ok", c_int), ("vec_ok_q", c_int),
+        ("vec_ok", c_int), ("vec_ok_q", c_int), ("gather_rows", c_int),
     ]
 
 

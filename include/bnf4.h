@@ -144,6 +144,9 @@ typedef struct bnf4_rowquant_desc {
     int nvec;
     int32_t* t_out;
     int vec_ok, vec_ok_q; /* set by the library */
+    /* BNF4_FE_POS_GELU(_ABSMEAN) only: when > 0 the fp32 input is a table of gather_rows rows per member and the input
+     * row of output row (member, i) is member * gather_rows + tokens[(i % row_mod) * token_stride] (row_mod 0: i). */
+    int gather_rows;
 } bnf4_rowquant_desc;
 
 int bnf4_rowquant(int front_end, const bnf4_rowquant_desc* desc, void* stream);
