@@ -55,13 +55,14 @@ def _operands(m, n, k, rank, R, seed=0):
     return a, sfa, b, sfb, A, t, pairs
 
 
-def bench_gemm(m, variants, iters):
-    k, R = 512, 4096
+def bench_gemm(m, variants, iters, n_arg=0, k_arg=0):
+    k, R = (k_arg or 512), 4096
     for v in variants:
-        n = 1024 if v.startswith("gelu") else 512
+        n = n_arg or (1024 if v.startswith("gelu") else 512)
         a, sfa, b, sfb, A, t, pairs = _operands(m, n, k, 1, R)
         alpha = float(1 / np.sqrt(k))
-        d = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        ldd = (n + 31) & ~31
+        d = torch.empty((m, ldd), dtype=torch.float32, device="cuda")
         d8 = torch.empty((m, n), dtype=torch.int8, device="cuda")
         codes = torch.zeros(m * n // 2, dtype=torch.uint8, device="cuda")
         sf = torch.zeros(H.sf_bytes(m, n), dtype=torch.uint8, device="cuda")
@@ -72,7 +73,7 @@ def bench_gemm(m, variants, iters):
 
         def run():
             if v == "plain":
-                H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32)
+                H.gemm_nvfp4_ex(**base, d=d, ldd=ldd, epilogue=H.EPI_F32)
             elif v == "direct":
                 lib.load().bnf4_set_option(b"gemm_tma_store", 0)
                 H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32)
@@ -82,7 +83,7 @@ def bench_gemm(m, variants, iters):
                 H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32)
                 lib.load().bnf4_set_option(b"gemm_tma_store", 1)
             elif v == "lora":
-                H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32, **lora)
+                H.gemm_nvfp4_ex(**base, d=d, ldd=ldd, epilogue=H.EPI_F32, **lora)
             elif v == "gelu":
                 H.gemm_nvfp4_ex(**base, epilogue=H.EPI_GELU_I8, act_scale=1.0, d_i8=d8, ld_i8=n)
             elif v == "gelufp4":
@@ -157,6 +158,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "efla", "rowquant", "sweep"])
     ap.add_argument("--m", type=int, default=65536)
+    ap.add_argument("--n", type=int, default=0, help="gemm: output columns (default 512, 1024 for the GELU variants)")
+    ap.add_argument("--k", type=int, default=0, help="gemm: reduction length (default 512)")
     ap.add_argument("--variants", default="plain,lora,direct,gelu,gelufp4")
     ap.add_argument("--seqs", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=65536)
@@ -164,7 +167,7 @@ def main():
     ap.add_argument("--mma", type=int, default=1, help="efla: 1 = tensor-core scan kernel, 0 = multiply-add scan kernel")
     a = ap.parse_args()
     if a.what == "gemm":
-        bench_gemm(a.m, a.variants.split(","), a.iters)
+        bench_gemm(a.m, a.variants.split(","), a.iters, a.n, a.k)
     elif a.what == "sweep":
         bench_sweep(a.iters)
     elif a.what == "efla":
