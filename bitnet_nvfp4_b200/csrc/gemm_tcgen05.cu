@@ -244,34 +244,51 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
+            // like the MMA issuer, this thread shares an issue port with busy epilogue warps: running indices instead of
+            // divisions, addresses advanced by constants
             int kc = 0;  // k-block counter across tiles
+            int s = 0;
+            uint32_t empty_parity = 1;  // parity of the phase that precedes the first completion: the first pass does not wait
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int n_tile = tile % args.n_tiles, m_tile = tile / args.n_tiles;
-                const uint8_t* sfa_tile = static_cast<const uint8_t*>(p.sfa) + static_cast<size_t>(m_tile) * args.k_atoms * 512;
-                const uint8_t* sfb_tile = static_cast<const uint8_t*>(p.sfb) + static_cast<size_t>(n_tile) * args.k_atoms * 512;
+                const uint8_t* sfa_src = static_cast<const uint8_t*>(p.sfa) + static_cast<size_t>(m_tile) * args.k_atoms * 512;
+                const uint8_t* sfb_src = static_cast<const uint8_t*>(p.sfb) + static_cast<size_t>(n_tile) * args.k_atoms * 512;
+                const int my = m_tile * BM, ny = n_tile * BN;
+                int atoms_left = args.k_atoms;
                 for (int ks = 0; ks < num_ks; ++ks, ++kc) {
-                    const int s = kc % kStages, use = kc / kStages;
-                    if (use >= 1) {
-                        ok = mbar_wait(bar_empty + 8 * s, (use - 1) & 1, 1);
+                    if (kc >= kStages) {
+                        ok = mbar_wait(bar_empty + 8 * s, empty_parity, 1);
                         if (!ok) break;
                     }
-                    const int atoms = min(4, args.k_atoms - ks * 4);
-                    const uint32_t sf_bytes_stage = static_cast<uint32_t>(atoms) * 512u;
+                    const uint32_t sf_bytes_stage = static_cast<uint32_t>(min(4, atoms_left)) * 512u;
+                    atoms_left -= 4;
                     const uint32_t bar = bar_full + 8 * s;
                     const bool load_a = !((args.timing_aid & 2) && kc >= kStages), load_b = !((args.timing_aid & 1) && kc >= kStages);
                     mbar_expect_tx(bar, (load_a ? kStageABytes : 0) + (load_b ? kStageBBytes : 0) + 2 * sf_bytes_stage);
-                    if (load_a) tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, m_tile * BM, bar);
-                    if (load_b) tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, n_tile * BN, bar);
-                    bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
-                    bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_tile + static_cast<size_t>(ks) * 2048, sf_bytes_stage, bar);
+                    if (load_a) tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, my, bar);
+                    if (load_b) tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, ny, bar);
+                    bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_src, sf_bytes_stage, bar);
+                    bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_src, sf_bytes_stage, bar);
+                    sfa_src += 2048;
+                    sfb_src += 2048;
+                    if (++s == kStages) { s = 0; empty_parity ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
+            // This single thread's issue rate bounds the mainloop (it shares an issue port with four busy epilogue warps), so
+            // the loop is kept lean: descriptors are a stage-0 constant plus a stage / K-step increment of the 14-bit
+            // start-address field (bytes >> 4), and the four K-steps of a full stage are unrolled.
+            const uint64_t adesc0 = smem_desc(smem_base + kSmemA, 16, 1024, kLayoutSw128);
+            const uint64_t bdesc0 = smem_desc(smem_base + kSmemB, 16, 1024, kLayoutSw128);
+            const uint64_t sfadesc0 = smem_desc(smem_base + kSmemSfa, 0, 128, kLayoutNone);
+            const uint64_t sfbdesc0 = smem_desc(smem_base + kSmemSfb, 0, 128, kLayoutNone);
             int kc = 0, it = 0;
+            int s = 0;
+            uint32_t full_parity = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
                 const int buf = it & 1;
@@ -282,30 +299,45 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
                 const uint32_t acc_col = tmem_base + kAccCol + buf * BN;
                 for (int ks = 0; ks < num_ks; ++ks, ++kc) {
-                    const int s = kc % kStages, use = kc / kStages;
-                    ok = mbar_wait(bar_full + 8 * s, use & 1, 2);
+                    ok = mbar_wait(bar_full + 8 * s, full_parity, 2);
                     if (!ok) break;
                     tc_fence_after();
                     const int nk = min(4, (p.k - ks * BK) / UMMA_K);
-                    const uint32_t sfa_s = smem_base + kSmemSfa + s * kStageSfBytes;
-                    const uint32_t sfb_s = smem_base + kSmemSfb + s * kStageSfBytes;
                     const uint32_t t_sfa = tmem_base + kSfCol + s * 32;
                     const uint32_t t_sfb = t_sfa + 16;
-                    if (!((args.timing_aid & 4) && kc >= kStages)) {
-                        for (int j = 0; j < nk; ++j) {
-                            tc_cp_sf(t_sfa + 4 * j, smem_desc(sfa_s + 512 * j, 0, 128, kLayoutNone));
-                            tc_cp_sf(t_sfb + 4 * j, smem_desc(sfb_s + 512 * j, 0, 128, kLayoutNone));
+                    const uint64_t sfa_d = sfadesc0 + static_cast<uint64_t>(s * (kStageSfBytes >> 4));
+                    const uint64_t sfb_d = sfbdesc0 + static_cast<uint64_t>(s * (kStageSfBytes >> 4));
+                    const uint64_t a_d = adesc0 + static_cast<uint64_t>(s * (kStageABytes >> 4));
+                    const uint64_t b_d = bdesc0 + static_cast<uint64_t>(s * (kStageBBytes >> 4));
+                    const bool do_cp = !((args.timing_aid & 4) && kc >= kStages), do_mma = !((args.timing_aid & 8) && kc >= kStages);
+                    if (nk == 4) {
+                        if (do_cp) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
+                                tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            }
                         }
-                    }
-                    const uint32_t a_s = smem_base + kSmemA + s * kStageABytes;
-                    const uint32_t b_s = smem_base + kSmemB + s * kStageBBytes;
-                    for (int j = 0; j < nk; ++j) {
-                        if ((args.timing_aid & 8) && kc >= kStages) break;
-                        const uint64_t adesc = smem_desc(a_s + 32 * j, 16, 1024, kLayoutSw128);
-                        const uint64_t bdesc = smem_desc(b_s + 32 * j, 16, 1024, kLayoutSw128);
-                        tc_mma_nvf4(acc_col, adesc, bdesc, kIdesc, t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
+                        if (do_mma) {
+                            tc_mma_nvf4(acc_col, a_d, b_d, kIdesc, t_sfa, t_sfb, ks > 0 ? 1u : 0u);
+#pragma unroll
+                            for (int j = 1; j < 4; ++j)
+                                tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
+                                            t_sfa + 4 * j, t_sfb + 4 * j, 1u);
+                        }
+                    } else {
+                        for (int j = 0; j < nk; ++j) {
+                            if (do_cp) {
+                                tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
+                                tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            }
+                        }
+                        for (int j = 0; j < nk && do_mma; ++j)
+                            tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
+                                        t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * s);  // frees this smem stage once the MMAs above have read it
+                    if (++s == kStages) { s = 0; full_parity ^= 1u; }
                 }
                 if (ok) tc_commit(bar_acc_full + 8 * buf);  // accumulator of this tile complete
             }
