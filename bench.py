@@ -120,7 +120,8 @@ def algorithmic_work(cfg, members: int):
         "pos_gelu_norm_quant": ("hbm", rows * (4 * H + H + fp4(H) + 16 * r)),
         "gemm_qkv": ("tensor", 2.0 * rows * (3 * H + 1) * H + 2.0 * rows * r * (3 * H + 1)),
         "efla_scan": ("hbm", rows * ((3 * H + 1) * 4 + 4 * H)),
-        "add_norm_quant": ("hbm", rows * (4 * H + H + H + fp4(H) + 16 * r)),
+        "add_norm_quant": ("hbm", rows * (4 * H + H + H + fp4(H) + 4 * r)),
+        "norm_quant": ("hbm", rows * (H + fp4(H) + 16 * r)),
         "gemm_ff1_gelu_fp4": ("tensor", 2.0 * rows * F * H + 2.0 * rows * r * F),
         "gemm_ff2": ("tensor", 2.0 * rows * H * F + 2.0 * rows * r * H),
         "gemm_head": ("tensor", 2.0 * rows * V * H + 2.0 * rows * r * V),
@@ -274,7 +275,7 @@ def main():
             # (HBM: measured copy bandwidth / nominal 8 TB/s; GEMMs: 4 x measured sustained bf16 / nominal dense FP4 9 PF)
             bound, amount = work[name]
             per_wave = cfg.layers if name in ("gemm_qkv", "efla_scan", "gemm_ff1_gelu_fp4", "gemm_ff2") else \
-                (2 * cfg.layers if name == "add_norm_quant" else 1)
+                (cfg.layers if name in ("add_norm_quant", "norm_quant") else 1)
             rate = amount * n_waves * per_wave / (ms * 1e-3)
             if bound == "hbm":
                 ent.update(achieved=rate / 1e9, unit="GB/s", frac_measured=rate / 1e9 / peaks["hbm_gbs"], frac_nominal=rate / 8e12)
@@ -288,7 +289,7 @@ def main():
         if ent["name"] in work:
             bound, amount = work[ent["name"]]
             per_layer = cfg.layers if ent["name"] in ("gemm_qkv", "efla_scan", "gemm_ff1_gelu_fp4", "gemm_ff2") else \
-                (2 * cfg.layers if ent["name"] == "add_norm_quant" else 1)
+                (cfg.layers if ent["name"] in ("add_norm_quant", "norm_quant") else 1)
             n_wave_launches = args.steps * ((my_pairs * 2 + wave_members - 1) // wave_members) * per_layer
             dur = ent["launch_groups_ms"] * 1e-3 / n_wave_launches
             if bound == "hbm":

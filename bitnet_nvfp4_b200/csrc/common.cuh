@@ -105,6 +105,25 @@ __device__ __forceinline__ float gelu_scaled(float x, float act_scale) {
 // rounding boundary; the caller then takes gelu_q8_exact, so the integer is always the one the tanhf form gives.
 constexpr float kRoundBias = 12582912.0f;      // 1.5 * 2^23
 constexpr int kRoundBiasBits = 0x4B400000;     // its bit pattern
+// four signed bytes -> four floats (exact small integers)
+__device__ __forceinline__ void bytes4_to_float(uint32_t w, float* out) {
+    const uint32_t u = w ^ 0x80808080u;  // byte + 128 as an unsigned byte
+    const float off = kRoundBias + 128.0f;
+    out[0] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7650)) - off;
+    out[1] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7651)) - off;
+    out[2] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7652)) - off;
+    out[3] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7653)) - off;
+}
+// low bytes of four floats biased by kRoundBias -> one word of four int8
+__device__ __forceinline__ uint32_t biased4_to_bytes(float a, float b, float c, float d) {
+    return __byte_perm(__byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040), __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040), 0x5410);
+}
+// Residual-stream update of the reference's add_scaled_to_int8 step (src/cuda_kernels.cu:3033-3143):
+// clip8(old + rint(y * add_scale)), computed on biased floats; returns the new value still biased by kRoundBias.
+__device__ __forceinline__ float resid_add_biased(float oldf, float y, float add_scale) {
+    const float t_r = __fmul_rn(y, add_scale) + kRoundBias;
+    return fminf(fmaxf(t_r + oldf, kRoundBias - 127.0f), kRoundBias + 127.0f);
+}
 __device__ __forceinline__ float gelu_q8_fast(float x, float act_scale, bool& ok, float& clamped) {
     const float kB = 2.0f * 0.7978845608028654f * 1.4426950408889634f;  // 2 c log2(e)
     const float kA = kB * 0.044715f;

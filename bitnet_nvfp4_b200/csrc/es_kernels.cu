@@ -10,6 +10,7 @@
 // All reductions run in a fixed order so that every rank of a data-parallel job computes identical bits
 // (the reference uses unordered float atomics).
 
+#include <algorithm>
 #include <mutex>
 
 #include "common.cuh"
@@ -257,60 +258,147 @@ __global__ void __launch_bounds__(256) z_dense_kernel(const float* __restrict__ 
 // Rank-r form of Z: Z[i][j] = cscale * sum_p w_p * (sum_r A[p][i][r] * B[p][r][j]), pairs in ascending order with one fused
 // multiply-add per pair (reference: src/efla_lm_kernels.cu:1854-1890 applied to the factored noise). The inner sum is a
 // small integer, so it is formed exactly in fp32 from factors converted once while they are staged in shared memory.
-// Tile: 16 rows x 64 columns per CTA, 4 columns per thread, 32 pairs per shared-memory chunk.
+//
+// One launch covers a table of matrices (all ternary matrices of a model): block b locates its matrix and its
+// 32-row x 64-column tile by walking the table. Thread (ty, tx) of the 8 x 16 thread tile keeps a 4 x 4 block of Z in
+// registers, so one pair costs three shared-memory loads (weight, 4 values of A, 4 of B) for 32 arithmetic
+// instructions; factors arrive in chunks of PC pairs, the next chunk's global loads in flight while the current one is
+// consumed (registers -> the other shared-memory buffer, one barrier per chunk). With nshards > 1 a matrix whose rows
+// divide by nshards is computed only for the rows of this shard.
+constexpr int kZTileRows = 32, kZTileCols = 64, kZThreads = 128;
+
+__device__ __forceinline__ void z_shard_rows(int rows, int shard, int nshards, int& r0, int& nr) {
+    r0 = 0;
+    nr = rows;
+    if (nshards > 1 && rows >= nshards && (rows % nshards) == 0) { nr = rows / nshards; r0 = shard * nr; }
+}
+
 template <int RANK>
-__global__ void __launch_bounds__(256) z_lowrank_kernel(const float* __restrict__ pair_weights, const int8_t* __restrict__ A,
-                                                        long long A_ps, const int8_t* __restrict__ B, long long B_ps, int pairs,
-                                                        int rows, int cols, float cscale, float* __restrict__ Z) {
-    constexpr int PC = 32;  // pairs per shared-memory chunk
-    __shared__ float a_sh[PC][16][RANK];
-    __shared__ __align__(16) float b_sh[PC][RANK][64];
-    __shared__ float w_sh[PC];
-    const int tr = threadIdx.x >> 4;        // 0..15 row in tile
-    const int tc = (threadIdx.x & 15) * 4;  // column group in tile
-    const int i = blockIdx.y * 16 + tr;
-    const int j0 = blockIdx.x * 64 + tc;
-    float z[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int p0 = 0; p0 < pairs; p0 += PC) {
-        __syncthreads();
-        for (int e = threadIdx.x; e < PC * 16 * RANK; e += 256) {
-            const int pp = e / (16 * RANK), rem = e - pp * 16 * RANK;  // rem = row * RANK + r: contiguous in A
-            const int gi = blockIdx.y * 16 + rem / RANK;
-            float v = 0.0f;
-            if (p0 + pp < pairs && gi < rows) v = static_cast<float>(A[static_cast<size_t>(p0 + pp) * A_ps + static_cast<size_t>(blockIdx.y) * 16 * RANK + rem]);
-            (&a_sh[pp][0][0])[rem] = v;
+__global__ void __launch_bounds__(kZThreads) z_lowrank_tiles_kernel(const float* __restrict__ pair_weights, const ZLowrankDesc* __restrict__ descs,
+                                                                    int ndesc, const ZLowrankDesc single, int pairs, float cscale, int shard,
+                                                                    int nshards) {
+    constexpr int PC = RANK <= 2 ? 16 : 8;  // pairs per chunk
+    constexpr int TR = kZTileRows, TC = kZTileCols;
+    constexpr int A_PER_THREAD = PC * TR * RANK / kZThreads;        // bytes of A per thread and chunk
+    constexpr int B_PER_THREAD = PC * RANK * (TC / 4) / kZThreads;  // 4-byte words of B per thread and chunk
+    __shared__ __align__(16) float a_sh[2][PC][RANK][TR];
+    __shared__ __align__(16) float b_sh[2][PC][RANK][TC];
+    __shared__ float w_sh[2][PC];
+
+    // which matrix, which tile
+    ZLowrankDesc d = single;
+    int tile = static_cast<int>(blockIdx.x);
+    int r0 = 0, nr = d.rows;
+    if (ndesc > 0) {
+        int i = 0;
+        for (;;) {
+            d = descs[i];
+            z_shard_rows(d.rows, shard, nshards, r0, nr);
+            const int tiles = ((nr + TR - 1) / TR) * ((d.cols + TC - 1) / TC);
+            if (tile < tiles) break;
+            tile -= tiles;
+            if (++i >= ndesc) return;
         }
-        for (int e = threadIdx.x; e < PC * RANK * 64; e += 256) {
-            const int pp = e / (RANK * 64), rem = e - pp * RANK * 64, r = rem >> 6, c = rem & 63;
-            const int gj = blockIdx.x * 64 + c;
-            float v = 0.0f;
-            if (p0 + pp < pairs && gj < cols) v = static_cast<float>(B[static_cast<size_t>(p0 + pp) * B_ps + static_cast<size_t>(r) * cols + gj]);
-            b_sh[pp][r][c] = v;
+    }
+    const int tiles_x = (d.cols + TC - 1) / TC;
+    const int by = tile / tiles_x, bx = tile - by * tiles_x;
+    const int row_base = r0 + by * TR, row_end = r0 + nr, col_base = bx * TC;
+    const int tid = static_cast<int>(threadIdx.x), ty = tid >> 4, tx = tid & 15;
+    const bool b_words = ((reinterpret_cast<uintptr_t>(d.B) & 3) == 0) && ((d.B_ps & 3) == 0) && ((d.cols & 3) == 0);
+
+    int a_raw[A_PER_THREAD];
+    uint32_t b_raw[B_PER_THREAD];
+    float w_raw = 0.0f;
+    auto fetch = [&](int p0) {
+#pragma unroll
+        for (int k = 0; k < A_PER_THREAD; ++k) {
+            const int e = tid + k * kZThreads;
+            const int pp = e / (TR * RANK), rem = e - pp * (TR * RANK);  // rem = row * RANK + r: contiguous in A
+            const int row = row_base + rem / RANK;
+            a_raw[k] = (p0 + pp < pairs && row < row_end) ? static_cast<int>(d.A[static_cast<size_t>(p0 + pp) * d.A_ps + static_cast<size_t>(row_base) * RANK + rem]) : 0;
         }
-        if (threadIdx.x < PC) w_sh[threadIdx.x] = (p0 + threadIdx.x < pairs) ? pair_weights[p0 + threadIdx.x] : 0.0f;
-        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < B_PER_THREAD; ++k) {
+            const int e = tid + k * kZThreads;
+            const int pp = e / (RANK * (TC / 4)), rem = e - pp * (RANK * (TC / 4)), r = rem / (TC / 4), c = (rem - r * (TC / 4)) * 4;
+            const int col = col_base + c;
+            uint32_t v = 0;
+            if (p0 + pp < pairs && col < d.cols) {
+                const int8_t* src = d.B + static_cast<size_t>(p0 + pp) * d.B_ps + static_cast<size_t>(r) * d.cols + col;
+                if (b_words) {
+                    v = *reinterpret_cast<const uint32_t*>(src);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (col + q < d.cols) v |= (static_cast<uint32_t>(static_cast<uint8_t>(src[q]))) << (8 * q);
+                }
+            }
+            b_raw[k] = v;
+        }
+        if (tid < PC) w_raw = (p0 + tid < pairs) ? pair_weights[p0 + tid] : 0.0f;
+    };
+    auto stage = [&](int buf) {
+#pragma unroll
+        for (int k = 0; k < A_PER_THREAD; ++k) {
+            const int e = tid + k * kZThreads;
+            const int pp = e / (TR * RANK), rem = e - pp * (TR * RANK);
+            a_sh[buf][pp][rem % RANK][rem / RANK] = static_cast<float>(a_raw[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < B_PER_THREAD; ++k) {
+            const int e = tid + k * kZThreads;
+            const int pp = e / (RANK * (TC / 4)), rem = e - pp * (RANK * (TC / 4)), r = rem / (TC / 4), c = (rem - r * (TC / 4)) * 4;
+            float f[4];
+            bytes4_to_float(b_raw[k], f);
+            *reinterpret_cast<float4*>(&b_sh[buf][pp][r][c]) = make_float4(f[0], f[1], f[2], f[3]);
+        }
+        if (tid < PC) w_sh[buf][tid] = w_raw;
+    };
+
+    float z[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) z[i][j] = 0.0f;
+
+    fetch(0);
+    stage(0);
+    __syncthreads();
+    int buf = 0;
+    for (int p0 = 0; p0 < pairs; p0 += PC, buf ^= 1) {
+        const bool more = p0 + PC < pairs;
+        if (more) fetch(p0 + PC);
         const int cnt = min(PC, pairs - p0);
 #pragma unroll 4
         for (int pp = 0; pp < cnt; ++pp) {
-            const float w = w_sh[pp];
-            float e[4] = {0.f, 0.f, 0.f, 0.f};
+            const float w = w_sh[buf][pp];
+            float e[4][4];
 #pragma unroll
             for (int r = 0; r < RANK; ++r) {
-                const float a = a_sh[pp][tr][r];
-                const float4 b4 = *reinterpret_cast<const float4*>(&b_sh[pp][r][tc]);
-                e[0] = fmaf(a, b4.x, e[0]);  // exact: small integers
-                e[1] = fmaf(a, b4.y, e[1]);
-                e[2] = fmaf(a, b4.z, e[2]);
-                e[3] = fmaf(a, b4.w, e[3]);
+                const float4 a4 = *reinterpret_cast<const float4*>(&a_sh[buf][pp][r][ty * 4]);
+                const float4 b4 = *reinterpret_cast<const float4*>(&b_sh[buf][pp][r][tx * 4]);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) e[i][j] = r == 0 ? __fmul_rn(av[i], bv[j]) : fmaf(av[i], bv[j], e[i][j]);  // exact: small integers
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) z[c] = fmaf(w, e[c], z[c]);
-        }
-    }
-    if (i < rows) {
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-            if (j0 + c < cols) Z[static_cast<size_t>(i) * cols + j0 + c] = __fmul_rn(cscale, z[c]);
+                for (int j = 0; j < 4; ++j) z[i][j] = fmaf(w, e[i][j], z[i][j]);
+        }
+        if (more) stage(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = row_base + ty * 4 + i;
+        if (row >= row_end) continue;
+        float* dst = d.Z + static_cast<size_t>(row) * d.cols + col_base + tx * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (col_base + tx * 4 + j < d.cols) dst[j] = __fmul_rn(cscale, z[i][j]);
     }
 }
 
@@ -417,6 +505,36 @@ int get_scratch(size_t floats, float** out) {
     *out = s.ptr;
     return BNF4_OK;
 }
+
+}  // namespace
+
+// d_descs: the table in device memory (nullptr with ndesc == 0: the single matrix h_descs[0], passed by value).
+// h_descs: the same table in host memory, for the grid size.
+int z_lowrank_launch(const float* pair_weights, const ZLowrankDesc* d_descs, const ZLowrankDesc* h_descs, int ndesc, int pairs, int rank,
+                     float cscale, int shard, int nshards, cudaStream_t st) {
+    if (rank < 1 || rank > 4) return set_error(BNF4_ERR_INVALID, "compute_z_lowrank: rank=%d outside [1,4]", rank);
+    if (nshards < 1 || shard < 0 || shard >= nshards) return set_error(BNF4_ERR_INVALID, "compute_z_lowrank: shard %d of %d", shard, nshards);
+    if (pairs <= 0) return set_error(BNF4_ERR_INVALID, "compute_z_lowrank: pairs=%d", pairs);
+    long long tiles = 0;
+    for (int i = 0; i < std::max(ndesc, 1); ++i) {
+        int nr = h_descs[i].rows;
+        if (ndesc > 0 && nshards > 1 && nr >= nshards && (nr % nshards) == 0) nr /= nshards;
+        tiles += static_cast<long long>((nr + kZTileRows - 1) / kZTileRows) * ((h_descs[i].cols + kZTileCols - 1) / kZTileCols);
+    }
+    if (tiles <= 0) return BNF4_OK;
+    if (tiles > 0x7fffffffLL) return set_error(BNF4_ERR_INVALID, "compute_z_lowrank: too many tiles");
+    const unsigned grid = static_cast<unsigned>(tiles);
+    const ZLowrankDesc single = h_descs[0];
+    switch (rank) {
+        case 1: z_lowrank_tiles_kernel<1><<<grid, kZThreads, 0, st>>>(pair_weights, d_descs, ndesc, single, pairs, cscale, shard, nshards); break;
+        case 2: z_lowrank_tiles_kernel<2><<<grid, kZThreads, 0, st>>>(pair_weights, d_descs, ndesc, single, pairs, cscale, shard, nshards); break;
+        case 3: z_lowrank_tiles_kernel<3><<<grid, kZThreads, 0, st>>>(pair_weights, d_descs, ndesc, single, pairs, cscale, shard, nshards); break;
+        default: z_lowrank_tiles_kernel<4><<<grid, kZThreads, 0, st>>>(pair_weights, d_descs, ndesc, single, pairs, cscale, shard, nshards); break;
+    }
+    return check_launch("z_lowrank_tiles_kernel");
+}
+
+namespace {
 
 int sumsq_into(const float* Z, int n, float* sumsq, cudaStream_t st) {
     const int nblocks = (n + 255) / 256;
@@ -525,20 +643,26 @@ int bnf4_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, 
     return sumsq_into(Z, n, sumsq, S(stream));
 }
 
+int bnf4_compute_z_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
+                           long long B_pair_stride, int pairs, int rows, int cols, int rank, float cscale, float* Z, void* stream) {
+    if (rows <= 0 || cols <= 0) return BNF4_OK;
+    if (!pair_weights || !A || !B || !Z) return set_error(BNF4_ERR_INVALID, "compute_z_lowrank: null pointer");
+    const ZLowrankDesc d = {A, A_pair_stride, B, B_pair_stride, Z, rows, cols};
+    return z_lowrank_launch(pair_weights, nullptr, &d, 0, pairs, rank, cscale, 0, 1, S(stream));
+}
+
+int bnf4_sumsq(const float* Z, int n, float* sumsq, void* stream) {
+    if (n <= 0) return BNF4_OK;
+    if (!Z || !sumsq) return set_error(BNF4_ERR_INVALID, "sumsq: null pointer");
+    return sumsq_into(Z, n, sumsq, S(stream));
+}
+
 int bnf4_compute_z_sumsq_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
                                  long long B_pair_stride, int pairs, int rows, int cols, int rank, float cscale, float* Z,
                                  float* sumsq, void* stream) {
     if (rows <= 0 || cols <= 0) return BNF4_OK;
-    if (!pair_weights || !A || !B || !Z || !sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: null pointer");
-    if (rank < 1 || rank > 4) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: rank=%d outside [1,4]", rank);
-    const dim3 grid((cols + 63) / 64, (rows + 15) / 16);
-    switch (rank) {
-        case 1: z_lowrank_kernel<1><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
-        case 2: z_lowrank_kernel<2><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
-        case 3: z_lowrank_kernel<3><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
-        default: z_lowrank_kernel<4><<<grid, 256, 0, S(stream)>>>(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, cscale, Z); break;
-    }
-    const int rc = check_launch("z_lowrank_kernel");
+    if (!sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq_lowrank: null pointer");
+    const int rc = bnf4_compute_z_lowrank(pair_weights, A, A_pair_stride, B, B_pair_stride, pairs, rows, cols, rank, cscale, Z, stream);
     if (rc) return rc;
     return sumsq_into(Z, rows * cols, sumsq, S(stream));
 }

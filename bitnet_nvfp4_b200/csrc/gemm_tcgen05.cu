@@ -162,6 +162,12 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
     return v;
 }
+// prmt.b32 in its default mode: a selector nibble with bit 3 set replicates the sign of the selected byte
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading byte
@@ -432,6 +438,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 fetch_ctx(tile + gridDim.x, nxt);
             }
 
+            // EPI_ADD_I8: this thread's 32 bytes of the residual stream, requested before the wait for the accumulator
+            int4 res0 = make_int4(0, 0, 0, 0), res1 = make_int4(0, 0, 0, 0);
+            bool res_vec = false;
+            if constexpr (EPI == EPI_ADD_I8) {
+                if (row_ok && chunk_ok) {
+                    const int8_t* xr = p.resid + static_cast<size_t>(row) * p.ld_resid + col0;
+                    res_vec = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && (col0 + 32 <= p.n);
+                    if (res_vec) {
+                        res0 = *reinterpret_cast<const int4*>(xr);
+                        res1 = *reinterpret_cast<const int4*>(xr + 16);
+                    }
+                }
+            }
+
             ok = mbar_wait(bar_acc_full + 8 * buf, (it >> 1) & 1, 3);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -527,6 +547,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
                             if (col0 + j < p.n) drow[j] = v[j];
+                    }
+                }
+            } else if constexpr (EPI == EPI_ADD_I8) {
+                if (row_ok) {
+                    int8_t* xr = p.resid + static_cast<size_t>(row) * p.ld_resid + col0;
+                    if (res_vec) {
+                        const uint32_t rw[8] = {static_cast<uint32_t>(res0.x), static_cast<uint32_t>(res0.y), static_cast<uint32_t>(res0.z), static_cast<uint32_t>(res0.w),
+                                                static_cast<uint32_t>(res1.x), static_cast<uint32_t>(res1.y), static_cast<uint32_t>(res1.z), static_cast<uint32_t>(res1.w)};
+                        // rint(v * add_scale) as the low 16 bits of the biased float, added to the sign-extended old bytes
+                        // and clipped with packed 16-bit integer operations (two elements per instruction)
+                        uint32_t upd[8];
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            uint32_t tb[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) tb[e] = __float_as_uint(__fmul_rn(v[4 * g + e], p.add_scale) + kRoundBias);
+                            const uint32_t r01 = __byte_perm(tb[0], tb[1], 0x5410), r23 = __byte_perm(tb[2], tb[3], 0x5410);
+                            const uint32_t o01 = prmt_b32(rw[g], 0u, 0x9180u), o23 = prmt_b32(rw[g], 0u, 0xB3A2u);
+                            const uint32_t s01 = __vmins2(__viaddmax_s16x2(r01, o01, 0xff81ff81u), 0x007f007fu);
+                            const uint32_t s23 = __vmins2(__viaddmax_s16x2(r23, o23, 0xff81ff81u), 0x007f007fu);
+                            upd[g] = __byte_perm(s01, s23, 0x6420);
+                        }
+                        reinterpret_cast<int4*>(xr)[0] = make_int4(static_cast<int>(upd[0]), static_cast<int>(upd[1]), static_cast<int>(upd[2]), static_cast<int>(upd[3]));
+                        reinterpret_cast<int4*>(xr)[1] = make_int4(static_cast<int>(upd[4]), static_cast<int>(upd[5]), static_cast<int>(upd[6]), static_cast<int>(upd[7]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) {
+                                const float t = resid_add_biased(static_cast<float>(xr[j]), v[j], p.add_scale);
+                                xr[j] = static_cast<int8_t>(__float_as_int(t) - kRoundBiasBits);
+                            }
+                        }
                     }
                 }
             } else {
@@ -691,6 +743,7 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     if (p.group_cols > 0 && (p.group_cols % 32) != 0) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: group_cols must be a multiple of 32");
     if (p.epilogue == EPI_F32 && !p.d) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null D");
     if (p.epilogue == EPI_GELU_I8 && !p.d_i8) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null int8 D");
+    if (p.epilogue == EPI_ADD_I8 && (!p.resid || p.ld_resid < p.n)) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: the residual epilogue needs resid and ld_resid >= n");
     if (p.epilogue == EPI_GELU_FP4) {
         if (!p.d_codes || !p.d_sf) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null FP4 D");
         if ((p.n % 32) != 0) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: FP4 output needs n %% 32 == 0");
@@ -740,6 +793,7 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
         case EPI_F32: return launch_t<EPI_F32>(ma, mb, md, args, grid, stream);
         case EPI_GELU_I8: return launch_t<EPI_GELU_I8>(ma, mb, md, args, grid, stream);
         case EPI_GELU_FP4: return launch_t<EPI_GELU_FP4>(ma, mb, md, args, grid, stream);
+        case EPI_ADD_I8: return launch_t<EPI_ADD_I8>(ma, mb, md, args, grid, stream);
     }
     return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: unknown epilogue %d", p.epilogue);
 }

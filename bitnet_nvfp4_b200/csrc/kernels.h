@@ -37,6 +37,7 @@ enum GemmEpilogue : int {
     EPI_F32 = BNF4_EPI_F32,            // fp32 D
     EPI_GELU_I8 = BNF4_EPI_GELU_I8,    // int8 D = clip8(rint(gelu(v) * act_scale))
     EPI_GELU_FP4 = BNF4_EPI_GELU_FP4,  // the above re-quantised to e2m1 codes + ue4m3 scales (+ int8 copy, + t of the next GEMM)
+    EPI_ADD_I8 = BNF4_EPI_ADD_I8,      // int8 residual stream updated in place: clip8(resid + rint(v * add_scale))
 };
 
 using GemmParams = bnf4_gemm_desc;
@@ -50,6 +51,18 @@ using EflaParams = bnf4_efla_desc;
 int efla_launch(const EflaParams& p, cudaStream_t stream);
 extern int g_efla_cols_per_lane;
 extern int g_efla_mma;
+
+// Rank-r noise sums Z of a table of matrices in one launch (es_kernels.cu).
+struct ZLowrankDesc {
+    const int8_t* A;  // [pairs][rows][rank]
+    long long A_ps;
+    const int8_t* B;  // [pairs][rank][cols]
+    long long B_ps;
+    float* Z;         // [rows][cols]
+    int rows, cols;
+};
+int z_lowrank_launch(const float* pair_weights, const ZLowrankDesc* d_descs, const ZLowrankDesc* h_descs, int ndesc, int pairs, int rank,
+                     float cscale, int shard, int nshards, cudaStream_t stream);
 
 void count_launch();
 

@@ -24,11 +24,11 @@ constexpr float kCRankBase = 0.6123724356957945f;  // sqrt(3/8)
 // Kernel classes for the optional timing breakdown (bnf4_model_get_timing).
 enum KernelClass : int {
     KC_GEN_NOISE = 0, KC_BETA_BIAS, KC_EMBED, KC_GEMM_WIN, KC_POS_GELU_NORM, KC_GEMM_QKV, KC_EFLA, KC_ADD_NORM, KC_GEMM_FF1,
-    KC_GEMM_FF2, KC_GEMM_HEAD, KC_CROSS_ENTROPY, KC_UPDATE_Z, KC_UPDATE_APPLY, KC_REQUANTIZE, kNumClasses
+    KC_GEMM_FF2, KC_GEMM_HEAD, KC_CROSS_ENTROPY, KC_UPDATE_Z, KC_UPDATE_APPLY, KC_REQUANTIZE, KC_NORM_QUANT, kNumClasses
 };
 const char* const kClassNames[kNumClasses] = {"gen_noise", "beta_bias", "embed_quant", "gemm_win", "pos_gelu_norm_quant", "gemm_qkv",
                                               "efla_scan", "add_norm_quant", "gemm_ff1_gelu_fp4", "gemm_ff2", "gemm_head",
-                                              "cross_entropy", "update_z_sumsq", "update_apply", "requantize_weights"};
+                                              "cross_entropy", "update_z_sumsq", "update_apply", "requantize_weights", "norm_quant"};
 
 // One entry of the per-step noise table: dst[pair][...] filled from the counter hash.
 struct GenDesc {
@@ -111,7 +111,8 @@ struct Model {
     float* y_emb;
     int32_t *t_a, *t_f;
     // update scratch
-    float *Z, *sumsq, *inv_rms;
+    float *Z, *Z_all, *sumsq, *inv_rms;
+    ZLowrankDesc *zdesc, *zdesc_ext;  // device tables of the update's matrices: Z inside Z_all / inside a caller's buffer
     int launches_per_wave = 0;
 
     // optional per-kernel-class timing with CUDA events on the launching stream
@@ -309,23 +310,29 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
             TRY(gemm_nvfp4_launch(g, st));
             ++launches;
         }
-        // ff2 -> y
-        TRY(gemm(KC_GEMM_FF2, m.a_f, m.sf_f, m.q_ff2[l], m.sfq_ff2[l], H, F, m.s_f, m.y, H, m.A_ff2[l] + P0 * H * r, static_cast<long long>(H) * r, m.t_f,
-                 r, m.s_f, 0));
-        ++launches;
-        {   // residual add + abs-mean norm -> a_h; t for the next layer's qkv or the head
+        {   // ff2, added into the residual stream by the epilogue: the fp32 product never leaves the SM
+            TimedScope ts(m, KC_GEMM_FF2, st);
+            bnf4_gemm_desc g = {};
+            g.a = m.a_f; g.b = m.q_ff2[l]; g.sfa = m.sf_f; g.sfb = m.sfq_ff2[l]; g.m = rows; g.n = H; g.k = F; g.alpha = m.s_f;
+            g.epilogue = EPI_ADD_I8; g.resid = m.x_q; g.ld_resid = H; g.add_scale = m.cfg.mlp_residual_scale;
+            g.rank = rank; g.rows_per_member = R; g.lora_t = m.t_f; g.t_stride = r; g.lora_A = m.A_ff2[l] + P0 * H * r;
+            g.lora_A_pair_stride = static_cast<long long>(H) * r; g.lora_scale = (sigma * m.s_f) * m.c_r;
+            TRY(gemm_nvfp4_launch(g, st));
+            ++launches;
+        }
+        {   // abs-mean norm of the residual stream -> a_h; t for the next layer's qkv or the head
             const bool last = (l == L - 1);
-            TimedScope ts(m, KC_ADD_NORM, st);
+            TimedScope ts(m, KC_NORM_QUANT, st);
             bnf4_rowquant_desc p = {};
             p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
-            p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.add_scale = m.cfg.mlp_residual_scale; p.norm_scale = m.cfg.ln_scale;
+            p.in_i8 = m.x_q; p.ld_in = H; p.norm_scale = m.cfg.ln_scale;
             p.out_codes = m.a_h; p.out_sf = m.sf_h;
             if (pert) {
                 if (last) { p.tvec = m.tB_head + P0 * r * H; p.tvec_pair_stride = static_cast<long long>(r) * H; p.nvec = r; }
                 else { p.tvec = m.tB_qkv[l + 1] + P0 * 4 * r * H; p.tvec_pair_stride = static_cast<long long>(4) * r * H; p.nvec = 4 * r; }
                 p.t_out = m.t_a;
             }
-            TRY(rowquant_dispatch(FE_ADD_ABSMEAN, p, st));
+            TRY(rowquant_dispatch(FE_ABSMEAN, p, st));
             ++launches;
         }
     }
@@ -346,6 +353,103 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
 using namespace bnf4;
 static inline cudaStream_t S(void* s) { return static_cast<cudaStream_t>(s); }
 static inline Model* M(void* h) { return static_cast<Model*>(h); }
+
+namespace {
+
+// One ternary matrix of the model as the update sees it: weights, shadow, the two noise factors and its shape.
+struct UpdMatrix {
+    int8_t* w;
+    float* shadow;
+    const int8_t* A;
+    long long A_stride;
+    const int8_t* Bt;
+    long long B_stride;
+    int rows, cols;
+};
+
+// Fixed order = order of the RMS-EMA slots.
+std::vector<UpdMatrix> update_matrices(Model& m) {
+    const int V = m.V, H = m.H, F = m.F, L = m.L, r = m.r;
+    const size_t hh = static_cast<size_t>(H) * H, hf = static_cast<size_t>(H) * F;
+    std::vector<UpdMatrix> v;
+    v.push_back({m.emb, m.sh_emb, m.embA, static_cast<long long>(V) * r, m.embB, static_cast<long long>(H) * r, V, H});
+    v.push_back({m.win, m.sh_win, m.A_win, static_cast<long long>(H) * r, m.tB_win, static_cast<long long>(H) * r, H, H});
+    for (int l = 0; l < L; ++l) {
+        const long long As = static_cast<long long>(3 * H + 1) * r, Bs = static_cast<long long>(4) * r * H;
+        int8_t* ws[4] = {m.wq + l * hh, m.wk + l * hh, m.wv + l * hh, m.wbeta + static_cast<size_t>(l) * H};
+        float* ss[4] = {m.sh_wq + l * hh, m.sh_wk + l * hh, m.sh_wv + l * hh, m.sh_wbeta + static_cast<size_t>(l) * H};
+        const int grows[4] = {H, H, H, 1};
+        for (int g = 0; g < 4; ++g)
+            v.push_back({ws[g], ss[g], m.A_qkv[l] + static_cast<size_t>(g) * H * r, As, m.tB_qkv[l] + static_cast<size_t>(g) * r * H, Bs, grows[g], H});
+        v.push_back({m.ff1 + l * hf, m.sh_ff1 + l * hf, m.A_ff1[l], static_cast<long long>(F) * r, m.tB_ff1[l], static_cast<long long>(r) * H, F, H});
+        v.push_back({m.ff2 + l * hf, m.sh_ff2 + l * hf, m.A_ff2[l], static_cast<long long>(H) * r, m.tB_ff2[l], static_cast<long long>(r) * F, H, F});
+    }
+    v.push_back({m.head, m.sh_head, m.A_head, static_cast<long long>(V) * r, m.tB_head, static_cast<long long>(H) * r, V, H});
+    return v;
+}
+
+// Device table of the matrices with Z laid out back to back from z_base (the order of update_matrices).
+std::vector<ZLowrankDesc> z_descs(Model& m, float* z_base) {
+    std::vector<ZLowrankDesc> d;
+    long long off = 0;
+    for (const UpdMatrix& x : update_matrices(m)) {
+        d.push_back({x.A, x.A_stride, x.Bt, x.B_stride, z_base + off, x.rows, x.cols});
+        off += static_cast<long long>(x.rows) * x.cols;
+    }
+    return d;
+}
+
+// Z of all matrices (the rows of this shard) in one launch. z_ext == nullptr: into the model's own buffer.
+int update_z(Model& m, const float* pair_weights, int shard, int nshards, float* z_ext, cudaStream_t st) {
+    const std::vector<ZLowrankDesc> h = z_descs(m, z_ext != nullptr ? z_ext : m.Z_all);
+    const ZLowrankDesc* dtab = m.zdesc;
+    if (z_ext != nullptr) {
+        // pageable source: the copy is staged before the call returns, so the host vector may go out of scope
+        TRY(check_cuda(cudaMemcpyAsync(m.zdesc_ext, h.data(), h.size() * sizeof(ZLowrankDesc), cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(zdesc)"));
+        dtab = m.zdesc_ext;
+    }
+    TimedScope ts(m, KC_UPDATE_Z, st, 1);
+    return z_lowrank_launch(pair_weights, dtab, h.data(), static_cast<int>(h.size()), m.pairs_step, m.r, m.c_r, shard, nshards, st);
+}
+
+// Applies the precomputed Z of every matrix, then updates the fp32 vectors and re-quantises the base weights.
+int update_apply(Model& m, const float* pair_weights, const float* z_all, const bnf4_update_cfg* u, cudaStream_t st) {
+    const int P = m.pairs_step;
+    const int V = m.V, H = m.H, L = m.L;
+    const float thresh = u->thresh * std::sqrt(static_cast<float>(P));
+    int slot = 0;
+    long long off = 0;
+    for (const UpdMatrix& x : update_matrices(m)) {
+        float* ema = m.rms_ema + (slot++);
+        const int n = x.rows * x.cols;
+        const float* Z = z_all + off;
+        off += n;
+        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
+        {
+            TimedScope ts(m, KC_UPDATE_Z, st, 2);
+            TRY(bnf4_sumsq(Z, n, m.sumsq, st));
+        }
+        TimedScope ts2(m, KC_UPDATE_APPLY, st, 2);
+        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
+        TRY(bnf4_update_shadow_ternary_device(x.w, x.shadow, Z, n, m.inv_rms, u->lr, thresh, st));
+    }
+    // fp32 vectors (reference: update_vector on the host, src/train_efla_lm.cpp:5648-5657)
+    auto vec = [&](float* v, int n, uint64_t salt) {
+        float* ema = m.rms_ema + (slot++);
+        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
+        TimedScope ts(m, KC_UPDATE_Z, st, 5);
+        TRY(bnf4_compute_z_sumsq(pair_weights, m.pair_seeds, salt, P, n, m.cfg.use_clt, m.cfg.clt_k, m.Z, m.sumsq, st));
+        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
+        return bnf4_update_vector_device(v, m.Z, n, m.inv_rms, u->lr, thresh, st);
+    };
+    TRY(vec(m.head_bias, V, kSaltHeadBias));
+    TRY(vec(m.beta_bias, L, kSaltBetaBias));
+    if (u->train_pos) TRY(vec(m.pos, m.T * H, kSaltPos));
+    TimedScope ts(m, KC_REQUANTIZE, st, 2 + 3 * L);
+    return quantize_base(m, st);
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -428,9 +532,20 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     }
     A_(qkv, Mr * m->FC); A_(y, Mr * H); A_(bb_eff, static_cast<size_t>(L) * W); A_(ce_partial, static_cast<size_t>(W) * 16); A_(losses, W);
     A_(t_a, Mr * 4 * r); A_(t_f, Mr * r);
-    A_(Z, std::max(hf, static_cast<size_t>(T) * H)); A_(sumsq, 1); A_(inv_rms, 1);
+    A_(Z, static_cast<size_t>(T) * H + V + L); A_(sumsq, 1); A_(inv_rms, 1);
+    {
+        size_t zn = 0;
+        for (const UpdMatrix& x : update_matrices(*m)) zn += static_cast<size_t>(x.rows) * x.cols;
+        const size_t nd = update_matrices(*m).size();
+        A_(Z_all, zn); A_(zdesc, nd); A_(zdesc_ext, nd);
+    }
 #undef A_
     if (rc) { bnf4_model_destroy(m); return rc; }
+    {
+        const std::vector<ZLowrankDesc> zd = z_descs(*m, m->Z_all);
+        rc = check_cuda(cudaMemcpy(m->zdesc, zd.data(), zd.size() * sizeof(ZLowrankDesc), cudaMemcpyHostToDevice), "cudaMemcpy(zdesc)");
+        if (rc) { bnf4_model_destroy(m); return rc; }
+    }
 
     if (m->dedup_input) {
         std::vector<uint8_t> ident(V);
@@ -615,51 +730,45 @@ int bnf4_model_eval_base(void* handle, float* loss, void* stream) {
 int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update_cfg* u, void* stream) {
     if (!handle || !pair_weights || !u) return set_error(BNF4_ERR_INVALID, "model_update: null argument");
     Model& m = *M(handle);
-    const int P = m.pairs_step;
-    if (P <= 0) return set_error(BNF4_ERR_INVALID, "model_update: no prepared step");
-    cudaStream_t st = S(stream);
-    const int V = m.V, H = m.H, F = m.F, L = m.L, r = m.r;
-    const float thresh = u->thresh * std::sqrt(static_cast<float>(P));
-    int slot = 0;
-    auto matrix = [&](int8_t* w, float* shadow, const int8_t* A, long long A_stride, const int8_t* Bt, long long B_stride, int rows, int cols) {
-        float* ema = m.rms_ema + (slot++);
-        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
-        {
-            TimedScope ts(m, KC_UPDATE_Z, st, 3);
-            TRY(bnf4_compute_z_sumsq_lowrank(pair_weights, A, A_stride, Bt, B_stride, P, rows, cols, r, m.c_r, m.Z, m.sumsq, st));
-        }
-        TimedScope ts2(m, KC_UPDATE_APPLY, st, 2);
-        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, rows * cols, m.inv_rms, st));
-        return bnf4_update_shadow_ternary_device(w, shadow, m.Z, rows * cols, m.inv_rms, u->lr, thresh, st);
-    };
-    const size_t hh = static_cast<size_t>(H) * H, hf = static_cast<size_t>(H) * F;
-    TRY(matrix(m.emb, m.sh_emb, m.embA, static_cast<long long>(V) * r, m.embB, static_cast<long long>(H) * r, V, H));
-    TRY(matrix(m.win, m.sh_win, m.A_win, static_cast<long long>(H) * r, m.tB_win, static_cast<long long>(H) * r, H, H));
-    for (int l = 0; l < L; ++l) {
-        const long long As = static_cast<long long>(3 * H + 1) * r, Bs = static_cast<long long>(4) * r * H;
-        int8_t* ws[4] = {m.wq + l * hh, m.wk + l * hh, m.wv + l * hh, m.wbeta + static_cast<size_t>(l) * H};
-        float* ss[4] = {m.sh_wq + l * hh, m.sh_wk + l * hh, m.sh_wv + l * hh, m.sh_wbeta + static_cast<size_t>(l) * H};
-        const int grows[4] = {H, H, H, 1};
-        for (int g = 0; g < 4; ++g)
-            TRY(matrix(ws[g], ss[g], m.A_qkv[l] + static_cast<size_t>(g) * H * r, As, m.tB_qkv[l] + static_cast<size_t>(g) * r * H, Bs, grows[g], H));
-        TRY(matrix(m.ff1 + l * hf, m.sh_ff1 + l * hf, m.A_ff1[l], static_cast<long long>(F) * r, m.tB_ff1[l], static_cast<long long>(r) * H, F, H));
-        TRY(matrix(m.ff2 + l * hf, m.sh_ff2 + l * hf, m.A_ff2[l], static_cast<long long>(H) * r, m.tB_ff2[l], static_cast<long long>(r) * F, H, F));
+    if (m.pairs_step <= 0) return set_error(BNF4_ERR_INVALID, "model_update: no prepared step");
+    TRY(update_z(m, pair_weights, 0, 1, nullptr, S(stream)));
+    return update_apply(m, pair_weights, m.Z_all, u, S(stream));
+}
+
+int bnf4_model_update_z_layout(void* handle, int nshards, int max_entries, long long* offsets, long long* elems, int* sharded,
+                               long long* total_elems) {
+    if (!handle || nshards < 1) { set_error(BNF4_ERR_INVALID, "model_update_z_layout: bad argument"); return -1; }
+    Model& m = *M(handle);
+    const std::vector<UpdMatrix> mats = update_matrices(m);
+    if (static_cast<int>(mats.size()) > max_entries && (offsets || elems || sharded)) {
+        set_error(BNF4_ERR_INVALID, "model_update_z_layout: %d entries needed, room for %d", static_cast<int>(mats.size()), max_entries);
+        return -1;
     }
-    TRY(matrix(m.head, m.sh_head, m.A_head, static_cast<long long>(V) * r, m.tB_head, static_cast<long long>(H) * r, V, H));
-    // fp32 vectors (reference: update_vector on the host, src/train_efla_lm.cpp:5648-5657)
-    auto vec = [&](float* v, int n, uint64_t salt) {
-        float* ema = m.rms_ema + (slot++);
-        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
-        TimedScope ts(m, KC_UPDATE_Z, st, 5);
-        TRY(bnf4_compute_z_sumsq(pair_weights, m.pair_seeds, salt, P, n, m.cfg.use_clt, m.cfg.clt_k, m.Z, m.sumsq, st));
-        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
-        return bnf4_update_vector_device(v, m.Z, n, m.inv_rms, u->lr, thresh, st);
-    };
-    TRY(vec(m.head_bias, V, kSaltHeadBias));
-    TRY(vec(m.beta_bias, L, kSaltBetaBias));
-    if (u->train_pos) TRY(vec(m.pos, m.T * H, kSaltPos));
-    TimedScope ts(m, KC_REQUANTIZE, st, 2 + 3 * L);
-    return quantize_base(m, st);
+    long long off = 0;
+    for (size_t i = 0; i < mats.size(); ++i) {
+        const long long n = static_cast<long long>(mats[i].rows) * mats[i].cols;
+        if (offsets) offsets[i] = off;
+        if (elems) elems[i] = n;
+        if (sharded) sharded[i] = (nshards > 1 && mats[i].rows >= nshards && (mats[i].rows % nshards) == 0) ? 1 : 0;
+        off += n;
+    }
+    if (total_elems) *total_elems = off;
+    return static_cast<int>(mats.size());
+}
+
+int bnf4_model_update_z(void* handle, const float* pair_weights, int shard, int nshards, float* z_all, void* stream) {
+    if (!handle || !pair_weights || !z_all) return set_error(BNF4_ERR_INVALID, "model_update_z: null argument");
+    if (nshards < 1 || shard < 0 || shard >= nshards) return set_error(BNF4_ERR_INVALID, "model_update_z: shard %d of %d", shard, nshards);
+    Model& m = *M(handle);
+    if (m.pairs_step <= 0) return set_error(BNF4_ERR_INVALID, "model_update_z: no prepared step");
+    return update_z(m, pair_weights, shard, nshards, z_all, S(stream));
+}
+
+int bnf4_model_update_apply(void* handle, const float* pair_weights, const float* z_all, const bnf4_update_cfg* u, void* stream) {
+    if (!handle || !pair_weights || !z_all || !u) return set_error(BNF4_ERR_INVALID, "model_update_apply: null argument");
+    Model& m = *M(handle);
+    if (m.pairs_step <= 0) return set_error(BNF4_ERR_INVALID, "model_update_apply: no prepared step");
+    return update_apply(m, pair_weights, z_all, u, S(stream));
 }
 
 int bnf4_model_set_timing(void* handle, int enable) {

@@ -269,8 +269,8 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
 }
 
 // ------------------------------------------------------------------------------------------------
-// Float-domain fast path for the three front-ends the population forward runs once or twice per layer
-// (embedding + rank-r noise, + pos / GELU / abs-mean norm, residual add + abs-mean norm).
+// Float-domain fast path for the front-ends the population forward runs once or twice per layer
+// (embedding + rank-r noise, + pos / GELU / abs-mean norm, residual add + abs-mean norm, abs-mean norm of int8 rows).
 //
 // Same results as rowquant_kernel, fewer and cheaper instructions: int8 values travel as exact small integers in
 // fp32 ("v"), or biased by 1.5 * 2^23 ("t = v + M", whose low byte is the int8), so that
@@ -285,20 +285,6 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
     return v;
 }
-// four signed bytes -> four floats
-__device__ __forceinline__ void bytes4_to_float(uint32_t w, float* out) {
-    const uint32_t u = w ^ 0x80808080u;  // byte + 128 as an unsigned byte
-    const float off = kRoundBias + 128.0f;
-    out[0] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7650)) - off;
-    out[1] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7651)) - off;
-    out[2] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7652)) - off;
-    out[3] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7653)) - off;
-}
-// low bytes of four biased floats -> one word
-__device__ __forceinline__ uint32_t biased4_to_bytes(float a, float b, float c, float d) {
-    return __byte_perm(__byte_perm(__float_as_uint(a), __float_as_uint(b), 0x0040), __byte_perm(__float_as_uint(c), __float_as_uint(d), 0x0040), 0x5410);
-}
-
 // Element ownership as in rowquant_kernel: lane l owns the 16-element scale blocks l, l + 32, ... (NB of them).
 template <int FE, int NB>
 __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowquant_fast_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
@@ -314,13 +300,33 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
     const uint32_t row_c = lut_a + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
     const uint32_t sf_c = lut_a + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
     const float M = kRoundBias;
-    constexpr bool kNorm = (FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN);
+    constexpr bool kNorm = (FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN || FE == FE_ABSMEAN);
 
     const int lane = threadIdx.x & 31;
     const int nblk = p.cols_out >> 4;
     const int k_atoms = sf_k_atoms(p.cols_out);
     const unsigned rows = static_cast<unsigned>(p.rows);
+    // FE_ABSMEAN moves only 512 + 288 bytes per 512-column row: with one row per warp in flight the loads would be
+    // latency-bound, so the next row of this warp is requested before the current one is processed
+    int4 pre[NB];
+    if constexpr (FE == FE_ABSMEAN) {
+        const unsigned row0 = blockIdx.x * 8u + (threadIdx.x >> 5);
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            pre[i] = make_int4(0, 0, 0, 0);
+            if (row0 < rows && lane + 32 * i < nblk) pre[i] = *reinterpret_cast<const int4*>(p.in_i8 + static_cast<size_t>(row0) * p.ld_in + ((lane + 32 * i) << 4));
+        }
+    }
     for (unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8u) {
+        int4 cur[NB];
+        if constexpr (FE == FE_ABSMEAN) {
+            const unsigned nrow = row + gridDim.x * 8u;
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                cur[i] = pre[i];
+                if (nrow < rows && lane + 32 * i < nblk) pre[i] = *reinterpret_cast<const int4*>(p.in_i8 + static_cast<size_t>(nrow) * p.ld_in + ((lane + 32 * i) << 4));
+            }
+        }
         const int member = p.rows_per_member > 0 ? static_cast<int>(row / static_cast<unsigned>(p.rows_per_member)) : 0;
         const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
         const int pair = member >> 1;
@@ -350,7 +356,16 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 for (int e = 0; e < 16; ++e) vf[i][e] = 0.0f;
                 continue;
             }
-            if constexpr (FE == FE_ADD_ABSMEAN) {
+            if constexpr (FE == FE_ABSMEAN) {
+                const int4 raw = cur[i];
+                const uint32_t rw[4] = {static_cast<uint32_t>(raw.x), static_cast<uint32_t>(raw.y), static_cast<uint32_t>(raw.z), static_cast<uint32_t>(raw.w)};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    bytes4_to_float(rw[q], &vf[i][4 * q]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sum_abs += fabsf(vf[i][4 * q + j]);
+                }
+            } else if constexpr (FE == FE_ADD_ABSMEAN) {
                 int8_t* xr = p.inout_i8 + static_cast<size_t>(row) * p.cols_in;
                 const float* yr = p.in_f32 + static_cast<size_t>(row) * p.ld_in;
                 const int4 raw = *reinterpret_cast<const int4*>(xr + k0);
@@ -367,8 +382,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // old + rint(y * add_scale), clipped to +-127, all on biased floats
-                        const float t_r = __fmul_rn(yy[j], p.add_scale) + M;
-                        tb[j] = fminf(fmaxf(t_r + oldf[j], M - 127.0f), M + 127.0f);
+                        tb[j] = resid_add_biased(oldf[j], yy[j], p.add_scale);
                         vf[i][4 * q + j] = tb[j] - M;
                         sum_abs += fabsf(vf[i][4 * q + j]);
                     }
@@ -573,9 +587,10 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
     const int nblk = p.cols_out >> 4;
     const uint8_t* lut = get_quant_lut();
     if (lut == nullptr) return BNF4_ERR_CUDA;
-    if constexpr (FE == FE_EMBED_LOWRANK || FE == FE_POS_GELU_ABSMEAN || FE == FE_ADD_ABSMEAN) {
+    if constexpr (FE == FE_EMBED_LOWRANK || FE == FE_POS_GELU_ABSMEAN || FE == FE_ADD_ABSMEAN || FE == FE_ABSMEAN) {
         auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
         bool fast = p.cols_in == p.cols_out && nblk <= 128 && (p.out_q == nullptr || p.vec_ok_q) && al16(p.inout_i8 ? p.inout_i8 : nullptr);
+        if (FE == FE_ABSMEAN) fast = fast && p.vec_ok && p.in_i8 != nullptr;
         if (FE == FE_ADD_ABSMEAN) fast = fast && al16(p.in_f32) && (p.ld_in % 4) == 0;
         if (FE == FE_POS_GELU_ABSMEAN)
             fast = fast && p.vec_ok && al16(p.pos) && (p.pos_noise == nullptr || (al16(p.pos_noise) && (p.noise_pair_stride % 16) == 0));

@@ -47,6 +47,7 @@ class GemmDesc(C.Structure):
         ("rank", c_int), ("rows_per_member", c_int), ("lora_t", c_void_p), ("t_stride", c_int),
         ("lora_A", c_void_p), ("lora_A_pair_stride", c_ll), ("lora_scale", c_float), ("group_cols", c_int),
         ("next_tvec", c_void_p), ("next_tvec_pair_stride", c_ll), ("next_nvec", c_int), ("next_t", c_void_p),
+        ("resid", c_void_p), ("ld_resid", c_int), ("add_scale", c_float),
     ]
 
 

@@ -49,6 +49,10 @@ _l.register({
     "bnf4_model_eval_pairs": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "bnf4_model_eval_base": (c_int, [c_void_p, c_void_p, c_void_p]),
     "bnf4_model_update": (c_int, [c_void_p, c_void_p, C.POINTER(UpdateCfg), c_void_p]),
+    "bnf4_model_update_z_layout": (c_int, [c_void_p, c_int, c_int, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong), C.POINTER(c_int),
+                                           C.POINTER(C.c_longlong)]),
+    "bnf4_model_update_z": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "bnf4_model_update_apply": (c_int, [c_void_p, c_void_p, c_void_p, C.POINTER(UpdateCfg), c_void_p]),
     "bnf4_model_read_buffer": (c_int, [c_void_p, C.c_char_p, c_void_p, C.c_size_t]),
     "bnf4_model_launches_per_wave": (c_int, [c_void_p]),
     "bnf4_model_wave_members": (c_int, [c_void_p]),
@@ -215,6 +219,31 @@ class PopulationModel:
         u = UpdateCfg(lr, thresh, int(use_adaptive), adaptive_beta, adaptive_eps, int(train_pos))
         _l.check(self.lib.bnf4_model_update(self.h, pair_weights.data_ptr(), C.byref(u), _stream()))
 
+    def z_layout(self, nshards: int):
+        """[(offset, elems, sharded)] of every ternary matrix inside the Z buffer of a sharded update, and its size in floats."""
+        n = self.lib.bnf4_model_update_z_layout(self.h, nshards, 0, None, None, None, None)
+        if n < 0:
+            _l.check(1)
+        off, el, sh, tot = (C.c_longlong * n)(), (C.c_longlong * n)(), (c_int * n)(), C.c_longlong(0)
+        if self.lib.bnf4_model_update_z_layout(self.h, nshards, n, off, el, sh, C.byref(tot)) < 0:
+            _l.check(1)
+        return [(off[i], el[i], bool(sh[i])) for i in range(n)], tot.value
+
+    def update_sharded(self, pair_weights: torch.Tensor, rank: int, world: int, group=None, lr=0.8, thresh=0.008, use_adaptive=True,
+                       adaptive_beta=0.95, adaptive_eps=1e-3, train_pos=True):
+        """The update of `update`, with Z of every ternary matrix computed by rows on `world` ranks and all-gathered in place
+        (same kernels, same summation order: the weights end bit-identical to `update`)."""
+        assert pair_weights.is_cuda and pair_weights.dtype == torch.float32 and pair_weights.numel() == self.pairs
+        key = world
+        if getattr(self, "_z_key", None) != key:
+            self._z_entries, total = self.z_layout(world)
+            self._z_all = torch.empty(total, dtype=torch.float32, device="cuda")
+            self._z_key = key
+        u = UpdateCfg(lr, thresh, int(use_adaptive), adaptive_beta, adaptive_eps, int(train_pos))
+        _l.check(self.lib.bnf4_model_update_z(self.h, pair_weights.data_ptr(), rank, world, self._z_all.data_ptr(), _stream()))
+        gather_z_shards(self._z_all, self._z_entries, rank, world, group)
+        _l.check(self.lib.bnf4_model_update_apply(self.h, pair_weights.data_ptr(), self._z_all.data_ptr(), C.byref(u), _stream()))
+
     def set_timing(self, enable: bool):
         _l.check(self.lib.bnf4_model_set_timing(self.h, int(enable)))
 
@@ -240,11 +269,27 @@ def shard_pairs(pairs_total: int, rank: int, world: int) -> tuple[int, int]:
     return begin, base + (1 if rank < rem else 0)
 
 
+def gather_z_shards(z_all: torch.Tensor, entries, rank: int, world: int, group=None):
+    """In-place all-gather of the row shards of every sharded matrix inside z_all: rank r owns the r-th of `world` equal
+    contiguous blocks of each (offset, elems, sharded=True) entry."""
+    import torch.distributed as dist
+    if world <= 1:
+        return
+    for off, n, sharded in entries:
+        if not sharded:
+            continue
+        full = z_all[off:off + n]
+        per = n // world
+        dist.all_gather_into_tensor(full, full[rank * per:(rank + 1) * per], group=group)
+
+
 def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world: int = 1, group=None, lr: float = 0.8,
             thresh: float = 0.008, fitness_mode: int = 0, fitness_clip: float = 3.0, losses_out: torch.Tensor | None = None,
-            **update_kw) -> torch.Tensor:
+            shard_update: bool = True, **update_kw) -> torch.Tensor:
     """One ES step on this rank: evaluate this rank's pairs, all-gather the per-member losses over `group`
-    (torch.distributed), shape the fitness and apply the identical deterministic update on every rank.
+    (torch.distributed), shape the fitness and apply the identical deterministic update on every rank. With more than one
+    rank the noise sums of the update are computed by rows across the ranks and all-gathered (shard_update=False replicates
+    them like the reference does); either way every rank ends with the same bits.
     `model` is a PopulationModel (or any object with prepare_step / eval_pairs / update). Returns all 2*pairs_total losses."""
     import torch.distributed as dist
     begin, count = shard_pairs(pairs_total, rank, world)
@@ -264,7 +309,10 @@ def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world
     else:
         losses = mine
     weights = shape_fitness(fitness_from_losses(losses), fitness_mode, fitness_clip)
-    model.update(weights, lr=lr, thresh=thresh, **update_kw)
+    if world > 1 and shard_update and hasattr(model, "update_sharded"):
+        model.update_sharded(weights, rank, world, group, lr=lr, thresh=thresh, **update_kw)
+    else:
+        model.update(weights, lr=lr, thresh=thresh, **update_kw)
     return losses
 
 

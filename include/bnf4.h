@@ -168,6 +168,10 @@ int bnf4_nvfp4_prepare_gemm(const void* a, const void* b, const void* sfa, const
 #define BNF4_EPI_F32 0
 #define BNF4_EPI_GELU_I8 1
 #define BNF4_EPI_GELU_FP4 2
+#define BNF4_EPI_ADD_I8 3 /* resid = clip8(resid + rint(v * add_scale)), in place: the add of the reference's
+                           * add_scaled_to_int8_absmean_norm_q_nvfp4 (src/cuda_kernels.cu:3033-3143) applied by the GEMM
+                           * that produces v, so that the fp32 product never travels through HBM; follow it with the
+                           * BNF4_FE_ABSMEAN quantiser over resid; |v * add_scale| must stay below 2^15 */
 
 /* Full form: strides, fused epilogues and the rank-r perturbation
  *   D += s_member * sum_r t[m][g*rank + r] * A_pair[n][r]
@@ -201,6 +205,9 @@ typedef struct bnf4_gemm_desc {
     long long next_tvec_pair_stride;
     int next_nvec;
     int32_t* next_t; /* [M][next_nvec], zeroed by the caller; accumulated with integer atomics */
+    int8_t* resid;   /* BNF4_EPI_ADD_I8: [M][ld_resid] int8, read and written */
+    int ld_resid;
+    float add_scale;
 } bnf4_gemm_desc;
 
 int bnf4_gemm_nvfp4_ex(const bnf4_gemm_desc* desc, void* stream);
@@ -324,6 +331,13 @@ int bnf4_compute_z_sumsq_static(const float* pair_weights, const uint64_t* pair_
 int bnf4_compute_z_sumsq_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
                                  long long B_pair_stride, int pairs, int rows, int cols, int rank, float cscale,
                                  float* Z, float* sumsq, void* stream);
+/* The two halves of the call above, for callers that compute row ranges of Z on different ranks and exchange them
+ * before the (order-sensitive) sum of squares: rows [r0, r0+n) of Z come from passing A + r0*rank, Z + r0*cols, rows = n. */
+int bnf4_compute_z_lowrank(const float* pair_weights, const int8_t* A, long long A_pair_stride, const int8_t* B,
+                           long long B_pair_stride, int pairs, int rows, int cols, int rank, float cscale, float* Z,
+                           void* stream);
+/* *sumsq += sum Z[i]^2, with the block structure and summation order of bnf4_compute_z_sumsq. */
+int bnf4_sumsq(const float* Z, int n, float* sumsq, void* stream);
 /* reference: update_inv_rms src/efla_lm_kernels.cu:2061-2073 (kernel :2003-2021). inv_rms = 1/sqrt(ema+eps)
  * evaluated with IEEE sqrt and divide (the reference's rsqrtf is within 2 ulp of it). */
 int bnf4_update_inv_rms(const float* sumsq, float* rms_ema, int use_adaptive, float adaptive_beta, float adaptive_eps,
@@ -422,6 +436,21 @@ int bnf4_model_eval_base(void* handle, float* loss, void* stream);
  * Applies the ES update to all ternary matrices and fp32 vectors and re-quantises the base weights.
  * Deterministic: every rank that calls it with the same inputs ends with identical bits. */
 int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update_cfg* ucfg, void* stream);
+/* The same update with the dominant part -- Z = sum_p w_p * noise_p for every ternary matrix -- split by rows over
+ * `nshards` ranks (the reference replicates it on every worker, src/train_efla_lm.cpp:5560-5660):
+ *   1. bnf4_model_update_z_layout: for matrix i of the model (fixed order), offsets[i] / elems[i] locate its Z inside one
+ *      caller-owned fp32 buffer `z_all`, and sharded[i] tells whether its rows divide by nshards (otherwise every rank
+ *      computes the whole matrix). Returns the number of matrices (<= max_entries, at most 6 + 6 per layer) or -1;
+ *      *total_elems receives the size of z_all in floats.
+ *   2. bnf4_model_update_z: rank `shard` fills rows [shard*rows/nshards, (shard+1)*rows/nshards) of every sharded matrix
+ *      (all rows of the others) in z_all.
+ *   3. the caller all-gathers each sharded matrix in place (contiguous row blocks in rank order);
+ *   4. bnf4_model_update_apply: sum of squares, RMS normalisation, shadow/ternary update of all matrices from z_all, the
+ *      fp32 vectors, and re-quantisation: the same kernels in the same order as bnf4_model_update, hence the same bits. */
+int bnf4_model_update_z_layout(void* handle, int nshards, int max_entries, long long* offsets, long long* elems, int* sharded,
+                               long long* total_elems);
+int bnf4_model_update_z(void* handle, const float* pair_weights, int shard, int nshards, float* z_all, void* stream);
+int bnf4_model_update_apply(void* handle, const float* pair_weights, const float* z_all, const bnf4_update_cfg* ucfg, void* stream);
 /* Debug/verification access to an internal wave buffer by name ("x_q", "a_h", "sf_h", "a_f", "sf_f", "qkv", "y",
  * "t_a", "t_f", "losses"): copies min(bytes, size) bytes to host. Synchronises. */
 int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes);

@@ -689,6 +689,9 @@ static double sumsq_blocks(const float* Z, int n) {
     return total;
 }
 
+// The sum of squares alone (for callers that assemble Z from row ranges before reducing it).
+ORC_API float orc_sumsq(const float* Z, int n) { return (float)sumsq_blocks(Z, n); }
+
 ORC_API float orc_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs,
                                   int n, int use_clt, int clt_k, float* Z) {
     std::vector<uint64_t> seeds(pairs);

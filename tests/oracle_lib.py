@@ -56,6 +56,7 @@ def lib():
         L.orc_cross_entropy_sum.restype = C.c_double
         L.orc_compute_z_sumsq.restype = cf
         L.orc_compute_z_sumsq_lowrank.restype = cf
+        L.orc_sumsq.restype = cf
         L.orc_update_inv_rms.restype = cf
         L.orc_model_create.restype = vp
         L.orc_model_forward.restype = C.c_double
@@ -224,6 +225,11 @@ def compute_z_sumsq_lowrank(pair_weights, pair_seeds, salt, rows, cols, rank, cs
     ss = lib().orc_compute_z_sumsq_lowrank(P(pair_weights), P(pair_seeds), cu64(salt), len(pair_weights), rows, cols, rank,
                                            int(use_clt), clt_k, cf(cscale), P(Z))
     return Z, ss
+
+
+def sumsq(Z):
+    Z = np.ascontiguousarray(Z, np.float32)
+    return lib().orc_sumsq(P(Z), len(Z))
 
 
 def update_inv_rms(sumsq, rms_ema, use_adaptive, beta, eps, n):

@@ -183,6 +183,46 @@ def test_gemm_gelu_fp4_epilogue(H):
     assert np.array_equal(nt.cpu().numpy(), got.astype(np.int32) @ tvec[0].astype(np.int32).T)
 
 
+@pytest.mark.parametrize("m,n,k,rank", [(512, 512, 1024, 1), (300, 512, 512, 0), (200, 72, 128, 2), (129, 200, 256, 0)])
+def test_gemm_residual_add_epilogue(H, m, n, k, rank):
+    """BNF4_EPI_ADD_I8: the GEMM adds its product into the int8 residual stream, resid = clip8(resid + rint(v * add_scale)).
+
+    Bit-exact against the oracle's add step applied to the same kernel's fp32 output (same accumulators, same epilogue
+    arithmetic up to the store); against the oracle's own GEMM an int8 may differ by one step where v * add_scale falls on a
+    rounding boundary. Ragged sizes take the per-byte path."""
+    import torch
+    rng = np.random.default_rng(5 * m + n + k + rank)
+    x, w, a, sfa, b, sfb = make_operands(rng, m, n, k)
+    alpha = float(np.float32(1.0) / np.sqrt(np.float32(k)))
+    add_scale = 0.37
+    R = 64 if m % 128 == 0 else m
+    kw = dict(a=dev(a), b=dev(b), sfa=dev(sfa), sfb=dev(sfb), m=m, n=n, k=k, alpha=alpha)
+    if rank:
+        pairs = (m // R + 1) // 2
+        A = rng.integers(-4, 5, (pairs, n, rank)).astype(np.int8)
+        t = rng.integers(-3000, 3000, (m, rank)).astype(np.int32)
+        lscale = float(np.float32(0.125) * np.float32(alpha) * np.float32(H.c_rank(rank)))
+        kw.update(rank=rank, rows_per_member=R, lora_t=dev(t), t_stride=rank, lora_A=dev(A), lora_A_pair_stride=n * rank, lora_scale=lscale)
+    resid0 = rng.integers(-127, 128, (m, n)).astype(np.int8)
+    d = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    H.gemm_nvfp4_ex(d=d, ldd=n, epilogue=H.EPI_F32, **kw)
+    resid = dev(resid0)
+    H.gemm_nvfp4_ex(epilogue=H.EPI_ADD_I8, resid=resid, ld_resid=n, add_scale=add_scale, **kw)
+    assert H.device_error() == 0
+    got = resid.cpu().numpy()
+    want = np.clip(resid0.astype(np.int32) + np.rint(d.cpu().numpy() * np.float32(add_scale)).astype(np.int32), -127, 127).astype(np.int8)
+    assert np.array_equal(got, want)
+    ref = orc.gemm_nvfp4(a, b, sfa, sfb, m, n, k, alpha)
+    if rank:
+        for mm in range(m // R):
+            blk = np.ascontiguousarray(ref[mm * R:(mm + 1) * R])
+            orc.lora_add(np.ascontiguousarray(t[mm * R:(mm + 1) * R]), A[mm // 2], n, (1.0 if mm % 2 == 0 else -1.0) * lscale, blk)
+            ref[mm * R:(mm + 1) * R] = blk
+    want2 = np.clip(resid0.astype(np.int32) + np.rint(ref * np.float32(add_scale)).astype(np.int32), -127, 127)
+    diff = np.abs(got.astype(np.int32) - want2)
+    assert diff.max() <= 1 and (diff != 0).mean() <= 5e-3
+
+
 def test_gemm_rejects_bad_arguments(H):
     import torch
     from bitnet_nvfp4_b200 import lib

@@ -174,3 +174,51 @@ def test_checkpoint_resume_is_bit_identical(tmp_path):
     (sa, ea), (sb, eb) = a.get_optimizer_state(), b.get_optimizer_state()
     assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
     assert (sa != np.round(sa)).any()  # the shadows really carry fractional state
+
+
+@pytest.mark.parametrize("nshards", [2, 4])
+def test_sharded_update_is_bit_identical(nshards):
+    """Z of every ternary matrix computed in row shards (one call per emulated rank into one buffer, which is what the
+    in-place all-gather leaves on every rank) and applied == the replicated update: weights and optimiser state."""
+    import ctypes as C
+    import torch
+    from bitnet_nvfp4_b200 import lib, population
+    kw = dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=2, max_pairs=8, wave_members=8)
+    rng = np.random.default_rng(23)
+    pw = torch.from_numpy(orc.shape_pair_weights(rng.standard_normal(8).astype(np.float32))).cuda()
+    _, _, _, _, a = make(kw)
+    _, _, _, _, b = make(kw)
+    for epoch in range(2):
+        a.prepare_step(1, epoch, 8)
+        a.update(pw, lr=0.8, thresh=0.008)
+        b.prepare_step(1, epoch, 8)
+        entries, total = b.z_layout(nshards)
+        assert total == sum(n for _, n, _ in entries) and any(s for _, _, s in entries) and not all(s for _, _, s in entries)
+        z_all = torch.full((total,), float("nan"), dtype=torch.float32, device="cuda")
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for shard in range(nshards):
+            lib.check(b.lib.bnf4_model_update_z(b.h, pw.data_ptr(), shard, nshards, z_all.data_ptr(), stream))
+        assert not torch.isnan(z_all).any()
+        u = population.UpdateCfg(0.8, 0.008, 1, 0.95, 1e-3, 1)
+        lib.check(b.lib.bnf4_model_update_apply(b.h, pw.data_ptr(), z_all.data_ptr(), C.byref(u), stream))
+    wa, wb = a.get_weights(), b.get_weights()
+    for k in wa:
+        assert np.array_equal(wa[k], wb[k]), k
+    (sa, ea), (sb, eb) = a.get_optimizer_state(), b.get_optimizer_state()
+    assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
+
+
+def test_two_gpu_sharded_update_matches_replicated():
+    """NCCL run of tests/multigpu_sharded_update.py on two GPUs (skipped on a single-GPU box)."""
+    import os
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                          "--master-port", "29511", os.path.join(here, "multigpu_sharded_update.py")], capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "sharded update OK on 2 ranks" in out.stdout

@@ -44,16 +44,48 @@ class OracleEvaluator:
             out += [om.forward(self.tok, self.tgt, ps, 1), om.forward(self.tok, self.tgt, ps, -1)]
         return torch.tensor(out, dtype=torch.float32)
 
+    def _matrices(self):
+        H, V = self.cfg.hidden, self.cfg.vocab
+        return (("emb", V, H), ("win", H, H), ("head", V, H))
+
+    def _apply(self, name, rows, cols, Z, lr, th):
+        ss = orc.sumsq(Z)
+        inv, self.ema[name] = orc.update_inv_rms(ss, self.ema.get(name, 0.0), True, 0.95, 1e-3, rows * cols)
+        orc.update_shadow_ternary(self.w[name].reshape(-1), self.shadow[name].reshape(-1), Z, inv, lr, th)
+
     def update(self, pair_weights, lr, thresh):
         from bitnet_nvfp4_b200 import host
+        self.sharded_updates = getattr(self, "sharded_updates", 0)
         pw = pair_weights.numpy().astype(np.float32)
         seeds = orc.fill_pair_seeds(self.seed, self.epoch, self.pairs)
         th = float(np.float32(thresh) * np.sqrt(np.float32(self.pairs)))
-        H, F, V = self.cfg.hidden, self.cfg.hidden * self.cfg.mlp_mult, self.cfg.vocab
-        for name, rows, cols in (("emb", V, H), ("win", H, H), ("head", V, H)):
-            Z, ss = orc.compute_z_sumsq_lowrank(pw, seeds, SALT[name], rows, cols, self.cfg.rank, host.c_rank(self.cfg.rank))
-            inv, self.ema[name] = orc.update_inv_rms(ss, self.ema.get(name, 0.0), True, 0.95, 1e-3, rows * cols)
-            orc.update_shadow_ternary(self.w[name].reshape(-1), self.shadow[name].reshape(-1), Z, inv, lr, th)
+        for name, rows, cols in self._matrices():
+            Z, _ = orc.compute_z_sumsq_lowrank(pw, seeds, SALT[name], rows, cols, self.cfg.rank, host.c_rank(self.cfg.rank))
+            self._apply(name, rows, cols, Z, lr, th)
+
+    def update_sharded(self, pair_weights, rank, world, group, lr, thresh):
+        """Row-sharded Z + the product's in-place all-gather (population.gather_z_shards), then the same apply step."""
+        from bitnet_nvfp4_b200 import host, population
+        self.sharded_updates = getattr(self, "sharded_updates", 0) + 1
+        pw = pair_weights.numpy().astype(np.float32)
+        seeds = orc.fill_pair_seeds(self.seed, self.epoch, self.pairs)
+        th = float(np.float32(thresh) * np.sqrt(np.float32(self.pairs)))
+        entries, off = [], 0
+        for name, rows, cols in self._matrices():
+            entries.append((off, rows * cols, rows % world == 0))
+            off += rows * cols
+        z_all = torch.full((off,), float("nan"), dtype=torch.float32)
+        for (name, rows, cols), (o, n, sharded) in zip(self._matrices(), entries):
+            Z, _ = orc.compute_z_sumsq_lowrank(pw, seeds, SALT[name], rows, cols, self.cfg.rank, host.c_rank(self.cfg.rank))
+            if sharded:  # this rank contributes only its rows
+                per = n // world
+                z_all[o + rank * per:o + (rank + 1) * per] = torch.from_numpy(Z[rank * per:(rank + 1) * per])
+            else:
+                z_all[o:o + n] = torch.from_numpy(Z)
+        population.gather_z_shards(z_all, entries, rank, world, group)
+        assert not torch.isnan(z_all).any()
+        for (name, rows, cols), (o, n, _) in zip(self._matrices(), entries):
+            self._apply(name, rows, cols, z_all[o:o + n].numpy().copy(), lr, th)
 
 
 def _setup():
@@ -74,6 +106,7 @@ def _worker(rank, world, port, pairs, q):
     losses = None
     for epoch in range(2):
         losses = population.es_step(ev, 1, epoch, pairs, rank, world, lr=0.8, thresh=0.008)
+    assert ev.sharded_updates == 2  # with more than one rank the step takes the row-sharded update
     q.put((rank, sorted(set(ev.evaluated)), losses.numpy(), {k: ev.w[k].copy() for k in ("emb", "win", "head")}))
     dist.destroy_process_group()
 
