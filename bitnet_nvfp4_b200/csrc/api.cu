@@ -63,7 +63,7 @@ int bnf4_set_option(const char* name, int value) {
         return BNF4_OK;
     }
     if (name && std::strcmp(name, "efla_mma") == 0) {
-        g_efla_mma = value ? 1 : 0;
+        g_efla_mma = value < 0 ? 0 : (value > 2 ? 2 : value);
         return BNF4_OK;
     }
     return set_error(BNF4_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");

@@ -264,6 +264,10 @@ __device__ __forceinline__ void mma_f16_1688(float& d0, float& d1, float& d2, fl
         : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3)
         : "r"(a0), "r"(a1), "r"(b0));
 }
+// c (16 x 8, fp16, in place) += a (16 x 8) * b (8 x 8): fp16 accumulators, one rounding to nearest of the exact sum
+__device__ __forceinline__ void mma_f16acc_1688(uint32_t& c0, uint32_t& c1, uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f16.f16.f16.f16 {%0, %1}, {%2, %3}, {%4}, {%0, %1};" : "+r"(c0), "+r"(c1) : "r"(a0), "r"(a1), "r"(b0));
+}
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 hv = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&hv);
@@ -276,6 +280,12 @@ constexpr int kScanMmaCtasPerSm = 3;
 // dynamic shared memory per warp: ring, alpha*k (fp32), and the four fp16 columns q^ hi, q^ mid, k hi, k mid
 constexpr int kScanWarpSmemBytes = kScanRing * kScanSlotFloats * 4 + kScanVecBufs * 64 * 4 + kScanVecBufs * 4 * 64 * 2;
 constexpr int kScanMmaSmemBytes = kScanWarps * kScanWarpSmemBytes;
+constexpr int kScan2CtasPerSm = 4;
+constexpr int kScan2QkRing = 8;                // q, k, beta of two groups of four tokens
+constexpr int kScan2QkSlotFloats = 2 * 64 + 4;  // q[64], k[64], beta (+ padding to 16 bytes)
+// per warp: q/k ring, v ring, (hi, mid) words of alpha * k, the four fp16 columns q^ hi, q^ mid, k hi, k mid, eight zero words
+constexpr int kScan2WarpSmemBytes = kScan2QkRing * kScan2QkSlotFloats * 4 + kScanRing * 64 * 4 + kScanVecBufs * 64 * 4 + kScanVecBufs * 4 * 64 * 2 + 32;
+constexpr int kScan2SmemBytes = kScanWarps * kScan2WarpSmemBytes;
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gsrc) : "memory");
@@ -476,10 +486,199 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan6
     cp_async_wait<0>();
 }
 
+__global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_mma2_kernel(const EflaParams p) {
+    constexpr int HD = 64;
+    extern __shared__ __align__(16) uint8_t scan_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // raw inputs: q, k, beta are dead once their group of four tokens has been prepared (two groups in the ring: one being
+    // prepared, one in flight); v is read token by token one group later (three groups)
+    float* qk_sh = reinterpret_cast<float*>(scan_smem + warp * kScan2WarpSmemBytes);   // [kScan2QkRing][kScan2QkSlotFloats]
+    float* v_sh = qk_sh + kScan2QkRing * kScan2QkSlotFloats;                            // [kScanRing][64]
+    uint32_t* kw_sh = reinterpret_cast<uint32_t*>(v_sh + kScanRing * HD);               // [kScanVecBufs][64] (hi, mid) halves of alpha * k; d at (d % 8) * 8 + d / 8
+    __half* b_sh = reinterpret_cast<__half*>(kw_sh + kScanVecBufs * HD);                  // [kScanVecBufs][4][64] q^ hi, q^ mid, k hi, k mid, permuted
+    uint32_t* zero_sh = reinterpret_cast<uint32_t*>(b_sh + kScanVecBufs * 4 * HD);        // [8] zeros: the alpha * k words of lanes whose rows of B are zero
+    if (lane < 8) zero_sh[lane] = 0u;
+    const long long unit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;  // (sequence, head)
+    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
+    const long long seq = unit / p.heads;
+    const int h = static_cast<int>(unit - seq * p.heads);
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
+    const int g = lane >> 2, tq = lane & 3;
+
+    uint32_t Sh[4][4][4];  // [mt][ks][i]: the A fragment (i = 0: n = g, d pair 2tq; 1: n = g + 8; 2: n = g, d pair 2tq + 8; 3: n = g + 8)
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
+
+    const size_t row0 = static_cast<size_t>(seq) * p.T;
+    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
+    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
+    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
+    const float* bb = p.beta_raw + row0 * p.ld_beta;
+    float* ob = p.out + row0 * p.ld_out + h * HD;
+
+    // asynchronous copy of four tokens' inputs (one group) into their ring slots; every lane commits one group, empty or not
+    auto issue_group = [&](int tok0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int tok = tok0 + j;
+            if (tok < p.T) {
+                float* slot = qk_sh + (tok % kScan2QkRing) * kScan2QkSlotFloats;
+                const size_t o = static_cast<size_t>(tok) * p.ld_qkv;
+                const int l16 = lane & 15;
+                cp_async16(slot + (lane < 16 ? 0 : HD) + 4 * l16, (lane < 16 ? qb : kb) + o + 4 * l16);
+                if (lane < 16) cp_async16(v_sh + (tok % kScanRing) * HD + 4 * l16, vb + o + 4 * l16);
+                else if (lane == 16) cp_async4(slot + 2 * HD, bb + static_cast<size_t>(tok) * p.ld_beta);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // Per-token vectors, four tokens at a time: lanes 8 j .. 8 j + 7 prepare token tok0 + j, eight elements each
+    // (d = 8 l + e), so the reductions are three shuffle levels deep and the scalar chain (sigmoid, expm1, divisions)
+    // runs once per four tokens. The permuted layout puts the element pairs (d, d + 1) next to each other, so the
+    // packed fp16 conversions are stored as they are.
+    const int pj = lane >> 3, pl = lane & 7;
+    auto prepare4 = [&](int tok0) {
+        const int tok = min(tok0 + pj, p.T - 1);  // past the end: the last token again (never used)
+        const float* slot = qk_sh + (tok % kScan2QkRing) * kScan2QkSlotFloats;
+        const int buf = (tok0 + pj) % kScanVecBufs;
+        const float4 qa = *reinterpret_cast<const float4*>(slot + 8 * pl), qc = *reinterpret_cast<const float4*>(slot + 8 * pl + 4);
+        const float4 ka = *reinterpret_cast<const float4*>(slot + HD + 8 * pl), kc = *reinterpret_cast<const float4*>(slot + HD + 8 * pl + 4);
+        const float rbr = slot[2 * HD];
+        const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qc.x, qc.y, qc.z, qc.w};
+        const float kv[8] = {ka.x, ka.y, ka.z, ka.w, kc.x, kc.y, kc.z, kc.w};
+        float qss = 0.0f, kss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { qss = fmaf(qv[e], qv[e], qss); kss = fmaf(kv[e], kv[e], kss); }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            qss += __shfl_xor_sync(0xffffffffu, qss, o);
+            kss += __shfl_xor_sync(0xffffffffu, kss, o);
+        }
+        const float q_inv = rsqrtf(qss + p.eps);
+        const float lambda = kss < p.eps ? p.eps : kss;
+        const float beta = sigmoidf_dev(rbr + beta_bias);
+        float alpha, kscale = 1.0f;
+        if (p.method == 0) { alpha = beta; kscale = rsqrtf(lambda + p.eps); }
+        else alpha = -expm1f(-(beta * lambda)) / (lambda + p.eps);
+        // element d = 8 pl + e sits at (e / 2) * 16 + (pl / 2) * 4 + (e % 2) + 2 * (pl % 2) of the permuted order
+        const int pbase = (pl >> 1) * 4 + 2 * (pl & 1);
+        uint32_t* kw_dst = kw_sh + buf * HD + pl;
+        __half* b_dst = b_sh + buf * 4 * HD + pbase;
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+            const float kn0 = kv[2 * e2] * kscale, kn1 = kv[2 * e2 + 1] * kscale, qn0 = qv[2 * e2] * q_inv, qn1 = qv[2 * e2 + 1] * q_inv;
+            {   // alpha * k as unscaled (hi, mid) halves, one word per element
+                const float ak0 = alpha * kn0, ak1 = alpha * kn1;
+                const __half2 ah = __floats2half2_rn(ak0, ak1);
+                const float2 ahf = __half22float2(ah);
+                const __half2 am = __floats2half2_rn(ak0 - ahf.x, ak1 - ahf.y);
+                kw_dst[(2 * e2) * 8] = __byte_perm(*reinterpret_cast<const uint32_t*>(&ah), *reinterpret_cast<const uint32_t*>(&am), 0x5410);
+                kw_dst[(2 * e2 + 1) * 8] = __byte_perm(*reinterpret_cast<const uint32_t*>(&ah), *reinterpret_cast<const uint32_t*>(&am), 0x7632);
+            }
+            // two-term fp16 splits with packed conversions
+            const __half2 qh = __floats2half2_rn(qn0, qn1), kh = __floats2half2_rn(kn0, kn1);
+            const float2 qhf = __half22float2(qh), khf = __half22float2(kh);
+            const __half2 qm = __floats2half2_rn((qn0 - qhf.x) * 2048.0f, (qn1 - qhf.y) * 2048.0f);
+            const __half2 km = __floats2half2_rn((kn0 - khf.x) * 2048.0f, (kn1 - khf.y) * 2048.0f);
+            *reinterpret_cast<__half2*>(b_dst + 0 * HD + 16 * e2) = qh;
+            *reinterpret_cast<__half2*>(b_dst + 1 * HD + 16 * e2) = qm;
+            *reinterpret_cast<__half2*>(b_dst + 2 * HD + 16 * e2) = kh;
+            *reinterpret_cast<__half2*>(b_dst + 3 * HD + 16 * e2) = km;
+        }
+    };
+
+    float kS[4][2];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) kS[mt][0] = kS[mt][1] = 0.0f;  // zero initial state
+    issue_group(0);
+    issue_group(4);
+    cp_async_wait<0>();
+    __syncwarp();
+    prepare4(0);
+
+    int rg = 0;  // ring group (four slots) that holds tokens t0 .. t0 + 3
+    for (int t0 = 0; t0 < p.T; t0 += 4) {
+        const int gb = (t0 >> 2) & 1;  // vector buffers gb * 4 .. gb * 4 + 3 hold tokens t0 .. t0 + 3
+        {
+            // start of a group of four tokens: fetch the group after next, prepare the next one
+            __syncwarp();  // everyone is done with the ring slots and vector buffers of the previous group
+            issue_group(t0 + 8);
+            cp_async_wait<1>();  // everything but the newest group has landed: tokens <= t0 + 7
+            __syncwarp();
+            prepare4(t0 + 4);
+            __syncwarp();
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = t0 + j;
+        if (t >= p.T) break;
+        const int cur = gb * 4 + j, nxt = j < 3 ? cur + 1 : (gb ^ 1) * 4;
+        const float* vslot = v_sh + (rg * 4 + j) * HD;
+        // A operand of the update: columns (0, 1) = diff hi, (2, 3) = diff mid for rows n = g, g + 8 of every n-tile; lanes
+        // tq = 0 hold the hi pair, the others the mid pair (their rows of B beyond 3 are zero)
+        uint32_t da[4][2];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const float d0 = vslot[16 * mt + g] - kS[mt][0], d1 = vslot[16 * mt + 8 + g] - kS[mt][1];
+            const __half2 hp = __floats2half2_rn(d0, d1);
+            const float2 hf = __half22float2(hp);
+            const __half2 mp = __floats2half2_rn(d0 - hf.x, d1 - hf.y);
+            const uint32_t sel = tq == 0 ? *reinterpret_cast<const uint32_t*>(&hp) : *reinterpret_cast<const uint32_t*>(&mp);
+            da[mt][0] = __byte_perm(sel, sel, 0x1010);
+            da[mt][1] = __byte_perm(sel, sel, 0x3232);
+        }
+        // B operand of the update for d = 8 j + g (j = 2 ks + half): rows (0, 1) and (2, 3) = (hi, mid) of alpha * k[d]
+        const uint32_t* kw_src = tq < 2 ? kw_sh + cur * HD + g * 8 : zero_sh;
+        const uint4 kwa = *reinterpret_cast<const uint4*>(kw_src), kwb = *reinterpret_cast<const uint4*>(kw_src + 4);
+        const uint32_t kw[8] = {kwa.x, kwa.y, kwa.z, kwa.w, kwb.x, kwb.y, kwb.z, kwb.w};
+        // B fragment of the readout: columns 0,1 = q^ of token t, 2,3 = k of token t+1
+        const __half* b_src = b_sh + ((g < 2 ? cur : nxt) * 4 + (g & 3)) * HD + tq * 16;
+        float D[4][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) D[mt][0] = D[mt][1] = D[mt][2] = D[mt][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
+            if (g >= 4) bf = make_uint2(0u, 0u);
+            // update with fp16 accumulators: S16' = fp16_rn(S16 + diff (alpha k)^T), the state registers are both C and D
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                mma_f16acc_1688(Sh[mt][ks][0], Sh[mt][ks][1], da[mt][0], da[mt][1], kw[2 * ks]);
+                mma_f16acc_1688(Sh[mt][ks][2], Sh[mt][ks][3], da[mt][0], da[mt][1], kw[2 * ks + 1]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+                mma_f16_16816(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
+        }
+
+        // column pair of this lane: tq = 0 -> (q^ hi, q^ mid): y of token t;  tq = 1 -> (k hi, k mid): k.S of token t + 1
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const float r0 = fmaf(D[mt][1], 1.0f / 2048.0f, D[mt][0]);  // n = 16 mt + g
+            const float r1 = fmaf(D[mt][3], 1.0f / 2048.0f, D[mt][2]);  // n = 16 mt + g + 8
+            if (tq == 0) {
+                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + g] = r0;
+                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + 8 + g] = r1;
+            }
+            kS[mt][0] = __shfl_sync(0xffffffffu, r0, (lane & ~3) | 1);
+            kS[mt][1] = __shfl_sync(0xffffffffu, r1, (lane & ~3) | 1);
+        }
+      }
+        rg = rg == 2 ? 0 : rg + 1;
+    }
+    cp_async_wait<0>();
+}
+
 }  // namespace
 
 int g_efla_cols_per_lane = 2;  // host toggle (option "efla_cols_per_lane")
-int g_efla_mma = 1;            // host toggle (option "efla_mma"): 1 = tensor-core scan kernel, 0 = multiply-add scan kernel
+int g_efla_mma = 2;            // host toggle (option "efla_mma"): 2 = tensor-core scan kernel with fp16 accumulators (default),
+                               // 1 = tensor-core scan kernel with the fp32 rank-1 term, 0 = multiply-add scan kernel
 
 int efla_launch(const EflaParams& p, cudaStream_t stream) {
     if (p.seqs <= 0 || p.T <= 0) return BNF4_OK;
@@ -490,6 +689,20 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
         const long long units = p.seqs * static_cast<long long>(p.heads);
         const bool aligned = ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0 &&
                              (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
+        if (g_efla_mma >= 2 && aligned) {
+            const long long ctas = (units + kScanWarps - 1) / kScanWarps;
+            static bool configured2[64] = {};
+            int dev = 0;
+            int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+            if (rc) return rc;
+            if (dev < 0 || dev >= 64 || !configured2[dev]) {
+                rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScan2SmemBytes), "cudaFuncSetAttribute(efla_scan64_mma2_kernel)");
+                if (rc) return rc;
+                if (dev >= 0 && dev < 64) configured2[dev] = true;
+            }
+            efla_scan64_mma2_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScan2SmemBytes, stream>>>(p);
+            return check_launch("efla_scan64_mma2_kernel");
+        }
         if (g_efla_mma && aligned) {
             const long long ctas = (units + kScanWarps - 1) / kScanWarps;
             // function attributes are per device: set once for each device this process uses

@@ -306,27 +306,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
     const int nblk = p.cols_out >> 4;
     const int k_atoms = sf_k_atoms(p.cols_out);
     const unsigned rows = static_cast<unsigned>(p.rows);
-    // FE_ABSMEAN moves only 512 + 288 bytes per 512-column row: with one row per warp in flight the loads would be
-    // latency-bound, so the next row of this warp is requested before the current one is processed
-    int4 pre[NB];
-    if constexpr (FE == FE_ABSMEAN) {
-        const unsigned row0 = blockIdx.x * 8u + (threadIdx.x >> 5);
-#pragma unroll
-        for (int i = 0; i < NB; ++i) {
-            pre[i] = make_int4(0, 0, 0, 0);
-            if (row0 < rows && lane + 32 * i < nblk) pre[i] = *reinterpret_cast<const int4*>(p.in_i8 + static_cast<size_t>(row0) * p.ld_in + ((lane + 32 * i) << 4));
-        }
-    }
     for (unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8u) {
-        int4 cur[NB];
-        if constexpr (FE == FE_ABSMEAN) {
-            const unsigned nrow = row + gridDim.x * 8u;
-#pragma unroll
-            for (int i = 0; i < NB; ++i) {
-                cur[i] = pre[i];
-                if (nrow < rows && lane + 32 * i < nblk) pre[i] = *reinterpret_cast<const int4*>(p.in_i8 + static_cast<size_t>(nrow) * p.ld_in + ((lane + 32 * i) << 4));
-            }
-        }
         const int member = p.rows_per_member > 0 ? static_cast<int>(row / static_cast<unsigned>(p.rows_per_member)) : 0;
         const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
         const int pair = member >> 1;
@@ -357,7 +337,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 continue;
             }
             if constexpr (FE == FE_ABSMEAN) {
-                const int4 raw = cur[i];
+                const int4 raw = *reinterpret_cast<const int4*>(p.in_i8 + static_cast<size_t>(row) * p.ld_in + k0);
                 const uint32_t rw[4] = {static_cast<uint32_t>(raw.x), static_cast<uint32_t>(raw.y), static_cast<uint32_t>(raw.z), static_cast<uint32_t>(raw.w)};
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {

@@ -119,7 +119,7 @@ def bench_sweep(iters):
     assert H.device_error() == 0
 
 
-def bench_efla(seqs, iters, mma=1):
+def bench_efla(seqs, iters, mma=2):
     T, hidden, heads, fc = 128, 512, 8, 1568
     lib.load().bnf4_set_option(b"efla_mma", mma)
     qkv = torch.randn(seqs * T, fc, device="cuda") * 0.3
@@ -133,7 +133,7 @@ def bench_efla(seqs, iters, mma=1):
 
     ms = _time(run, iters, warm=2)
     rows = seqs * T
-    print(f"efla_scan ({'tensor-core' if mma else 'multiply-add'} kernel) seqs={seqs} T={T} heads={heads}x64: {ms:.4f} ms  {rows * ((3 * hidden + 1) * 4 + 4 * hidden) / ms / 1e6:7.1f} GB/s algorithmic  "
+    print(f"efla_scan ({('multiply-add', 'tensor-core fp32 rank-1', 'tensor-core fp16 accumulators')[mma]} kernel) seqs={seqs} T={T} heads={heads}x64: {ms:.4f} ms  {rows * ((3 * hidden + 1) * 4 + 4 * hidden) / ms / 1e6:7.1f} GB/s algorithmic  "
           f"{rows * heads / ms / 1e3:7.1f} M head-steps/s")
 
 
@@ -164,7 +164,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--iters", type=int, default=5)
-    ap.add_argument("--mma", type=int, default=1, help="efla: 1 = tensor-core scan kernel, 0 = multiply-add scan kernel")
+    ap.add_argument("--mma", type=int, default=2, help="efla scan kernel: 2 = tensor cores with fp16 accumulators, 1 = tensor cores with an fp32 rank-1 term, 0 = multiply-add")
     a = ap.parse_args()
     if a.what == "gemm":
         bench_gemm(a.m, a.variants.split(","), a.iters, a.n, a.k)

@@ -41,8 +41,8 @@ const char* bnf4_version(void);
 /* Number of kernels this library has launched from this process (all threads). */
 unsigned long long bnf4_launch_count(void);
 /* Options: "gemm_tma_store" (1 default; 0 = direct-store epilogue; 2 and 3 are timing aids that compute the tiles but
- * leave D unwritten: 2 stages them in shared memory, 3 does not); "efla_mma" (1 default: tensor-core scan kernel for
- * heads of 64 with on-chip state; 0: the multiply-add scan kernel); "efla_cols_per_lane" (1 or 2, multiply-add kernel
+ * leave D unwritten: 2 stages them in shared memory, 3 does not); "efla_mma" (scan kernel for heads of 64 with on-chip
+ * state: 2 default = tensor cores with fp16 accumulators, 1 = tensor cores with an fp32 rank-1 term, 0 = multiply-add); "efla_cols_per_lane" (1 or 2, multiply-add kernel
  * only). Returns BNF4_ERR_INVALID if unknown. */
 int bnf4_set_option(const char* name, int value);
 /* Reads and clears the device-side error word set by a kernel whose bounded wait expired.

@@ -102,9 +102,10 @@ def test_efla_scan_whole_sequence(H, hidden, heads, seqs, T, force_generic):
 
 
 def test_efla_scan_tensor_core_kernel_agrees_with_multiply_add_kernel(H):
-    """The two register-state scan kernels (tensor-core and packed multiply-add) implement the same recurrence; they differ
-    in fp32 summation order only, which shows up as rare one-ulp flips of the fp16 state. Both must sit within the
-    oracle tolerance of each other, and the bulk of the outputs must agree to fp32 summation accuracy."""
+    """The three register-state scan kernels (tensor-core with fp16 accumulators, tensor-core with an fp32 rank-1 term, packed
+    multiply-add) implement the same recurrence; they differ in fp32 summation order / the rounding point of the rank-1
+    product only, which shows up as rare one-ulp flips of the fp16 state. All must sit within the oracle tolerance of each
+    other, and the bulk of the outputs must agree to fp32 summation accuracy."""
     import torch
     from bitnet_nvfp4_b200 import lib
     rng = np.random.default_rng(99)
@@ -113,7 +114,7 @@ def test_efla_scan_tensor_core_kernel_agrees_with_multiply_add_kernel(H):
     qd = dev(make_qkv(rng, seqs * T, hidden, fc, 0.3))
     outs = []
     try:
-        for mma in (1, 0):
+        for mma in (2, 1, 0):
             assert lib.load().bnf4_set_option(b"efla_mma", mma) == 0
             out = torch.empty((seqs * T, hidden), dtype=torch.float32, device="cuda")
             H.efla_scan(state=None, state_fp16=1, q=qd, k=qd[:, hidden:], v=qd[:, 2 * hidden:], beta_raw=qd[:, 3 * hidden:], ld_qkv=fc,
@@ -121,11 +122,11 @@ def test_efla_scan_tensor_core_kernel_agrees_with_multiply_add_kernel(H):
                         out=out, ld_out=hidden)
             outs.append(out.cpu().numpy())
     finally:
-        lib.load().bnf4_set_option(b"efla_mma", 1)
-    a, b = outs
-    scale = np.abs(b).max()
-    assert np.abs(a - b).max() <= 3e-3 * scale
-    assert np.median(np.abs(a - b)) <= 1e-5 * scale
+        lib.load().bnf4_set_option(b"efla_mma", 2)
+    scale = np.abs(outs[2]).max()
+    for a, b in ((outs[0], outs[2]), (outs[1], outs[2]), (outs[0], outs[1])):
+        assert np.abs(a - b).max() <= 3e-3 * scale
+        assert np.median(np.abs(a - b)) <= 1e-5 * scale
 
 
 # ---------------------------------------------------------------------------------------------- cross entropy
