@@ -619,32 +619,32 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
         if (t >= p.T) break;
         const int cur = gb * 4 + j, nxt = j < 3 ? cur + 1 : (gb ^ 1) * 4;
         const float* vslot = v_sh + (rg * 4 + j) * HD;
-        // A operand of the update: columns (0, 1) = diff hi, (2, 3) = diff mid for rows n = g, g + 8 of every n-tile; lanes
-        // tq = 0 hold the hi pair, the others the mid pair (their rows of B beyond 3 are zero)
+        // A operand of the update for rows n = g, g + 8 of every n-tile: lanes tq = 1 hold diff hi (columns 2, 3), lanes tq = 2
+        // diff mid (columns 4, 5), where hi = diff with the mantissa cut to 11 bits and mid = diff - hi (exact in fp32, then
+        // rounded to fp16: diff = hi + mid to 2^-21). Lanes tq = 0 and 3 hold finite values that meet zero rows of B. The
+        // k.S of this token sits in the lane's own readout columns (2 tq, 2 tq + 1 hold k hi, k mid for tq >= 1).
         uint32_t da[4][2];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) {
             const float d0 = vslot[16 * mt + g] - kS[mt][0], d1 = vslot[16 * mt + 8 + g] - kS[mt][1];
-            const __half2 hp = __floats2half2_rn(d0, d1);
-            const float2 hf = __half22float2(hp);
-            const __half2 mp = __floats2half2_rn(d0 - hf.x, d1 - hf.y);
-            const uint32_t sel = tq == 0 ? *reinterpret_cast<const uint32_t*>(&hp) : *reinterpret_cast<const uint32_t*>(&mp);
-            da[mt][0] = __byte_perm(sel, sel, 0x1010);
-            da[mt][1] = __byte_perm(sel, sel, 0x3232);
+            const float h0 = __uint_as_float(__float_as_uint(d0) & 0xffffe000u), h1 = __uint_as_float(__float_as_uint(d1) & 0xffffe000u);
+            const float x0 = tq == 1 ? h0 : d0 - h0, x1 = tq == 1 ? h1 : d1 - h1;
+            da[mt][0] = pack_half2(x0, x0);
+            da[mt][1] = pack_half2(x1, x1);
         }
-        // B operand of the update for d = 8 j + g (j = 2 ks + half): rows (0, 1) and (2, 3) = (hi, mid) of alpha * k[d]
-        const uint32_t* kw_src = tq < 2 ? kw_sh + cur * HD + g * 8 : zero_sh;
+        // B operand of the update for d = 8 j + g (j = 2 ks + half): rows (2, 3) and (4, 5) = (hi, mid) of alpha * k[d]
+        const uint32_t* kw_src = (tq == 1 || tq == 2) ? kw_sh + cur * HD + g * 8 : zero_sh;
         const uint4 kwa = *reinterpret_cast<const uint4*>(kw_src), kwb = *reinterpret_cast<const uint4*>(kw_src + 4);
         const uint32_t kw[8] = {kwa.x, kwa.y, kwa.z, kwa.w, kwb.x, kwb.y, kwb.z, kwb.w};
-        // B fragment of the readout: columns 0,1 = q^ of token t, 2,3 = k of token t+1
-        const __half* b_src = b_sh + ((g < 2 ? cur : nxt) * 4 + (g & 3)) * HD + tq * 16;
+        // B fragment of the readout: columns 0,1 = q^ (hi, mid) of token t; 2,3 = 4,5 = 6,7 = k (hi, mid) of token t + 1, so that
+        // lanes tq >= 1 find k.S of the next token in their own accumulator columns
+        const __half* b_src = b_sh + (g < 2 ? cur * 4 + g : nxt * 4 + 2 + (g & 1)) * HD + tq * 16;
         float D[4][4];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) D[mt][0] = D[mt][1] = D[mt][2] = D[mt][3] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-            uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
-            if (g >= 4) bf = make_uint2(0u, 0u);
+            const uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
             // update with fp16 accumulators: S16' = fp16_rn(S16 + diff (alpha k)^T), the state registers are both C and D
 #pragma unroll
             for (int mt = 0; mt < 4; ++mt) {
@@ -656,17 +656,15 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
                 mma_f16_16816(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
         }
 
-        // column pair of this lane: tq = 0 -> (q^ hi, q^ mid): y of token t;  tq = 1 -> (k hi, k mid): k.S of token t + 1
+        // column pair of this lane: tq = 0 -> (q^ hi, q^ mid): y of token t;  tq >= 1 -> (k hi, k mid): k.S of token t + 1
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) {
-            const float r0 = fmaf(D[mt][1], 1.0f / 2048.0f, D[mt][0]);  // n = 16 mt + g
-            const float r1 = fmaf(D[mt][3], 1.0f / 2048.0f, D[mt][2]);  // n = 16 mt + g + 8
+            kS[mt][0] = fmaf(D[mt][1], 1.0f / 2048.0f, D[mt][0]);  // n = 16 mt + g
+            kS[mt][1] = fmaf(D[mt][3], 1.0f / 2048.0f, D[mt][2]);  // n = 16 mt + g + 8
             if (tq == 0) {
-                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + g] = r0;
-                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + 8 + g] = r1;
+                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + g] = kS[mt][0];
+                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + 8 + g] = kS[mt][1];
             }
-            kS[mt][0] = __shfl_sync(0xffffffffu, r0, (lane & ~3) | 1);
-            kS[mt][1] = __shfl_sync(0xffffffffu, r1, (lane & ~3) | 1);
         }
       }
         rg = rg == 2 ? 0 : rg + 1;
