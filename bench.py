@@ -298,7 +298,7 @@ def main():
                 achieved, peak, unit = amount / dur / 1e12, 4.0 * peaks["bf16_tflops_sustained"], "TFLOP/s"
             # DRAM bytes (read + write) per row from the ncu capture of a smaller launch of the same kernel
             # (profiles/efla_scan64_seqs512_T128.md: 527.85 MB for 65536 rows), scaled by the rows of one launch here
-            ncu_bytes_per_row = {"efla_scan": 527.85e6 / 65536}
+            ncu_bytes_per_row = {"efla_scan": 524.71e6 / 65536}
             traffic = ncu_bytes_per_row[ent["name"]] * wave_members * cfg.batch * cfg.seq if ent["name"] in ncu_bytes_per_row else None
             roof = {"kernel": ent["name"], "bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                     "traffic": traffic, "avg_launch_ms": dur * 1e3, "peak_source": peak_src +

@@ -229,8 +229,9 @@ __global__ void init_shadow_kernel(const int8_t* __restrict__ w, float* __restri
 }
 
 // Z for the dense (full-matrix noise) form; 256 threads per block, one element each.
+// Elements idx0 .. idx0 + n - 1 of the vector (the hash is keyed by the element's index in the whole vector) go to Z[0 .. n).
 __global__ void __launch_bounds__(256) z_dense_kernel(const float* __restrict__ pair_weights, const uint64_t* __restrict__ pair_seeds,
-                                                      uint64_t salt, int pairs, int n, int use_clt, int clt_k, float* __restrict__ Z) {
+                                                      uint64_t salt, int pairs, int idx0, int n, int use_clt, int clt_k, float* __restrict__ Z) {
     extern __shared__ uint8_t zsm[];
     uint64_t* seeds = reinterpret_cast<uint64_t*>(zsm);
     float* wts = reinterpret_cast<float*>(zsm + sizeof(uint64_t) * 256);
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(256) z_dense_kernel(const float* __restrict__ 
             for (int p = 0; p < cnt; ++p) {
                 const float w = wts[p];
                 if (w == 0.0f) continue;
-                z = fmaf(w, static_cast<float>(noise_hash(seeds[p], static_cast<uint64_t>(idx), use_clt != 0, clt_k)), z);
+                z = fmaf(w, static_cast<float>(noise_hash(seeds[p], static_cast<uint64_t>(idx0 + idx), use_clt != 0, clt_k)), z);
             }
         }
     }
@@ -508,6 +509,14 @@ int get_scratch(size_t floats, float** out) {
 
 }  // namespace
 
+// Dense-noise Z of elements idx0 .. idx0 + n - 1 of a vector into Z[0 .. n).
+int z_dense_launch(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int idx0, int n, int use_clt, int clt_k,
+                   float* Z, cudaStream_t st) {
+    if (n <= 0) return BNF4_OK;
+    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), st>>>(pair_weights, pair_seeds, salt, pairs, idx0, n, use_clt, clt_k, Z);
+    return check_launch("z_dense_kernel");
+}
+
 // d_descs: the table in device memory (nullptr with ndesc == 0: the single matrix h_descs[0], passed by value).
 // h_descs: the same table in host memory, for the grid size.
 int z_lowrank_launch(const float* pair_weights, const ZLowrankDesc* d_descs, const ZLowrankDesc* h_descs, int ndesc, int pairs, int rank,
@@ -637,7 +646,7 @@ int bnf4_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, 
                          int clt_k, float* Z, float* sumsq, void* stream) {
     if (n <= 0) return BNF4_OK;
     if (!pair_weights || !pair_seeds || !Z || !sumsq) return set_error(BNF4_ERR_INVALID, "compute_z_sumsq: null pointer");
-    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), S(stream)>>>(pair_weights, pair_seeds, salt, pairs, n, use_clt, clt_k, Z);
+    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), S(stream)>>>(pair_weights, pair_seeds, salt, pairs, 0, n, use_clt, clt_k, Z);
     const int rc = check_launch("z_dense_kernel");
     if (rc) return rc;
     return sumsq_into(Z, n, sumsq, S(stream));
@@ -756,7 +765,7 @@ extern "C" int bnf4_compute_z_sumsq_static(const float* pair_weights, const uint
     int rc = static_partials(&partial);
     if (rc) return rc;
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
-    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), st>>>(pair_weights, pair_seeds, salt, pairs, n, use_clt, clt_k, Z);
+    z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), st>>>(pair_weights, pair_seeds, salt, pairs, 0, n, use_clt, clt_k, Z);
     rc = check_launch("z_dense_kernel");
     if (rc) return rc;
     // Every partial the final kernel reads (indices 0 .. ceil(n/256)-1) is written by the block kernel of this same

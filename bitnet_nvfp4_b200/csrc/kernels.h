@@ -64,6 +64,9 @@ struct ZLowrankDesc {
 int z_lowrank_launch(const float* pair_weights, const ZLowrankDesc* d_descs, const ZLowrankDesc* h_descs, int ndesc, int pairs, int rank,
                      float cscale, int shard, int nshards, cudaStream_t stream);
 
+int z_dense_launch(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int idx0, int n, int use_clt, int clt_k,
+                   float* Z, cudaStream_t stream);
+
 void count_launch();
 
 }  // namespace bnf4

@@ -42,11 +42,11 @@ struct GenDesc {
 };
 
 // block_map[b] = (descriptor << 20) | block within that descriptor: every launched block has work.
-__global__ void gen_noise_kernel(const GenDesc* __restrict__ descs, const uint32_t* __restrict__ block_map,
+__global__ void gen_noise_kernel(const GenDesc* __restrict__ descs, const uint32_t* __restrict__ block_map, int block0, int pair0,
                                  const uint64_t* __restrict__ pair_seeds, int use_clt, int clt_k) {
-    const uint32_t bm = block_map[blockIdx.x];
+    const uint32_t bm = block_map[block0 + blockIdx.x];
     const GenDesc d = descs[bm >> 20];
-    const int pair = blockIdx.y;
+    const int pair = pair0 + blockIdx.y;
     const long long n = static_cast<long long>(d.n_major) * d.rank;
     const long long idx = static_cast<long long>(bm & 0xfffffu) * blockDim.x + threadIdx.x;
     if (idx >= n) return;
@@ -99,7 +99,8 @@ struct Model {
     GenDesc* gen_descs;
     uint32_t* gen_block_map;
     int num_gen = 0;
-    int gen_blocks = 0;
+    int gen_blocks = 0, gen_blocks_factors = 0;
+    int eval_begin = 0, eval_end = 0;  // pairs whose evaluation-only noise the last prepare_step generated
     // wave buffers
     int8_t* x_q;
     uint8_t *a_h, *sf_h, *a_f, *sf_f;
@@ -388,6 +389,23 @@ std::vector<UpdMatrix> update_matrices(Model& m) {
     return v;
 }
 
+// The fp32 vectors of the update, after the matrices in the Z buffer (reference: update_vector, src/train_efla_lm.cpp:5648-5657).
+struct UpdVector {
+    float* v;
+    int n;
+    uint64_t salt;
+};
+std::vector<UpdVector> update_vectors(Model& m) {
+    return {{m.head_bias, m.V, kSaltHeadBias}, {m.beta_bias, m.L, kSaltBetaBias}, {m.pos, m.T * m.H, kSaltPos}};
+}
+// A vector is computed in element ranges by the ranks only when that saves real work.
+inline bool vector_sharded(int n, int nshards) { return nshards > 1 && n >= 4096 && (n % nshards) == 0; }
+long long z_matrix_elems(Model& m) {
+    long long n = 0;
+    for (const UpdMatrix& x : update_matrices(m)) n += static_cast<long long>(x.rows) * x.cols;
+    return n;
+}
+
 // Device table of the matrices with Z laid out back to back from z_base (the order of update_matrices).
 std::vector<ZLowrankDesc> z_descs(Model& m, float* z_base) {
     std::vector<ZLowrankDesc> d;
@@ -408,14 +426,23 @@ int update_z(Model& m, const float* pair_weights, int shard, int nshards, float*
         TRY(check_cuda(cudaMemcpyAsync(m.zdesc_ext, h.data(), h.size() * sizeof(ZLowrankDesc), cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(zdesc)"));
         dtab = m.zdesc_ext;
     }
-    TimedScope ts(m, KC_UPDATE_Z, st, 1);
-    return z_lowrank_launch(pair_weights, dtab, h.data(), static_cast<int>(h.size()), m.pairs_step, m.r, m.c_r, shard, nshards, st);
+    float* zb = z_ext != nullptr ? z_ext : m.Z_all;
+    TimedScope ts(m, KC_UPDATE_Z, st, 4);
+    TRY(z_lowrank_launch(pair_weights, dtab, h.data(), static_cast<int>(h.size()), m.pairs_step, m.r, m.c_r, shard, nshards, st));
+    long long off = z_matrix_elems(m);
+    for (const UpdVector& x : update_vectors(m)) {
+        int i0 = 0, cnt = x.n;
+        if (vector_sharded(x.n, nshards)) { cnt = x.n / nshards; i0 = shard * cnt; }
+        TRY(z_dense_launch(pair_weights, m.pair_seeds, x.salt, m.pairs_step, i0, cnt, m.cfg.use_clt, m.cfg.clt_k, zb + off + i0, st));
+        off += x.n;
+    }
+    return BNF4_OK;
 }
 
 // Applies the precomputed Z of every matrix, then updates the fp32 vectors and re-quantises the base weights.
 int update_apply(Model& m, const float* pair_weights, const float* z_all, const bnf4_update_cfg* u, cudaStream_t st) {
     const int P = m.pairs_step;
-    const int V = m.V, H = m.H, L = m.L;
+    const int L = m.L;
     const float thresh = u->thresh * std::sqrt(static_cast<float>(P));
     int slot = 0;
     long long off = 0;
@@ -433,18 +460,18 @@ int update_apply(Model& m, const float* pair_weights, const float* z_all, const 
         TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
         TRY(bnf4_update_shadow_ternary_device(x.w, x.shadow, Z, n, m.inv_rms, u->lr, thresh, st));
     }
-    // fp32 vectors (reference: update_vector on the host, src/train_efla_lm.cpp:5648-5657)
-    auto vec = [&](float* v, int n, uint64_t salt) {
+    // fp32 vectors
+    for (const UpdVector& x : update_vectors(m)) {
+        const float* Z = z_all + off;
+        off += x.n;
+        if (x.v == m.pos && !u->train_pos) continue;
         float* ema = m.rms_ema + (slot++);
         TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
-        TimedScope ts(m, KC_UPDATE_Z, st, 5);
-        TRY(bnf4_compute_z_sumsq(pair_weights, m.pair_seeds, salt, P, n, m.cfg.use_clt, m.cfg.clt_k, m.Z, m.sumsq, st));
-        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
-        return bnf4_update_vector_device(v, m.Z, n, m.inv_rms, u->lr, thresh, st);
-    };
-    TRY(vec(m.head_bias, V, kSaltHeadBias));
-    TRY(vec(m.beta_bias, L, kSaltBetaBias));
-    if (u->train_pos) TRY(vec(m.pos, m.T * H, kSaltPos));
+        TimedScope ts(m, KC_UPDATE_APPLY, st, 4);
+        TRY(bnf4_sumsq(Z, x.n, m.sumsq, st));
+        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, x.n, m.inv_rms, st));
+        TRY(bnf4_update_vector_device(x.v, Z, x.n, m.inv_rms, u->lr, thresh, st));
+    }
     TimedScope ts(m, KC_REQUANTIZE, st, 2 + 3 * L);
     return quantize_base(m, st);
 }
@@ -534,7 +561,7 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     A_(t_a, Mr * 4 * r); A_(t_f, Mr * r);
     A_(Z, static_cast<size_t>(T) * H + V + L); A_(sumsq, 1); A_(inv_rms, 1);
     {
-        size_t zn = 0;
+        size_t zn = static_cast<size_t>(V) + L + static_cast<size_t>(T) * H;
         for (const UpdMatrix& x : update_matrices(*m)) zn += static_cast<size_t>(x.rows) * x.cols;
         const size_t nd = update_matrices(*m).size();
         A_(Z_all, zn); A_(zdesc, nd); A_(zdesc_ext, nd);
@@ -579,6 +606,9 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     m->num_gen = static_cast<int>(gd.size());
     std::vector<uint32_t> bmap;
     for (size_t i = 0; i < gd.size(); ++i) {
+        // the last three tables (positional, head-bias and beta-bias noise) are read by the evaluation of a pair only;
+        // the factor tables before them are also read by the update, for all pairs
+        if (i + 3 == gd.size()) m->gen_blocks_factors = static_cast<int>(bmap.size());
         const long long nb = (static_cast<long long>(gd[i].n_major) * gd[i].rank + 255) / 256;
         if (nb > 0xfffff || i > 0xfff) { bnf4_model_destroy(m); return set_error(BNF4_ERR_INVALID, "model_create: noise table too large"); }
         for (long long b = 0; b < nb; ++b) bmap.push_back(static_cast<uint32_t>(i << 20) | static_cast<uint32_t>(b));
@@ -694,17 +724,32 @@ int bnf4_model_set_tokens(void* handle, const uint8_t* tokens, const uint8_t* ta
     return check_cuda(cudaMemcpyAsync(m.targets, targets, m.R, kind, S(stream)), "cudaMemcpyAsync(targets)");
 }
 
-int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pairs, void* stream) {
+int bnf4_model_prepare_step_range(void* handle, uint64_t seed, uint64_t epoch, int pairs, int eval_begin, int eval_count, void* stream) {
     if (!handle) return set_error(BNF4_ERR_INVALID, "model_prepare_step: null handle");
     Model& m = *M(handle);
     if (pairs <= 0 || pairs > m.cfg.max_pairs) return set_error(BNF4_ERR_INVALID, "model_prepare_step: pairs=%d outside [1,%d]", pairs, m.cfg.max_pairs);
     if (pairs > 65535) return set_error(BNF4_ERR_INVALID, "model_prepare_step: at most 65535 pairs");
+    if (eval_begin < 0 || eval_count < 0 || eval_begin + eval_count > pairs)
+        return set_error(BNF4_ERR_INVALID, "model_prepare_step: evaluation range [%d,%d) outside the %d pairs of the step", eval_begin, eval_begin + eval_count, pairs);
     m.pairs_step = pairs;
+    m.eval_begin = eval_begin;
+    m.eval_end = eval_begin + eval_count;
     TRY(bnf4_fill_pair_seeds(seed, epoch, pairs, m.pair_seeds, stream));
-    const dim3 grid(m.gen_blocks, pairs);
-    TimedScope ts(m, KC_GEN_NOISE, S(stream), 2);
-    gen_noise_kernel<<<grid, 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
-    return check_launch("gen_noise_kernel");
+    TimedScope ts(m, KC_GEN_NOISE, S(stream), 3);
+    // rank-r factors of all pairs (the update reads them all) ...
+    gen_noise_kernel<<<dim3(m.gen_blocks_factors, pairs), 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, 0, 0, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
+    TRY(check_launch("gen_noise_kernel"));
+    // ... and the per-pair vectors only for the pairs this process evaluates
+    if (eval_count > 0) {
+        gen_noise_kernel<<<dim3(m.gen_blocks - m.gen_blocks_factors, eval_count), 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, m.gen_blocks_factors,
+                                                                                                        eval_begin, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
+        TRY(check_launch("gen_noise_kernel"));
+    }
+    return BNF4_OK;
+}
+
+int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pairs, void* stream) {
+    return bnf4_model_prepare_step_range(handle, seed, epoch, pairs, 0, pairs, stream);
 }
 
 int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* losses, void* stream) {
@@ -712,6 +757,9 @@ int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* l
     Model& m = *M(handle);
     if (pair_begin < 0 || pair_count < 0 || pair_begin + pair_count > m.pairs_step)
         return set_error(BNF4_ERR_INVALID, "model_eval_pairs: pairs [%d,%d) outside the prepared step of %d pairs", pair_begin, pair_begin + pair_count, m.pairs_step);
+    if (pair_count > 0 && (pair_begin < m.eval_begin || pair_begin + pair_count > m.eval_end))
+        return set_error(BNF4_ERR_INVALID, "model_eval_pairs: pairs [%d,%d) outside the range [%d,%d) the step was prepared for", pair_begin,
+                         pair_begin + pair_count, m.eval_begin, m.eval_end);
     const int wave_pairs = m.W / 2;
     for (int p = 0; p < pair_count; p += wave_pairs) {
         const int np = std::min(wave_pairs, pair_count - p);
@@ -740,8 +788,10 @@ int bnf4_model_update_z_layout(void* handle, int nshards, int max_entries, long 
     if (!handle || nshards < 1) { set_error(BNF4_ERR_INVALID, "model_update_z_layout: bad argument"); return -1; }
     Model& m = *M(handle);
     const std::vector<UpdMatrix> mats = update_matrices(m);
-    if (static_cast<int>(mats.size()) > max_entries && (offsets || elems || sharded)) {
-        set_error(BNF4_ERR_INVALID, "model_update_z_layout: %d entries needed, room for %d", static_cast<int>(mats.size()), max_entries);
+    const std::vector<UpdVector> vecs = update_vectors(m);
+    const int total = static_cast<int>(mats.size() + vecs.size());
+    if (total > max_entries && (offsets || elems || sharded)) {
+        set_error(BNF4_ERR_INVALID, "model_update_z_layout: %d entries needed, room for %d", total, max_entries);
         return -1;
     }
     long long off = 0;
@@ -752,8 +802,15 @@ int bnf4_model_update_z_layout(void* handle, int nshards, int max_entries, long 
         if (sharded) sharded[i] = (nshards > 1 && mats[i].rows >= nshards && (mats[i].rows % nshards) == 0) ? 1 : 0;
         off += n;
     }
+    for (size_t i = 0; i < vecs.size(); ++i) {
+        const size_t j = mats.size() + i;
+        if (offsets) offsets[j] = off;
+        if (elems) elems[j] = vecs[i].n;
+        if (sharded) sharded[j] = vector_sharded(vecs[i].n, nshards) ? 1 : 0;
+        off += vecs[i].n;
+    }
     if (total_elems) *total_elems = off;
-    return static_cast<int>(mats.size());
+    return total;
 }
 
 int bnf4_model_update_z(void* handle, const float* pair_weights, int shard, int nshards, float* z_all, void* stream) {

@@ -46,6 +46,7 @@ _l.register({
     "bnf4_model_get_weights": (c_int, [c_void_p, C.POINTER(ModelWeights)]),
     "bnf4_model_set_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "bnf4_model_prepare_step": (c_int, [c_void_p, C.c_uint64, C.c_uint64, c_int, c_void_p]),
+    "bnf4_model_prepare_step_range": (c_int, [c_void_p, C.c_uint64, C.c_uint64, c_int, c_int, c_int, c_void_p]),
     "bnf4_model_eval_pairs": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "bnf4_model_eval_base": (c_int, [c_void_p, c_void_p, c_void_p]),
     "bnf4_model_update": (c_int, [c_void_p, c_void_p, C.POINTER(UpdateCfg), c_void_p]),
@@ -201,6 +202,12 @@ class PopulationModel:
         _l.check(self.lib.bnf4_model_prepare_step(self.h, seed, epoch, pairs, _stream()))
         self.pairs = pairs
 
+    def prepare_step_range(self, seed: int, epoch: int, pairs: int, eval_begin: int, eval_count: int):
+        """prepare_step for a rank that evaluates only pairs [eval_begin, eval_begin + eval_count): the per-pair noise that
+        only an evaluation reads is generated for that range alone."""
+        self.pairs = pairs
+        _l.check(self.lib.bnf4_model_prepare_step_range(self.h, seed, epoch, pairs, eval_begin, eval_count, _stream()))
+
     def eval_pairs(self, pair_begin: int, pair_count: int, out: torch.Tensor | None = None) -> torch.Tensor:
         """Returns a float32 CUDA tensor [2*pair_count]: (loss+, loss-) per pair."""
         if out is None:
@@ -272,15 +279,21 @@ def shard_pairs(pairs_total: int, rank: int, world: int) -> tuple[int, int]:
 def gather_z_shards(z_all: torch.Tensor, entries, rank: int, world: int, group=None):
     """In-place all-gather of the row shards of every sharded matrix inside z_all: rank r owns the r-th of `world` equal
     contiguous blocks of each (offset, elems, sharded=True) entry."""
+    import contextlib
     import torch.distributed as dist
     if world <= 1:
         return
-    for off, n, sharded in entries:
-        if not sharded:
-            continue
-        full = z_all[off:off + n]
-        per = n // world
-        dist.all_gather_into_tensor(full, full[rank * per:(rank + 1) * per], group=group)
+    # NCCL: one grouped launch for all tensors; other backends: one collective per tensor
+    batch = contextlib.nullcontext()
+    if dist.get_backend(group) == "nccl" and hasattr(dist, "_coalescing_manager"):
+        batch = dist._coalescing_manager(group=group, device=z_all.device, async_ops=False)
+    with batch:
+        for off, n, sharded in entries:
+            if not sharded:
+                continue
+            full = z_all[off:off + n]
+            per = n // world
+            dist.all_gather_into_tensor(full, full[rank * per:(rank + 1) * per], group=group)
 
 
 def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world: int = 1, group=None, lr: float = 0.8,
@@ -293,7 +306,10 @@ def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world
     `model` is a PopulationModel (or any object with prepare_step / eval_pairs / update). Returns all 2*pairs_total losses."""
     import torch.distributed as dist
     begin, count = shard_pairs(pairs_total, rank, world)
-    model.prepare_step(seed, epoch, pairs_total)
+    if world > 1 and hasattr(model, "prepare_step_range"):
+        model.prepare_step_range(seed, epoch, pairs_total, begin, count)
+    else:
+        model.prepare_step(seed, epoch, pairs_total)
     mine = model.eval_pairs(begin, count)
     if world > 1:
         if pairs_total % world == 0:

@@ -430,6 +430,12 @@ int bnf4_model_prepare_step(void* handle, uint64_t seed, uint64_t epoch, int pai
 /* Evaluates pairs [pair_begin, pair_begin + pair_count): losses[2*i], losses[2*i+1] = mean cross-entropy of the
  * + and - member of pair pair_begin + i. Device output. */
 int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* losses, void* stream);
+/* bnf4_model_prepare_step for a process that evaluates only pairs [eval_begin, eval_begin + eval_count) of the step: the
+ * rank-r factors are generated for all pairs (the update reads them all), the noise that only an evaluation reads
+ * (positional table, head bias, beta bias: two thirds of the bytes) for that range only. bnf4_model_eval_pairs rejects
+ * pairs outside the range. */
+int bnf4_model_prepare_step_range(void* handle, uint64_t seed, uint64_t epoch, int pairs, int eval_begin, int eval_count,
+                                  void* stream);
 /* Mean cross-entropy of the unperturbed model on the current tokens (device output, 1 float). */
 int bnf4_model_eval_base(void* handle, float* loss, void* stream);
 /* pair_weights: shaped fitness of ALL pairs of the step (device, `pairs` floats as passed to prepare_step).
@@ -438,15 +444,16 @@ int bnf4_model_eval_base(void* handle, float* loss, void* stream);
 int bnf4_model_update(void* handle, const float* pair_weights, const bnf4_update_cfg* ucfg, void* stream);
 /* The same update with the dominant part -- Z = sum_p w_p * noise_p for every ternary matrix -- split by rows over
  * `nshards` ranks (the reference replicates it on every worker, src/train_efla_lm.cpp:5560-5660):
- *   1. bnf4_model_update_z_layout: for matrix i of the model (fixed order), offsets[i] / elems[i] locate its Z inside one
- *      caller-owned fp32 buffer `z_all`, and sharded[i] tells whether its rows divide by nshards (otherwise every rank
- *      computes the whole matrix). Returns the number of matrices (<= max_entries, at most 6 + 6 per layer) or -1;
- *      *total_elems receives the size of z_all in floats.
- *   2. bnf4_model_update_z: rank `shard` fills rows [shard*rows/nshards, (shard+1)*rows/nshards) of every sharded matrix
- *      (all rows of the others) in z_all.
- *   3. the caller all-gathers each sharded matrix in place (contiguous row blocks in rank order);
- *   4. bnf4_model_update_apply: sum of squares, RMS normalisation, shadow/ternary update of all matrices from z_all, the
- *      fp32 vectors, and re-quantisation: the same kernels in the same order as bnf4_model_update, hence the same bits. */
+ *   1. bnf4_model_update_z_layout: for tensor i of the model (the ternary matrices in a fixed order, then head bias,
+ *      beta bias and the positional table), offsets[i] / elems[i] locate its Z inside one caller-owned fp32 buffer
+ *      `z_all`, and sharded[i] tells whether it is computed in nshards equal contiguous parts (matrices whose rows
+ *      divide by nshards, vectors of at least 4096 elements; otherwise every rank computes the whole tensor). Returns
+ *      the number of tensors (<= max_entries, at most 6 + 6 per layer) or -1; *total_elems receives the size of
+ *      z_all in floats.
+ *   2. bnf4_model_update_z: rank `shard` fills its part of every sharded tensor (all of the others) in z_all.
+ *   3. the caller all-gathers each sharded tensor in place (contiguous blocks in rank order);
+ *   4. bnf4_model_update_apply: sum of squares, RMS normalisation, shadow/ternary update of all matrices and the update of
+ *      the fp32 vectors from z_all, and re-quantisation: the same kernels in the same order as bnf4_model_update, hence the same bits. */
 int bnf4_model_update_z_layout(void* handle, int nshards, int max_entries, long long* offsets, long long* elems, int* sharded,
                                long long* total_elems);
 int bnf4_model_update_z(void* handle, const float* pair_weights, int shard, int nshards, float* z_all, void* stream);

@@ -183,7 +183,7 @@ def test_sharded_update_is_bit_identical(nshards):
     import ctypes as C
     import torch
     from bitnet_nvfp4_b200 import lib, population
-    kw = dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=2, max_pairs=8, wave_members=8)
+    kw = dict(hidden=128, layers=2, seq=32, batch=4, heads=2, rank=2, max_pairs=8, wave_members=8)  # positional table: 4096 elements, sharded
     rng = np.random.default_rng(23)
     pw = torch.from_numpy(orc.shape_pair_weights(rng.standard_normal(8).astype(np.float32))).cuda()
     _, _, _, _, a = make(kw)
@@ -206,6 +206,30 @@ def test_sharded_update_is_bit_identical(nshards):
         assert np.array_equal(wa[k], wb[k]), k
     (sa, ea), (sb, eb) = a.get_optimizer_state(), b.get_optimizer_state()
     assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
+
+
+def test_prepare_step_for_a_pair_range():
+    """A rank that evaluates pairs [2, 5) generates the evaluation-only noise for those pairs alone: same losses as after
+    a full prepare_step, and pairs outside the range are refused."""
+    import torch
+    from bitnet_nvfp4_b200 import lib
+    kw = dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=6, wave_members=4)
+    _, _, _, _, a = make(kw)
+    _, _, _, _, b = make(kw)
+    a.prepare_step(9, 1, 6)
+    want = a.eval_pairs(2, 3).cpu().numpy()
+    b.prepare_step_range(9, 1, 6, 2, 3)
+    got = b.eval_pairs(2, 3).cpu().numpy()
+    assert np.array_equal(got, want)
+    with pytest.raises(lib.Bnf4Error):
+        b.eval_pairs(0, 1)
+    # the update reads the factors of all pairs: identical after a ranged prepare
+    pw = torch.from_numpy(orc.shape_pair_weights(np.random.default_rng(3).standard_normal(6).astype(np.float32))).cuda()
+    a.update(pw)
+    b.update(pw)
+    wa, wb = a.get_weights(), b.get_weights()
+    for k in wa:
+        assert np.array_equal(wa[k], wb[k]), k
 
 
 def test_two_gpu_sharded_update_matches_replicated():
