@@ -258,6 +258,12 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// d = a (16 x 16) * b (16 x 8): no accumulator input
+__device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
 // d (in place) += a (16 x 8) * b (8 x 8)
 __device__ __forceinline__ void mma_f16_1688(float& d0, float& d1, float& d2, float& d3, uint32_t a0, uint32_t a1, uint32_t b0) {
     asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
@@ -601,6 +607,7 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
     __syncwarp();
     prepare4(0);
 
+    float* orow = ob + g;  // this lane's output columns of the current token
     int rg = 0;  // ring group (four slots) that holds tokens t0 .. t0 + 3
     for (int t0 = 0; t0 < p.T; t0 += 4) {
         const int gb = (t0 >> 2) & 1;  // vector buffers gb * 4 .. gb * 4 + 3 hold tokens t0 .. t0 + 3
@@ -639,21 +646,26 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
         // B fragment of the readout: columns 0,1 = q^ (hi, mid) of token t; 2,3 = 4,5 = 6,7 = k (hi, mid) of token t + 1, so that
         // lanes tq >= 1 find k.S of the next token in their own accumulator columns
         const __half* b_src = b_sh + (g < 2 ? cur * 4 + g : nxt * 4 + 2 + (g & 1)) * HD + tq * 16;
-        float D[4][4];
+        // update with fp16 accumulators: S16' = fp16_rn(S16 + diff (alpha k)^T), the state registers are both C and D. n-tile by
+        // n-tile, so that the first MMAs of a token need only the first n-tile's diff
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) D[mt][0] = D[mt][1] = D[mt][2] = D[mt][3] = 0.0f;
+        for (int mt = 0; mt < 4; ++mt) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
-            // update with fp16 accumulators: S16' = fp16_rn(S16 + diff (alpha k)^T), the state registers are both C and D
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) {
+            for (int ks = 0; ks < 4; ++ks) {
                 mma_f16acc_1688(Sh[mt][ks][0], Sh[mt][ks][1], da[mt][0], da[mt][1], kw[2 * ks]);
                 mma_f16acc_1688(Sh[mt][ks][2], Sh[mt][ks][3], da[mt][0], da[mt][1], kw[2 * ks + 1]);
             }
+        }
+        // readout, d-tile by d-tile: the four n-tiles' accumulation chains interleave and finish in n-tile order
+        float D[4][4];
 #pragma unroll
-            for (int mt = 0; mt < 4; ++mt)
-                mma_f16_16816(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                if (ks == 0) mma_f16_16816_zero(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
+                else mma_f16_16816(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
+            }
         }
 
         // column pair of this lane: tq = 0 -> (q^ hi, q^ mid): y of token t;  tq >= 1 -> (k hi, k mid): k.S of token t + 1
@@ -662,10 +674,11 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
             kS[mt][0] = fmaf(D[mt][1], 1.0f / 2048.0f, D[mt][0]);  // n = 16 mt + g
             kS[mt][1] = fmaf(D[mt][3], 1.0f / 2048.0f, D[mt][2]);  // n = 16 mt + g + 8
             if (tq == 0) {
-                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + g] = kS[mt][0];
-                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + 8 + g] = kS[mt][1];
+                orow[16 * mt] = kS[mt][0];
+                orow[16 * mt + 8] = kS[mt][1];
             }
         }
+        orow += p.ld_out;
       }
         rg = rg == 2 ? 0 : rg + 1;
     }
