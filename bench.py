@@ -135,7 +135,10 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--pop", type=int, default=2048)
+    ap.add_argument("--pop", type=int, default=0, help="population (default 2048; 128 with --stress)")
+    ap.add_argument("--stress", action="store_true",
+                    help="the scaled-up stress widths instead of the default model: hidden 2048, 12 layers, 32 heads of 64, MLP 8192, seq 512, "
+                         "batch 16, rank-4 perturbations")
     ap.add_argument("--wave", type=int, default=0, help="members per wave (0 = library default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-pairs", type=int, default=1, help="pairs in the CPU-baseline sample")
@@ -146,9 +149,16 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     from bitnet_nvfp4_b200 import population, synth  # noqa: E402  (imports torch)
-    cfg = population.Config(max_pairs=args.pop // 2, wave_members=args.wave)
+    if args.pop <= 0:
+        args.pop = 128 if args.stress else 2048
+    if args.stress:
+        cfg = population.Config(hidden=2048, layers=12, mlp_mult=4, seq=512, batch=16, heads=32, rank=4, max_pairs=args.pop // 2,
+                                wave_members=args.wave)
+        args.no_cpu_baseline = True
+    else:
+        cfg = population.Config(max_pairs=args.pop // 2, wave_members=args.wave)
     tokens_per_step = args.pop * cfg.batch * cfg.seq
-    workload = (f"default ES step: pop={args.pop} (antithetic pairs), batch={cfg.batch}, seq={cfg.seq}, hidden={cfg.hidden}, "
+    workload = (f"{'stress-width' if args.stress else 'default'} ES step: pop={args.pop} (antithetic pairs), batch={cfg.batch}, seq={cfg.seq}, hidden={cfg.hidden}, "
                 f"layers={cfg.layers}, mlp_mult={cfg.mlp_mult}, heads={cfg.heads}x{cfg.hidden // cfg.heads}, rank-{cfg.rank} "
                 f"perturbation, sigma=2^-{cfg.sigma_shift}, lr=0.8, thresh=0.008, centered-rank fitness")
     config = {"workload": workload, "pop": args.pop, "global_batch_tokens": tokens_per_step,

@@ -217,3 +217,26 @@ def test_pos_gelu_absmean_fused_population(H):
     assert same(yq, rq) and same(codes, rc) and same(sf, rs)
     tref = np.concatenate([rq[m * R:(m + 1) * R].astype(np.int32) @ tvec[m // 2].astype(np.int32).T for m in range(2 * pairs)])
     assert same(tout, tref)
+
+
+@pytest.mark.parametrize("hid,nvec", [(512, 4), (2048, 1), (128, 3)])
+def test_absmean_int8_rows_with_projections(H, hid, nvec):
+    """FE_ABSMEAN on int8 rows (the quantiser that follows the residual-add GEMM epilogue) with the rank-r projections of
+    the next GEMM: normalised int8, codes, scales and t all bit-exact."""
+    import torch
+    rng = np.random.default_rng(hid + nvec)
+    pairs, R = 2, 24
+    rows = 2 * pairs * R
+    x = rng.integers(-127, 128, (rows, hid)).astype(np.int8)
+    x[5, :] = 0
+    tvec = rng.integers(-4, 5, (pairs, nvec, hid)).astype(np.int8)
+    yq = torch.zeros((rows, hid), dtype=torch.int8, device="cuda")
+    codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
+    tout = torch.zeros((rows, nvec), dtype=torch.int32, device="cuda")
+    H.rowquant(H.FE_ABSMEAN, rows=rows, cols_in=hid, cols_out=hid, rows_per_member=R, in_i8=dev(x), ld_in=hid, norm_scale=1.7,
+               out_q=yq, ld_q=hid, out_codes=codes, out_sf=sf, tvec=dev(tvec), tvec_pair_stride=nvec * hid, nvec=nvec, t_out=tout)
+    rq, rc, rs = orc.absmean_norm_q(x.copy(), None, 0.0, 1.7)
+    assert same(yq, rq) and same(codes, rc) and same(sf, rs)
+    tref = np.concatenate([rq[m * R:(m + 1) * R].astype(np.int32) @ tvec[m // 2].astype(np.int32).T for m in range(2 * pairs)])
+    assert same(tout, tref)
