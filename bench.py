@@ -289,6 +289,16 @@ def main():
             rate = amount * n_waves * per_wave / (ms * 1e-3)
             if bound == "hbm":
                 ent.update(achieved=rate / 1e9, unit="GB/s", frac_measured=rate / 1e9 / peaks["hbm_gbs"], frac_nominal=rate / 8e12)
+                if name == "efla_scan":
+                    # not bandwidth-bound in this formulation: also the arithmetic rate (6 * head_dim^2 flops per head and token)
+                    # and the share of the mma.sync tensor pipe that its 48 MMAs per head and token (8.6 cycles each per SM
+                    # sub-partition, measured) take at the sampled SM clock
+                    hd = cfg.hidden // cfg.heads
+                    rows_total = amount / ((3 * cfg.hidden + 1) * 4 + 4 * cfg.hidden) * n_waves * per_wave
+                    ent["achieved_tflops"] = rows_total * 6.0 * cfg.heads * hd * hd / (ms * 1e-3) / 1e12
+                    if hd == 64:
+                        sms = torch.cuda.get_device_properties(local_rank).multi_processor_count
+                        ent["mma_pipe_frac"] = rows_total * cfg.heads * 48 * 8.6 / (4 * sms * 1.965e9 * ms * 1e-3)
             else:
                 ent.update(achieved=rate / 1e12, unit="TFLOP/s", frac_measured=rate / 1e12 / (4.0 * peaks["bf16_tflops_sustained"]),
                            frac_nominal=rate / 9e15)
