@@ -141,7 +141,7 @@ def main():
                          "batch 16, rank-4 perturbations")
     ap.add_argument("--wave", type=int, default=0, help="members per wave (0 = library default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-pairs", type=int, default=1, help="pairs in the CPU-baseline sample")
+    ap.add_argument("--cpu-pairs", type=int, default=6, help="pairs in the CPU-baseline sample (about 2 s of CPU work each on 16 threads)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
