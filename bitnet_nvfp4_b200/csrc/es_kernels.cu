@@ -474,6 +474,78 @@ __global__ void add_scaled_kernel(float* __restrict__ out, const float* __restri
     if (i < n) out[i] = fmaf(scale, noise[i], out[i]);
 }
 
+// ---- the apply phase of the ES update for a table of tensors: four launches instead of five per tensor -------------------
+// Same arithmetic, block structure and summation order as sumsq_blocks / sumsq_final / inv_rms / update_shadow /
+// update_vector above, so the bits are those of the per-tensor calls. Block b of the grid belongs to the tensor whose
+// [block0, block0 + ceil(n / 256)) contains it.
+__device__ __forceinline__ int find_tensor(const UpdApplyDesc* __restrict__ d, int ndesc, int block) {
+    int lo = 0, hi = ndesc - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (d[mid].block0 <= block) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+__global__ void __launch_bounds__(256) sumsq_blocks_batched_kernel(const UpdApplyDesc* __restrict__ d, int ndesc, float* __restrict__ partial) {
+    __shared__ float sh[256];
+    __shared__ int ti;
+    if (threadIdx.x == 0) ti = find_tensor(d, ndesc, static_cast<int>(blockIdx.x));
+    __syncthreads();
+    const UpdApplyDesc& x = d[ti];
+    const int idx = (static_cast<int>(blockIdx.x) - x.block0) * 256 + threadIdx.x;
+    const float z = idx < x.n ? x.Z[idx] : 0.0f;
+    sh[threadIdx.x] = __fmul_rn(z, z);
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) sh[threadIdx.x] += sh[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) partial[blockIdx.x] = sh[0];
+}
+// one warp per tensor; then its lane 0 turns the sum into inv_rms (and advances the tensor's RMS-EMA)
+__global__ void sumsq_final_inv_rms_batched_kernel(const UpdApplyDesc* __restrict__ d, const float* __restrict__ partial, int use_adaptive,
+                                                   float beta, float eps, float* __restrict__ inv_rms_out) {
+    __shared__ double lane_sum[32];
+    const UpdApplyDesc& x = d[blockIdx.x];
+    const int lane = threadIdx.x;
+    const int nblocks = (x.n + 255) / 256;
+    const float* part = partial + x.block0;
+    const int per = (nblocks + 31) / 32;
+    double t = 0.0;
+    for (int b = lane * per; b < min(nblocks, (lane + 1) * per); ++b) t += static_cast<double>(part[b]);
+    lane_sum[lane] = t;
+    __syncwarp();
+    if (lane == 0) {
+        double tot = 0.0;
+        for (int l = 0; l < 32; ++l) tot += lane_sum[l];
+        const float sumsq = static_cast<float>(tot);
+        float inv = 1.0f;
+        if (use_adaptive) {
+            const float ms = __fdiv_rn(sumsq, static_cast<float>(x.n));
+            float ema = x.ema[0];
+            if (ema == 0.0f) ema = ms;
+            ema = fmaf(beta, ema, __fmul_rn(1.0f - beta, ms));
+            x.ema[0] = ema;
+            inv = __fdiv_rn(1.0f, __fsqrt_rn(ema + eps));
+        }
+        inv_rms_out[blockIdx.x] = inv;
+    }
+}
+__global__ void __launch_bounds__(256) update_batched_kernel(const UpdApplyDesc* __restrict__ d, int ndesc, const float* __restrict__ inv_rms,
+                                                             float lr, float thresh) {
+    __shared__ int ti;
+    if (threadIdx.x == 0) ti = find_tensor(d, ndesc, static_cast<int>(blockIdx.x));
+    __syncthreads();
+    const UpdApplyDesc& x = d[ti];
+    const int i = (static_cast<int>(blockIdx.x) - x.block0) * 256 + threadIdx.x;
+    if (i >= x.n) return;
+    const float g = __fmul_rn(inv_rms[ti], x.Z[i]);
+    if (fabsf(g) < thresh) return;
+    const float s = fmaf(lr, g, x.target[i]);
+    x.target[i] = s;
+    if (x.w != nullptr) x.w[i] = static_cast<int8_t>(clip_ternary(__float2int_rn(s)));
+}
+
 // library-owned scratch for the block partials of sum(Z^2), one per device
 struct Scratch {
     float* ptr = nullptr;
@@ -515,6 +587,21 @@ int z_dense_launch(const float* pair_weights, const uint64_t* pair_seeds, uint64
     if (n <= 0) return BNF4_OK;
     z_dense_kernel<<<(n + 255) / 256, 256, 256 * (sizeof(uint64_t) + sizeof(float)), st>>>(pair_weights, pair_seeds, salt, pairs, idx0, n, use_clt, clt_k, Z);
     return check_launch("z_dense_kernel");
+}
+
+// Apply phase for a table of tensors (block0 filled by the caller: running sum of ceil(n / 256)); partial holds one float
+// per block, inv_rms one per tensor.
+int update_apply_batched(const UpdApplyDesc* d_descs, int ndesc, int total_blocks, float* partial, float* inv_rms, int use_adaptive, float beta,
+                         float eps, float lr, float thresh, cudaStream_t st) {
+    if (ndesc <= 0 || total_blocks <= 0) return BNF4_OK;
+    sumsq_blocks_batched_kernel<<<total_blocks, 256, 0, st>>>(d_descs, ndesc, partial);
+    int rc = check_launch("sumsq_blocks_batched_kernel");
+    if (rc) return rc;
+    sumsq_final_inv_rms_batched_kernel<<<ndesc, 32, 0, st>>>(d_descs, partial, use_adaptive, beta, eps, inv_rms);
+    rc = check_launch("sumsq_final_inv_rms_batched_kernel");
+    if (rc) return rc;
+    update_batched_kernel<<<total_blocks, 256, 0, st>>>(d_descs, ndesc, inv_rms, lr, thresh);
+    return check_launch("update_batched_kernel");
 }
 
 // d_descs: the table in device memory (nullptr with ndesc == 0: the single matrix h_descs[0], passed by value).

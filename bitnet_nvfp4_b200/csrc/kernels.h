@@ -64,6 +64,17 @@ struct ZLowrankDesc {
 int z_lowrank_launch(const float* pair_weights, const ZLowrankDesc* d_descs, const ZLowrankDesc* h_descs, int ndesc, int pairs, int rank,
                      float cscale, int shard, int nshards, cudaStream_t stream);
 
+// Apply phase of the ES update over a table of tensors (es_kernels.cu).
+struct UpdApplyDesc {
+    int8_t* w;       // ternary weights (nullptr for an fp32 vector)
+    float* target;   // fp32 shadow of a matrix, or the vector itself
+    const float* Z;  // noise sum
+    float* ema;      // the tensor's RMS-EMA slot
+    int n;
+    int block0;      // first 256-element block of this tensor in the launch
+};
+int update_apply_batched(const UpdApplyDesc* d_descs, int ndesc, int total_blocks, float* partial, float* inv_rms, int use_adaptive, float beta,
+                         float eps, float lr, float thresh, cudaStream_t stream);
 int z_dense_launch(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int idx0, int n, int use_clt, int clt_k,
                    float* Z, cudaStream_t stream);
 

@@ -113,6 +113,8 @@ struct Model {
     int32_t *t_a, *t_f;
     // update scratch
     float *Z, *Z_all, *sumsq, *inv_rms;
+    UpdApplyDesc* upd_descs;  // table, block partials and inv_rms of the batched apply phase
+    float *upd_partial, *upd_inv;
     ZLowrankDesc *zdesc, *zdesc_ext;  // device tables of the update's matrices: Z inside Z_all / inside a caller's buffer
     int launches_per_wave = 0;
 
@@ -439,38 +441,35 @@ int update_z(Model& m, const float* pair_weights, int shard, int nshards, float*
     return BNF4_OK;
 }
 
-// Applies the precomputed Z of every matrix, then updates the fp32 vectors and re-quantises the base weights.
+// Applies the precomputed Z of every tensor (sum of squares, RMS-EMA, gated update: four launches for all of them) and
+// re-quantises the base weights.
 int update_apply(Model& m, const float* pair_weights, const float* z_all, const bnf4_update_cfg* u, cudaStream_t st) {
+    (void)pair_weights;
     const int P = m.pairs_step;
     const int L = m.L;
     const float thresh = u->thresh * std::sqrt(static_cast<float>(P));
-    int slot = 0;
+    std::vector<UpdApplyDesc> h;
+    int slot = 0, block0 = 0;
     long long off = 0;
     for (const UpdMatrix& x : update_matrices(m)) {
-        float* ema = m.rms_ema + (slot++);
         const int n = x.rows * x.cols;
-        const float* Z = z_all + off;
+        h.push_back({x.w, x.shadow, z_all + off, m.rms_ema + (slot++), n, block0});
+        block0 += (n + 255) / 256;
         off += n;
-        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
-        {
-            TimedScope ts(m, KC_UPDATE_Z, st, 2);
-            TRY(bnf4_sumsq(Z, n, m.sumsq, st));
-        }
-        TimedScope ts2(m, KC_UPDATE_APPLY, st, 2);
-        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, n, m.inv_rms, st));
-        TRY(bnf4_update_shadow_ternary_device(x.w, x.shadow, Z, n, m.inv_rms, u->lr, thresh, st));
     }
-    // fp32 vectors
     for (const UpdVector& x : update_vectors(m)) {
         const float* Z = z_all + off;
         off += x.n;
         if (x.v == m.pos && !u->train_pos) continue;
-        float* ema = m.rms_ema + (slot++);
-        TRY(check_cuda(cudaMemsetAsync(m.sumsq, 0, sizeof(float), st), "cudaMemsetAsync(sumsq)"));
-        TimedScope ts(m, KC_UPDATE_APPLY, st, 4);
-        TRY(bnf4_sumsq(Z, x.n, m.sumsq, st));
-        TRY(bnf4_update_inv_rms(m.sumsq, ema, u->use_adaptive, u->adaptive_beta, u->adaptive_eps, x.n, m.inv_rms, st));
-        TRY(bnf4_update_vector_device(x.v, Z, x.n, m.inv_rms, u->lr, thresh, st));
+        h.push_back({nullptr, x.v, Z, m.rms_ema + (slot++), x.n, block0});
+        block0 += (x.n + 255) / 256;
+    }
+    {
+        TimedScope ts(m, KC_UPDATE_APPLY, st, 3);
+        // pageable source: the copy is staged before the call returns
+        TRY(check_cuda(cudaMemcpyAsync(m.upd_descs, h.data(), h.size() * sizeof(UpdApplyDesc), cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(upd_descs)"));
+        TRY(update_apply_batched(m.upd_descs, static_cast<int>(h.size()), block0, m.upd_partial, m.upd_inv, u->use_adaptive, u->adaptive_beta,
+                                 u->adaptive_eps, u->lr, thresh, st));
     }
     TimedScope ts(m, KC_REQUANTIZE, st, 2 + 3 * L);
     return quantize_base(m, st);
@@ -565,6 +564,9 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
         for (const UpdMatrix& x : update_matrices(*m)) zn += static_cast<size_t>(x.rows) * x.cols;
         const size_t nd = update_matrices(*m).size();
         A_(Z_all, zn); A_(zdesc, nd); A_(zdesc_ext, nd);
+        size_t nblk = (static_cast<size_t>(V) + 255) / 256 + (static_cast<size_t>(L) + 255) / 256 + (static_cast<size_t>(T) * H + 255) / 256;
+        for (const UpdMatrix& x : update_matrices(*m)) nblk += (static_cast<size_t>(x.rows) * x.cols + 255) / 256;
+        A_(upd_descs, nd + 3); A_(upd_partial, nblk); A_(upd_inv, nd + 3);
     }
 #undef A_
     if (rc) { bnf4_model_destroy(m); return rc; }
