@@ -246,7 +246,20 @@ __global__ void __launch_bounds__(256) z_dense_kernel(const float* __restrict__ 
         __syncthreads();
         const int cnt = min(256, pairs - p0);
         if (idx < n) {
-            for (int p = 0; p < cnt; ++p) {
+            // four independent hash chains in flight; the multiply-adds stay in pair order (pairs of weight zero are skipped,
+            // like in the reference)
+            int p = 0;
+            for (; p + 4 <= cnt; p += 4) {
+                float e[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) e[q] = static_cast<float>(noise_hash(seeds[p + q], static_cast<uint64_t>(idx0 + idx), use_clt != 0, clt_k));
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float w = wts[p + q];
+                    if (w != 0.0f) z = fmaf(w, e[q], z);
+                }
+            }
+            for (; p < cnt; ++p) {
                 const float w = wts[p];
                 if (w == 0.0f) continue;
                 z = fmaf(w, static_cast<float>(noise_hash(seeds[p], static_cast<uint64_t>(idx0 + idx), use_clt != 0, clt_k)), z);

@@ -1,6 +1,6 @@
 #!/usr/bin/env python
-"""Regenerates the golden fixtures of tests/golden/ (run in a container that has /root/reference and the CUTLASS
-headers; the fixtures themselves are committed and need neither).
+"""Regenerates the golden fixtures of tests/golden/ (run where a checkout of the reference project and the CUTLASS headers are present;
+the fixtures themselves are committed and need neither).
 
   cutlass_codec.npz   e2m1 / ue4m3 conversions and the scale-factor layout, produced by gen_codec_golden.cpp from the
                       CUTLASS headers found in the image (the reference's own CUTLASS pin is unknown: the submodule is
