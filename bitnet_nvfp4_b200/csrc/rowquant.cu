@@ -286,7 +286,8 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
     return v;
 }
 // Element ownership as in rowquant_kernel: lane l owns the 16-element scale blocks l, l + 32, ... (NB of them).
-template <int FE, int NB>
+// NV = upper bound of p.nvec this instance handles (4 or kMaxTVec): the projection loops carry no tests beyond it.
+template <int FE, int NB, int NV>
 __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowquant_fast_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
     __shared__ __align__(16) uint8_t lut_s[kQuantLutSignedBytes];
     {
@@ -467,9 +468,9 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
         }
 
         // ---------------- stage 3: int8 copy, codes, scales, rank-r projections ----------------
-        int tacc[kMaxTVec];
+        int tacc[NV];
 #pragma unroll
-        for (int v = 0; v < kMaxTVec; ++v) tacc[v] = 0;
+        for (int v = 0; v < NV; ++v) tacc[v] = 0;
 #pragma unroll
         for (int i = 0; i < NB; ++i) {
             const int kb = lane + 32 * i;
@@ -481,12 +482,21 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
             if (active) {
                 float tq[16];
                 float am = 0.0f;
+                if (kNorm && inv > 1.0f) {  // same for the whole row; only then can |v| * inv pass 127
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    float n = vf[i][e];
-                    if constexpr (kNorm) n = fminf(fmaxf(__fmul_rn(n, inv), -127.0f), 127.0f);
-                    am = fmaxf(am, fabsf(n));
-                    tq[e] = n + M;
+                    for (int e = 0; e < 16; ++e) {
+                        const float n = fminf(fmaxf(__fmul_rn(vf[i][e], inv), -127.0f), 127.0f);
+                        am = fmaxf(am, fabsf(n));
+                        tq[e] = n + M;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        float n = vf[i][e];
+                        if constexpr (kNorm) n = __fmul_rn(n, inv);
+                        am = fmaxf(am, fabsf(n));
+                        tq[e] = n + M;
+                    }
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) w[q] = biased4_to_bytes(tq[4 * q], tq[4 * q + 1], tq[4 * q + 2], tq[4 * q + 3]);
@@ -515,7 +525,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
             if (p.nvec > 0 && active) {
                 const int8_t* tv = p.tvec + static_cast<size_t>(pair) * p.tvec_pair_stride + k0;
 #pragma unroll
-                for (int vg = 0; vg < kMaxTVec / 4; ++vg) {
+                for (int vg = 0; vg < NV / 4; ++vg) {
                     if (4 * vg < p.nvec) {  // warp-uniform; projections come in groups of four or fewer
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -536,7 +546,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
         }
         if (p.nvec > 0) {
 #pragma unroll
-            for (int vg = 0; vg < kMaxTVec / 4; ++vg) {
+            for (int vg = 0; vg < NV / 4; ++vg) {
                 if (4 * vg < p.nvec) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -590,9 +600,15 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
                 kernel<<<grid, warps * 32, 0, stream>>>(p, lut);
                 return BNF4_OK;
             };
-            if (nblk <= 32) rc = run(rowquant_fast_kernel<FE, 1>);
-            else if (nblk <= 64) rc = run(rowquant_fast_kernel<FE, 2>);
-            else rc = run(rowquant_fast_kernel<FE, 4>);
+            if (p.nvec <= 4) {
+                if (nblk <= 32) rc = run(rowquant_fast_kernel<FE, 1, 4>);
+                else if (nblk <= 64) rc = run(rowquant_fast_kernel<FE, 2, 4>);
+                else rc = run(rowquant_fast_kernel<FE, 4, 4>);
+            } else {
+                if (nblk <= 32) rc = run(rowquant_fast_kernel<FE, 1, kMaxTVec>);
+                else if (nblk <= 64) rc = run(rowquant_fast_kernel<FE, 2, kMaxTVec>);
+                else rc = run(rowquant_fast_kernel<FE, 4, kMaxTVec>);
+            }
             if (rc) return rc;
             return check_launch("rowquant_fast_kernel");
         }

@@ -84,6 +84,8 @@ def bench_gemm(m, variants, iters, n_arg=0, k_arg=0):
                 lib.load().bnf4_set_option(b"gemm_tma_store", 1)
             elif v == "lora":
                 H.gemm_nvfp4_ex(**base, d=d, ldd=ldd, epilogue=H.EPI_F32, **lora)
+            elif v == "addi8":  # the product added into an int8 residual stream (the ff2 form)
+                H.gemm_nvfp4_ex(**base, epilogue=H.EPI_ADD_I8, resid=d8, ld_resid=n, add_scale=0.0625, **lora)
             elif v == "gelu":
                 H.gemm_nvfp4_ex(**base, epilogue=H.EPI_GELU_I8, act_scale=1.0, d_i8=d8, ld_i8=n)
             elif v == "gelufp4":
@@ -93,7 +95,7 @@ def bench_gemm(m, variants, iters, n_arg=0, k_arg=0):
                 raise SystemExit(f"unknown variant {v}")
 
         ms = _time(run, iters)
-        out_bytes = m * n * (4 if v in ("plain", "direct", "lora") or v.startswith("aid") else (1 if v == "gelu" else 0.5625))
+        out_bytes = m * n * (4 if v in ("plain", "direct", "lora") or v.startswith("aid") else (1 if v in ("gelu", "addi8") else 0.5625))
         print(f"gemm {v:8s} M={m} N={n} K={k}: {ms:.4f} ms  {2 * m * n * k / ms / 1e9:8.1f} TFLOP/s  output {out_bytes / ms / 1e6:7.1f} GB/s")
     assert H.device_error() == 0
 
@@ -137,7 +139,7 @@ def bench_efla(seqs, iters, mma=2):
           f"{rows * heads / ms / 1e3:7.1f} M head-steps/s")
 
 
-def bench_rowquant(rows, iters):
+def bench_rowquant(rows, iters, fe="add"):
     hid = 512
     x = torch.randint(-127, 128, (rows, hid), dtype=torch.int8, device="cuda")
     y = torch.randn(rows, hid, device="cuda") * 20
@@ -145,6 +147,15 @@ def bench_rowquant(rows, iters):
     codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
     sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
     t = torch.zeros(rows, 4, dtype=torch.int32, device="cuda")
+
+    def run_norm():
+        H.rowquant(H.FE_ABSMEAN, rows=rows, cols_in=hid, cols_out=hid, rows_per_member=4096, in_i8=x, ld_in=hid, norm_scale=1.0,
+                   out_codes=codes, out_sf=sf, tvec=tv, tvec_pair_stride=4 * hid, nvec=4, t_out=t)
+
+    if fe == "norm":  # int8 rows in (the quantiser after the residual-add GEMM epilogue)
+        ms = _time(run_norm, iters)
+        print(f"rowquant int8 absmean+quant rows={rows}: {ms:.4f} ms  {rows * (hid + hid // 2 + hid // 16 + 16) / ms / 1e6:7.1f} GB/s algorithmic")
+        return
 
     def run():
         H.rowquant(H.FE_ADD_ABSMEAN, rows=rows, cols_in=hid, cols_out=hid, rows_per_member=4096, sigma=0.125, inout_i8=x, in_f32=y,
@@ -163,6 +174,7 @@ def main():
     ap.add_argument("--variants", default="plain,lora,direct,gelu,gelufp4")
     ap.add_argument("--seqs", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--fe", default="add", choices=["add", "norm"], help="rowquant: residual add + abs-mean norm (fp32 in) or abs-mean norm of int8 rows")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--mma", type=int, default=2, help="efla scan kernel: 2 = tensor cores with fp16 accumulators, 1 = tensor cores with an fp32 rank-1 term, 0 = multiply-add")
     a = ap.parse_args()
@@ -173,7 +185,7 @@ def main():
     elif a.what == "efla":
         bench_efla(a.seqs, a.iters, a.mma)
     else:
-        bench_rowquant(a.rows, a.iters)
+        bench_rowquant(a.rows, a.iters, a.fe)
 
 
 if __name__ == "__main__":

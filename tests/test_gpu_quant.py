@@ -229,6 +229,9 @@ def test_absmean_int8_rows_with_projections(H, hid, nvec):
     rows = 2 * pairs * R
     x = rng.integers(-127, 128, (rows, hid)).astype(np.int8)
     x[5, :] = 0
+    x[6, :] = 0
+    x[6, :5] = [127, -127, 100, -80, 3]  # abs-mean below 1 -> scale 1.7 > 1: the normalised values clip at +-127
+    x[7, :] = rng.integers(-1, 2, hid)    # abs-mean just below 1
     tvec = rng.integers(-4, 5, (pairs, nvec, hid)).astype(np.int8)
     yq = torch.zeros((rows, hid), dtype=torch.int8, device="cuda")
     codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
