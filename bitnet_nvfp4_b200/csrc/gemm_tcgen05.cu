@@ -468,7 +468,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
 
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(p.alpha, __uint_as_float(acc[j]));
+            for (int j = 0; j < 32; j += 2) {  // packed fp32 pairs: each half rounds like the scalar instruction
+                const float2 t2 = __fmul2_rn(make_float2(p.alpha, p.alpha), make_float2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1])));
+                v[j] = t2.x;
+                v[j + 1] = t2.y;
+            }
             if (p.beta != 0.0f && row_ok) {
                 const float* crow = p.c + static_cast<size_t>(row) * p.ldc + col0;
 #pragma unroll
@@ -479,12 +483,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 // sum_r t[r]*A[n][r] is an integer below 2^24: float products and sums are exact
                 if (a_staged && p.rank == 1) {
 #pragma unroll
+                    const float2 tr2 = make_float2(tr[0], tr[0]), ls2 = make_float2(lsign, lsign);
+#pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const float4 a4 = *reinterpret_cast<const float4*>(loraA_sh + 4 * j);
-                        v[4 * j + 0] = fmaf(lsign, __fmul_rn(tr[0], a4.x), v[4 * j + 0]);
-                        v[4 * j + 1] = fmaf(lsign, __fmul_rn(tr[0], a4.y), v[4 * j + 1]);
-                        v[4 * j + 2] = fmaf(lsign, __fmul_rn(tr[0], a4.z), v[4 * j + 2]);
-                        v[4 * j + 3] = fmaf(lsign, __fmul_rn(tr[0], a4.w), v[4 * j + 3]);
+                        const float2 lo = __ffma2_rn(ls2, __fmul2_rn(tr2, make_float2(a4.x, a4.y)), make_float2(v[4 * j + 0], v[4 * j + 1]));
+                        const float2 hi = __ffma2_rn(ls2, __fmul2_rn(tr2, make_float2(a4.z, a4.w)), make_float2(v[4 * j + 2], v[4 * j + 3]));
+                        v[4 * j + 0] = lo.x; v[4 * j + 1] = lo.y; v[4 * j + 2] = hi.x; v[4 * j + 3] = hi.y;
                     }
                 } else if (a_staged) {
 #pragma unroll
