@@ -109,10 +109,13 @@ constexpr int kRoundBiasBits = 0x4B400000;     // its bit pattern
 __device__ __forceinline__ void bytes4_to_float(uint32_t w, float* out) {
     const uint32_t u = w ^ 0x80808080u;  // byte + 128 as an unsigned byte
     const float off = kRoundBias + 128.0f;
-    out[0] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7650)) - off;
-    out[1] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7651)) - off;
-    out[2] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7652)) - off;
-    out[3] = __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7653)) - off;
+    // packed fp32 pairs: each half is the scalar subtraction
+    const float2 noff = make_float2(-off, -off);
+    const float2 lo = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7650)),
+                                             __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7651))), noff);
+    const float2 hi = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7652)),
+                                             __uint_as_float(__byte_perm(u, static_cast<uint32_t>(kRoundBiasBits), 0x7653))), noff);
+    out[0] = lo.x; out[1] = lo.y; out[2] = hi.x; out[3] = hi.y;
 }
 // low bytes of four floats biased by kRoundBias -> one word of four int8
 __device__ __forceinline__ uint32_t biased4_to_bytes(float a, float b, float c, float d) {

@@ -491,11 +491,13 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                     }
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        float n = vf[i][e];
-                        if constexpr (kNorm) n = __fmul_rn(n, inv);
-                        am = fmaxf(am, fabsf(n));
-                        tq[e] = n + M;
+                    for (int e = 0; e < 16; e += 2) {  // packed fp32 pairs: each half rounds like the scalar instruction
+                        float2 n = make_float2(vf[i][e], vf[i][e + 1]);
+                        if constexpr (kNorm) n = __fmul2_rn(n, make_float2(inv, inv));
+                        am = fmaxf(am, fmaxf(fabsf(n.x), fabsf(n.y)));
+                        const float2 t2 = __fadd2_rn(n, make_float2(M, M));
+                        tq[e] = t2.x;
+                        tq[e + 1] = t2.y;
                     }
                 }
 #pragma unroll
