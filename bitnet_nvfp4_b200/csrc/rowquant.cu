@@ -361,11 +361,18 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                     float oldf[4], tb[4];
                     bytes4_to_float(rw[q], oldf);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        // old + rint(y * add_scale), clipped to +-127, all on biased floats
-                        tb[j] = resid_add_biased(oldf[j], yy[j], p.add_scale);
-                        vf[i][4 * q + j] = tb[j] - M;
-                        sum_abs += fabsf(vf[i][4 * q + j]);
+                    for (int j = 0; j < 4; j += 2) {
+                        // old + rint(y * add_scale), clipped to +-127, all on biased floats: resid_add_biased on packed fp32 pairs
+                        // (each half rounds like the scalar instruction)
+                        const float2 tr = __fadd2_rn(__fmul2_rn(make_float2(yy[j], yy[j + 1]), make_float2(p.add_scale, p.add_scale)), make_float2(M, M));
+                        const float2 sm = __fadd2_rn(tr, make_float2(oldf[j], oldf[j + 1]));
+                        tb[j] = fminf(fmaxf(sm.x, M - 127.0f), M + 127.0f);
+                        tb[j + 1] = fminf(fmaxf(sm.y, M - 127.0f), M + 127.0f);
+                        const float2 vv = __fadd2_rn(make_float2(tb[j], tb[j + 1]), make_float2(-M, -M));
+                        vf[i][4 * q + j] = vv.x;
+                        vf[i][4 * q + j + 1] = vv.y;
+                        sum_abs += fabsf(vv.x);
+                        sum_abs += fabsf(vv.y);
                     }
                     upd[q] = biased4_to_bytes(tb[0], tb[1], tb[2], tb[3]);
                 }
