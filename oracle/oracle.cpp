@@ -591,11 +591,89 @@ ORC_API void orc_efla_step_half_qkv_fused(uint16_t* S, const float* qkv, int fus
                       heads, method, eps, out + (size_t)b * hidden);
 }
 
+// ---------------------------------------------------------------------------------------------
+// What-if variants of the scan, used only to measure how far a faster formulation may depart from the
+// reference's rounding before the per-member loss leaves its 1e-4 bar. state_round_every: 1 = the reference
+// (state rounded to fp16 after every token, src/efla_lm_kernels.cu:1349); C > 1 = state carried in fp32 and
+// rounded to fp16 after every C-th token (a chunked delta rule that keeps an fp16 state between chunks);
+// 0 = never rounded. operand_bits: 0 = fp32 operands (the reference); otherwise q_hat, k, alpha*k and v-k.S are
+// rounded to that many explicit mantissa bits (10 = tf32/fp16 precision, 7 = bf16) before every product, which is
+// what a tensor-core contraction with fp32 accumulation would see. Process-global; default = the reference.
+// ---------------------------------------------------------------------------------------------
+static int g_state_round_every = 1;
+static int g_operand_bits = 0;
+ORC_API void orc_set_efla_variant(int state_round_every, int operand_bits) {
+    g_state_round_every = state_round_every;
+    g_operand_bits = operand_bits;
+}
+
+static inline float round_mantissa(float x, int bits) {
+    if (bits <= 0 || bits >= 23) return x;
+    uint32_t u;
+    std::memcpy(&u, &x, 4);
+    const int drop = 23 - bits;
+    const uint32_t half = (1u << (drop - 1)) - 1u + ((u >> drop) & 1u);  // round to nearest even
+    u = (u + half) & ~((1u << drop) - 1u);
+    std::memcpy(&x, &u, 4);
+    return x;
+}
+
+static void efla_scan_variant_seq(const float* qkv, int fused_cols, float beta_bias, int hidden, int heads, int T,
+                                  int method, float eps, float* out, int round_every, int bits) {
+    const int hd = hidden / heads;
+    std::vector<float> S((size_t)hidden * hd, 0.0f), qn(hd), ku(hd), ak(hd), diff(hd);
+    for (int t = 0; t < T; ++t) {
+        const float* row = qkv + (size_t)t * fused_cols;
+        const float beta = sigmoidf(row[3 * hidden] + beta_bias);
+        for (int h = 0; h < heads; ++h) {
+            const float* q = row + h * hd;
+            const float* k = row + hidden + h * hd;
+            const float* v = row + 2 * hidden + h * hd;
+            float* Sh = S.data() + (size_t)h * hd * hd;
+            float qss = 0.0f, kss = 0.0f;
+            for (int j = 0; j < hd; ++j) { qss = std::fmaf(q[j], q[j], qss); kss = std::fmaf(k[j], k[j], kss); }
+            const float q_inv = 1.0f / std::sqrt(qss + eps);
+            const float lambda = kss < eps ? eps : kss;
+            const float alpha = method == 0 ? beta : -std::expm1(-(beta * lambda)) / (lambda + eps);
+            const float kinv = (method == 0) ? 1.0f / std::sqrt(lambda + eps) : 1.0f;
+            for (int j = 0; j < hd; ++j) {
+                const float kj = (method == 0) ? k[j] * kinv : k[j];
+                qn[j] = round_mantissa(q[j] * q_inv, bits);
+                ku[j] = round_mantissa(kj, bits);
+                ak[j] = round_mantissa(alpha * kj, bits);
+            }
+            for (int n = 0; n < hd; ++n) {
+                float acc = 0.0f;
+                for (int d = 0; d < hd; ++d) acc = std::fmaf(ku[d], Sh[(size_t)d * hd + n], acc);
+                diff[n] = round_mantissa(v[n] - acc, bits);
+            }
+            const bool round_now = round_every > 0 && ((t + 1) % round_every == 0);
+            for (int d = 0; d < hd; ++d)
+                for (int n = 0; n < hd; ++n) {
+                    const float s = std::fmaf(ak[d], diff[n], Sh[(size_t)d * hd + n]);
+                    Sh[(size_t)d * hd + n] = round_now ? f16_to_f32(f32_to_f16(s)) : s;
+                }
+            for (int n = 0; n < hd; ++n) {
+                float acc = 0.0f;
+                for (int d = 0; d < hd; ++d) acc = std::fmaf(Sh[(size_t)d * hd + n], qn[d], acc);
+                out[(size_t)t * hidden + h * hd + n] = acc;
+            }
+        }
+    }
+}
+
 // Sequence form: qkv [seqs][T][fused_cols], state zero-initialised per sequence, out [seqs][T][hidden].
 // beta_bias_seq: one value per sequence (per-member perturbed bias).
 ORC_API void orc_efla_scan(const float* qkv, int fused_cols, const float* beta_bias_seq, int hidden, int heads,
                            int seqs, int T, int method, float eps, float* out) {
     const int hd = hidden / heads;
+    if (g_state_round_every != 1 || g_operand_bits != 0) {
+#pragma omp parallel for schedule(dynamic, 1)
+        for (int s = 0; s < seqs; ++s)
+            efla_scan_variant_seq(qkv + (size_t)s * T * fused_cols, fused_cols, beta_bias_seq[s], hidden, heads, T, method,
+                                  eps, out + (size_t)s * T * hidden, g_state_round_every, g_operand_bits);
+        return;
+    }
 #pragma omp parallel for schedule(dynamic, 1)
     for (int s = 0; s < seqs; ++s) {
         std::vector<uint16_t> S((size_t)hidden * hd, 0);

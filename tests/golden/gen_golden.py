@@ -20,7 +20,10 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-CUTLASS = Path("/opt/prime-rl/.venv/lib/python3.12/site-packages/flashinfer/data/cutlass/include")
+sys.path.insert(0, str(ROOT / "oracle"))
+import paths as oracle_paths  # noqa: E402
+
+CUTLASS = oracle_paths.cutlass_include()
 
 
 def gen_codec():
