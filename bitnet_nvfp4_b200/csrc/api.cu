@@ -54,16 +54,13 @@ unsigned long long bnf4_launch_count(void) { return g_launches.load(); }
 
 int bnf4_set_option(const char* name, int value) {
     if (name && std::strcmp(name, "gemm_tma_store") == 0) {
+        if (value != 0 && value != 1) return set_error(BNF4_ERR_INVALID, "gemm_tma_store must be 0 or 1");
         g_gemm_allow_tma_store = value;
         return BNF4_OK;
     }
-    if (name && std::strcmp(name, "efla_cols_per_lane") == 0) {
-        if (value != 1 && value != 2) return set_error(BNF4_ERR_INVALID, "efla_cols_per_lane must be 1 or 2");
-        g_efla_cols_per_lane = value;
-        return BNF4_OK;
-    }
-    if (name && std::strcmp(name, "efla_mma") == 0) {
-        g_efla_mma = value < 0 ? 0 : (value > 2 ? 2 : value);
+    if (name && std::strcmp(name, "efla_chunked") == 0) {
+        if (value != 0 && value != 1) return set_error(BNF4_ERR_INVALID, "efla_chunked must be 0 or 1");
+        g_efla_chunked = value;
         return BNF4_OK;
     }
     return set_error(BNF4_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
@@ -211,15 +208,16 @@ int bnf4_nvfp4_prepare_gemm(const void* a, const void* b, const void* sfa, const
 }
 
 // Host function (reference: shape_pair_weights src/train_efla_lm.cpp:3898-3952). Ties in the rank sort are
-// broken by index so that every rank of a data-parallel job shapes identically.
+// broken by index so that every rank of a data-parallel job shapes identically. `mode` takes the values of the
+// reference's TrainConfig::FitnessMode (src/train_efla_lm.cpp:260): 0 sign, 1 z-score, 2 centered rank.
 int bnf4_shape_pair_weights(float* w, int n, int mode, float clip) {
     if (n <= 0) return BNF4_OK;
     if (!w) return set_error(BNF4_ERR_INVALID, "shape_pair_weights: null pointer");
-    if (mode == 2) {
+    if (mode == BNF4_FITNESS_SIGN) {
         for (int i = 0; i < n; ++i) w[i] = w[i] > 0.0f ? 1.0f : (w[i] < 0.0f ? -1.0f : 0.0f);
         return BNF4_OK;
     }
-    if (mode == 0) {
+    if (mode == BNF4_FITNESS_CENTERED_RANK) {
         std::vector<int> order(n);
         for (int i = 0; i < n; ++i) order[i] = i;
         std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return w[a] < w[b]; });
@@ -228,7 +226,7 @@ int bnf4_shape_pair_weights(float* w, int n, int mode, float clip) {
         else
             for (int r = 0; r < n; ++r) ranked[order[r]] = static_cast<float>(r) / static_cast<float>(n - 1) - 0.5f;
         for (int i = 0; i < n; ++i) w[i] = ranked[i];
-    } else if (mode != 1) {
+    } else if (mode != BNF4_FITNESS_ZSCORE) {
         return set_error(BNF4_ERR_INVALID, "shape_pair_weights: unknown mode %d", mode);
     }
     float mean = 0.0f;

@@ -7,9 +7,9 @@
 //   kS[n] = sum_d k[d] S[d,n];  diff = v - kS;  S[d,n] <- fp16_rn(S[d,n] + alpha k[d] diff[n]);  y[n] = sum_d S[d,n] q^[d]
 // The reference keeps S (hidden x hidden, fp16) in HBM and streams it four times per token through six
 // kernels. Columns of S are independent, so here the state never leaves the SM:
-//   * scan kernel, head_dim 64: one warp owns one (sequence, head); the 64x64 state lives in registers
-//     (each lane owns two columns) for all T tokens; q/k/v of the next token are prefetched while the
-//     current one is processed. HBM traffic is the algorithmic minimum: read q,k,v,beta, write y.
+//   * scan kernel, head_dim 64: one warp owns one (sequence, head); the 64x64 state lives in registers as
+//     tensor-core fragments for all T tokens; q/k/v of later tokens arrive through asynchronous copies while
+//     the current one is processed. HBM traffic is the algorithmic minimum: read q,k,v,beta, write y.
 //   * generic kernel, any head_dim: one CTA owns a column slice of one (sequence, head) in shared
 //     memory; also serves the reference's single-step entry points (state loaded from / stored to HBM).
 // heads == 1 reproduces the reference; beta is one scalar per row, q-norm / lambda / alpha are per head.
@@ -109,143 +109,23 @@ __global__ void efla_generic_kernel(const EflaParams p) {
         for (int d = 0; d < hd; ++d) Sg[static_cast<size_t>(d) * hd + n] = S[d * nc + j];
 }
 
-// ------------------------------------------------------------------------------------------------
-// Scan kernel for head_dim 64, fp16-rounded state held in registers (fp32 containers), zero initial state.
-// One warp = one (sequence, head); lane owns columns lane and lane+32.
-// ------------------------------------------------------------------------------------------------
 constexpr int kScanWarps = 4;
 
-// NCOL = 2: one warp per (sequence, head), lane owns columns lane and lane+32 (128 state registers).
-// NCOL = 1: two warps per (sequence, head), lane owns one column (64 state registers, twice the warps per SM).
-// The state is held as float2 pairs over adjacent rows (d, d+1) so that the three multiply-adds per state element
-// (k.S, the rank-1 update, S.q^) issue as packed fma.rn.f32x2 instructions.
-template <int NCOL>
-__global__ void __launch_bounds__(kScanWarps * 32, NCOL == 1 ? 4 : 2) efla_scan64_kernel(const EflaParams p) {
-    constexpr int HD = 64, HP = HD / 2;
-    __shared__ __align__(16) float sh[kScanWarps][3][HD];  // k, q^, alpha*k per warp
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long wunit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;
-    const long long unit = NCOL == 1 ? (wunit >> 1) : wunit;  // (sequence, head)
-    const int colbase = NCOL == 1 ? static_cast<int>(wunit & 1) * 32 : 0;
-    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
-    const long long seq = unit / p.heads;
-    const int h = static_cast<int>(unit - seq * p.heads);
-    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
-
-    float2 S[NCOL][HP];  // S[c][j] = (S[2j][col c], S[2j+1][col c])
-#pragma unroll
-    for (int c = 0; c < NCOL; ++c)
-#pragma unroll
-        for (int j = 0; j < HP; ++j) S[c][j] = make_float2(0.0f, 0.0f);
-
-    const size_t row0 = static_cast<size_t>(seq) * p.T;
-    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
-    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
-    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
-    const float* bb = p.beta_raw + row0 * p.ld_beta;
-    float* ob = p.out + row0 * p.ld_out + h * HD;
-
-    // prefetch token 0 (q and k: all 64 elements across the warp; v: this lane's columns)
-    float q0 = qb[lane], q1 = qb[lane + 32], k0 = kb[lane], k1 = kb[lane + 32], br = bb[0];
-    float vv[NCOL];
-#pragma unroll
-    for (int c = 0; c < NCOL; ++c) vv[c] = vb[colbase + lane + 32 * c];
-
-    float* k_s = sh[warp][0];
-    float* q_s = sh[warp][1];
-    float* a_s = sh[warp][2];
-
-    for (int t = 0; t < p.T; ++t) {
-        const float cq0 = q0, cq1 = q1, ck0 = k0, ck1 = k1, cbr = br;
-        float cv[NCOL];
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c) cv[c] = vv[c];
-        if (t + 1 < p.T) {
-            const size_t o = static_cast<size_t>(t + 1) * p.ld_qkv;
-            q0 = qb[o + lane]; q1 = qb[o + lane + 32];
-            k0 = kb[o + lane]; k1 = kb[o + lane + 32];
-#pragma unroll
-            for (int c = 0; c < NCOL; ++c) vv[c] = vb[o + colbase + lane + 32 * c];
-            br = bb[static_cast<size_t>(t + 1) * p.ld_beta];
-        }
-        const float qss = warp_sum_f(fmaf(cq0, cq0, cq1 * cq1));
-        const float kss = warp_sum_f(fmaf(ck0, ck0, ck1 * ck1));
-        const float q_inv = rsqrtf(qss + p.eps);
-        const float lambda = kss < p.eps ? p.eps : kss;
-        const float beta = sigmoidf_dev(cbr + beta_bias);
-        float alpha, kscale = 1.0f;
-        if (p.method == 0) { alpha = beta; kscale = rsqrtf(lambda + p.eps); }
-        else alpha = -expm1f(-(beta * lambda)) / (lambda + p.eps);
-
-        __syncwarp();
-        k_s[lane] = ck0 * kscale; k_s[lane + 32] = ck1 * kscale;
-        q_s[lane] = cq0 * q_inv;  q_s[lane + 32] = cq1 * q_inv;
-        a_s[lane] = alpha * (ck0 * kscale); a_s[lane + 32] = alpha * (ck1 * kscale);
-        __syncwarp();
-
-        // kS for this lane's columns: two packed partial sums per column (even / odd rows twice over)
-        float2 acc[NCOL][2];
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c) acc[c][0] = acc[c][1] = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int j = 0; j < HP; j += 2) {
-            const float4 kk = *reinterpret_cast<const float4*>(k_s + 2 * j);
-#pragma unroll
-            for (int c = 0; c < NCOL; ++c) {
-                acc[c][0] = __ffma2_rn(make_float2(kk.x, kk.y), S[c][j], acc[c][0]);
-                acc[c][1] = __ffma2_rn(make_float2(kk.z, kk.w), S[c][j + 1], acc[c][1]);
-            }
-        }
-        float2 diff2[NCOL];
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c) {
-            const float d = cv[c] - ((acc[c][0].x + acc[c][0].y) + (acc[c][1].x + acc[c][1].y));
-            diff2[c] = make_float2(d, d);
-        }
-
-        // state update (rounded to fp16 every step) fused with the readout of the updated state
-        float2 y[NCOL][2];
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c) y[c][0] = y[c][1] = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int j = 0; j < HP; j += 2) {
-            const float4 ak = *reinterpret_cast<const float4*>(a_s + 2 * j);
-            const float4 qq = *reinterpret_cast<const float4*>(q_s + 2 * j);
-#pragma unroll
-            for (int c = 0; c < NCOL; ++c) {
-                const float2 s0 = __ffma2_rn(make_float2(ak.x, ak.y), diff2[c], S[c][j]);
-                const float2 s1 = __ffma2_rn(make_float2(ak.z, ak.w), diff2[c], S[c][j + 1]);
-                const float2 r0 = __half22float2(__floats2half2_rn(s0.x, s0.y));
-                const float2 r1 = __half22float2(__floats2half2_rn(s1.x, s1.y));
-                S[c][j] = r0;
-                S[c][j + 1] = r1;
-                y[c][0] = __ffma2_rn(r0, make_float2(qq.x, qq.y), y[c][0]);
-                y[c][1] = __ffma2_rn(r1, make_float2(qq.z, qq.w), y[c][1]);
-            }
-        }
-#pragma unroll
-        for (int c = 0; c < NCOL; ++c)
-            ob[static_cast<size_t>(t) * p.ld_out + colbase + lane + 32 * c] = (y[c][0].x + y[c][0].y) + (y[c][1].x + y[c][1].y);
-    }
-}
-
-
 // ------------------------------------------------------------------------------------------------
-// Tensor-core form of the scan kernel (head_dim 64, fp16-rounded state, zero initial state).
+// Scan kernel for head_dim 64 (fp16-rounded state, zero initial state): one warp owns one (sequence, head) for all T
+// tokens.
 //
 // The state is exactly representable in fp16 (it is rounded to fp16 every token), so it lives in registers ONLY as
-// packed halves, laid out as the A fragments of mma.sync.m16n8k16 with A[n][d] = S[d,n]. Per token and per 16 x 16
-// tile of the state:
-//   1. update:   S32 = S16 * I + (alpha k) diff^T      two m16n8k8 MMAs against an 8 x 8 identity; the rank-1 term,
-//                computed with packed fp32 multiplies, enters as the fp32 accumulator C, so the tensor core performs the
-//                fp16 -> fp32 widening and the addition in one step;
-//   2. rounding: S16' = fp16_rn(S32)                   packed conversions, which directly produce the next A fragment;
-//   3. readout:  D += S16' * B                          one m16n8k16 MMA with B[d][j] = { q^ hi, q^ mid 2^11, k' hi,
-//                k' mid 2^11, 0, 0, 0, 0 }: columns 0-1 give y_t = S'^T q^_t, columns 2-3 give k'.S' of the NEXT token.
+// packed halves, laid out as the A fragments of mma.sync.m16n8k16 with A[n][d] = S[d,n] -- which are at the same time
+// the C/D fragments of two m16n8k8 MMAs with fp16 accumulators. Per token and per 16 x 16 tile of the state:
+//   1. update:   S16' = fp16_rn(S16 + diff (alpha k)^T)   two m16n8k8.f16.f16.f16.f16 MMAs whose accumulator registers
+//                are the state: A holds diff split into fp16 (hi, mid) over four K columns, B the (hi, mid) halves of
+//                alpha k, so the tensor core forms the exact partial products, adds the state and rounds once;
+//   2. readout:  D += S16' * B                             one m16n8k16 MMA (fp32 accumulators) with B[d][j] = { q^ hi,
+//                q^ mid 2^11, 3 x (k' hi, k' mid 2^11) }: columns 0-1 give y_t = S'^T q^_t, the others k'.S' of the NEXT
+//                token in every other lane's own columns.
 // x = hi + mid is the two-term fp16 split of an fp32 value (hi = fp16(x), mid = fp16((x - hi) 2^11) / 2^11, error
-// <= 2^-24 |x|), so every product is exact in fp32. Compared with the multiply-add kernels the deviations are the
-// order/rounding of fp32 accumulation inside the tensor core and one extra fp32 rounding of (alpha k)*diff before
-// the addition; both are far below the fp16 rounding of the state that follows.
+// <= 2^-24 |x|), so every product is exact in fp32.
 //
 // Fragment coordinates (g = lane / 4, tq = lane % 4): for n-tile mt and d-tile ks the lane holds S[d][n] for
 // n = 16 mt + g + {0, 8} and d = 16 ks + 2 tq + {0, 1, 8, 9}.
@@ -264,12 +144,6 @@ __device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], uint32_t a0, u
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
-// d (in place) += a (16 x 8) * b (8 x 8)
-__device__ __forceinline__ void mma_f16_1688(float& d0, float& d1, float& d2, float& d3, uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
-        : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3)
-        : "r"(a0), "r"(a1), "r"(b0));
-}
 // c (16 x 8, fp16, in place) += a (16 x 8) * b (8 x 8): fp16 accumulators, one rounding to nearest of the exact sum
 __device__ __forceinline__ void mma_f16acc_1688(uint32_t& c0, uint32_t& c1, uint32_t a0, uint32_t a1, uint32_t b0) {
     asm("mma.sync.aligned.m16n8k8.row.col.f16.f16.f16.f16 {%0, %1}, {%2, %3}, {%4}, {%0, %1};" : "+r"(c0), "+r"(c1) : "r"(a0), "r"(a1), "r"(b0));
@@ -279,13 +153,8 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&hv);
 }
 
-constexpr int kScanRing = 12;                // ring of raw q/k/v/beta per warp: three groups of four tokens
-constexpr int kScanSlotFloats = 3 * 64 + 4;  // q[64], k[64], v[64], beta (+ padding to 16 bytes)
+constexpr int kScanRing = 12;                // ring of raw v per warp: three groups of four tokens
 constexpr int kScanVecBufs = 8;              // prepared vectors per warp: two groups of four tokens
-constexpr int kScanMmaCtasPerSm = 3;
-// dynamic shared memory per warp: ring, alpha*k (fp32), and the four fp16 columns q^ hi, q^ mid, k hi, k mid
-constexpr int kScanWarpSmemBytes = kScanRing * kScanSlotFloats * 4 + kScanVecBufs * 64 * 4 + kScanVecBufs * 4 * 64 * 2;
-constexpr int kScanMmaSmemBytes = kScanWarps * kScanWarpSmemBytes;
 constexpr int kScan2CtasPerSm = 4;
 constexpr int kScan2QkRing = 8;                // q, k, beta of two groups of four tokens
 constexpr int kScan2QkSlotFloats = 2 * 64 + 4;  // q[64], k[64], beta (+ padding to 16 bytes)
@@ -302,195 +171,6 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__global__ void __launch_bounds__(kScanWarps * 32, kScanMmaCtasPerSm) efla_scan64_mma_kernel(const EflaParams p) {
-    constexpr int HD = 64;
-    extern __shared__ __align__(16) uint8_t scan_smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float* in_sh = reinterpret_cast<float*>(scan_smem + warp * kScanWarpSmemBytes);  // [kScanRing][kScanSlotFloats]
-    float* a_sh = in_sh + kScanRing * kScanSlotFloats;                               // [kScanVecBufs][64]   alpha * k, permuted
-    __half* b_sh = reinterpret_cast<__half*>(a_sh + kScanVecBufs * HD);              // [kScanVecBufs][4][64] q^ hi, q^ mid, k hi, k mid, permuted
-    const long long unit = static_cast<long long>(blockIdx.x) * kScanWarps + warp;  // (sequence, head)
-    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
-    const long long seq = unit / p.heads;
-    const int h = static_cast<int>(unit - seq * p.heads);
-    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
-    const int g = lane >> 2, tq = lane & 3;
-
-    uint32_t Sh[4][4][4];  // [mt][ks][i]: the A fragment (i = 0: n = g, d pair 2tq; 1: n = g + 8; 2: n = g, d pair 2tq + 8; 3: n = g + 8)
-#pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
-    // 8 x 8 identity as a B fragment: this lane holds rows 2tq, 2tq + 1 of column g
-    const uint32_t ident = pack_half2(2 * tq == g ? 1.0f : 0.0f, 2 * tq + 1 == g ? 1.0f : 0.0f);
-
-    const size_t row0 = static_cast<size_t>(seq) * p.T;
-    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
-    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
-    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
-    const float* bb = p.beta_raw + row0 * p.ld_beta;
-    float* ob = p.out + row0 * p.ld_out + h * HD;
-
-    // asynchronous copy of four tokens' inputs (one group) into their ring slots; every lane commits one group, empty or not
-    auto issue_group = [&](int tok0) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int tok = tok0 + j;
-            if (tok < p.T) {
-                float* slot = in_sh + (tok % kScanRing) * kScanSlotFloats;
-                const size_t o = static_cast<size_t>(tok) * p.ld_qkv;
-                const int l16 = lane & 15;
-                cp_async16(slot + (lane < 16 ? 0 : HD) + 4 * l16, (lane < 16 ? qb : kb) + o + 4 * l16);
-                if (lane < 16) cp_async16(slot + 2 * HD + 4 * l16, vb + o + 4 * l16);
-                else if (lane == 16) cp_async4(slot + 3 * HD, bb + static_cast<size_t>(tok) * p.ld_beta);
-            }
-        }
-        cp_async_commit();
-    };
-
-    // Per-token vectors, four tokens at a time: lanes 8 j .. 8 j + 7 prepare token tok0 + j, eight elements each
-    // (d = 8 l + e), so the reductions are three shuffle levels deep and the scalar chain (sigmoid, expm1, divisions)
-    // runs once per four tokens. The permuted layout puts the element pairs (d, d + 1) next to each other, so the
-    // packed fp16 conversions are stored as they are.
-    const int pj = lane >> 3, pl = lane & 7;
-    auto prepare4 = [&](int tok0) {
-        const int tok = min(tok0 + pj, p.T - 1);  // past the end: the last token again (never used)
-        const float* slot = in_sh + (tok % kScanRing) * kScanSlotFloats;
-        const int buf = (tok0 + pj) % kScanVecBufs;
-        const float4 qa = *reinterpret_cast<const float4*>(slot + 8 * pl), qc = *reinterpret_cast<const float4*>(slot + 8 * pl + 4);
-        const float4 ka = *reinterpret_cast<const float4*>(slot + HD + 8 * pl), kc = *reinterpret_cast<const float4*>(slot + HD + 8 * pl + 4);
-        const float rbr = slot[3 * HD];
-        const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qc.x, qc.y, qc.z, qc.w};
-        const float kv[8] = {ka.x, ka.y, ka.z, ka.w, kc.x, kc.y, kc.z, kc.w};
-        float qss = 0.0f, kss = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) { qss = fmaf(qv[e], qv[e], qss); kss = fmaf(kv[e], kv[e], kss); }
-#pragma unroll
-        for (int o = 4; o > 0; o >>= 1) {
-            qss += __shfl_xor_sync(0xffffffffu, qss, o);
-            kss += __shfl_xor_sync(0xffffffffu, kss, o);
-        }
-        const float q_inv = rsqrtf(qss + p.eps);
-        const float lambda = kss < p.eps ? p.eps : kss;
-        const float beta = sigmoidf_dev(rbr + beta_bias);
-        float alpha, kscale = 1.0f;
-        if (p.method == 0) { alpha = beta; kscale = rsqrtf(lambda + p.eps); }
-        else alpha = -expm1f(-(beta * lambda)) / (lambda + p.eps);
-        // element d = 8 pl + e sits at (e / 2) * 16 + (pl / 2) * 4 + (e % 2) + 2 * (pl % 2) of the permuted order
-        const int pbase = (pl >> 1) * 4 + 2 * (pl & 1);
-        float* a_dst = a_sh + buf * HD + pbase;
-        __half* b_dst = b_sh + buf * 4 * HD + pbase;
-#pragma unroll
-        for (int e2 = 0; e2 < 4; ++e2) {
-            const float kn0 = kv[2 * e2] * kscale, kn1 = kv[2 * e2 + 1] * kscale, qn0 = qv[2 * e2] * q_inv, qn1 = qv[2 * e2 + 1] * q_inv;
-            *reinterpret_cast<float2*>(a_dst + 16 * e2) = make_float2(alpha * kn0, alpha * kn1);
-            // two-term fp16 splits with packed conversions
-            const __half2 qh = __floats2half2_rn(qn0, qn1), kh = __floats2half2_rn(kn0, kn1);
-            const float2 qhf = __half22float2(qh), khf = __half22float2(kh);
-            const __half2 qm = __floats2half2_rn((qn0 - qhf.x) * 2048.0f, (qn1 - qhf.y) * 2048.0f);
-            const __half2 km = __floats2half2_rn((kn0 - khf.x) * 2048.0f, (kn1 - khf.y) * 2048.0f);
-            *reinterpret_cast<__half2*>(b_dst + 0 * HD + 16 * e2) = qh;
-            *reinterpret_cast<__half2*>(b_dst + 1 * HD + 16 * e2) = qm;
-            *reinterpret_cast<__half2*>(b_dst + 2 * HD + 16 * e2) = kh;
-            *reinterpret_cast<__half2*>(b_dst + 3 * HD + 16 * e2) = km;
-        }
-    };
-
-    float kS[4][2];
-#pragma unroll
-    for (int mt = 0; mt < 4; ++mt) kS[mt][0] = kS[mt][1] = 0.0f;  // zero initial state
-    issue_group(0);
-    issue_group(4);
-    cp_async_wait<0>();
-    __syncwarp();
-    prepare4(0);
-
-    int rg = 0;  // ring group (four slots) that holds tokens t0 .. t0 + 3
-    for (int t0 = 0; t0 < p.T; t0 += 4) {
-        const int gb = (t0 >> 2) & 1;  // vector buffers gb * 4 .. gb * 4 + 3 hold tokens t0 .. t0 + 3
-        {
-            // start of a group of four tokens: fetch the group after next, prepare the next one
-            __syncwarp();  // everyone is done with the ring slots and vector buffers of the previous group
-            issue_group(t0 + 8);
-            cp_async_wait<1>();  // everything but the newest group has landed: tokens <= t0 + 7
-            __syncwarp();
-            prepare4(t0 + 4);
-            __syncwarp();
-        }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int t = t0 + j;
-        if (t >= p.T) break;
-        const int cur = gb * 4 + j, nxt = j < 3 ? cur + 1 : (gb ^ 1) * 4;
-        const float* vslot = in_sh + (rg * 4 + j) * kScanSlotFloats + 2 * HD;
-        float2 diff2[4][2];
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const float d = vslot[16 * mt + 8 * hh + g] - kS[mt][hh];
-                diff2[mt][hh] = make_float2(d, d);
-            }
-
-        // per d-tile operands: alpha*k pairs (update) and the B fragment: columns 0,1 = q^ of token t, 2,3 = k of token t+1
-        const float* a_src = a_sh + cur * HD + tq * 16;
-        const __half* b_src = b_sh + ((g < 2 ? cur : nxt) * 4 + (g & 3)) * HD + tq * 16;
-        float D[4][4];
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) D[mt][0] = D[mt][1] = D[mt][2] = D[mt][3] = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            const float4 av = *reinterpret_cast<const float4*>(a_src + ks * 4);
-            uint2 bf = *reinterpret_cast<const uint2*>(b_src + ks * 4);
-            if (g >= 4) bf = make_uint2(0u, 0u);
-            const float2 alo = make_float2(av.x, av.y), ahi = make_float2(av.z, av.w);
-            // the four n-tiles are independent: issue each stage for all of them so that MMA latency overlaps
-            float cs[4][8];
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) {
-                // rank-1 term for the lane's elements: (d pair) x (n = g, g + 8)
-                const float2 c0 = __fmul2_rn(alo, diff2[mt][0]), c1 = __fmul2_rn(alo, diff2[mt][1]);
-                const float2 c2 = __fmul2_rn(ahi, diff2[mt][0]), c3 = __fmul2_rn(ahi, diff2[mt][1]);
-                cs[mt][0] = c0.x; cs[mt][1] = c0.y; cs[mt][2] = c1.x; cs[mt][3] = c1.y;
-                cs[mt][4] = c2.x; cs[mt][5] = c2.y; cs[mt][6] = c3.x; cs[mt][7] = c3.y;
-            }
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) {
-                mma_f16_1688(cs[mt][0], cs[mt][1], cs[mt][2], cs[mt][3], Sh[mt][ks][0], Sh[mt][ks][1], ident);  // d pair 2tq
-                mma_f16_1688(cs[mt][4], cs[mt][5], cs[mt][6], cs[mt][7], Sh[mt][ks][2], Sh[mt][ks][3], ident);  // d pair 2tq + 8
-            }
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt) {
-                Sh[mt][ks][0] = pack_half2(cs[mt][0], cs[mt][1]);  // the state is rounded to fp16 every token
-                Sh[mt][ks][1] = pack_half2(cs[mt][2], cs[mt][3]);
-                Sh[mt][ks][2] = pack_half2(cs[mt][4], cs[mt][5]);
-                Sh[mt][ks][3] = pack_half2(cs[mt][6], cs[mt][7]);
-            }
-#pragma unroll
-            for (int mt = 0; mt < 4; ++mt)
-                mma_f16_16816(D[mt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], bf.x, bf.y);
-        }
-
-        // column pair of this lane: tq = 0 -> (q^ hi, q^ mid): y of token t;  tq = 1 -> (k hi, k mid): k.S of token t + 1
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-            const float r0 = fmaf(D[mt][1], 1.0f / 2048.0f, D[mt][0]);  // n = 16 mt + g
-            const float r1 = fmaf(D[mt][3], 1.0f / 2048.0f, D[mt][2]);  // n = 16 mt + g + 8
-            if (tq == 0) {
-                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + g] = r0;
-                ob[static_cast<size_t>(t) * p.ld_out + 16 * mt + 8 + g] = r1;
-            }
-            kS[mt][0] = __shfl_sync(0xffffffffu, r0, (lane & ~3) | 1);
-            kS[mt][1] = __shfl_sync(0xffffffffu, r1, (lane & ~3) | 1);
-        }
-      }
-        rg = rg == 2 ? 0 : rg + 1;
-    }
-    cp_async_wait<0>();
-}
 
 __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_mma2_kernel(const EflaParams p) {
     constexpr int HD = 64;
@@ -685,58 +365,343 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
     cp_async_wait<0>();
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Chunked scan kernel for head_dim 64 (zero initial state): the delta rule of 16 tokens at a time as dense tensor-core
+// contractions (the WY / UT-transform form). With S0 the state at the start of a chunk, K, Q^, V the chunk's rows
+// (16 x 64), a_s = alpha_s:
+//     W  = V - K S0                        (16 x 64)   the tokens' v - k.S against the chunk's initial state
+//     L[t,s] = a_s (k_t . k_s), s < t      (16 x 16)   how token s's update changes token t's k.S
+//     U  = (I + L)^-1 W                                 the tokens' true "diff" rows u_t = v_t - k_t.S_{t-1}
+//     Y  = Q^ S0 + P U,  P[t,s] = a_s (q^_t . k_s), s <= t      the readouts y_t = S_t^T q^_t
+//     S' = S0 + (a K)^T U                               the state after the chunk
+// This is the same recurrence as the per-token form (src/efla_lm_kernels.cu:590-726) in exact arithmetic. What differs
+// is rounding: the state is rounded to fp16 at the end of every chunk instead of after every token, and the operands of
+// the contractions are fp16 with fp32 accumulation. Against the per-token form the outputs move by about 1.5e-3 of
+// max |y| -- the size of the fp16 rounding noise that the per-token form itself carries relative to exact arithmetic.
+//
+// One warp owns one (sequence, head). Everything is held transposed so that accumulator fragments turn into the next
+// contraction's A fragments without shuffles: the state lives in registers as the A fragments of S^T (n x d, the layout
+// of the per-token kernel), W^T, U^T, Y^T are (n x token) accumulators, and K, Q^, a K, T = (I + L)^-1 and P are read from
+// shared memory as B fragments with ldmatrix. (I + L)^-1 is formed by forward substitution in fp32, one column per lane.
+// Per chunk: 128 m16n8k16 MMAs (the per-token kernel: 768 MMAs for 16 tokens) and about 700 other warp instructions.
+// ------------------------------------------------------------------------------------------------
+constexpr int kChunk = 16;
+constexpr int kChunkWarps = 4;
+constexpr int kCkQKStride = 72;  // floats per row of the raw q / k tiles: 16-byte pieces of two lanes per row never share a bank group
+constexpr int kCkVStride = 68;   // floats per row of the raw v tile: the accumulator-shaped reads are conflict-free
+constexpr int kCkHStride = 72;   // halves per row of the prepared operands (-K, Q^, a K): conflict-free ldmatrix rows
+constexpr int kCkTStride = 24;   // halves per row of T and P
+constexpr int kCkRawQ = 0;
+constexpr int kCkRawK = kCkRawQ + kChunk * kCkQKStride * 4;
+constexpr int kCkRawV = kCkRawK + kChunk * kCkQKStride * 4;
+constexpr int kCkBeta = kCkRawV + kChunk * kCkVStride * 4;
+constexpr int kCkAlpha = kCkBeta + kChunk * 4;
+constexpr int kCkL = kCkAlpha + kChunk * 4;
+constexpr int kCkNK = kCkL + kChunk * kChunk * 4;
+constexpr int kCkQh = kCkNK + kChunk * kCkHStride * 2;
+constexpr int kCkAK = kCkQh + kChunk * kCkHStride * 2;
+constexpr int kCkT = kCkAK + kChunk * kCkHStride * 2;
+constexpr int kCkP = kCkT + kChunk * kCkTStride * 2;
+constexpr int kCkWarpBytes = kCkP + kChunk * kCkTStride * 2;
+constexpr int kCkSmemBytes = kChunkWarps * kCkWarpBytes;
+static_assert(kCkWarpBytes % 16 == 0 && kCkL % 16 == 0 && kCkNK % 16 == 0 && kCkT % 16 == 0, "16-byte aligned shared-memory regions");
+
+__device__ __forceinline__ void mma_f16acc_16816(uint32_t& c0, uint32_t& c1, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f16.f16.f16.f16 {%0, %1}, {%2, %3, %4, %5}, {%6, %7}, {%0, %1};"
+        : "+r"(c0), "+r"(c1)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+}
+
+__global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const EflaParams p) {
+    constexpr int HD = 64;
+    extern __shared__ __align__(16) uint8_t scan_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* wsm = scan_smem + warp * kCkWarpBytes;
+    float* rawq = reinterpret_cast<float*>(wsm + kCkRawQ);
+    float* rawk = reinterpret_cast<float*>(wsm + kCkRawK);
+    float* rawv = reinterpret_cast<float*>(wsm + kCkRawV);
+    float* beta_sh = reinterpret_cast<float*>(wsm + kCkBeta);
+    float* alpha_sh = reinterpret_cast<float*>(wsm + kCkAlpha);
+    float* L_sh = reinterpret_cast<float*>(wsm + kCkL);
+    __half* nk_sh = reinterpret_cast<__half*>(wsm + kCkNK);
+    __half* qh_sh = reinterpret_cast<__half*>(wsm + kCkQh);
+    __half* ak_sh = reinterpret_cast<__half*>(wsm + kCkAK);
+    __half* t_sh = reinterpret_cast<__half*>(wsm + kCkT);
+    __half* p_sh = reinterpret_cast<__half*>(wsm + kCkP);
+    const long long unit = static_cast<long long>(blockIdx.x) * kChunkWarps + warp;  // (sequence, head)
+    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
+    const long long seq = unit / p.heads;
+    const int h = static_cast<int>(unit - seq * p.heads);
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
+    const int g = lane >> 2, tq = lane & 3;
+
+    // state S^T as A fragments: Sh[mt][ks][i] holds S[d][n] for n = 16 mt + g (+ 8 for odd i), d = 16 ks + 2 tq + {0, 1} (+ 8 for i >= 2)
+    uint32_t Sh[4][4][4];
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
+
+    const size_t row0 = static_cast<size_t>(seq) * p.T;
+    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
+    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
+    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
+    const float* bb = p.beta_raw + row0 * p.ld_beta;
+    float* ob = p.out + row0 * p.ld_out + h * HD;
+
+    // asynchronous copy of one chunk's q, k, v, beta rows into the raw tiles (16-byte pieces: lane = piece within a pair of rows)
+    auto issue_chunk = [&](int t0) {
+        const int piece = lane & 15, rsel = lane >> 4;
+#pragma unroll
+        for (int j = 0; j < kChunk / 2; ++j) {
+            const int r = 2 * j + rsel;
+            if (t0 + r < p.T) {
+                const size_t o = static_cast<size_t>(t0 + r) * p.ld_qkv + 4 * piece;
+                cp_async16(rawq + r * kCkQKStride + 4 * piece, qb + o);
+                cp_async16(rawk + r * kCkQKStride + 4 * piece, kb + o);
+                cp_async16(rawv + r * kCkVStride + 4 * piece, vb + o);
+            }
+        }
+        if (lane < kChunk && t0 + lane < p.T) cp_async4(beta_sh + lane, bb + static_cast<size_t>(t0 + lane) * p.ld_beta);
+        cp_async_commit();
+    };
+
+    // ldmatrix row addresses of this lane: matrix j = lane / 8, row lane % 8
+    const int lm_j = lane >> 3, lm_r = lane & 7;
+    // operands stored [token][d]: matrices (tokens 0-7 | d 0-7), (0-7 | 8-15), (8-15 | 0-7), (8-15 | 8-15) of a 16-wide d block
+    const uint32_t lm_tok_off = static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kCkHStride + (lm_j & 1) * 8) * 2u;
+    const uint32_t nk_addr = static_cast<uint32_t>(__cvta_generic_to_shared(nk_sh)) + lm_tok_off;
+    const uint32_t qh_addr = static_cast<uint32_t>(__cvta_generic_to_shared(qh_sh)) + lm_tok_off;
+    const uint32_t lm_ts_off = static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kCkTStride + (lm_j & 1) * 8) * 2u;
+    const uint32_t t_addr = static_cast<uint32_t>(__cvta_generic_to_shared(t_sh)) + lm_ts_off;
+    const uint32_t p_addr = static_cast<uint32_t>(__cvta_generic_to_shared(p_sh)) + lm_ts_off;
+    // a K read transposed: matrices (tokens 0-7 | d-tile), (8-15 | d-tile), (0-7 | d-tile + 1), (8-15 | d-tile + 1)
+    const uint32_t ak_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ak_sh)) +
+                             static_cast<uint32_t>(((lm_j & 1) * 8 + lm_r) * kCkHStride + (lm_j >> 1) * 8) * 2u;
+
+    issue_chunk(0);
+    for (int t0 = 0; t0 < p.T; t0 += kChunk) {
+        cp_async_wait<0>();
+        __syncwarp();
+        // ---------------- per-token scalars and fp16 operands: two lanes per token, alternate 16-byte pieces ----------------
+        {
+            const int tt = lane >> 1, hh = lane & 1;
+            const bool valid = t0 + tt < p.T;
+            float qv[32], kv[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 a = *reinterpret_cast<const float4*>(rawq + tt * kCkQKStride + (2 * j + hh) * 4);
+                const float4 b = *reinterpret_cast<const float4*>(rawk + tt * kCkQKStride + (2 * j + hh) * 4);
+                qv[4 * j] = valid ? a.x : 0.0f; qv[4 * j + 1] = valid ? a.y : 0.0f; qv[4 * j + 2] = valid ? a.z : 0.0f; qv[4 * j + 3] = valid ? a.w : 0.0f;
+                kv[4 * j] = valid ? b.x : 0.0f; kv[4 * j + 1] = valid ? b.y : 0.0f; kv[4 * j + 2] = valid ? b.z : 0.0f; kv[4 * j + 3] = valid ? b.w : 0.0f;
+            }
+            float qss = 0.0f, kss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) { qss = fmaf(qv[e], qv[e], qss); kss = fmaf(kv[e], kv[e], kss); }
+            qss += __shfl_xor_sync(0xffffffffu, qss, 1);
+            kss += __shfl_xor_sync(0xffffffffu, kss, 1);
+            const float q_inv = rsqrtf(qss + p.eps);
+            const float lambda = kss < p.eps ? p.eps : kss;
+            const float beta = sigmoidf_dev((valid ? beta_sh[tt] : 0.0f) + beta_bias);
+            float alpha, kscale = 1.0f;
+            if (p.method == 0) { alpha = beta; kscale = rsqrtf(lambda + p.eps); }
+            else alpha = -expm1f(-(beta * lambda)) / (lambda + p.eps);
+            if (!valid) alpha = 0.0f;
+            if (hh == 0) alpha_sh[tt] = alpha;
+            const float nks = -kscale, aks = alpha * kscale;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int o = tt * kCkHStride + (2 * j + hh) * 4;
+                uint2 wq, wk, wa;
+                wq.x = pack_half2(qv[4 * j] * q_inv, qv[4 * j + 1] * q_inv); wq.y = pack_half2(qv[4 * j + 2] * q_inv, qv[4 * j + 3] * q_inv);
+                wk.x = pack_half2(kv[4 * j] * nks, kv[4 * j + 1] * nks);     wk.y = pack_half2(kv[4 * j + 2] * nks, kv[4 * j + 3] * nks);
+                wa.x = pack_half2(kv[4 * j] * aks, kv[4 * j + 1] * aks);     wa.y = pack_half2(kv[4 * j + 2] * aks, kv[4 * j + 3] * aks);
+                *reinterpret_cast<uint2*>(qh_sh + o) = wq;
+                *reinterpret_cast<uint2*>(nk_sh + o) = wk;
+                *reinterpret_cast<uint2*>(ak_sh + o) = wa;
+            }
+        }
+        // ---------------- W^T starts as V^T: element (n, token) of this lane's accumulator positions ----------------
+        float Wc[4][2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = 8 * nt + 2 * tq + e;
+                const bool valid = t0 + tok < p.T;
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    Wc[mt][nt][e] = valid ? rawv[tok * kCkVStride + 16 * mt + g] : 0.0f;
+                    Wc[mt][nt][2 + e] = valid ? rawv[tok * kCkVStride + 16 * mt + 8 + g] : 0.0f;
+                }
+            }
+        __syncwarp();  // the raw tiles are free, the prepared operands are visible
+        issue_chunk(t0 + kChunk);
+
+        // ---------------- W^T = V^T + S0^T (-K^T); G = K K^T; -Q^ K^T ----------------
+        uint32_t kf[4][4], qf[4][4];  // per 16-wide d block: B fragments {b0, b1} for tokens 0-7 (regs 0, 1) and 8-15 (regs 2, 3)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            ldmatrix_x4(kf[ks], nk_addr + ks * 32);
+            ldmatrix_x4(qf[ks], qh_addr + ks * 32);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+                    mma_f16_16816(Wc[mt][nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+        float Gc[2][4], Xc[2][4];  // rows t = g (+ 8 for i >= 2), columns s = 8 nt + 2 tq + (i & 1);  Xc = -(q^_t . k_s)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Gc[nt][i] = Xc[nt][i] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                mma_f16_16816(Gc[nt], kf[ks][0], kf[ks][2], kf[ks][1], kf[ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+                mma_f16_16816(Xc[nt], qf[ks][0], qf[ks][2], qf[ks][1], qf[ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+            }
+        // L[t][s] = a_s G[t][s] (s < t) in fp32 for the substitution; P[t][s] = a_s (q^_t . k_s) (s <= t) in fp16
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const int s0 = 8 * nt + 2 * tq;
+            const float2 al = *reinterpret_cast<const float2*>(alpha_sh + s0);
+#pragma unroll
+            for (int hr = 0; hr < 2; ++hr) {
+                const int t = g + 8 * hr;
+                const float l0 = s0 < t ? al.x * Gc[nt][2 * hr] : 0.0f, l1 = s0 + 1 < t ? al.y * Gc[nt][2 * hr + 1] : 0.0f;
+                const float p0 = s0 <= t ? -al.x * Xc[nt][2 * hr] : 0.0f, p1 = s0 + 1 <= t ? -al.y * Xc[nt][2 * hr + 1] : 0.0f;
+                *reinterpret_cast<float2*>(L_sh + t * kChunk + s0) = make_float2(l0, l1);
+                *reinterpret_cast<uint32_t*>(p_sh + t * kCkTStride + s0) = pack_half2(p0, p1);
+            }
+        }
+        __syncwarp();
+        // ---------------- T = (I + L)^-1 by forward substitution, lane c owns column c ----------------
+        {
+            const int c = lane & 15;
+            float col[kChunk];
+#pragma unroll
+            for (int t = 0; t < kChunk; ++t) {
+                float acc = t == c ? 1.0f : 0.0f;
+#pragma unroll
+                for (int s4 = 0; s4 < t; s4 += 4) {
+                    const float4 lv = *reinterpret_cast<const float4*>(L_sh + t * kChunk + s4);
+                    acc = fmaf(-lv.x, col[s4], acc);
+                    if (s4 + 1 < t) acc = fmaf(-lv.y, col[s4 + 1], acc);
+                    if (s4 + 2 < t) acc = fmaf(-lv.z, col[s4 + 2], acc);
+                    if (s4 + 3 < t) acc = fmaf(-lv.w, col[s4 + 3], acc);
+                }
+                col[t] = acc;
+            }
+            if (lane < kChunk) {
+#pragma unroll
+                for (int t = 0; t < kChunk; ++t) t_sh[t * kCkTStride + c] = __float2half_rn(col[t]);
+            }
+        }
+        __syncwarp();
+        uint32_t tf[4], pf[4];
+        ldmatrix_x4(tf, t_addr);
+        ldmatrix_x4(pf, p_addr);
+        // ---------------- U^T = W^T T^T ----------------
+        uint32_t Up[4][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const uint32_t w0 = pack_half2(Wc[mt][0][0], Wc[mt][0][1]), w1 = pack_half2(Wc[mt][0][2], Wc[mt][0][3]);
+            const uint32_t w2 = pack_half2(Wc[mt][1][0], Wc[mt][1][1]), w3 = pack_half2(Wc[mt][1][2], Wc[mt][1][3]);
+            float Uc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) mma_f16_16816_zero(Uc[nt], w0, w1, w2, w3, tf[2 * nt], tf[2 * nt + 1]);
+            Up[mt][0] = pack_half2(Uc[0][0], Uc[0][1]); Up[mt][1] = pack_half2(Uc[0][2], Uc[0][3]);
+            Up[mt][2] = pack_half2(Uc[1][0], Uc[1][1]); Up[mt][3] = pack_half2(Uc[1][2], Uc[1][3]);
+        }
+        // ---------------- Y^T = S0^T Q^^T + U^T P^T ----------------
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            float Yc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) mma_f16_16816_zero(Yc[nt], Up[mt][0], Up[mt][1], Up[mt][2], Up[mt][3], pf[2 * nt], pf[2 * nt + 1]);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+                    mma_f16_16816(Yc[nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], qf[ks][2 * nt], qf[ks][2 * nt + 1]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int tok = t0 + 8 * nt + 2 * tq + e;
+                    if (tok < p.T) {
+                        float* orow = ob + static_cast<size_t>(tok) * p.ld_out + 16 * mt + g;
+                        orow[0] = Yc[nt][e];
+                        orow[8] = Yc[nt][2 + e];
+                    }
+                }
+        }
+        // ---------------- S^T += U^T (a K): fp16 accumulators = the state registers, rounded once per chunk ----------------
+#pragma unroll
+        for (int dp = 0; dp < 4; ++dp) {
+            uint32_t af[4];
+            ldmatrix_x4_trans(af, ak_addr + dp * 32);
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                mma_f16acc_16816(Sh[mt][dp][0], Sh[mt][dp][1], Up[mt][0], Up[mt][1], Up[mt][2], Up[mt][3], af[0], af[1]);
+                mma_f16acc_16816(Sh[mt][dp][2], Sh[mt][dp][3], Up[mt][0], Up[mt][1], Up[mt][2], Up[mt][3], af[2], af[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
 }  // namespace
 
-int g_efla_cols_per_lane = 2;  // host toggle (option "efla_cols_per_lane")
-int g_efla_mma = 2;            // host toggle (option "efla_mma"): 2 = tensor-core scan kernel with fp16 accumulators (default),
-                               // 1 = tensor-core scan kernel with the fp32 rank-1 term, 0 = multiply-add scan kernel
+int g_efla_chunked = 1;  // host toggle (option "efla_chunked"): what BNF4_EFLA_AUTO picks for heads of 64 with on-chip state
 
 int efla_launch(const EflaParams& p, cudaStream_t stream) {
     if (p.seqs <= 0 || p.T <= 0) return BNF4_OK;
     if (p.heads <= 0 || p.hidden <= 0 || (p.hidden % p.heads) != 0) return set_error(BNF4_ERR_INVALID, "efla: hidden=%d heads=%d", p.hidden, p.heads);
     if (!p.q || !p.k || !p.v || !p.beta_raw || !p.out) return set_error(BNF4_ERR_INVALID, "efla: null pointer");
     const int hd = p.hidden / p.heads;
-    if (p.state == nullptr && p.state_fp16 && hd == 64 && !p.force_generic) {
+    if (p.variant < 0 || p.variant > 3) return set_error(BNF4_ERR_INVALID, "efla: variant=%d outside [0,3]", p.variant);
+    const bool regs_ok = p.state == nullptr && p.state_fp16 && hd == 64 &&
+                         ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0 &&
+                         (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
+    if ((p.variant == BNF4_EFLA_PER_TOKEN || p.variant == BNF4_EFLA_CHUNKED) && !regs_ok)
+        return set_error(BNF4_ERR_INVALID, "efla: the register-state kernels need head_dim 64, no HBM state, an fp16 state and 16-byte aligned q, k, v");
+    if (regs_ok && p.variant != BNF4_EFLA_GENERIC) {
+        const bool chunked = p.variant == BNF4_EFLA_CHUNKED || (p.variant == BNF4_EFLA_AUTO && g_efla_chunked != 0);
         const long long units = p.seqs * static_cast<long long>(p.heads);
-        const bool aligned = ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0 &&
-                             (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
-        if (g_efla_mma >= 2 && aligned) {
-            const long long ctas = (units + kScanWarps - 1) / kScanWarps;
-            static bool configured2[64] = {};
-            int dev = 0;
-            int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+        const long long ctas = (units + kScanWarps - 1) / kScanWarps;
+        static_assert(kScanWarps == kChunkWarps, "one grid computation for both register-state kernels");
+        // function attributes are per device: set once for each device this process uses
+        static bool configured[64] = {};
+        int dev = 0;
+        int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+        if (rc) return rc;
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
+            rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScan2SmemBytes), "cudaFuncSetAttribute(efla_scan64_mma2_kernel)");
             if (rc) return rc;
-            if (dev < 0 || dev >= 64 || !configured2[dev]) {
-                rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScan2SmemBytes), "cudaFuncSetAttribute(efla_scan64_mma2_kernel)");
-                if (rc) return rc;
-                if (dev >= 0 && dev < 64) configured2[dev] = true;
-            }
-            efla_scan64_mma2_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScan2SmemBytes, stream>>>(p);
-            return check_launch("efla_scan64_mma2_kernel");
-        }
-        if (g_efla_mma && aligned) {
-            const long long ctas = (units + kScanWarps - 1) / kScanWarps;
-            // function attributes are per device: set once for each device this process uses
-            static bool configured[64] = {};
-            int dev = 0;
-            int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+            rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
             if (rc) return rc;
-            if (dev < 0 || dev >= 64 || !configured[dev]) {
-                rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanMmaSmemBytes), "cudaFuncSetAttribute(efla_scan64_mma_kernel)");
-                if (rc) return rc;
-                if (dev >= 0 && dev < 64) configured[dev] = true;
-            }
-            efla_scan64_mma_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScanMmaSmemBytes, stream>>>(p);
-            return check_launch("efla_scan64_mma_kernel");
+            if (dev >= 0 && dev < 64) configured[dev] = true;
         }
-        if (g_efla_cols_per_lane == 2) {
-            const long long ctas = (units + kScanWarps - 1) / kScanWarps;
-            efla_scan64_kernel<2><<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
-        } else {
-            const long long ctas = (2 * units + kScanWarps - 1) / kScanWarps;
-            efla_scan64_kernel<1><<<static_cast<unsigned>(ctas), kScanWarps * 32, 0, stream>>>(p);
+        if (chunked) {
+            efla_chunk16_kernel<<<static_cast<unsigned>(ctas), kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
+            return check_launch("efla_chunk16_kernel");
         }
-        return check_launch("efla_scan64_kernel");
+        efla_scan64_mma2_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScan2SmemBytes, stream>>>(p);
+        return check_launch("efla_scan64_mma2_kernel");
     }
     if ((hd % 32) != 0) return set_error(BNF4_ERR_INVALID, "efla: head_dim=%d must be a multiple of 32", hd);
     if (p.seqs > 65535) return set_error(BNF4_ERR_INVALID, "efla (generic kernel): at most 65535 sequences per call");

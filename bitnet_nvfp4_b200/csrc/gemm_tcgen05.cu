@@ -190,7 +190,6 @@ constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >
 struct KernelArgs {
     GemmParams p;
     int use_tma_store;
-    int timing_aid;  // results invalid; after the first kStages k-blocks: bit 0 no B loads, bit 1 no A loads, bit 2 no scale copies, bit 3 no MMAs
     int k_atoms;  // scale atoms along K
     const uint8_t* lut;  // table of the block quantiser (EPI_GELU_FP4)
     int total_tiles;
@@ -270,10 +269,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     const uint32_t sf_bytes_stage = static_cast<uint32_t>(min(4, atoms_left)) * 512u;
                     atoms_left -= 4;
                     const uint32_t bar = bar_full + 8 * s;
-                    const bool load_a = !((args.timing_aid & 2) && kc >= kStages), load_b = !((args.timing_aid & 1) && kc >= kStages);
-                    mbar_expect_tx(bar, (load_a ? kStageABytes : 0) + (load_b ? kStageBBytes : 0) + 2 * sf_bytes_stage);
-                    if (load_a) tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, my, bar);
-                    if (load_b) tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, ny, bar);
+                    mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
+                    tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, my, bar);
+                    tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, ny, bar);
                     bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_src, sf_bytes_stage, bar);
                     bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_src, sf_bytes_stage, bar);
                     sfa_src += 2048;
@@ -315,30 +313,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     const uint64_t sfb_d = sfbdesc0 + static_cast<uint64_t>(s * (kStageSfBytes >> 4));
                     const uint64_t a_d = adesc0 + static_cast<uint64_t>(s * (kStageABytes >> 4));
                     const uint64_t b_d = bdesc0 + static_cast<uint64_t>(s * (kStageBBytes >> 4));
-                    const bool do_cp = !((args.timing_aid & 4) && kc >= kStages), do_mma = !((args.timing_aid & 8) && kc >= kStages);
                     if (nk == 4) {
-                        if (do_cp) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
-                                tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
-                            }
+                        for (int j = 0; j < 4; ++j) {
+                            tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
                         }
-                        if (do_mma) {
-                            tc_mma_nvf4(acc_col, a_d, b_d, kIdesc, t_sfa, t_sfb, ks > 0 ? 1u : 0u);
+                        tc_mma_nvf4(acc_col, a_d, b_d, kIdesc, t_sfa, t_sfb, ks > 0 ? 1u : 0u);
 #pragma unroll
-                            for (int j = 1; j < 4; ++j)
-                                tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
-                                            t_sfa + 4 * j, t_sfb + 4 * j, 1u);
-                        }
+                        for (int j = 1; j < 4; ++j)
+                            tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
+                                        t_sfa + 4 * j, t_sfb + 4 * j, 1u);
                     } else {
                         for (int j = 0; j < nk; ++j) {
-                            if (do_cp) {
-                                tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
-                                tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
-                            }
+                            tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
                         }
-                        for (int j = 0; j < nk && do_mma; ++j)
+                        for (int j = 0; j < nk; ++j)
                             tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
                                         t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
                     }
@@ -482,7 +473,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             if (p.rank > 0 && row_ok) {
                 // sum_r t[r]*A[n][r] is an integer below 2^24: float products and sums are exact
                 if (a_staged && p.rank == 1) {
-#pragma unroll
                     const float2 tr2 = make_float2(tr[0], tr[0]), ls2 = make_float2(lsign, lsign);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -524,10 +514,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             }
 
             if constexpr (EPI == EPI_F32) {
-                if (args.use_tma_store == 3) {
-                    // timing aid: the tile is computed but not written
-                    if (v[0] == 123456.789f && v[31] == 9.87654321f) p.d[0] = v[5];
-                } else if (args.use_tma_store) {
+                if (args.use_tma_store) {
                     // stage the 32x32 box in 128B-swizzled shared memory, then one TMA store (clips at M and N)
                     if (it > 0) {
                         if (lane == 0) bulk_wait_read<0>();
@@ -538,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     for (int j = 0; j < 8; ++j) dst[j ^ (lane & 7)] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0 && args.use_tma_store == 1) {
+                    if (lane == 0) {
                         tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
                         bulk_commit();
                     }
@@ -567,7 +554,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         for (int g = 0; g < 8; ++g) {
                             uint32_t tb[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) tb[e] = __float_as_uint(__fmul_rn(v[4 * g + e], p.add_scale) + kRoundBias);
+                            for (int e = 0; e < 4; ++e)  // clamped first: the 16-bit field below must not wrap for huge products
+                                tb[e] = __float_as_uint(fminf(fmaxf(__fmul_rn(v[4 * g + e], p.add_scale), -512.0f), 512.0f) + kRoundBias);
                             const uint32_t r01 = __byte_perm(tb[0], tb[1], 0x5410), r23 = __byte_perm(tb[2], tb[3], 0x5410);
                             const uint32_t o01 = prmt_b32(rw[g], 0u, 0x9180u), o23 = prmt_b32(rw[g], 0u, 0xB3A2u);
                             const uint32_t s01 = __vmins2(__viaddmax_s16x2(r01, o01, 0xff81ff81u), 0x007f007fu);
@@ -775,12 +763,11 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
         if (args.lut == nullptr) return BNF4_ERR_CUDA;
     }
     args.use_tma_store = 0;
-    args.timing_aid = g_gemm_allow_tma_store >> 2;
     if (p.epilogue == EPI_F32 && (reinterpret_cast<uintptr_t>(p.d) & 15) == 0 && (p.ldd % 4) == 0 && p.ldd >= p.n) {
         rc = make_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.d, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.m),
                          static_cast<uint64_t>(p.ldd) * 4, 32, 32, "D");
         if (rc) return rc;
-        args.use_tma_store = g_gemm_allow_tma_store & 3;  // 0 direct stores, 1 TMA stores; 2 / 3 are timing aids (no output written)
+        args.use_tma_store = g_gemm_allow_tma_store != 0;  // 0 direct stores, 1 TMA stores
     } else {
         md = ma;  // unused
     }

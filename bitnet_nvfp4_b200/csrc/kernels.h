@@ -49,8 +49,7 @@ extern int g_gemm_allow_tma_store;
 // EFLA recurrence (efla.cu). Parameter block = the public bnf4_efla_desc.
 using EflaParams = bnf4_efla_desc;
 int efla_launch(const EflaParams& p, cudaStream_t stream);
-extern int g_efla_cols_per_lane;
-extern int g_efla_mma;
+extern int g_efla_chunked;
 
 // Rank-r noise sums Z of a table of matrices in one launch (es_kernels.cu).
 struct ZLowrankDesc {

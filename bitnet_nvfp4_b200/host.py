@@ -264,8 +264,11 @@ def update_shadow_ternary_device(w, shadow, Z, inv_rms, lr, thresh):
     _l.check(_l.load().bnf4_update_shadow_ternary_device(_p(w), _p(shadow), _p(Z), Z.numel(), _p(inv_rms), lr, thresh, _stream()))
 
 
-def shape_pair_weights(w_host, mode=0, clip=3.0):
-    """Host-side fitness shaping on a float32 numpy array (in place)."""
+FITNESS_SIGN, FITNESS_ZSCORE, FITNESS_CENTERED_RANK = 0, 1, 2  # the reference's TrainConfig::FitnessMode values
+
+
+def shape_pair_weights(w_host, mode=FITNESS_CENTERED_RANK, clip=3.0):
+    """Host-side fitness shaping on a float32 numpy array (in place); mode as in the reference's FitnessMode enum."""
     import numpy as np
     assert w_host.dtype == np.float32 and w_host.flags["C_CONTIGUOUS"]
     _l.check(_l.load().bnf4_shape_pair_weights(w_host.ctypes.data, w_host.size, mode, clip))

@@ -60,7 +60,7 @@ class EflaDesc(C.Structure):
         ("ld_qkv", c_int), ("ld_beta", c_int),
         ("beta_bias", c_float), ("beta_bias_seq", c_void_p), ("seqs_per_bias", c_int),
         ("hidden", c_int), ("heads", c_int), ("seqs", c_ll), ("T", c_int), ("method", c_int), ("eps", c_float),
-        ("out", c_void_p), ("ld_out", c_int), ("force_generic", c_int),
+        ("out", c_void_p), ("ld_out", c_int), ("variant", c_int),
     ]
 
 

@@ -237,7 +237,7 @@ class PopulationModel:
         return [(off[i], el[i], bool(sh[i])) for i in range(n)], tot.value
 
     def update_sharded(self, pair_weights: torch.Tensor, rank: int, world: int, group=None, lr=0.8, thresh=0.008, use_adaptive=True,
-                       adaptive_beta=0.95, adaptive_eps=1e-3, train_pos=True):
+                       adaptive_beta=0.95, adaptive_eps=1e-3, train_pos=True, spans=None):
         """The update of `update`, with Z of every ternary matrix computed by rows on `world` ranks and all-gathered in place
         (same kernels, same summation order: the weights end bit-identical to `update`)."""
         assert pair_weights.is_cuda and pair_weights.dtype == torch.float32 and pair_weights.numel() == self.pairs
@@ -248,7 +248,8 @@ class PopulationModel:
             self._z_key = key
         u = UpdateCfg(lr, thresh, int(use_adaptive), adaptive_beta, adaptive_eps, int(train_pos))
         _l.check(self.lib.bnf4_model_update_z(self.h, pair_weights.data_ptr(), rank, world, self._z_all.data_ptr(), _stream()))
-        gather_z_shards(self._z_all, self._z_entries, rank, world, group)
+        with _span(spans, "z_allgather"):
+            gather_z_shards(self._z_all, self._z_entries, rank, world, group)
         _l.check(self.lib.bnf4_model_update_apply(self.h, pair_weights.data_ptr(), self._z_all.data_ptr(), C.byref(u), _stream()))
 
     def set_timing(self, enable: bool):
@@ -266,6 +267,26 @@ class PopulationModel:
         out = np.zeros(count, dtype)
         _l.check(self.lib.bnf4_model_read_buffer(self.h, name.encode(), out.ctypes.data, out.nbytes))
         return out
+
+
+class _span:
+    """Records a CUDA-event pair on the current stream around a block and appends (name, start, end) to `spans`: the time the
+    stream spends between the two events is the exposed time of the collectives issued inside. No-op when spans is None."""
+
+    def __init__(self, spans, name):
+        self.spans, self.name = spans, name
+
+    def __enter__(self):
+        if self.spans is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+    def __exit__(self, *exc):
+        if self.spans is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            self.spans.append((self.name, self.a, b))
+        return False
 
 
 def shard_pairs(pairs_total: int, rank: int, world: int) -> tuple[int, int]:
@@ -297,13 +318,14 @@ def gather_z_shards(z_all: torch.Tensor, entries, rank: int, world: int, group=N
 
 
 def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world: int = 1, group=None, lr: float = 0.8,
-            thresh: float = 0.008, fitness_mode: int = 0, fitness_clip: float = 3.0, losses_out: torch.Tensor | None = None,
-            shard_update: bool = True, **update_kw) -> torch.Tensor:
+            thresh: float = 0.008, fitness_mode: int = 2, fitness_clip: float = 3.0, losses_out: torch.Tensor | None = None,
+            shard_update: bool = True, spans: list | None = None, **update_kw) -> torch.Tensor:
     """One ES step on this rank: evaluate this rank's pairs, all-gather the per-member losses over `group`
     (torch.distributed), shape the fitness and apply the identical deterministic update on every rank. With more than one
     rank the noise sums of the update are computed by rows across the ranks and all-gathered (shard_update=False replicates
     them like the reference does); either way every rank ends with the same bits.
-    `model` is a PopulationModel (or any object with prepare_step / eval_pairs / update). Returns all 2*pairs_total losses."""
+    `model` is a PopulationModel (or any object with prepare_step / eval_pairs / update). Returns all 2*pairs_total losses.
+    `spans`: optional list that receives (name, start event, end event) around every collective (CUDA devices only)."""
     import torch.distributed as dist
     begin, count = shard_pairs(pairs_total, rank, world)
     if world > 1 and hasattr(model, "prepare_step_range"):
@@ -314,7 +336,8 @@ def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world
     if world > 1:
         if pairs_total % world == 0:
             losses = losses_out if losses_out is not None else torch.empty(2 * pairs_total, dtype=mine.dtype, device=mine.device)
-            dist.all_gather_into_tensor(losses, mine, group=group)
+            with _span(spans if mine.is_cuda else None, "loss_allgather"):
+                dist.all_gather_into_tensor(losses, mine, group=group)
         else:  # ragged shards: gather with padding
             cap = 2 * (pairs_total // world + 1)
             padded = torch.zeros(cap, dtype=mine.dtype, device=mine.device)
@@ -326,7 +349,7 @@ def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world
         losses = mine
     weights = shape_fitness(fitness_from_losses(losses), fitness_mode, fitness_clip)
     if world > 1 and shard_update and hasattr(model, "update_sharded"):
-        model.update_sharded(weights, rank, world, group, lr=lr, thresh=thresh, **update_kw)
+        model.update_sharded(weights, rank, world, group, lr=lr, thresh=thresh, **({"spans": spans} if spans is not None else {}), **update_kw)
     else:
         model.update(weights, lr=lr, thresh=thresh, **update_kw)
     return losses
@@ -338,7 +361,7 @@ def fitness_from_losses(losses: torch.Tensor) -> torch.Tensor:
     return -(l2[:, 0] - l2[:, 1])
 
 
-def shape_fitness(fitness: torch.Tensor, mode: int = 0, clip: float = 3.0) -> torch.Tensor:
+def shape_fitness(fitness: torch.Tensor, mode: int = 2, clip: float = 3.0) -> torch.Tensor:
     """Centered-rank shaping on the host (2 KB round trip), returned as a CUDA tensor."""
     from . import host
     w = fitness.detach().to("cpu", torch.float32).contiguous().numpy().copy()

@@ -40,10 +40,10 @@ const char* bnf4_last_error(void);
 const char* bnf4_version(void);
 /* Number of kernels this library has launched from this process (all threads). */
 unsigned long long bnf4_launch_count(void);
-/* Options: "gemm_tma_store" (1 default; 0 = direct-store epilogue; 2 and 3 are timing aids that compute the tiles but
- * leave D unwritten: 2 stages them in shared memory, 3 does not); "efla_mma" (scan kernel for heads of 64 with on-chip
- * state: 2 default = tensor cores with fp16 accumulators, 1 = tensor cores with an fp32 rank-1 term, 0 = multiply-add); "efla_cols_per_lane" (1 or 2, multiply-add kernel
- * only). Returns BNF4_ERR_INVALID if unknown. */
+/* Options: "gemm_tma_store" (1 default = fp32 tiles leave through swizzled staging and TMA stores; 0 = direct stores);
+ * "efla_chunked" (what BNF4_EFLA_AUTO means for heads of 64 with on-chip state: 1 = the chunked kernel, 0 = the
+ * per-token kernel that reproduces the reference's fp16 rounding of the state after every token).
+ * Returns BNF4_ERR_INVALID for an unknown name or a value outside the listed ones. */
 int bnf4_set_option(const char* name, int value);
 /* Reads and clears the device-side error word set by a kernel whose bounded wait expired.
  * Synchronises `stream`. *code = 0 when clean. */
@@ -250,8 +250,13 @@ typedef struct bnf4_efla_desc {
     float eps;
     float* out; /* row r at out + r*ld_out */
     int ld_out;
-    int force_generic; /* 1: never take the head_dim-64 register kernel (for testing) */
+    int variant; /* BNF4_EFLA_*: which kernel runs. AUTO: for heads of 64 with no HBM state, the chunked or the per-token
+                    register-state kernel as option "efla_chunked" says; the generic kernel otherwise. */
 } bnf4_efla_desc;
+#define BNF4_EFLA_AUTO 0
+#define BNF4_EFLA_GENERIC 1   /* any head_dim, state in shared memory (and in HBM between calls), per-token fp16 rounding */
+#define BNF4_EFLA_PER_TOKEN 2 /* heads of 64: state in registers, rounded to fp16 after every token like the reference */
+#define BNF4_EFLA_CHUNKED 3   /* heads of 64: 16 tokens per step as tensor-core contractions, state rounded to fp16 per chunk */
 
 int bnf4_efla_scan(const bnf4_efla_desc* desc, void* stream);
 /* reference: efla_step_half_qkv_fused src/efla_lm_kernels.cu:2367-2447 (6 kernels; one here). The scratch
@@ -354,8 +359,13 @@ int bnf4_update_vector_device(float* v, const float* Z, int n, const float* inv_
                               void* stream);
 /* reference: add_scaled src/efla_lm_kernels.cu:1769-1779 (out[i] += scale * noise[i]) */
 int bnf4_add_scaled(float* out, const float* noise, int n, float scale, void* stream);
-/* Centered-rank / z-score / sign shaping of the pair fitness vector on the host (pure function, no GPU):
- * reference shape_pair_weights src/train_efla_lm.cpp:3898-3952; ties broken by index. mode 0/1/2. */
+/* Sign / z-score / centered-rank shaping of the pair fitness vector on the host (pure function, no GPU):
+ * reference shape_pair_weights src/train_efla_lm.cpp:3898-3952; ties broken by index. `mode` takes the integer
+ * values of the reference's TrainConfig::FitnessMode (src/train_efla_lm.cpp:260), so a driver can pass
+ * (int)cfg.fitness_mode unchanged; the reference's default is centered rank. */
+#define BNF4_FITNESS_SIGN 0
+#define BNF4_FITNESS_ZSCORE 1
+#define BNF4_FITNESS_CENTERED_RANK 2
 int bnf4_shape_pair_weights(float* h_w, int n, int mode, float clip);
 
 /* ---------------------------------------------------------------------------------------------

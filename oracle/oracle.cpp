@@ -253,6 +253,15 @@ using namespace orc;
 // C entry points (loaded with ctypes by the tests / bench)
 // =============================================================================================
 
+// Thread count of the OpenMP loops: launchers such as torchrun export OMP_NUM_THREADS=1 to their workers.
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -715,16 +724,17 @@ ORC_API double orc_cross_entropy_sum(const float* logits, int ld, const float* b
 }
 
 // ---------------------------------------------------------------------------------------------
-// a11: shape_pair_weights (src/train_efla_lm.cpp:3898-3952). mode 0 centered-rank, 1 z-score, 2 sign.
+// a11: shape_pair_weights (src/train_efla_lm.cpp:3898-3952). mode = the reference's
+// TrainConfig::FitnessMode value (src/train_efla_lm.cpp:260): 0 sign, 1 z-score, 2 centered rank.
 // Ties in the rank sort are broken by index (the reference's std::sort leaves them unspecified).
 // ---------------------------------------------------------------------------------------------
 ORC_API void orc_shape_pair_weights(float* w, int n, int mode, float clip) {
     if (n <= 0) return;
-    if (mode == 2) {
+    if (mode == 0) {
         for (int i = 0; i < n; ++i) w[i] = w[i] > 0.0f ? 1.0f : (w[i] < 0.0f ? -1.0f : 0.0f);
         return;
     }
-    if (mode == 0) {
+    if (mode == 2) {
         std::vector<int> order(n);
         for (int i = 0; i < n; ++i) order[i] = i;
         std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return w[a] < w[b]; });

@@ -101,6 +101,7 @@ void orc_efla_step_half_qkv_fused(uint16_t* S, const float* qkv, int fused_cols,
                                   int heads, int batch, int method, float eps, float* out);
 void orc_efla_scan(const float* qkv, int fused_cols, const float* beta_bias_seq, int hidden, int heads, int seqs,
                    int T, int method, float eps, float* out);
+void orc_set_num_threads(int n);
 // What-if variants of the scan (state rounding cadence, operand precision); (1, 0) = the reference.
 void orc_set_efla_variant(int state_round_every, int operand_bits);
 double orc_cross_entropy_sum(const float* logits, int ld, const float* bias, const float* bias_noise, float bns,

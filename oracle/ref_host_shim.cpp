@@ -6,9 +6,28 @@
 // (rng, noise hash, ternary init, fitness shaping, token cross-entropy, batch sampling) against the real reference code.
 // The device entry points the driver references are resolved by libbnf4.so -- linking this file is at the
 // same time the proof that the reference driver links against the library unchanged.
+//
+// The reference driver takes its NVFP4 path only where cudaGetDeviceProperties reports compute capability 12 or above
+// (src/train_efla_lm.cpp:727-730, :4944) because its own GEMM is an sm_120 CUTLASS instantiation; on anything else it
+// falls back to its dp4a experiment back-end. This library provides the NVFP4 entry points on sm_100, so the shim answers
+// that one query with major = 12 on a compute-capability-10 device. The reference source is not touched: the query goes
+// through the macro below. A maintainer who links the library makes the same one-line change to the two gates.
+#include <cuda_runtime.h>
+
+static cudaError_t shim_device_properties(cudaDeviceProp* prop, int dev) {
+    const cudaError_t e = cudaGetDeviceProperties(prop, dev);
+    if (e == cudaSuccess && prop->major == 10) prop->major = 12;
+    return e;
+}
+#ifdef cudaGetDeviceProperties
+#undef cudaGetDeviceProperties
+#endif
+#define cudaGetDeviceProperties(p, d) shim_device_properties((p), (d))
+
 #define main ref_train_main
 #include "train_efla_lm.cpp"
 #undef main
+#undef cudaGetDeviceProperties
 
 #include <cstring>
 
@@ -30,8 +49,7 @@ REF_API float ref_init_rand(int8_t* out, int rows, int cols, uint64_t seed) {
 }
 REF_API void ref_shape_pair_weights(float* w, int n, int mode, float clip) {
     TrainConfig cfg;
-    cfg.fitness_mode = mode == 0 ? TrainConfig::FitnessMode::CenteredRank
-                                 : (mode == 1 ? TrainConfig::FitnessMode::ZScore : TrainConfig::FitnessMode::Sign);
+    cfg.fitness_mode = static_cast<TrainConfig::FitnessMode>(mode);  // the reference's own enum value
     cfg.fitness_clip = clip;
     std::vector<float> v(w, w + n);
     shape_pair_weights(v, cfg);
@@ -54,5 +72,105 @@ REF_API int ref_sample_batch_packed(const char* path, int batch, int seq_len, ui
     return 0;
 }
 // The reference driver itself (argv as for its executable), running on this library's kernels.
-REF_API int ref_train(int argc, char** argv) { return ref_train_main(argc, argv); }
+REF_API int ref_train(int argc, char** argv) {
+    try {
+        return ref_train_main(argc, argv);
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "ref_train: %s\n", e.what());
+        return 100;
+    }
+}
+
+// One antithetic pair through the reference's OWN model classes (DeviceWeights, CudaEflaLm) with its default flags:
+// weights and positional table initialised as its main() does (src/train_efla_lm.cpp:4889-4921), seeds and per-pair
+// vectors derived as its eval_worker does (:5369-5457), then evaluate_loss for the unperturbed model and for anti = +1, -1.
+// Every kernel entry point those classes call resolves to this library. out3 = {loss(anti 0), loss(+1), loss(-1)}.
+REF_API int ref_eval_pair(int hidden, int layers, int mlp_mult, int batch, int seq_len, const uint8_t* tokens, const uint8_t* targets,
+                          uint64_t seed, uint64_t epoch, int pair, int sigma_shift, float* out3, char* err, int err_len) {
+    try {
+        TrainConfig cfg;
+        cfg.hidden = hidden; cfg.layers = layers; cfg.mlp_mult = mlp_mult; cfg.batch = batch; cfg.seq_len = seq_len; cfg.seed = seed;
+        const int dev = 0;
+        cuda_check(cudaSetDevice(dev), "cudaSetDevice");
+        EflaLmWeights w;
+        w.emb.init_rand(cfg.vocab, cfg.hidden, 0x1000ULL);
+        w.win.init_rand(cfg.hidden, cfg.hidden, 0x2000ULL);
+        w.wq.resize(layers); w.wk.resize(layers); w.wv.resize(layers); w.wbeta.resize(layers); w.ff1.resize(layers); w.ff2.resize(layers);
+        const int ffn_dim = cfg.hidden * std::max(1, cfg.mlp_mult);
+        for (int l = 0; l < layers; ++l) {
+            const uint64_t base = 0x3000ULL + static_cast<uint64_t>(l) * 8;
+            w.wq[l].init_rand(cfg.hidden, cfg.hidden, base + 0);
+            w.wk[l].init_rand(cfg.hidden, cfg.hidden, base + 1);
+            w.wv[l].init_rand(cfg.hidden, cfg.hidden, base + 2);
+            w.wbeta[l].init_rand(1, cfg.hidden, base + 3);
+            w.ff1[l].init_rand(ffn_dim, cfg.hidden, base + 4);
+            w.ff2[l].init_rand(cfg.hidden, ffn_dim, base + 5);
+        }
+        w.head.init_rand(cfg.vocab, cfg.hidden, 0x7000ULL);
+        w.head_bias.assign(cfg.vocab, 0.0f);
+        w.beta_bias.assign(layers, -2.0f);
+        std::vector<float> pos(static_cast<size_t>(seq_len) * hidden, 0.0f);
+        {
+            uint64_t st = 0xABCDEFULL;
+            for (size_t i = 0; i < pos.size(); ++i) pos[i] = (static_cast<float>(rng::splitmix64(st) & 0xFFFF) / 65535.0f - 0.5f) * 0.04f;
+        }
+        cudaDeviceProp prop{};
+        shim_device_properties(&prop, dev);
+        const bool nvfp4 = cfg.gemm_backend == TrainConfig::GemmBackend::CutlassNvfp4 && prop.major >= 12;
+        auto wdev = std::make_shared<DeviceWeights>(dev, cfg.vocab, cfg.hidden, cfg.layers, cfg.mlp_mult, cfg.batch, false, nvfp4,
+                                                    nvfp4 && cfg.use_fused_qkv);
+        wdev->win_out_scale = w.win.out_scale; wdev->q_out_scale = w.wq[0].out_scale; wdev->k_out_scale = w.wk[0].out_scale;
+        wdev->v_out_scale = w.wv[0].out_scale; wdev->beta_out_scale = w.wbeta[0].out_scale; wdev->ff1_out_scale = w.ff1[0].out_scale;
+        wdev->ff2_out_scale = w.ff2[0].out_scale; wdev->head_out_scale = w.head.out_scale;
+        CudaEflaLm model(dev, cfg.vocab, cfg.hidden, cfg.layers, cfg.mlp_mult, cfg.batch, cfg.seq_len, cfg.state_dim, cfg.state_fp16,
+                         cfg.use_cuda_graph, cfg.graph_full_eval, cfg.use_nvtx, cfg.use_fused_qkv, cfg.use_qkv_split_kernel, cfg.qkv_split_vec4,
+                         cfg.use_qkv_split_bias, cfg.use_fused_ff1, cfg.use_fused_head_loss, cfg.use_fused_noise_gemm, cfg.use_fused_efla,
+                         cfg.use_efla_mixed, cfg.use_efla_fuse_diff, cfg.use_efla_update_wmma, cfg.use_tiled_gemm, cfg.use_packed_gemm,
+                         cfg.use_packed_gemm_bitnet, cfg.gemm_backend, cfg.nvfp4_schedule, cfg.nvfp4_quant_mode, cfg.nvfp4_stage_count,
+                         cfg.nvfp4_decomp, cfg.nvfp4_splits, cfg.nvfp4_autotune, cfg.nvfp4_tune_schedule, cfg.nvfp4_tune_quant,
+                         cfg.nvfp4_tune_stages, cfg.nvfp4_tune_decomp, cfg.nvfp4_tune_splits, cfg.noise_batch, wdev);
+        model.set_pos_embedding(pos);
+        model.sync_base_weights(w);
+        model.upload_tokens_async_packed(tokens, targets, 0);
+        model.set_active_tokens(0);
+        model.set_head_bias(w.head_bias.data());
+        const int method_id = static_cast<int>(cfg.method);
+        auto eval = [&](int anti, const float* hb_noise, const float* bb_noise) {
+            return model.evaluate_loss(method_id, anti, sigma_shift, cfg.act_scale, cfg.mlp_act_scale, cfg.ln_scale, cfg.residual_scale,
+                                       cfg.mlp_residual_scale, cfg.gate_scale, cfg.state_decay, cfg.int8_residual, cfg.absmean_norm,
+                                       /*head_bias*/ nullptr, hb_noise, w.beta_bias.data(), bb_noise);
+        };
+        // per-pair seeds and vectors, as eval_worker derives them
+        const float noise_scale = 1.0f / static_cast<float>(1 << sigma_shift);
+        const uint64_t pair_seed = rng::mix(cfg.seed, rng::mix(epoch, static_cast<uint64_t>(pair)));
+        std::vector<float> beta_bias_noise(layers), pos_noise, pos_noisy(pos.size()), head_bias_noise;
+        const uint64_t beta_seed = rng::mix(pair_seed, kSaltBetaBias);
+        for (int l = 0; l < layers; ++l)
+            beta_bias_noise[l] = static_cast<float>(noise_hash(beta_seed, static_cast<uint64_t>(l), 1, cfg.use_clt_noise, cfg.clt_k));
+        fill_noise_vector(pos_noise, static_cast<int>(pos.size()), rng::mix(pair_seed, kSaltPos), cfg.use_clt_noise, cfg.clt_k);
+        std::vector<uint64_t> s_wq(layers), s_wk(layers), s_wv(layers), s_wb(layers), s_f1(layers), s_f2(layers);
+        for (int l = 0; l < layers; ++l) {
+            const uint64_t lu = static_cast<uint64_t>(l);
+            s_wq[l] = rng::mix(pair_seed, rng::mix(lu, kSaltWq)); s_wk[l] = rng::mix(pair_seed, rng::mix(lu, kSaltWk));
+            s_wv[l] = rng::mix(pair_seed, rng::mix(lu, kSaltWv)); s_wb[l] = rng::mix(pair_seed, rng::mix(lu, kSaltWbeta));
+            s_f1[l] = rng::mix(pair_seed, rng::mix(lu, kSaltFf1)); s_f2[l] = rng::mix(pair_seed, rng::mix(lu, kSaltFf2));
+        }
+        fill_noise_vector(head_bias_noise, cfg.vocab, rng::mix(pair_seed, kSaltHeadBias), cfg.use_clt_noise, cfg.clt_k);
+
+        out3[0] = eval(0, head_bias_noise.data(), beta_bias_noise.data());
+        model.set_noise_seeds(rng::mix(pair_seed, kSaltEmb), rng::mix(pair_seed, kSaltWin), s_wq, s_wk, s_wv, s_wb, s_f1, s_f2,
+                              rng::mix(pair_seed, kSaltHead), cfg.use_clt_noise, cfg.clt_k);
+        for (size_t i = 0; i < pos.size(); ++i) pos_noisy[i] = pos[i] + noise_scale * pos_noise[i];
+        model.set_pos_embedding(pos_noisy);
+        out3[1] = eval(+1, head_bias_noise.data(), beta_bias_noise.data());
+        for (size_t i = 0; i < pos.size(); ++i) pos_noisy[i] = pos[i] - noise_scale * pos_noise[i];
+        model.set_pos_embedding(pos_noisy);
+        out3[2] = eval(-1, head_bias_noise.data(), beta_bias_noise.data());
+        cuda_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+        return 0;
+    } catch (const std::exception& e) {
+        if (err && err_len > 0) std::snprintf(err, static_cast<size_t>(err_len), "%s", e.what());
+        return 1;
+    }
+}
 }

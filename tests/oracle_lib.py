@@ -202,7 +202,7 @@ def cross_entropy_sum(logits, bias, bias_noise, bns, targets, target_stride=1):
     return tot, row_loss
 
 
-def shape_pair_weights(w, mode=0, clip=3.0):
+def shape_pair_weights(w, mode=2, clip=3.0):
     w = np.ascontiguousarray(w, np.float32).copy()
     lib().orc_shape_pair_weights(P(w), len(w), mode, cf(clip))
     return w
