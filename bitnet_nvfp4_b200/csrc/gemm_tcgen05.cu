@@ -584,12 +584,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 float tb[32];  // rounded values still biased by 1.5 * 2^23: the low byte of the bit pattern is the int8
                 float am[2] = {0.0f, 0.0f};  // max |value| of the two 16-element scale blocks
                 int w[8];
+                const bool lower_clamp = p.act_scale > 700.0f;
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
                     bool fast_ok = true;
-                    float fc[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) tb[4 * g + e] = gelu_q8_fast(v[4 * g + e], p.act_scale, fast_ok, fc[e]);
+                    float fc[4];  // the rounded integers as floats
+                    gelu_q8_fast2(v[4 * g], v[4 * g + 1], p.act_scale, lower_clamp, fast_ok, tb[4 * g], tb[4 * g + 1], fc[0], fc[1]);
+                    gelu_q8_fast2(v[4 * g + 2], v[4 * g + 3], p.act_scale, lower_clamp, fast_ok, tb[4 * g + 2], tb[4 * g + 3], fc[2], fc[3]);
                     if (!fast_ok) {  // some value too close to a rounding boundary: redo the four with the tanhf form
                         float tbx[4], fcx[4];
                         gelu_q8_exact4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3], p.act_scale, tbx, fcx);

@@ -70,6 +70,15 @@ def nvfp4_quantize_b(w: torch.Tensor, k_out: int | None = None):
     return codes, sf
 
 
+def nvfp4_quantize_f32(x: torch.Tensor, k_out: int | None = None):
+    """fp32 rows straight to NVFP4 (no int8 stage)."""
+    m, k_in = x.shape
+    k_out = k_out or k_in
+    _, codes, sf = _alloc_q(m, k_out, x.device, want_q=False)
+    _l.check(_l.load().bnf4_nvfp4_quantize_f32(_p(x), m, k_in, k_out, _p(codes), _p(sf), _stream()))
+    return codes, sf
+
+
 def nvfp4_quantize_wqkv_fused(wq, wk, wv, wb, hidden: int, rows_total: int, scale: float):
     codes = torch.zeros(matrix_bytes(rows_total, hidden), dtype=torch.uint8, device=wq.device)
     sf = torch.zeros(sf_bytes(rows_total, hidden), dtype=torch.uint8, device=wq.device)

@@ -86,6 +86,7 @@ _PROTOS = {
     "bnf4_nvfp4_sfb_bytes": (c_size_t, [c_int, c_int, c_int]),
     "bnf4_rowquant": (c_int, [c_int, C.POINTER(RowQuantDesc), c_void_p]),
     "bnf4_nvfp4_quantize_a": (c_int, [_I8P, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "bnf4_nvfp4_quantize_f32": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "bnf4_nvfp4_quantize_b": (c_int, [_I8P, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "bnf4_nvfp4_quantize_wqkv_fused": (c_int, [_I8P, _I8P, _I8P, _I8P, c_int, c_int, c_int, c_int, c_float, c_float,
                                                c_float, c_float, c_void_p, c_void_p, c_void_p]),

@@ -68,6 +68,11 @@ size_t bnf4_nvfp4_sfb_bytes(int m, int n, int k);
 int bnf4_nvfp4_quantize_a(const int8_t* in, int m, int n, int k_in, int k_out, void* out, void* sfa, void* stream);
 /* reference: nvfp4_quantize_b src/cuda_kernels.cu:4240-4264 */
 int bnf4_nvfp4_quantize_b(const int8_t* in, int m, int n, int k_in, int k_out, void* out, void* sfb, void* stream);
+/* fp32 rows straight to NVFP4 (no int8 stage): scale byte = ue4m3(max|x| / 6) per 16 elements (1.0 where that rounds to
+ * zero), codes = e2m1(x / scale), the rules of nvfp4_quantize_a applied to fp32 values. The reference's driver always
+ * quantises through int8 (src/cuda_kernels.cu:1783-1878); this is the "quantised on the fly from fp32" form, whose fp32
+ * tensor scale is the GEMM's alpha. k_in <= k_out, k_out a multiple of 16 (columns past k_in read as zero). */
+int bnf4_nvfp4_quantize_f32(const float* in, int rows, int k_in, int k_out, void* out, void* sf, void* stream);
 /* reference: nvfp4_quantize_wqkv_fused src/cuda_kernels.cu:4266-4306 (kernel :2748-2854) */
 int bnf4_nvfp4_quantize_wqkv_fused(const int8_t* wq, const int8_t* wk, const int8_t* wv, const int8_t* wb, int batch,
                                    int hidden, int k_out, int rows_total, float q_scale, float k_scale, float v_scale,

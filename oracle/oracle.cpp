@@ -601,6 +601,51 @@ ORC_API void orc_efla_step_half_qkv_fused(uint16_t* S, const float* qkv, int fus
 }
 
 // ---------------------------------------------------------------------------------------------
+// Inputs of the single-GEMM benchmark configuration. The reference has no Gaussian generator (its noise is the CLT sum of
+// ternary draws above), so the N(0,1) map for fp32 test inputs is DEFINED here: Box-Muller on two 53-bit uniforms drawn
+// with the reference's counter functions, element idx of stream (seed, tag) -> st = mix(mix(seed, tag), idx),
+// u1 = ((splitmix64(st) >> 11) + 1) 2^-53 in (0, 1], u2 = (splitmix64(st) >> 11) 2^-53, z = sqrt(-2 ln u1) cos(2 pi u2),
+// evaluated in double and rounded once to fp32 after the scale.
+// ---------------------------------------------------------------------------------------------
+ORC_API void orc_gaussian_f32(uint64_t seed, uint64_t tag, size_t n, float scale, float* out) {
+    const uint64_t base = orc_mix(seed, tag);
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)n; ++i) {
+        uint64_t st = orc_mix(base, (uint64_t)i);
+        const double u1 = (double)((orc_splitmix64(&st) >> 11) + 1) * (1.0 / 9007199254740992.0);
+        const double u2 = (double)(orc_splitmix64(&st) >> 11) * (1.0 / 9007199254740992.0);
+        out[i] = (float)((double)scale * std::sqrt(-2.0 * std::log(u1)) * std::cos(6.283185307179586476925286766559 * u2));
+    }
+}
+
+// fp32 rows straight to NVFP4 (no int8 stage): the block rule of nvfp4_quantize_rowmajor (src/cuda_kernels.cu:1545-1625)
+// applied to fp32 values: amax = max |x|, s = amax > 0 ? amax / 6 : 1, sq = ue4m3(s) (1.0 if that decodes to 0),
+// codes = e2m1(x / float(sq)). Columns past k_in are zero.
+ORC_API void orc_quantize_direct_f32(const float* in, int rows, int k_in, int k_out, uint8_t* codes, uint8_t* sf) {
+    std::memset(codes, 0, (size_t)rows * k_out / 2);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r)
+        for (int kb = 0; kb < k_out / 16; ++kb) {
+            float x[16], amax = 0.0f;
+            for (int e = 0; e < 16; ++e) {
+                const int c = kb * 16 + e;
+                x[e] = c < k_in ? in[(size_t)r * k_in + c] : 0.0f;
+                amax = std::fmax(amax, std::fabs(x[e]));
+            }
+            const float s = amax > 0.0f ? amax / 6.0f : 1.0f;
+            int sq = orc_ue4m3_encode(s);
+            float sfv = orc_ue4m3_decode(sq);
+            if (sfv == 0.0f) { sq = 0x38; sfv = 1.0f; }
+            sf[orc_sf_offset(r, kb, k_out)] = (uint8_t)sq;
+            for (int e = 0; e < 16; ++e) {
+                const size_t idx = (size_t)r * k_out + kb * 16 + e;
+                const int c = orc_e2m1_encode(x[e] / sfv);
+                codes[idx / 2] |= (uint8_t)(c << (4 * (idx & 1)));
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------------------------
 // What-if variants of the scan, used only to measure how far a faster formulation may depart from the
 // reference's rounding before the per-member loss leaves its 1e-4 bar. state_round_every: 1 = the reference
 // (state rounded to fp16 after every token, src/efla_lm_kernels.cu:1349); C > 1 = state carried in fp32 and

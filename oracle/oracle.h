@@ -102,6 +102,8 @@ void orc_efla_step_half_qkv_fused(uint16_t* S, const float* qkv, int fused_cols,
 void orc_efla_scan(const float* qkv, int fused_cols, const float* beta_bias_seq, int hidden, int heads, int seqs,
                    int T, int method, float eps, float* out);
 void orc_set_num_threads(int n);
+void orc_gaussian_f32(uint64_t seed, uint64_t tag, size_t n, float scale, float* out);
+void orc_quantize_direct_f32(const float* in, int rows, int k_in, int k_out, uint8_t* codes, uint8_t* sf);
 // What-if variants of the scan (state rounding cadence, operand precision); (1, 0) = the reference.
 void orc_set_efla_variant(int state_round_every, int operand_bits);
 double orc_cross_entropy_sum(const float* logits, int ld, const float* bias, const float* bias_noise, float bns,

@@ -99,6 +99,23 @@ def quantize_rowmajor(x: np.ndarray, k_out: int | None = None):
     return codes, sf
 
 
+def gaussian_f32(seed: int, tag: int, n: int, scale: float = 1.0) -> np.ndarray:
+    """The oracle's N(0,1) map (Box-Muller on the reference's counter functions), times `scale`, as fp32."""
+    out = np.zeros(n, np.float32)
+    lib().orc_gaussian_f32(cu64(seed), cu64(tag), csz(n), cf(scale), P(out))
+    return out
+
+
+def quantize_direct_f32(x: np.ndarray, k_out: int | None = None):
+    x = np.ascontiguousarray(x, np.float32)
+    rows, k_in = x.shape
+    k_out = k_out or k_in
+    codes = np.zeros(rows * k_out // 2, np.uint8)
+    sf = np.zeros(sf_bytes(rows, k_out), np.uint8)
+    lib().orc_quantize_direct_f32(P(x), rows, k_in, k_out, P(codes), P(sf))
+    return codes, sf
+
+
 def quantize_wqkv_fused(wq, wk, wv, wb, hidden: int, scale: float):
     rows = 3 * hidden + 1
     codes = np.zeros(rows * hidden // 2 + 8, np.uint8)

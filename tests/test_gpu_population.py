@@ -64,6 +64,54 @@ def test_member_losses_match_oracle(cfg_kw):
     assert np.abs(losses[0::2] - losses[1::2]).min() > 0
 
 
+def test_config1_population_of_64():
+    """BASELINE configuration 1 as written: pop = 64 (32 antithetic pairs) of the default model (4 layers, hidden 512, 8 heads of
+    64, MLP 1024, batch 32, seq 128, Zipf tokens seed 123): every member's mean cross-entropy within 1e-4 relative of the
+    oracle. About a minute of CPU work for the 64 oracle forwards."""
+    from bitnet_nvfp4_b200 import host
+    cfg, w, tok, tgt, model = make(dict(hidden=512, layers=4, seq=128, batch=32, heads=8, rank=1, max_pairs=32, wave_members=64))
+    seed, epoch, pairs = 1, 0, 32
+    model.prepare_step(seed, epoch, pairs)
+    losses = model.eval_pairs(0, pairs).cpu().numpy()
+    assert host.device_error() == 0
+    om = orc.OracleModel(oracle_cfg(cfg), w)
+    worst = 0.0
+    for p in range(pairs):
+        ps = orc.mix(seed, orc.mix(epoch, p))
+        for s, anti in enumerate((1, -1)):
+            ref = om.forward(tok, tgt, ps, anti)
+            worst = max(worst, abs(losses[2 * p + s] - ref) / abs(ref))
+    assert worst <= 1e-4, worst
+    assert len(np.unique(losses)) == 64
+
+
+def test_live_attention_branch():
+    """With the default scales and ternary initial weights the attention branch never reaches the int8 residual stream
+    (|y| stays below 0.5, so rint(y * residual_scale) = 0): the 1e-4 loss bar above does not see the EFLA scan. With
+    residual_scale = 16 it does, and the loss becomes chaotic: one int8 step flipped in one layer moves k, v and therefore the
+    state of every later token (on the CPU oracle alone, rounding the scan's operands to 16 mantissa bits already moves member
+    losses by 5e-3 relative). Losses can then only agree statistically; the scan itself is held to its own bound in
+    test_gpu_efla_loss_update.py."""
+    from bitnet_nvfp4_b200 import host
+    cfg, w, tok, tgt, model = make(dict(hidden=256, layers=2, seq=64, batch=8, heads=4, rank=1, max_pairs=8, wave_members=16,
+                                        residual_scale=16.0))
+    seed, epoch, pairs = 1, 2, 8
+    model.prepare_step(seed, epoch, pairs)
+    losses = model.eval_pairs(0, pairs).cpu().numpy()
+    assert host.device_error() == 0
+    om = orc.OracleModel(oracle_cfg(cfg), w)
+    taps = {"attn_y": np.zeros((cfg.layers, cfg.batch * cfg.seq, cfg.hidden), np.float32)}
+    ref = []
+    for p in range(pairs):
+        ps = orc.mix(seed, orc.mix(epoch, p))
+        for anti in (1, -1):
+            ref.append(om.forward(tok, tgt, ps, anti, taps if not ref else None))
+    ref = np.array(ref)
+    assert np.abs(taps["attn_y"][0]).max() * 16.0 > 1.0     # the branch is live: its contribution rounds to non-zero int8 steps
+    rel = np.abs(losses - ref) / np.abs(ref)
+    assert rel.max() <= 3e-2 and rel.mean() <= 1e-2, (rel.max(), rel.mean())
+
+
 def test_wave_split_is_invisible():
     """The same pairs evaluated in waves of 2 or of 8 members give identical losses."""
     kw = dict(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=6)
