@@ -191,6 +191,7 @@ struct KernelArgs {
     GemmParams p;
     int use_tma_store;
     int k_atoms;  // scale atoms along K
+    uint32_t group_magic;  // ceil(2^32 / group_cols) (0 when group_cols == 0)
     const uint8_t* lut;  // table of the block quantiser (EPI_GELU_FP4)
     int total_tiles;
     int n_tiles;  // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile (N fastest: CTAs that share A rows run together)
@@ -255,8 +256,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             int s = 0;
             uint32_t empty_parity = 1;  // parity of the phase that precedes the first completion: the first pass does not wait
             bool ok = true;
+            const int step_n = static_cast<int>(gridDim.x % static_cast<unsigned>(args.n_tiles)), step_m = static_cast<int>(gridDim.x / static_cast<unsigned>(args.n_tiles));
+            int m_tile = static_cast<int>(blockIdx.x / static_cast<unsigned>(args.n_tiles)) - step_m;
+            int n_tile = static_cast<int>(blockIdx.x % static_cast<unsigned>(args.n_tiles)) - step_n;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int n_tile = tile % args.n_tiles, m_tile = tile / args.n_tiles;
+                n_tile += step_n;
+                m_tile += step_m;
+                if (n_tile >= args.n_tiles) { n_tile -= args.n_tiles; ++m_tile; }
                 const uint8_t* sfa_src = static_cast<const uint8_t*>(p.sfa) + static_cast<size_t>(m_tile) * args.k_atoms * 512;
                 const uint8_t* sfb_src = static_cast<const uint8_t*>(p.sfb) + static_cast<size_t>(n_tile) * args.k_atoms * 512;
                 const int my = m_tile * BM, ny = n_tile * BN;
@@ -367,47 +373,81 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             bool a_staged;
         };
         const int row_in_tile = q * 32 + lane;
-        auto fetch_ctx = [&](int tile_, LoraCtx& cx) {
+        // Tile coordinates advance by additions (tiles are walked in steps of gridDim.x): no division per tile.
+        const int step_n = static_cast<int>(gridDim.x % static_cast<unsigned>(args.n_tiles)), step_m = static_cast<int>(gridDim.x / static_cast<unsigned>(args.n_tiles));
+        struct TileIdx { int m_tile, n_tile; };
+        auto advance = [&](TileIdx& t) {
+            t.n_tile += step_n;
+            t.m_tile += step_m;
+            if (t.n_tile >= args.n_tiles) { t.n_tile -= args.n_tiles; ++t.m_tile; }
+        };
+        // Members are visited in ascending order, so when tiles never straddle members (rows_per_member a multiple of the
+        // tile height) the member of the next tile is tracked with comparisons instead of a division per row.
+        const bool tile_uniform_member = p.rows_per_member > 0 && (p.rows_per_member % BM) == 0;
+        int trk_member = 0;
+        long long trk_end = p.rows_per_member;  // first row of member trk_member + 1
+        const uint32_t group_magic = args.group_magic;  // ceil(2^32 / group_cols): exact quotients for columns below 65536
+        auto fetch_ctx = [&](const TileIdx& t, bool valid, LoraCtx& cx) {
             cx.pair = 0;
             cx.lsign = 0.0f;
             cx.tr[0] = cx.tr[1] = cx.tr[2] = cx.tr[3] = 0;
             cx.aval[0] = cx.aval[1] = cx.aval[2] = cx.aval[3] = 0;
             cx.a_staged = false;
-            if (p.rank <= 0 || tile_ >= total_tiles) return;
-            const int n_tile_ = tile_ % args.n_tiles, m_tile_ = tile_ / args.n_tiles;
-            const int m0_ = m_tile_ * BM, n0_ = n_tile_ * BN;
+            if (p.rank <= 0 || !valid) return;
+            const int m0_ = t.m_tile * BM, n0_ = t.n_tile * BN;
             const long long row_ = static_cast<long long>(m0_) + row_in_tile;
             const int col0_ = n0_ + c * 32;
-            if (row_ < p.m) {
+            int pair_first, pair_last;
+            if (tile_uniform_member) {
+                while (m0_ >= trk_end) { ++trk_member; trk_end += p.rows_per_member; }
+                pair_first = pair_last = trk_member >> 1;
+                if (row_ < p.m) {
+                    cx.pair = pair_first;
+                    cx.lsign = (trk_member & 1) ? -p.lora_scale : p.lora_scale;
+                }
+            } else {
                 // rows fit 31 bits (p.m is an int): 32-bit divisions
-                const int member = p.rows_per_member > 0 ? static_cast<int>(static_cast<unsigned>(row_) / static_cast<unsigned>(p.rows_per_member)) : 0;
-                cx.pair = member >> 1;
-                cx.lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
-                if (col0_ < p.n) {
-                    const int g = p.group_cols > 0 ? (col0_ / p.group_cols) : 0;
-#pragma unroll
-                    for (int r = 0; r < 4; ++r)
-                        if (r < p.rank) cx.tr[r] = __ldg(p.lora_t + static_cast<size_t>(row_) * p.t_stride + g * p.rank + r);
+                const unsigned rpm = static_cast<unsigned>(p.rows_per_member);
+                if (row_ < p.m) {
+                    const int member = p.rows_per_member > 0 ? static_cast<int>(static_cast<unsigned>(row_) / rpm) : 0;
+                    cx.pair = member >> 1;
+                    cx.lsign = (member & 1) ? -p.lora_scale : p.lora_scale;
+                }
+                const unsigned last_row = static_cast<unsigned>(min(static_cast<long long>(p.m), static_cast<long long>(m0_) + BM) - 1);
+                pair_first = p.rows_per_member > 0 ? static_cast<int>(static_cast<unsigned>(m0_) / rpm) >> 1 : 0;
+                pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / rpm) >> 1 : 0;
+            }
+            if (row_ < p.m && col0_ < p.n) {
+                const int g = p.group_cols > 0 ? static_cast<int>(__umulhi(static_cast<uint32_t>(col0_), group_magic)) : 0;
+                const int* tp = p.lora_t + static_cast<size_t>(row_) * p.t_stride + g * p.rank;
+                cx.tr[0] = __ldg(tp);
+                if (p.rank > 1) {
+                    cx.tr[1] = __ldg(tp + 1);
+                    if (p.rank > 2) cx.tr[2] = __ldg(tp + 2);
+                    if (p.rank > 3) cx.tr[3] = __ldg(tp + 3);
                 }
             }
-            const unsigned last_row = static_cast<unsigned>(min(static_cast<long long>(p.m), static_cast<long long>(m0_) + BM) - 1);
-            const int pair_first = p.rows_per_member > 0 ? static_cast<int>(static_cast<unsigned>(m0_) / static_cast<unsigned>(p.rows_per_member)) >> 1 : 0;
-            const int pair_last = p.rows_per_member > 0 ? static_cast<int>(last_row / static_cast<unsigned>(p.rows_per_member)) >> 1 : 0;
             cx.a_staged = (pair_first == pair_last);
             const int n = col0_ + lane;
             if (cx.a_staged && n < p.n) {
                 const int8_t* Ag = p.lora_A + static_cast<size_t>(pair_first) * p.lora_A_pair_stride + static_cast<size_t>(n) * p.rank;
-#pragma unroll
-                for (int r = 0; r < 4; ++r)
-                    if (r < p.rank) cx.aval[r] = __ldg(Ag + r);
+                cx.aval[0] = __ldg(Ag);
+                if (p.rank > 1) {
+                    cx.aval[1] = __ldg(Ag + 1);
+                    if (p.rank > 2) cx.aval[2] = __ldg(Ag + 2);
+                    if (p.rank > 3) cx.aval[3] = __ldg(Ag + 3);
+                }
             }
         };
+        TileIdx cur_t{static_cast<int>(blockIdx.x / static_cast<unsigned>(args.n_tiles)), static_cast<int>(blockIdx.x % static_cast<unsigned>(args.n_tiles))};
+        TileIdx nxt_t = cur_t;
         LoraCtx nxt;
-        fetch_ctx(blockIdx.x, nxt);
+        fetch_ctx(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
-            const int n_tile = tile % args.n_tiles, m_tile = tile / args.n_tiles;
-            const int m0 = m_tile * BM, n0 = n_tile * BN;
+            cur_t = nxt_t;
+            advance(nxt_t);
+            const int m0 = cur_t.m_tile * BM, n0 = cur_t.n_tile * BN;
             const long long row = static_cast<long long>(m0) + row_in_tile;
             const bool row_ok = row < p.m;
             const int col0 = n0 + c * 32;
@@ -426,7 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         if (r < p.rank) loraA_sh[r * 32 + lane] = static_cast<float>(nxt.aval[r]);
                 }
                 __syncwarp();
-                fetch_ctx(tile + gridDim.x, nxt);
+                fetch_ctx(nxt_t, tile + static_cast<int>(gridDim.x) < total_tiles, nxt);
             }
 
             // EPI_ADD_I8: this thread's 32 bytes of the residual stream, requested before the wait for the accumulator
@@ -581,25 +621,66 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     for (int j = 0; j < 32; ++j)
                         if (col0 + j >= p.n) v[j] = 0.0f;  // gelu(0) = 0
                 }
-                float tb[32];  // rounded values still biased by 1.5 * 2^23: the low byte of the bit pattern is the int8
-                float am[2] = {0.0f, 0.0f};  // max |value| of the two 16-element scale blocks
-                int w[8];
+                // One 16-element scale block at a time: its 16 values take the fast evaluation in one straight-line stretch (no
+                // branch between groups, so the scheduler interleaves them); a group with a value too close to a rounding
+                // boundary is flagged and redone with the tanhf form (about one group in a thousand). tb holds the rounded
+                // values still biased by 1.5 * 2^23: the low byte of the bit pattern is the int8.
                 const bool lower_clamp = p.act_scale > 700.0f;
+                const uint32_t lut_s = smem_base + kSmemEpi;
+                const uint32_t kBias = static_cast<uint32_t>(kRoundBiasBits);
+                const uint32_t row_c = lut_s + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
+                const uint32_t sf_c = lut_s + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
+                int w[8];
+                uint32_t sfv[2] = {0u, 0u}, codes[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    bool fast_ok = true;
-                    float fc[4];  // the rounded integers as floats
-                    gelu_q8_fast2(v[4 * g], v[4 * g + 1], p.act_scale, lower_clamp, fast_ok, tb[4 * g], tb[4 * g + 1], fc[0], fc[1]);
-                    gelu_q8_fast2(v[4 * g + 2], v[4 * g + 3], p.act_scale, lower_clamp, fast_ok, tb[4 * g + 2], tb[4 * g + 3], fc[2], fc[3]);
-                    if (!fast_ok) {  // some value too close to a rounding boundary: redo the four with the tanhf form
-                        float tbx[4], fcx[4];
-                        gelu_q8_exact4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3], p.act_scale, tbx, fcx);
+                for (int blk = 0; blk < 2; ++blk) {
+                    float tb[16];
+                    float am = 0.0f;  // max |value| of the block
+                    uint32_t bad = 0;
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) { tb[4 * g + e] = tbx[e]; fc[e] = fcx[e]; }
+                    for (int g = 0; g < 4; ++g) {
+                        const int j = 16 * blk + 4 * g;
+                        bool fast_ok = true;
+                        float fc[4];  // the rounded integers as floats
+                        gelu_q8_fast2(v[j], v[j + 1], p.act_scale, lower_clamp, fast_ok, tb[4 * g], tb[4 * g + 1], fc[0], fc[1]);
+                        gelu_q8_fast2(v[j + 2], v[j + 3], p.act_scale, lower_clamp, fast_ok, tb[4 * g + 2], tb[4 * g + 3], fc[2], fc[3]);
+                        bad |= fast_ok ? 0u : (1u << g);
+                        am = fmaxf(fmaxf(am, fmaxf(fabsf(fc[0]), fabsf(fc[1]))), fmaxf(fabsf(fc[2]), fabsf(fc[3])));
                     }
-                    am[g >> 2] = fmaxf(fmaxf(am[g >> 2], fmaxf(fabsf(fc[0]), fabsf(fc[1]))), fmaxf(fabsf(fc[2]), fabsf(fc[3])));
-                    w[g] = static_cast<int>(__byte_perm(__byte_perm(__float_as_uint(tb[4 * g]), __float_as_uint(tb[4 * g + 1]), 0x0040),
-                                                        __byte_perm(__float_as_uint(tb[4 * g + 2]), __float_as_uint(tb[4 * g + 3]), 0x0040), 0x5410));
+                    if (bad != 0) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if ((bad >> g) & 1u) {
+                                const int j = 16 * blk + 4 * g;
+                                float tbx[4], fcx[4];
+                                gelu_q8_exact4(v[j], v[j + 1], v[j + 2], v[j + 3], p.act_scale, tbx, fcx);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) tb[4 * g + e] = tbx[e];
+                            }
+                        }
+                        am = 0.0f;
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) am = fmaxf(am, fabsf(tb[e] - kRoundBias));
+                    }
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                        w[4 * blk + g] = static_cast<int>(__byte_perm(__byte_perm(__float_as_uint(tb[4 * g]), __float_as_uint(tb[4 * g + 1]), 0x0040),
+                                                                      __byte_perm(__float_as_uint(tb[4 * g + 2]), __float_as_uint(tb[4 * g + 3]), 0x0040), 0x5410));
+                    if constexpr (EPI == EPI_GELU_FP4) {
+                        // code(v) = table[amax][v + 128] and scale byte = table_sf[amax], addressed straight from the biased bit
+                        // patterns: bits(t) - kRoundBiasBits is the integer.
+                        const uint32_t ab = __float_as_uint(am + kRoundBias);
+                        sfv[blk] = lds_u8(ab + sf_c);
+                        const uint32_t rowbase = ab * static_cast<uint32_t>(kQuantLutSignedStride) + row_c;
+                        uint32_t cl[8], ch[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            cl[e] = lds_u8(__float_as_uint(tb[e]) + rowbase) << (4 * e);
+                            ch[e] = lds_u8(__float_as_uint(tb[8 + e]) + rowbase) << (4 * e);
+                        }
+                        codes[2 * blk] = ((cl[0] | cl[1]) | (cl[2] | cl[3])) | ((cl[4] | cl[5]) | (cl[6] | cl[7]));
+                        codes[2 * blk + 1] = ((ch[0] | ch[1]) | (ch[2] | ch[3])) | ((ch[4] | ch[5]) | (ch[6] | ch[7]));
+                    }
                 }
                 if (row_ok && p.d_i8 != nullptr) {
                     int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
@@ -614,27 +695,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
                 if constexpr (EPI == EPI_GELU_FP4) {
                     if (row_ok) {
-                        // code(v) = table[amax][v + 128] and scale byte = table_sf[amax], addressed straight from the biased
-                        // bit patterns: bits(t) - kRoundBiasBits is the integer.
-                        const uint32_t lut_s = smem_base + kSmemEpi;
-                        const uint32_t kBias = static_cast<uint32_t>(kRoundBiasBits);
-                        const uint32_t row_c = lut_s + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
-                        const uint32_t sf_c = lut_s + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
-                        uint32_t sfv[2], codes[4];
-#pragma unroll
-                        for (int blk = 0; blk < 2; ++blk) {
-                            const uint32_t ab = __float_as_uint(am[blk] + kRoundBias);
-                            sfv[blk] = lds_u8(ab + sf_c);
-                            const uint32_t rowbase = ab * static_cast<uint32_t>(kQuantLutSignedStride) + row_c;
-                            uint32_t lo = 0, hi = 0;
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                lo |= lds_u8(__float_as_uint(tb[16 * blk + e]) + rowbase) << (4 * e);
-                                hi |= lds_u8(__float_as_uint(tb[16 * blk + 8 + e]) + rowbase) << (4 * e);
-                            }
-                            codes[2 * blk] = lo;
-                            codes[2 * blk + 1] = hi;
-                        }
                         const uint32_t s0 = sfv[0], s1 = sfv[1], lo0 = codes[0], hi0 = codes[1], lo1 = codes[2], hi1 = codes[3];
                         *reinterpret_cast<uint4*>(p.d_codes + (static_cast<size_t>(row) * p.n + col0) / 2) = make_uint4(lo0, hi0, lo1, hi1);
                         const int kb = col0 >> 4;
@@ -758,6 +818,8 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     KernelArgs args;
     args.p = p;
     args.k_atoms = sf_k_atoms(p.k);
+    args.group_magic = p.group_cols > 0 ? static_cast<uint32_t>(((1ull << 32) + static_cast<unsigned long long>(p.group_cols) - 1) / static_cast<unsigned long long>(p.group_cols)) : 0u;
+    if (p.group_cols > 0 && p.n >= 65536) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: column groups need n < 65536");
     args.lut = nullptr;
     if (p.epilogue == EPI_GELU_FP4) {
         args.lut = get_quant_lut();
