@@ -129,8 +129,9 @@ def oracle_pairs_seconds(orc, om, tok, tgt, pairs: int) -> float:
     return time.perf_counter() - t0
 
 
-def algorithmic_work(cfg, members: int, dedup_input: bool):
-    """Per kernel class: (bound, bytes or flops, launches per wave) for ONE launch over a wave of `members` members."""
+def algorithmic_work(cfg, members: int, dedup_input: bool, half_io: bool):
+    """Per kernel class: (bound, bytes or flops, launches per wave) for ONE launch over a wave of `members` members.
+    half_io: q | k | v and the scan's output travel as IEEE halves (heads of 64 with the chunked scan)."""
     H, F, V, T, B, L, r = cfg.hidden, cfg.hidden * cfg.mlp_mult, cfg.vocab, cfg.seq, cfg.batch, cfg.layers, cfg.rank
     rows = members * B * T
     erows = members * V if dedup_input else rows  # the embedding and its projection run once per (member, distinct token)
@@ -140,8 +141,8 @@ def algorithmic_work(cfg, members: int, dedup_input: bool):
         "gemm_win": ("tensor", 2.0 * erows * H * H + 2.0 * erows * r * H, 1),
         "pos_gelu_norm_quant": ("hbm", rows * (4 * H + H + fp4(H) + 16 * r), 1),
         "gemm_qkv": ("tensor", 2.0 * rows * (3 * H + 1) * H + 2.0 * rows * r * (3 * H + 1), L),
-        "efla_scan": ("hbm", rows * ((3 * H + 1) * 4 + 4 * H), L),
-        "add_norm_quant": ("hbm", rows * (4 * H + H + H + fp4(H) + 4 * r), L),
+        "efla_scan": ("hbm", rows * ((3 * H * 2 + 4 + 2 * H) if half_io else ((3 * H + 1) * 4 + 4 * H)), L),
+        "add_norm_quant": ("hbm", rows * ((2 if half_io else 4) * H + H + H + fp4(H) + 4 * r), L),
         "norm_quant": ("hbm", rows * (H + fp4(H) + 16 * r), L),
         "gemm_ff1_gelu_fp4": ("tensor", 2.0 * rows * F * H + 2.0 * rows * r * F, L),
         "gemm_ff2": ("tensor", 2.0 * rows * H * F + 2.0 * rows * r * H, L),
@@ -490,7 +491,8 @@ def main():
     peaks, peak_src = load_peaks()
     wave_members = model.wave_members
     dedup_input = cfg.vocab <= 256 and cfg.vocab < cfg.batch * cfg.seq
-    work = algorithmic_work(cfg, wave_members, dedup_input)
+    half_io = (cfg.hidden // cfg.heads) == 64 and not args.exact_scan
+    work = algorithmic_work(cfg, wave_members, dedup_input, half_io)
     n_waves = args.steps * ((my_pairs * 2 + wave_members - 1) // wave_members)
     fp4_peak = 4.0 * peaks["bf16_tflops_sustained"]
     kernels = []

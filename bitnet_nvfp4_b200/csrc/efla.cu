@@ -61,9 +61,9 @@ __global__ void efla_generic_kernel(const EflaParams p) {
 
     for (int t = 0; t < p.T; ++t) {
         const size_t row = static_cast<size_t>(seq) * p.T + t;
-        const float* qr = p.q + row * p.ld_qkv + h * hd;
-        const float* kr = p.k + row * p.ld_qkv + h * hd;
-        const float* vr = p.v + row * p.ld_qkv + h * hd;
+        const float* qr = static_cast<const float*>(p.q) + row * p.ld_qkv + h * hd;
+        const float* kr = static_cast<const float*>(p.k) + row * p.ld_qkv + h * hd;
+        const float* vr = static_cast<const float*>(p.v) + row * p.ld_qkv + h * hd;
         __syncthreads();  // previous step finished with q_sh / k_sh
         float qss = 0.0f, kss = 0.0f;
         for (int d = j; d < hd; d += nc) {
@@ -102,7 +102,7 @@ __global__ void efla_generic_kernel(const EflaParams p) {
                 S[d * nc + j] = sn;
                 y = fmaf(StateCvt<ST>::load(sn), q_sh[d] * q_inv, y);
             }
-            p.out[row * p.ld_out + h * hd + n] = y;
+            static_cast<float*>(p.out)[row * p.ld_out + h * hd + n] = y;
         }
     }
     if (Sg != nullptr && col_ok)
@@ -200,11 +200,11 @@ __global__ void __launch_bounds__(kScanWarps * 32, kScan2CtasPerSm) efla_scan64_
             for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
 
     const size_t row0 = static_cast<size_t>(seq) * p.T;
-    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
-    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
-    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
+    const float* qb = static_cast<const float*>(p.q) + row0 * p.ld_qkv + h * HD;
+    const float* kb = static_cast<const float*>(p.k) + row0 * p.ld_qkv + h * HD;
+    const float* vb = static_cast<const float*>(p.v) + row0 * p.ld_qkv + h * HD;
     const float* bb = p.beta_raw + row0 * p.ld_beta;
-    float* ob = p.out + row0 * p.ld_out + h * HD;
+    float* ob = static_cast<float*>(p.out) + row0 * p.ld_out + h * HD;
 
     // asynchronous copy of four tokens' inputs (one group) into their ring slots; every lane commits one group, empty or not
     auto issue_group = [&](int tok0) {
@@ -392,6 +392,10 @@ constexpr int kCkQKStride = 72;  // floats per row of the raw q / k tiles: 16-by
 constexpr int kCkVStride = 68;   // floats per row of the raw v tile: the accumulator-shaped reads are conflict-free
 constexpr int kCkHStride = 72;   // halves per row of the prepared operands (-K, Q^, a K): conflict-free ldmatrix rows
 constexpr int kCkTStride = 24;   // halves per row of T and P
+// the same tiles when q, k, v arrive as halves: strides in halves (160-byte q / k rows, 144-byte v rows)
+constexpr int kCkQKStrideH = 80;
+constexpr int kCkVStrideH = 72;
+constexpr int kCkYStrideH = 72;  // halves per row of the output staging tile (in the -K / Q^ region, dead once their fragments are loaded)
 constexpr int kCkRawQ = 0;
 constexpr int kCkRawK = kCkRawQ + kChunk * kCkQKStride * 4;
 constexpr int kCkRawV = kCkRawK + kChunk * kCkQKStride * 4;
@@ -419,6 +423,7 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sad
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
 }
 
+template <bool IN16, bool OUT16>
 __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const EflaParams p) {
     constexpr int HD = 64;
     extern __shared__ __align__(16) uint8_t scan_smem[];
@@ -435,6 +440,8 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
     __half* ak_sh = reinterpret_cast<__half*>(wsm + kCkAK);
     __half* t_sh = reinterpret_cast<__half*>(wsm + kCkT);
     __half* p_sh = reinterpret_cast<__half*>(wsm + kCkP);
+    __half* y_sh = nk_sh;  // output staging (OUT16): the -K / Q^ tiles are dead once their fragments sit in registers
+    static_assert(kChunk * kCkYStrideH * 2 <= 2 * kChunk * kCkHStride * 2, "output staging fits the -K / Q^ region");
     const long long unit = static_cast<long long>(blockIdx.x) * kChunkWarps + warp;  // (sequence, head)
     if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
     const long long seq = unit / p.heads;
@@ -452,23 +459,45 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
             for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
 
     const size_t row0 = static_cast<size_t>(seq) * p.T;
-    const float* qb = p.q + row0 * p.ld_qkv + h * HD;
-    const float* kb = p.k + row0 * p.ld_qkv + h * HD;
-    const float* vb = p.v + row0 * p.ld_qkv + h * HD;
+    // element type of q, k, v: fp32 or (IN16) halves; ld_qkv counts elements of that type
+    const float* qb = static_cast<const float*>(p.q) + row0 * p.ld_qkv + h * HD;
+    const float* kb = static_cast<const float*>(p.k) + row0 * p.ld_qkv + h * HD;
+    const float* vb = static_cast<const float*>(p.v) + row0 * p.ld_qkv + h * HD;
+    const __half* qbh = static_cast<const __half*>(p.q) + row0 * p.ld_qkv + h * HD;
+    const __half* kbh = static_cast<const __half*>(p.k) + row0 * p.ld_qkv + h * HD;
+    const __half* vbh = static_cast<const __half*>(p.v) + row0 * p.ld_qkv + h * HD;
     const float* bb = p.beta_raw + row0 * p.ld_beta;
-    float* ob = p.out + row0 * p.ld_out + h * HD;
+    float* ob = static_cast<float*>(p.out) + row0 * p.ld_out + h * HD;
+    __half* obh = static_cast<__half*>(p.out) + row0 * p.ld_out + h * HD;
+    __half* rawqh = reinterpret_cast<__half*>(rawq);
+    __half* rawkh = reinterpret_cast<__half*>(rawk);
+    __half* rawvh = reinterpret_cast<__half*>(rawv);
 
-    // asynchronous copy of one chunk's q, k, v, beta rows into the raw tiles (16-byte pieces: lane = piece within a pair of rows)
+    // asynchronous copy of one chunk's q, k, v, beta rows into the raw tiles (16-byte pieces)
     auto issue_chunk = [&](int t0) {
-        const int piece = lane & 15, rsel = lane >> 4;
+        if constexpr (IN16) {  // 8 pieces per 128-byte row: lane = piece within a group of four rows
+            const int piece = lane & 7, rsel = lane >> 3;
 #pragma unroll
-        for (int j = 0; j < kChunk / 2; ++j) {
-            const int r = 2 * j + rsel;
-            if (t0 + r < p.T) {
-                const size_t o = static_cast<size_t>(t0 + r) * p.ld_qkv + 4 * piece;
-                cp_async16(rawq + r * kCkQKStride + 4 * piece, qb + o);
-                cp_async16(rawk + r * kCkQKStride + 4 * piece, kb + o);
-                cp_async16(rawv + r * kCkVStride + 4 * piece, vb + o);
+            for (int j = 0; j < kChunk / 4; ++j) {
+                const int r = 4 * j + rsel;
+                if (t0 + r < p.T) {
+                    const size_t o = static_cast<size_t>(t0 + r) * p.ld_qkv + 8 * piece;
+                    cp_async16(rawqh + r * kCkQKStrideH + 8 * piece, qbh + o);
+                    cp_async16(rawkh + r * kCkQKStrideH + 8 * piece, kbh + o);
+                    cp_async16(rawvh + r * kCkVStrideH + 8 * piece, vbh + o);
+                }
+            }
+        } else {  // 16 pieces per 256-byte row: lane = piece within a pair of rows
+            const int piece = lane & 15, rsel = lane >> 4;
+#pragma unroll
+            for (int j = 0; j < kChunk / 2; ++j) {
+                const int r = 2 * j + rsel;
+                if (t0 + r < p.T) {
+                    const size_t o = static_cast<size_t>(t0 + r) * p.ld_qkv + 4 * piece;
+                    cp_async16(rawq + r * kCkQKStride + 4 * piece, qb + o);
+                    cp_async16(rawk + r * kCkQKStride + 4 * piece, kb + o);
+                    cp_async16(rawv + r * kCkVStride + 4 * piece, vb + o);
+                }
             }
         }
         if (lane < kChunk && t0 + lane < p.T) cp_async4(beta_sh + lane, bb + static_cast<size_t>(t0 + lane) * p.ld_beta);
@@ -496,13 +525,30 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
         {
             const int tt = lane >> 1, hh = lane & 1;
             const bool valid = t0 + tt < p.T;
+            // the lane's 32 elements of q and of k: 16-byte pieces 2 j + hh (four fp32, or eight halves: elements
+            // 8 (2 j + hh) .. + 7); element e of the register array is column kcol(e)
             float qv[32], kv[32];
+            if constexpr (IN16) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float4 a = *reinterpret_cast<const float4*>(rawq + tt * kCkQKStride + (2 * j + hh) * 4);
-                const float4 b = *reinterpret_cast<const float4*>(rawk + tt * kCkQKStride + (2 * j + hh) * 4);
-                qv[4 * j] = valid ? a.x : 0.0f; qv[4 * j + 1] = valid ? a.y : 0.0f; qv[4 * j + 2] = valid ? a.z : 0.0f; qv[4 * j + 3] = valid ? a.w : 0.0f;
-                kv[4 * j] = valid ? b.x : 0.0f; kv[4 * j + 1] = valid ? b.y : 0.0f; kv[4 * j + 2] = valid ? b.z : 0.0f; kv[4 * j + 3] = valid ? b.w : 0.0f;
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 a = *reinterpret_cast<const uint4*>(rawqh + tt * kCkQKStrideH + (2 * j + hh) * 8);
+                    const uint4 b = *reinterpret_cast<const uint4*>(rawkh + tt * kCkQKStrideH + (2 * j + hh) * 8);
+                    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[e])), fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
+                        qv[8 * j + 2 * e] = valid ? fa.x : 0.0f; qv[8 * j + 2 * e + 1] = valid ? fa.y : 0.0f;
+                        kv[8 * j + 2 * e] = valid ? fb.x : 0.0f; kv[8 * j + 2 * e + 1] = valid ? fb.y : 0.0f;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 a = *reinterpret_cast<const float4*>(rawq + tt * kCkQKStride + (2 * j + hh) * 4);
+                    const float4 b = *reinterpret_cast<const float4*>(rawk + tt * kCkQKStride + (2 * j + hh) * 4);
+                    qv[4 * j] = valid ? a.x : 0.0f; qv[4 * j + 1] = valid ? a.y : 0.0f; qv[4 * j + 2] = valid ? a.z : 0.0f; qv[4 * j + 3] = valid ? a.w : 0.0f;
+                    kv[4 * j] = valid ? b.x : 0.0f; kv[4 * j + 1] = valid ? b.y : 0.0f; kv[4 * j + 2] = valid ? b.z : 0.0f; kv[4 * j + 3] = valid ? b.w : 0.0f;
+                }
             }
             float qss = 0.0f, kss = 0.0f;
 #pragma unroll
@@ -520,7 +566,9 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
             const float nks = -kscale, aks = alpha * kscale;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int o = tt * kCkHStride + (2 * j + hh) * 4;
+                // register elements 4 j .. 4 j + 3 are four consecutive columns starting at c0
+                const int c0 = IN16 ? (2 * (j >> 1) + hh) * 8 + 4 * (j & 1) : (2 * j + hh) * 4;
+                const int o = tt * kCkHStride + c0;
                 uint2 wq, wk, wa;
                 wq.x = pack_half2(qv[4 * j] * q_inv, qv[4 * j + 1] * q_inv); wq.y = pack_half2(qv[4 * j + 2] * q_inv, qv[4 * j + 3] * q_inv);
                 wk.x = pack_half2(kv[4 * j] * nks, kv[4 * j + 1] * nks);     wk.y = pack_half2(kv[4 * j + 2] * nks, kv[4 * j + 3] * nks);
@@ -540,8 +588,13 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
                 const bool valid = t0 + tok < p.T;
 #pragma unroll
                 for (int mt = 0; mt < 4; ++mt) {
-                    Wc[mt][nt][e] = valid ? rawv[tok * kCkVStride + 16 * mt + g] : 0.0f;
-                    Wc[mt][nt][2 + e] = valid ? rawv[tok * kCkVStride + 16 * mt + 8 + g] : 0.0f;
+                    if constexpr (IN16) {
+                        Wc[mt][nt][e] = valid ? __half2float(rawvh[tok * kCkVStrideH + 16 * mt + g]) : 0.0f;
+                        Wc[mt][nt][2 + e] = valid ? __half2float(rawvh[tok * kCkVStrideH + 16 * mt + 8 + g]) : 0.0f;
+                    } else {
+                        Wc[mt][nt][e] = valid ? rawv[tok * kCkVStride + 16 * mt + g] : 0.0f;
+                        Wc[mt][nt][2 + e] = valid ? rawv[tok * kCkVStride + 16 * mt + 8 + g] : 0.0f;
+                    }
                 }
             }
         __syncwarp();  // the raw tiles are free, the prepared operands are visible
@@ -641,13 +694,27 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int tok = t0 + 8 * nt + 2 * tq + e;
-                    if (tok < p.T) {
-                        float* orow = ob + static_cast<size_t>(tok) * p.ld_out + 16 * mt + g;
+                    const int tl = 8 * nt + 2 * tq + e;
+                    if constexpr (OUT16) {  // staged as halves, written out row by row below
+                        y_sh[tl * kCkYStrideH + 16 * mt + g] = __float2half_rn(Yc[nt][e]);
+                        y_sh[tl * kCkYStrideH + 16 * mt + 8 + g] = __float2half_rn(Yc[nt][2 + e]);
+                    } else if (t0 + tl < p.T) {
+                        float* orow = ob + static_cast<size_t>(t0 + tl) * p.ld_out + 16 * mt + g;
                         orow[0] = Yc[nt][e];
                         orow[8] = Yc[nt][2 + e];
                     }
                 }
+        }
+        if constexpr (OUT16) {
+            __syncwarp();
+            // 16 rows x 128 bytes: 16-byte pieces, eight per row
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int tl = 4 * j + (lane >> 3), piece = lane & 7;
+                if (t0 + tl < p.T)
+                    *reinterpret_cast<uint4*>(obh + static_cast<size_t>(t0 + tl) * p.ld_out + 8 * piece) =
+                        *reinterpret_cast<const uint4*>(y_sh + tl * kCkYStrideH + 8 * piece);
+            }
         }
         // ---------------- S^T += U^T (a K): fp16 accumulators = the state registers, rounded once per chunk ----------------
 #pragma unroll
@@ -677,6 +744,8 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
     const bool regs_ok = p.state == nullptr && p.state_fp16 && hd == 64 &&
                          ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v)) & 15) == 0 &&
                          (p.ld_qkv % 4) == 0;  // 16-byte asynchronous copies of q, k, v
+    if ((p.qkv_f16 || p.out_f16) && (!regs_ok || p.variant == BNF4_EFLA_GENERIC || p.variant == BNF4_EFLA_PER_TOKEN))
+        return set_error(BNF4_ERR_INVALID, "efla: fp16 q, k, v or output are supported by the chunked kernel only");
     if ((p.variant == BNF4_EFLA_PER_TOKEN || p.variant == BNF4_EFLA_CHUNKED) && !regs_ok)
         return set_error(BNF4_ERR_INVALID, "efla: the register-state kernels need head_dim 64, no HBM state, an fp16 state and 16-byte aligned q, k, v");
     if (regs_ok && p.variant != BNF4_EFLA_GENERIC) {
@@ -692,14 +761,24 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
         if (dev < 0 || dev >= 64 || !configured[dev]) {
             rc = check_cuda(cudaFuncSetAttribute(efla_scan64_mma2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScan2SmemBytes), "cudaFuncSetAttribute(efla_scan64_mma2_kernel)");
             if (rc) return rc;
-            rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
+            rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
+            if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
+            if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
+            if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
             if (rc) return rc;
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
         if (chunked) {
-            efla_chunk16_kernel<<<static_cast<unsigned>(ctas), kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
+            if (p.qkv_f16 && ((p.ld_qkv % 8) != 0)) return set_error(BNF4_ERR_INVALID, "efla: fp16 q, k, v need ld_qkv %% 8 == 0");
+            if (p.out_f16 && (((p.ld_out % 8) != 0) || (reinterpret_cast<uintptr_t>(p.out) & 15))) return set_error(BNF4_ERR_INVALID, "efla: fp16 output needs 16-byte aligned rows");
+            const unsigned grid = static_cast<unsigned>(ctas);
+            if (p.qkv_f16 && p.out_f16) efla_chunk16_kernel<true, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
+            else if (p.qkv_f16) efla_chunk16_kernel<true, false><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
+            else if (p.out_f16) efla_chunk16_kernel<false, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
+            else efla_chunk16_kernel<false, false><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
             return check_launch("efla_chunk16_kernel");
         }
+        if (p.qkv_f16 || p.out_f16) return set_error(BNF4_ERR_INVALID, "efla: fp16 q, k, v or output are supported by the chunked kernel only");
         efla_scan64_mma2_kernel<<<static_cast<unsigned>(ctas), kScanWarps * 32, kScan2SmemBytes, stream>>>(p);
         return check_launch("efla_scan64_mma2_kernel");
     }

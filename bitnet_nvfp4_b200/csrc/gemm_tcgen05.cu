@@ -581,6 +581,34 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                             if (col0 + j < p.n) drow[j] = v[j];
                     }
                 }
+            } else if constexpr (EPI == EPI_F16) {
+                if (col0 < p.n_f16) {
+                    // 32 rows x 32 halves staged as 64-byte rows, then one TMA store (clips at M; n_f16 is a multiple of 32)
+                    if (it > 0) {
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(epi_gen + lane * 64);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int jj = j;
+                        const __half2 h0 = __floats2half2_rn(v[8 * jj], v[8 * jj + 1]), h1 = __floats2half2_rn(v[8 * jj + 2], v[8 * jj + 3]);
+                        const __half2 h2 = __floats2half2_rn(v[8 * jj + 4], v[8 * jj + 5]), h3 = __floats2half2_rn(v[8 * jj + 6], v[8 * jj + 7]);
+                        dst[jj] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                                             *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
+                        bulk_commit();
+                    }
+                } else if (row_ok) {
+                    float* drow = p.d + static_cast<size_t>(row) * p.ldd + (col0 - p.n_f16);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.n) drow[j] = v[j];
+                }
             } else if constexpr (EPI == EPI_ADD_I8) {
                 if (row_ok) {
                     int8_t* xr = p.resid + static_cast<size_t>(row) * p.ld_resid + col0;
@@ -715,7 +743,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
             }
         }
-        if constexpr (EPI == EPI_F32) {
+        if constexpr (EPI == EPI_F32 || EPI == EPI_F16) {
             if (args.use_tma_store) {
                 if (lane == 0) bulk_wait_read<0>();
                 __syncwarp();
@@ -753,7 +781,7 @@ EncodeTiledFn get_encode_fn() {
 }
 
 int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t dim0, uint64_t dim1, uint64_t stride1_bytes,
-                uint32_t box0, uint32_t box1, const char* what) {
+                uint32_t box0, uint32_t box1, const char* what, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn fn = get_encode_fn();
     if (fn == nullptr) return set_error(BNF4_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {dim0, dim1};
@@ -761,7 +789,7 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint
     const cuuint32_t box[2] = {box0, box1};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(BNF4_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with %d", what, static_cast<int>(r));
     return BNF4_OK;
 }
@@ -798,6 +826,11 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     if (p.epilogue == EPI_F32 && !p.d) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null D");
     if (p.epilogue == EPI_GELU_I8 && !p.d_i8) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null int8 D");
     if (p.epilogue == EPI_ADD_I8 && (!p.resid || p.ld_resid < p.n)) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: the residual epilogue needs resid and ld_resid >= n");
+    if (p.epilogue == EPI_F16) {
+        if (!p.d_f16 || p.n_f16 <= 0 || (p.n_f16 % 32) != 0 || p.n_f16 > p.n) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: the fp16 epilogue needs d_f16 and n_f16 a multiple of 32 within n");
+        if ((reinterpret_cast<uintptr_t>(p.d_f16) & 15) || (p.ld_f16 % 8) != 0 || p.ld_f16 < p.n_f16) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: fp16 D misaligned");
+        if (p.n > p.n_f16 && (!p.d || p.ldd < p.n - p.n_f16)) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: the fp32 tail of the fp16 epilogue needs d and ldd >= n - n_f16");
+    }
     if (p.epilogue == EPI_GELU_FP4) {
         if (!p.d_codes || !p.d_sf) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: null FP4 D");
         if ((p.n % 32) != 0) return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: FP4 output needs n %% 32 == 0");
@@ -831,6 +864,12 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
                          static_cast<uint64_t>(p.ldd) * 4, 32, 32, "D");
         if (rc) return rc;
         args.use_tma_store = g_gemm_allow_tma_store != 0;  // 0 direct stores, 1 TMA stores
+    } else if (p.epilogue == EPI_F16) {
+        // the half columns leave through a 32 x 32 box of halves (64-byte rows, unswizzled staging)
+        rc = make_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, p.d_f16, static_cast<uint64_t>(p.n_f16), static_cast<uint64_t>(p.m),
+                         static_cast<uint64_t>(p.ld_f16) * 2, 32, 32, "D (fp16)", CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        args.use_tma_store = 1;
     } else {
         md = ma;  // unused
     }
@@ -849,6 +888,7 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
         case EPI_GELU_I8: return launch_t<EPI_GELU_I8>(ma, mb, md, args, grid, stream);
         case EPI_GELU_FP4: return launch_t<EPI_GELU_FP4>(ma, mb, md, args, grid, stream);
         case EPI_ADD_I8: return launch_t<EPI_ADD_I8>(ma, mb, md, args, grid, stream);
+        case EPI_F16: return launch_t<EPI_F16>(ma, mb, md, args, grid, stream);
     }
     return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: unknown epilogue %d", p.epilogue);
 }

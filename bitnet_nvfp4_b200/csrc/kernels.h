@@ -38,6 +38,7 @@ enum GemmEpilogue : int {
     EPI_GELU_I8 = BNF4_EPI_GELU_I8,    // int8 D = clip8(rint(gelu(v) * act_scale))
     EPI_GELU_FP4 = BNF4_EPI_GELU_FP4,  // the above re-quantised to e2m1 codes + ue4m3 scales (+ int8 copy, + t of the next GEMM)
     EPI_ADD_I8 = BNF4_EPI_ADD_I8,      // int8 residual stream updated in place: clip8(resid + rint(v * add_scale))
+    EPI_F16 = BNF4_EPI_F16,            // leading columns as IEEE halves, the rest fp32
 };
 
 using GemmParams = bnf4_gemm_desc;

@@ -261,18 +261,41 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
         TRY(rowquant_dispatch(FE_POS_GELU_ABSMEAN, p, st));
         ++launches;
     }
+    // With heads of 64 and the chunked scan, q | k | v travel as IEEE halves (the scan rounds its operands to fp16 anyway) and
+    // so does the scan's output: the projection writes [rows][3H] halves + [rows] fp32 beta_raw into the qkv buffer, the
+    // scan writes [rows][H] halves into the y buffer. Otherwise everything stays fp32 (the reference's interface).
+    const bool half_io = m.hd == 64 && g_efla_chunked != 0;
+    __half* qkv16 = reinterpret_cast<__half*>(m.qkv);
+    float* beta16 = m.qkv + (static_cast<size_t>(rows) * 3 * H + 1) / 2;  // behind the halves
     for (int l = 0; l < L; ++l) {
-        // fused QKV(+beta) projection -> qkv [rows][FC]; out_scale is folded into the weight scales (alpha = 1)
-        TRY(gemm(KC_GEMM_QKV, m.a_h, m.sf_h, m.q_qkv[l], m.sfq_qkv[l], 3 * H + 1, H, 1.0f, m.qkv, FC, m.A_qkv[l] + P0 * (3 * H + 1) * r,
-                 static_cast<long long>(3 * H + 1) * r, m.t_a, 4 * r, m.s_h, H));
+        // fused QKV(+beta) projection; out_scale is folded into the weight scales (alpha = 1)
+        if (half_io) {
+            TimedScope ts(m, KC_GEMM_QKV, st);
+            bnf4_gemm_desc g = {};
+            g.a = m.a_h; g.b = m.q_qkv[l]; g.sfa = m.sf_h; g.sfb = m.sfq_qkv[l]; g.m = rows; g.n = 3 * H + 1; g.k = H; g.alpha = 1.0f;
+            g.epilogue = EPI_F16; g.d_f16 = qkv16; g.ld_f16 = 3 * H; g.n_f16 = 3 * H; g.d = beta16; g.ldd = 1;
+            g.rank = rank; g.rows_per_member = R; g.lora_t = m.t_a; g.t_stride = 4 * r; g.lora_A = m.A_qkv[l] + P0 * (3 * H + 1) * r;
+            g.lora_A_pair_stride = static_cast<long long>(3 * H + 1) * r; g.lora_scale = (sigma * m.s_h) * m.c_r; g.group_cols = H;
+            TRY(gemm_nvfp4_launch(g, st));
+        } else {
+            TRY(gemm(KC_GEMM_QKV, m.a_h, m.sf_h, m.q_qkv[l], m.sfq_qkv[l], 3 * H + 1, H, 1.0f, m.qkv, FC, m.A_qkv[l] + P0 * (3 * H + 1) * r,
+                     static_cast<long long>(3 * H + 1) * r, m.t_a, 4 * r, m.s_h, H));
+        }
         ++launches;
         {   // recurrence over the whole sequence -> y
             TimedScope ts(m, KC_EFLA, st);
             bnf4_efla_desc e = {};
-            e.state = nullptr; e.state_fp16 = 1; e.q = m.qkv; e.k = m.qkv + H; e.v = m.qkv + 2 * H; e.beta_raw = m.qkv + 3 * H;
-            e.ld_qkv = FC; e.ld_beta = FC; e.beta_bias_seq = m.bb_eff + static_cast<size_t>(l) * nm; e.seqs_per_bias = m.B;
+            e.state = nullptr; e.state_fp16 = 1;
+            if (half_io) {
+                e.q = qkv16; e.k = qkv16 + H; e.v = qkv16 + 2 * H; e.beta_raw = beta16; e.ld_qkv = 3 * H; e.ld_beta = 1;
+                e.qkv_f16 = 1; e.out_f16 = 1; e.out = m.y; e.ld_out = H;
+            } else {
+                e.q = m.qkv; e.k = m.qkv + H; e.v = m.qkv + 2 * H; e.beta_raw = m.qkv + 3 * H; e.ld_qkv = FC; e.ld_beta = FC;
+                e.out = m.y; e.ld_out = H;
+            }
+            e.beta_bias_seq = m.bb_eff + static_cast<size_t>(l) * nm; e.seqs_per_bias = m.B;
             e.hidden = H; e.heads = m.cfg.heads; e.seqs = static_cast<long long>(nm) * m.B; e.T = m.T; e.method = m.cfg.method;
-            e.eps = m.cfg.eps; e.out = m.y; e.ld_out = H;
+            e.eps = m.cfg.eps;
             // the generic kernel addresses sequences with blockIdx.z: split large waves
             if (m.hd == 64) {
                 TRY(efla_launch(e, st));
@@ -282,8 +305,8 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
                     bnf4_efla_desc ee = e;
                     const long long cnt = std::min<long long>(32768, e.seqs - s0);
                     const size_t ro = static_cast<size_t>(s0) * m.T;
-                    ee.q = e.q + ro * FC; ee.k = e.k + ro * FC; ee.v = e.v + ro * FC; ee.beta_raw = e.beta_raw + ro * FC;
-                    ee.out = e.out + ro * H; ee.seqs = cnt;
+                    ee.q = m.qkv + ro * FC; ee.k = m.qkv + H + ro * FC; ee.v = m.qkv + 2 * H + ro * FC; ee.beta_raw = e.beta_raw + ro * FC;
+                    ee.out = m.y + ro * H; ee.seqs = cnt;
                     if ((s0 % m.B) != 0) return set_error(BNF4_ERR_INVALID, "efla split not aligned to batch");
                     ee.beta_bias_seq = e.beta_bias_seq + s0 / m.B;
                     TRY(efla_launch(ee, st));
@@ -295,7 +318,8 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
             TimedScope ts(m, KC_ADD_NORM, st);
             bnf4_rowquant_desc p = {};
             p.rows = rows; p.cols_in = H; p.cols_out = H; p.rows_per_member = R; p.sigma = sigma;
-            p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.add_scale = m.cfg.residual_scale; p.norm_scale = m.cfg.ln_scale;
+            p.inout_i8 = m.x_q; p.in_f32 = m.y; p.ld_in = H; p.in_f16 = half_io ? 1 : 0;
+            p.add_scale = m.cfg.residual_scale; p.norm_scale = m.cfg.ln_scale;
             p.out_codes = m.a_h; p.out_sf = m.sf_h;
             if (pert) { p.tvec = m.tB_ff1[l] + P0 * r * H; p.tvec_pair_stride = static_cast<long long>(r) * H; p.nvec = r; p.t_out = m.t_a; }
             TRY(rowquant_dispatch(FE_ADD_ABSMEAN, p, st));

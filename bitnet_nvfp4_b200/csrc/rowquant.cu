@@ -352,8 +352,19 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 const int4 raw = *reinterpret_cast<const int4*>(xr + k0);
                 const uint32_t rw[4] = {static_cast<uint32_t>(raw.x), static_cast<uint32_t>(raw.y), static_cast<uint32_t>(raw.z), static_cast<uint32_t>(raw.w)};
                 float4 y4[4];
+                if (p.in_f16) {  // the branch output as IEEE halves (exact widening)
+                    const uint4* yh = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.in_f32) + static_cast<size_t>(row) * p.ld_in + k0);
+                    const uint4 h0 = __ldcs(yh), h1 = __ldcs(yh + 1);
+                    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) y4[q] = __ldcs(reinterpret_cast<const float4*>(yr + k0 + 4 * q));
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&hw[2 * q])), hi = __half22float2(*reinterpret_cast<const __half2*>(&hw[2 * q + 1]));
+                        y4[q] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) y4[q] = __ldcs(reinterpret_cast<const float4*>(yr + k0 + 4 * q));
+                }
                 uint32_t upd[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -590,7 +601,8 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
         auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
         bool fast = p.cols_in == p.cols_out && nblk <= 128 && (p.out_q == nullptr || p.vec_ok_q) && al16(p.inout_i8 ? p.inout_i8 : nullptr);
         if (FE == FE_ABSMEAN) fast = fast && p.vec_ok && p.in_i8 != nullptr;
-        if (FE == FE_ADD_ABSMEAN) fast = fast && al16(p.in_f32) && (p.ld_in % 4) == 0;
+        if (FE == FE_ADD_ABSMEAN) fast = fast && al16(p.in_f32) && (p.ld_in % (p.in_f16 ? 8 : 4)) == 0;
+        if (FE == FE_ADD_ABSMEAN && p.in_f16 && !fast) return set_error(BNF4_ERR_INVALID, "rowquant: fp16 input needs 16-byte aligned rows and cols_in == cols_out <= 2048");
         if (FE == FE_POS_GELU_ABSMEAN)
             fast = fast && p.vec_ok && al16(p.pos) && (p.pos_noise == nullptr || (al16(p.pos_noise) && (p.noise_pair_stride % 16) == 0));
         if (FE == FE_EMBED_LOWRANK)
@@ -652,7 +664,8 @@ int rowquant_dispatch(int fe, RowQuantParams p, cudaStream_t stream) {
         if (!aligned16(p.inout_i8, p.cols_in))
             return set_error(BNF4_ERR_INVALID, "rowquant: residual stream must be 16-byte aligned with hidden %% 16 == 0");
     }
-    if (fe == FE_ADD_ABSMEAN && !aligned16(p.in_f32, static_cast<long long>(p.ld_in) * 4))
+    if (p.in_f16 && fe != FE_ADD_ABSMEAN) return set_error(BNF4_ERR_INVALID, "rowquant: fp16 input is supported by the residual-add front-end only");
+    if (fe == FE_ADD_ABSMEAN && !aligned16(p.in_f32, static_cast<long long>(p.ld_in) * (p.in_f16 ? 2 : 4)))
         return set_error(BNF4_ERR_INVALID, "rowquant: fp32 input must be 16-byte aligned");
     if ((fe == FE_POS_GELU || fe == FE_POS_GELU_ABSMEAN || fe == FE_EMBED_DENSE || fe == FE_EMBED_LOWRANK || fe == FE_ADD_ABSMEAN || fe == FE_ABSMEAN) &&
         p.cols_in != p.cols_out)

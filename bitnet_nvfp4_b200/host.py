@@ -13,7 +13,7 @@ import torch
 from . import lib as _l
 
 FE_INT8, FE_WQKV, FE_EMBED_DENSE, FE_EMBED_LOWRANK, FE_POS_GELU, FE_POS_GELU_ABSMEAN, FE_ACT, FE_ABSMEAN, FE_ADD_ABSMEAN = range(9)
-EPI_F32, EPI_GELU_I8, EPI_GELU_FP4, EPI_ADD_I8 = range(4)
+EPI_F32, EPI_GELU_I8, EPI_GELU_FP4, EPI_ADD_I8, EPI_F16 = range(5)
 
 C_RANK_BASE = 0.6123724356957945  # sqrt(3/8)
 

@@ -31,7 +31,7 @@ class RowQuantDesc(C.Structure):
         ("act_mode", c_int), ("act_scale", c_float), ("add_scale", c_float), ("norm_scale", c_float),
         ("out_q", c_void_p), ("ld_q", c_int), ("out_codes", c_void_p), ("out_sf", c_void_p),
         ("tvec", c_void_p), ("tvec_pair_stride", c_ll), ("nvec", c_int), ("t_out", c_void_p),
-        ("vec_ok", c_int), ("vec_ok_q", c_int), ("gather_rows", c_int),
+        ("vec_ok", c_int), ("vec_ok_q", c_int), ("gather_rows", c_int), ("in_f16", c_int),
     ]
 
 
@@ -48,6 +48,7 @@ class GemmDesc(C.Structure):
         ("lora_A", c_void_p), ("lora_A_pair_stride", c_ll), ("lora_scale", c_float), ("group_cols", c_int),
         ("next_tvec", c_void_p), ("next_tvec_pair_stride", c_ll), ("next_nvec", c_int), ("next_t", c_void_p),
         ("resid", c_void_p), ("ld_resid", c_int), ("add_scale", c_float),
+        ("d_f16", c_void_p), ("ld_f16", c_int), ("n_f16", c_int),
     ]
 
 
@@ -60,7 +61,7 @@ class EflaDesc(C.Structure):
         ("ld_qkv", c_int), ("ld_beta", c_int),
         ("beta_bias", c_float), ("beta_bias_seq", c_void_p), ("seqs_per_bias", c_int),
         ("hidden", c_int), ("heads", c_int), ("seqs", c_ll), ("T", c_int), ("method", c_int), ("eps", c_float),
-        ("out", c_void_p), ("ld_out", c_int), ("variant", c_int),
+        ("out", c_void_p), ("ld_out", c_int), ("variant", c_int), ("qkv_f16", c_int), ("out_f16", c_int),
     ]
 
 

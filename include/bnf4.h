@@ -152,6 +152,7 @@ typedef struct bnf4_rowquant_desc {
     /* BNF4_FE_POS_GELU(_ABSMEAN) only: when > 0 the fp32 input is a table of gather_rows rows per member and the input
      * row of output row (member, i) is member * gather_rows + tokens[(i % row_mod) * token_stride] (row_mod 0: i). */
     int gather_rows;
+    int in_f16; /* BNF4_FE_ADD_ABSMEAN: in_f32 points at IEEE halves and ld_in counts halves (16-byte aligned rows) */
 } bnf4_rowquant_desc;
 
 int bnf4_rowquant(int front_end, const bnf4_rowquant_desc* desc, void* stream);
@@ -177,6 +178,8 @@ int bnf4_nvfp4_prepare_gemm(const void* a, const void* b, const void* sfa, const
                            * add_scaled_to_int8_absmean_norm_q_nvfp4 (src/cuda_kernels.cu:3033-3143) applied by the GEMM
                            * that produces v, so that the fp32 product never travels through HBM; follow it with the
                            * BNF4_FE_ABSMEAN quantiser over resid; |v * add_scale| must stay below 2^15 */
+#define BNF4_EPI_F16 4 /* D rounded to IEEE half (round to nearest even) for the leading n_f16 columns, fp32 for the rest: the
+                          fused q | k | v | beta projection feeding the chunked EFLA scan, which rounds its operands to fp16 anyway */
 
 /* Full form: strides, fused epilogues and the rank-r perturbation
  *   D += s_member * sum_r t[m][g*rank + r] * A_pair[n][r]
@@ -213,6 +216,10 @@ typedef struct bnf4_gemm_desc {
     int8_t* resid;   /* BNF4_EPI_ADD_I8: [M][ld_resid] int8, read and written */
     int ld_resid;
     float add_scale;
+    void* d_f16;     /* BNF4_EPI_F16: columns [0, n_f16) as IEEE halves [M][ld_f16]; columns [n_f16, n) as fp32 in d, where
+                        column j lands at d[row * ldd + (j - n_f16)] */
+    int ld_f16;      /* in halves, a multiple of 8 */
+    int n_f16;       /* a multiple of 32 */
 } bnf4_gemm_desc;
 
 int bnf4_gemm_nvfp4_ex(const bnf4_gemm_desc* desc, void* stream);
@@ -240,9 +247,9 @@ typedef struct bnf4_efla_desc {
     void* state;    /* optional HBM state [seqs][heads][hd][hd]; loaded before and stored after the T steps.
                        NULL: zero initial state, final state discarded (whole-sequence scan). */
     int state_fp16; /* 1: state is rounded to fp16 after every step (the reference default); 0: fp32 state */
-    const float* q; /* row r = seq*T + t at q + r*ld_qkv; head h at column h*hd (likewise k, v) */
-    const float* k;
-    const float* v;
+    const void* q; /* fp32 (or halves, see qkv_f16): row r = seq*T + t at q + r*ld_qkv; head h at column h*hd (likewise k, v) */
+    const void* k;
+    const void* v;
     const float* beta_raw; /* row r at beta_raw + r*ld_beta */
     int ld_qkv, ld_beta;
     float beta_bias;            /* used when beta_bias_seq == NULL */
@@ -253,10 +260,12 @@ typedef struct bnf4_efla_desc {
     int T;
     int method; /* 0 DeltaNet, 1 EFLA */
     float eps;
-    float* out; /* row r at out + r*ld_out */
+    void* out; /* fp32 (or halves, see out_f16): row r at out + r*ld_out */
     int ld_out;
     int variant; /* BNF4_EFLA_*: which kernel runs. AUTO: for heads of 64 with no HBM state, the chunked or the per-token
                     register-state kernel as option "efla_chunked" says; the generic kernel otherwise. */
+    int qkv_f16; /* 1: q, k, v are IEEE halves and ld_qkv counts halves (chunked kernel only; 16-byte aligned rows) */
+    int out_f16; /* 1: out is IEEE halves and ld_out counts halves (chunked kernel only; 16-byte aligned rows) */
 } bnf4_efla_desc;
 #define BNF4_EFLA_AUTO 0
 #define BNF4_EFLA_GENERIC 1   /* any head_dim, state in shared memory (and in HBM between calls), per-token fp16 rounding */

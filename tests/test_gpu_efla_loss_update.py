@@ -112,6 +112,48 @@ def test_efla_scan_whole_sequence(H, hidden, heads, seqs, T, variant):
     assert np.median(dev_) <= (3e-4 if variant == CHUNKED else 1e-4) * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("in16,out16", [(1, 0), (0, 1), (1, 1)])
+@pytest.mark.parametrize("hidden,heads,seqs,T", [(512, 8, 6, 128), (128, 2, 7, 40)])
+def test_efla_chunked_scan_with_half_inputs_and_outputs(H, hidden, heads, seqs, T, in16, out16):
+    """The chunked kernel reading q | k | v as IEEE halves and / or writing y as halves (what the batched driver uses): against
+    the oracle's per-token recurrence on the values the kernel is given, same bound as the fp32 interface plus half an fp16 ulp
+    of the output where y is rounded."""
+    import torch
+    rng = np.random.default_rng(hidden + T + 2 * in16 + out16)
+    fc = (3 * hidden + 1 + 31) & ~31
+    qkv = make_qkv(rng, seqs * T, hidden, fc, 0.4)
+    if in16:
+        qkv[:, :3 * hidden] = qkv[:, :3 * hidden].astype(np.float16).astype(np.float32)   # the values the kernel sees
+    bb = (rng.standard_normal(seqs) * 0.2 - 2.0).astype(np.float32)
+    ref = orc.efla_scan(qkv.reshape(seqs, T, fc), bb, hidden, heads)
+    out = torch.zeros((seqs * T, hidden), dtype=torch.float16 if out16 else torch.float32, device="cuda")
+    beta = dev(np.ascontiguousarray(qkv[:, 3 * hidden]))
+    if in16:
+        q16 = dev(np.ascontiguousarray(qkv[:, :3 * hidden]).astype(np.float16))
+        H.efla_scan(state=None, state_fp16=1, q=q16, k=q16[:, hidden:], v=q16[:, 2 * hidden:], beta_raw=beta, ld_qkv=3 * hidden, ld_beta=1,
+                    beta_bias_seq=dev(bb), seqs_per_bias=1, hidden=hidden, heads=heads, seqs=seqs, T=T, method=1, eps=1e-6, out=out,
+                    ld_out=hidden, variant=CHUNKED, qkv_f16=1, out_f16=out16)
+    else:
+        qd = dev(qkv)
+        H.efla_scan(state=None, state_fp16=1, q=qd, k=qd[:, hidden:], v=qd[:, 2 * hidden:], beta_raw=beta, ld_qkv=fc, ld_beta=1,
+                    beta_bias_seq=dev(bb), seqs_per_bias=1, hidden=hidden, heads=heads, seqs=seqs, T=T, method=1, eps=1e-6, out=out,
+                    ld_out=hidden, variant=CHUNKED, out_f16=out16)
+    got = out.float().cpu().numpy().reshape(seqs, T, hidden)
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= (SCAN_TOL + (2.0 ** -11 if out16 else 0.0)) * scale
+
+
+def test_efla_half_interface_is_chunked_only(H):
+    import torch
+    from bitnet_nvfp4_b200 import lib
+    q16 = torch.zeros((16, 192), dtype=torch.float16, device="cuda")
+    out = torch.zeros((16, 64), dtype=torch.float32, device="cuda")
+    beta = torch.zeros(16, dtype=torch.float32, device="cuda")
+    with pytest.raises(lib.Bnf4Error):
+        H.efla_scan(state=None, state_fp16=1, q=q16, k=q16[:, 64:], v=q16[:, 128:], beta_raw=beta, ld_qkv=192, ld_beta=1, beta_bias=-2.0,
+                    seqs_per_bias=1, hidden=64, heads=1, seqs=1, T=16, method=1, eps=1e-6, out=out, ld_out=64, variant=PER_TOKEN, qkv_f16=1)
+
+
 def _recover_states(y, q_scale):
     """y [64 probes][T][heads][64] with probe d reading row d of every head's state: S[t][head][d][n] as fp16 bit patterns."""
     s = (y / q_scale).astype(np.float16)          # y = S[d, n] * q^_d exactly (one fp32 rounding); the division undoes it

@@ -223,6 +223,29 @@ def test_gemm_residual_add_epilogue(H, m, n, k, rank):
     assert diff.max() <= 1 and (diff != 0).mean() <= 5e-3
 
 
+def test_gemm_fp16_epilogue_rounds_the_fp32_result(H):
+    """BNF4_EPI_F16 (the fused q | k | v | beta projection feeding the chunked scan): the leading columns are the fp32 epilogue's
+    values rounded once to IEEE half (bit for bit: same accumulators), the remaining columns stay fp32."""
+    import torch
+    rng = np.random.default_rng(77)
+    hid, R, pairs, rank = 128, 64, 2, 2
+    m, n, k = 2 * pairs * R, 3 * hid + 1, hid
+    x, w, a, sfa, b, sfb = make_operands(rng, m, n, k)
+    A = rng.integers(-4, 5, (pairs, n, rank)).astype(np.int8)
+    t = rng.integers(-500, 500, (m, 4 * rank)).astype(np.int32)
+    kw = dict(a=dev(a), b=dev(b), sfa=dev(sfa), sfb=dev(sfb), m=m, n=n, k=k, alpha=0.05, rank=rank, rows_per_member=R, lora_t=dev(t),
+              t_stride=4 * rank, lora_A=dev(A), lora_A_pair_stride=n * rank, lora_scale=0.003, group_cols=hid)
+    ld = (n + 31) & ~31
+    d32 = torch.zeros((m, ld), dtype=torch.float32, device="cuda")
+    H.gemm_nvfp4_ex(**kw, d=d32, ldd=ld, epilogue=H.EPI_F32)
+    d16 = torch.zeros((m, 3 * hid), dtype=torch.float16, device="cuda")
+    tail = torch.zeros((m, 1), dtype=torch.float32, device="cuda")
+    H.gemm_nvfp4_ex(**kw, d_f16=d16, ld_f16=3 * hid, n_f16=3 * hid, d=tail, ldd=1, epilogue=H.EPI_F16)
+    assert H.device_error() == 0
+    assert torch.equal(d16, d32[:, :3 * hid].to(torch.float16))
+    assert torch.equal(tail[:, 0], d32[:, 3 * hid])
+
+
 def test_gemm_rejects_bad_arguments(H):
     import torch
     from bitnet_nvfp4_b200 import lib

@@ -181,6 +181,29 @@ def test_add_scaled_absmean_norm_bit_exact(H, rows, hid, add_scale):
     assert same(q, rq) and same(codes, rc) and same(sf, rs)
 
 
+def test_add_absmean_with_half_branch_input(H):
+    """FE_ADD_ABSMEAN reading the branch output as IEEE halves (the scan's fp16 output): bit-exact against the oracle's
+    residual add + abs-mean norm on the same values widened to fp32."""
+    import torch
+    rng = np.random.default_rng(21)
+    rows, hid = 96, 512
+    x = rng.integers(-127, 128, (rows, hid)).astype(np.int8)
+    y16 = (rng.standard_normal((rows, hid)) * 3).astype(np.float16)
+    tvec = rng.integers(-4, 5, (1, 1, hid)).astype(np.int8)
+    xd = dev(x)
+    yq = torch.zeros((rows, hid), dtype=torch.int8, device="cuda")
+    codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
+    tout = torch.zeros((rows, 1), dtype=torch.int32, device="cuda")
+    H.rowquant(H.FE_ADD_ABSMEAN, rows=rows, cols_in=hid, cols_out=hid, rows_per_member=rows, sigma=0.125, inout_i8=xd, in_f32=dev(y16),
+               ld_in=hid, in_f16=1, add_scale=1.0, norm_scale=1.0, out_q=yq, ld_q=hid, out_codes=codes, out_sf=sf, tvec=dev(tvec),
+               tvec_pair_stride=hid, nvec=1, t_out=tout)
+    xr = x.copy()
+    rq, rc, rs = orc.absmean_norm_q(xr, y16.astype(np.float32), 1.0, 1.0)
+    assert same(xd, xr) and same(yq, rq) and same(codes, rc) and same(sf, rs)
+    assert same(tout, rq.astype(np.int32) @ tvec[0].astype(np.int32).T)
+
+
 def test_pos_gelu_absmean_fused_population(H):
     """FE_POS_GELU_ABSMEAN = add_pos_gelu (kept as residual stream) followed by abs-mean norm, with per-pair pos noise."""
     import torch
