@@ -227,18 +227,27 @@ def run_kernel(args):
     if args.kernel == "efla":
         T, hidden, heads, fc = 128, 512, 8, 1568
         seqs = args.seqs
-        qkv = torch.randn(seqs * T, fc, device="cuda") * 0.3
-        y = torch.empty(seqs * T, hidden, device="cuda")
         bb = torch.full((seqs // 32 + 1,), -2.0, device="cuda")
+        if args.half:   # q | k | v and the output as IEEE halves, beta_raw fp32: what the batched driver feeds the chunked kernel
+            qkv = (torch.randn(seqs * T, 3 * hidden, device="cuda") * 0.3).half()
+            beta = torch.randn(seqs * T, device="cuda")
+            y = torch.empty(seqs * T, hidden, device="cuda", dtype=torch.float16)
+            kw = dict(q=qkv, k=qkv[:, hidden:], v=qkv[:, 2 * hidden:], beta_raw=beta, ld_qkv=3 * hidden, ld_beta=1, qkv_f16=1, out_f16=1)
+            row_bytes = 3 * hidden * 2 + 4 + 2 * hidden
+        else:
+            qkv = torch.randn(seqs * T, fc, device="cuda") * 0.3
+            y = torch.empty(seqs * T, hidden, device="cuda")
+            kw = dict(q=qkv, k=qkv[:, hidden:], v=qkv[:, 2 * hidden:], beta_raw=qkv[:, 3 * hidden:], ld_qkv=fc, ld_beta=fc)
+            row_bytes = (3 * hidden + 1) * 4 + 4 * hidden
 
         def run():
-            H.efla_scan(state=None, state_fp16=1, q=qkv, k=qkv[:, hidden:], v=qkv[:, 2 * hidden:], beta_raw=qkv[:, 3 * hidden:], ld_qkv=fc,
-                        ld_beta=fc, beta_bias_seq=bb, seqs_per_bias=32, hidden=hidden, heads=heads, seqs=seqs, T=T, method=1, eps=1e-6,
-                        out=y, ld_out=hidden, variant=args.variant)
+            H.efla_scan(state=None, state_fp16=1, beta_bias_seq=bb, seqs_per_bias=32, hidden=hidden, heads=heads, seqs=seqs, T=T, method=1,
+                        eps=1e-6, out=y, ld_out=hidden, variant=args.variant, **kw)
 
         ms = _event_ms(run, args.iters)
-        gbs = seqs * T * ((3 * hidden + 1) * 4 + 4 * hidden) / ms / 1e6
-        out.update(case=f"seqs={seqs} T={T} heads={heads}x64 variant={args.variant}", ms=ms, achieved=gbs, unit="GB/s", frac=gbs / peaks["hbm_gbs"])
+        gbs = seqs * T * row_bytes / ms / 1e6
+        out.update(case=f"seqs={seqs} T={T} heads={heads}x64 variant={args.variant} half_io={int(args.half)}", ms=ms, achieved=gbs, unit="GB/s",
+                   frac=gbs / peaks["hbm_gbs"], algorithmic_bytes=seqs * T * row_bytes)
     elif args.kernel == "gemm":
         m, n, k, R = args.m, args.n, args.k, 4096
         a, sfa, b, sfb, A, t, pairs = _gemm_operands(H, m, n, k, args.rank, R)
@@ -247,6 +256,9 @@ def run_kernel(args):
                     lora_scale=0.01) if args.rank > 0 else {}
         base = dict(a=a, b=b, sfa=sfa, sfb=sfb, m=m, n=n, k=k, alpha=alpha)
         d = torch.empty((m, n), dtype=torch.float32, device="cuda") if args.epilogue == "f32" else None
+        n16 = (n - 1) // 32 * 32 if n % 32 else n   # f16 epilogue: leading multiple of 32 as halves, the rest (e.g. beta_raw) fp32
+        d16 = torch.empty((m, n16), dtype=torch.float16, device="cuda") if args.epilogue == "f16" else None
+        dtail = torch.empty((m, max(n - n16, 1)), dtype=torch.float32, device="cuda")
         d8 = torch.zeros((m, n), dtype=torch.int8, device="cuda")
         codes = torch.zeros(m * n // 2, dtype=torch.uint8, device="cuda")
         sf = torch.zeros(H.sf_bytes(m, n), dtype=torch.uint8, device="cuda")
@@ -256,6 +268,8 @@ def run_kernel(args):
         def run():
             if args.epilogue == "f32":
                 H.gemm_nvfp4_ex(**base, d=d, ldd=n, epilogue=H.EPI_F32, **lora)
+            elif args.epilogue == "f16":
+                H.gemm_nvfp4_ex(**base, d_f16=d16, ld_f16=n16, n_f16=n16, d=dtail, ldd=max(n - n16, 1), epilogue=H.EPI_F16, **lora)
             elif args.epilogue == "add_i8":
                 H.gemm_nvfp4_ex(**base, epilogue=H.EPI_ADD_I8, resid=d8, ld_resid=n, add_scale=0.0625, **lora)
             elif args.epilogue == "gelu_i8":
@@ -315,7 +329,8 @@ def main():
     ap.add_argument("--n", type=int, default=512)
     ap.add_argument("--k", type=int, default=512)
     ap.add_argument("--rank", type=int, default=-1, help="--kernel gemm / --sweep: rank of the perturbation term (defaults 1 / 4)")
-    ap.add_argument("--epilogue", default="f32", choices=["f32", "gelu_i8", "gelu_fp4", "add_i8"])
+    ap.add_argument("--epilogue", default="f32", choices=["f32", "f16", "gelu_i8", "gelu_fp4", "add_i8"])
+    ap.add_argument("--half", action="store_true", help="--kernel efla: q | k | v and the output as IEEE halves")
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--fe", default="add", choices=["add", "norm"])
     args = ap.parse_args()

@@ -117,6 +117,16 @@ struct Model {
     float *upd_partial, *upd_inv;
     ZLowrankDesc *zdesc, *zdesc_ext;  // device tables of the update's matrices: Z inside Z_all / inside a caller's buffer
     int launches_per_wave = 0;
+    // dense (rank 0) mode: the reference driver's own perturbation, one materialised noise matrix per weight matrix and pair,
+    // applied as a second GEMM with beta = 1 (src/train_efla_lm.cpp:2359-2367). One pair per wave.
+    bool dense = false;
+    uint64_t step_seed = 0, step_epoch = 0;
+    int8_t* E_all = nullptr;                 // noise of one pair, all matrices back to back (order of update_matrices)
+    uint8_t *qe_win, *sfe_win, *qe_head, *sfe_head;
+    std::vector<uint8_t*> qe_qkv, sfe_qkv, qe_ff1, sfe_ff1, qe_ff2, sfe_ff2;
+    bnf4_noise_desc* noise_descs = nullptr;  // device table for the batched fill
+    float* ff1_f = nullptr;                  // [2R][F] fp32 base product of ff1
+    int8_t* ff1_q = nullptr;                 // [2R][F] int8 GELU output
 
     // optional per-kernel-class timing with CUDA events on the launching stream
     bool timing = false;
@@ -374,6 +384,176 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
     return BNF4_OK;
 }
 
+
+// Offsets of the matrices inside E_all, in the order emb, win, per layer (wq, wk, wv, wbeta, ff1, ff2), head.
+struct DenseLayout {
+    size_t emb, win, head;
+    std::vector<size_t> wq, wk, wv, wbeta, ff1, ff2;
+    size_t total;
+};
+DenseLayout dense_layout(const Model& m) {
+    DenseLayout d;
+    const size_t vh = static_cast<size_t>(m.V) * m.H, hh = static_cast<size_t>(m.H) * m.H, hf = static_cast<size_t>(m.H) * m.F;
+    size_t o = 0;
+    d.emb = o; o += vh;
+    d.win = o; o += hh;
+    for (int l = 0; l < m.L; ++l) {
+        d.wq.push_back(o); o += hh;
+        d.wk.push_back(o); o += hh;
+        d.wv.push_back(o); o += hh;
+        d.wbeta.push_back(o); o += (static_cast<size_t>(m.H) + 15) / 16 * 16;
+        d.ff1.push_back(o); o += hf;
+        d.ff2.push_back(o); o += hf;
+    }
+    d.head = o; o += vh;
+    d.total = o;
+    return d;
+}
+
+// One antithetic pair in the reference driver's own form: dense CLT noise matrices from the pair's seeds
+// (set_noise_seeds, src/train_efla_lm.cpp:1946-2012), quantised to NVFP4 like the base weights, every projection as
+// D = alpha A W^T followed by D += (+-sigma alpha) A E^T (gemm_noisy :2349-2379, gemm_qkvb :2507-2523, gemm_ff1_gelu :2724-2747),
+// rows [0, R) = the + member, [R, 2R) = the - member. Layer-major over the tokens like the rank-r path.
+int run_pair_dense(Model& m, int pair, float* losses_out, cudaStream_t st) {
+    const int H = m.H, F = m.F, L = m.L, V = m.V, R = m.R, FC = m.FC;
+    const int rows = 2 * R;
+    const float sigma = m.sigma;
+    const DenseLayout lay = dense_layout(m);
+    const uint64_t pair_seed = mix_u64(m.step_seed, mix_u64(m.step_epoch, static_cast<uint64_t>(pair)));
+    {   // noise of all matrices in one launch, then their NVFP4 copies
+        std::vector<bnf4_noise_desc> nd;
+        const size_t vh = static_cast<size_t>(V) * H, hh = static_cast<size_t>(H) * H, hf = static_cast<size_t>(H) * F;
+        nd.push_back({m.E_all + lay.emb, vh, mix_u64(pair_seed, kSaltEmb)});
+        nd.push_back({m.E_all + lay.win, hh, mix_u64(pair_seed, kSaltWin)});
+        for (int l = 0; l < L; ++l) {
+            const uint64_t lu = static_cast<uint64_t>(l);
+            nd.push_back({m.E_all + lay.wq[l], hh, mix_u64(pair_seed, mix_u64(lu, kSaltWq))});
+            nd.push_back({m.E_all + lay.wk[l], hh, mix_u64(pair_seed, mix_u64(lu, kSaltWk))});
+            nd.push_back({m.E_all + lay.wv[l], hh, mix_u64(pair_seed, mix_u64(lu, kSaltWv))});
+            nd.push_back({m.E_all + lay.wbeta[l], static_cast<size_t>(H), mix_u64(pair_seed, mix_u64(lu, kSaltWbeta))});
+            nd.push_back({m.E_all + lay.ff1[l], hf, mix_u64(pair_seed, mix_u64(lu, kSaltFf1))});
+            nd.push_back({m.E_all + lay.ff2[l], hf, mix_u64(pair_seed, mix_u64(lu, kSaltFf2))});
+        }
+        nd.push_back({m.E_all + lay.head, vh, mix_u64(pair_seed, kSaltHead)});
+        TRY(check_cuda(cudaMemcpyAsync(m.noise_descs, nd.data(), nd.size() * sizeof(bnf4_noise_desc), cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(noise_descs)"));
+        TRY(check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize"));  // nd is a stack object: the copy must have read it
+        size_t maxn = 0;
+        for (const bnf4_noise_desc& x : nd) maxn = std::max(maxn, x.n);
+        TimedScope ts(m, KC_GEN_NOISE, st, 1);
+        TRY(bnf4_fill_ternary_noise_batched(m.noise_descs, static_cast<int>(nd.size()), static_cast<int>((maxn + 255) / 256), m.cfg.use_clt, m.cfg.clt_k, st));
+        auto plain = [&](const int8_t* w, int r_, int c_, uint8_t* codes, uint8_t* sf) {
+            bnf4_rowquant_desc q = {};
+            q.rows = r_; q.cols_in = c_; q.cols_out = c_; q.in_i8 = w; q.ld_in = c_; q.out_codes = codes; q.out_sf = sf;
+            return rowquant_dispatch(FE_INT8, q, st);
+        };
+        TRY(plain(m.E_all + lay.win, H, H, m.qe_win, m.sfe_win));
+        TRY(plain(m.E_all + lay.head, V, H, m.qe_head, m.sfe_head));
+        for (int l = 0; l < L; ++l) {
+            bnf4_rowquant_desc q = {};
+            q.rows = 3 * H + 1; q.cols_in = H; q.cols_out = H;
+            q.wq = m.E_all + lay.wq[l]; q.wk = m.E_all + lay.wk[l]; q.wv = m.E_all + lay.wv[l]; q.wb = m.E_all + lay.wbeta[l];
+            q.q_scale = q.k_scale = q.v_scale = q.b_scale = m.s_h;
+            q.out_codes = m.qe_qkv[l]; q.out_sf = m.sfe_qkv[l];
+            TRY(rowquant_dispatch(FE_WQKV, q, st));
+            TRY(plain(m.E_all + lay.ff1[l], F, H, m.qe_ff1[l], m.sfe_ff1[l]));
+            TRY(plain(m.E_all + lay.ff2[l], H, F, m.qe_ff2[l], m.sfe_ff2[l]));
+        }
+    }
+    {
+        TimedScope ts(m, KC_BETA_BIAS, st);
+        beta_bias_kernel<<<(2 * L + 127) / 128, 128, 0, st>>>(m.beta_bias, m.bb_noise + static_cast<size_t>(pair) * L, L, 2, sigma, m.bb_eff);
+        TRY(check_launch("beta_bias_kernel"));
+    }
+    // base product into d, then the two members' noise products added in place (alpha = +-sigma * alpha_base, beta = 1)
+    auto noisy = [&](int cls, const uint8_t* a, const uint8_t* sfa, int a_k, const uint8_t* b, const uint8_t* sfb, const uint8_t* be, const uint8_t* sfbe,
+                     int n, float alpha, float* d, int ldd) -> int {
+        TimedScope ts(m, cls, st, 3);
+        bnf4_gemm_desc g = {};
+        g.a = a; g.b = b; g.sfa = sfa; g.sfb = sfb; g.m = rows; g.n = n; g.k = a_k; g.alpha = alpha; g.d = d; g.ldd = ldd; g.epilogue = EPI_F32;
+        TRY(gemm_nvfp4_launch(g, st));
+        for (int mem = 0; mem < 2; ++mem) {
+            bnf4_gemm_desc e = g;
+            e.a = a + static_cast<size_t>(mem) * R * a_k / 2;
+            e.sfa = sfa + sf_offset(mem * R, 0, sf_k_atoms(a_k));
+            e.b = be; e.sfb = sfbe; e.m = R;
+            e.alpha = (mem == 0 ? sigma : -sigma) * alpha; e.beta = 1.0f;
+            e.c = d + static_cast<size_t>(mem) * R * ldd; e.ldc = ldd; e.d = d + static_cast<size_t>(mem) * R * ldd;
+            TRY(gemm_nvfp4_launch(e, st));
+        }
+        return BNF4_OK;
+    };
+    {   // embedding with the pair's dense noise: both members in one launch, the sign follows the member
+        TimedScope ts(m, KC_EMBED, st);
+        bnf4_rowquant_desc q = {};
+        q.rows = rows; q.cols_in = H; q.cols_out = H; q.rows_per_member = R; q.sigma = sigma;
+        q.tokens = m.tokens; q.token_stride = 1; q.row_mod = R; q.emb_w = m.emb; q.emb_noise = m.E_all + lay.emb; q.noise_pair_stride = 0;
+        q.out_codes = m.a_h; q.out_sf = m.sf_h;
+        TRY(rowquant_dispatch(FE_EMBED_DENSE, q, st));
+    }
+    TRY(noisy(KC_GEMM_WIN, m.a_h, m.sf_h, H, m.q_win, m.sfq_win, m.qe_win, m.sfe_win, H, m.s_h, m.y, H));
+    {
+        TimedScope ts(m, KC_POS_GELU_NORM, st);
+        bnf4_rowquant_desc q = {};
+        q.rows = rows; q.cols_in = H; q.cols_out = H; q.rows_per_member = R; q.sigma = sigma;
+        q.in_f32 = m.y; q.ld_in = H; q.inout_i8 = m.x_q; q.pos = m.pos; q.pos_mod = m.T;
+        q.pos_noise = m.pos_noise + static_cast<size_t>(pair) * m.T * H; q.noise_pair_stride = 0;
+        q.act_scale = m.cfg.act_scale; q.norm_scale = m.cfg.ln_scale; q.out_codes = m.a_h; q.out_sf = m.sf_h;
+        TRY(rowquant_dispatch(FE_POS_GELU_ABSMEAN, q, st));
+    }
+    for (int l = 0; l < L; ++l) {
+        // fused q | k | v | beta projection: out_scale folded into the scale bytes of W and of E alike (alpha = 1, noise alpha = +-sigma)
+        TRY(noisy(KC_GEMM_QKV, m.a_h, m.sf_h, H, m.q_qkv[l], m.sfq_qkv[l], m.qe_qkv[l], m.sfe_qkv[l], 3 * H + 1, 1.0f, m.qkv, FC));
+        {
+            TimedScope ts(m, KC_EFLA, st);
+            bnf4_efla_desc e = {};
+            e.state = nullptr; e.state_fp16 = 1; e.q = m.qkv; e.k = m.qkv + H; e.v = m.qkv + 2 * H; e.beta_raw = m.qkv + 3 * H;
+            e.ld_qkv = FC; e.ld_beta = FC; e.beta_bias_seq = m.bb_eff + static_cast<size_t>(l) * 2; e.seqs_per_bias = m.B;
+            e.hidden = H; e.heads = m.cfg.heads; e.seqs = 2LL * m.B; e.T = m.T; e.method = m.cfg.method; e.eps = m.cfg.eps;
+            e.out = m.y; e.ld_out = H;
+            TRY(efla_launch(e, st));
+        }
+        {
+            TimedScope ts(m, KC_ADD_NORM, st);
+            bnf4_rowquant_desc q = {};
+            q.rows = rows; q.cols_in = H; q.cols_out = H; q.rows_per_member = R; q.sigma = sigma;
+            q.inout_i8 = m.x_q; q.in_f32 = m.y; q.ld_in = H; q.add_scale = m.cfg.residual_scale; q.norm_scale = m.cfg.ln_scale;
+            q.out_codes = m.a_h; q.out_sf = m.sf_h;
+            TRY(rowquant_dispatch(FE_ADD_ABSMEAN, q, st));
+        }
+        {   // ff1: base product in fp32, the noise product through the GELU -> int8 epilogue with C = base, then NVFP4
+            TimedScope ts(m, KC_GEMM_FF1, st, 4);
+            bnf4_gemm_desc g = {};
+            g.a = m.a_h; g.b = m.q_ff1[l]; g.sfa = m.sf_h; g.sfb = m.sfq_ff1[l]; g.m = rows; g.n = F; g.k = H; g.alpha = m.s_h;
+            g.d = m.ff1_f; g.ldd = F; g.epilogue = EPI_F32;
+            TRY(gemm_nvfp4_launch(g, st));
+            for (int mem = 0; mem < 2; ++mem) {
+                bnf4_gemm_desc e = {};
+                e.a = m.a_h + static_cast<size_t>(mem) * R * H / 2; e.sfa = m.sf_h + sf_offset(mem * R, 0, sf_k_atoms(H));
+                e.b = m.qe_ff1[l]; e.sfb = m.sfe_ff1[l]; e.m = R; e.n = F; e.k = H;
+                e.alpha = (mem == 0 ? sigma : -sigma) * m.s_h; e.beta = 1.0f; e.c = m.ff1_f + static_cast<size_t>(mem) * R * F; e.ldc = F;
+                e.epilogue = EPI_GELU_I8; e.act_scale = m.cfg.mlp_act_scale; e.d_i8 = m.ff1_q + static_cast<size_t>(mem) * R * F; e.ld_i8 = F;
+                TRY(gemm_nvfp4_launch(e, st));
+            }
+            bnf4_rowquant_desc q = {};
+            q.rows = rows; q.cols_in = F; q.cols_out = F; q.in_i8 = m.ff1_q; q.ld_in = F; q.out_codes = m.a_f; q.out_sf = m.sf_f;
+            TRY(rowquant_dispatch(FE_INT8, q, st));
+        }
+        TRY(noisy(KC_GEMM_FF2, m.a_f, m.sf_f, F, m.q_ff2[l], m.sfq_ff2[l], m.qe_ff2[l], m.sfe_ff2[l], H, m.s_f, m.y, H));
+        {
+            TimedScope ts(m, KC_NORM_QUANT, st);
+            bnf4_rowquant_desc q = {};
+            q.rows = rows; q.cols_in = H; q.cols_out = H; q.rows_per_member = R; q.sigma = sigma;
+            q.inout_i8 = m.x_q; q.in_f32 = m.y; q.ld_in = H; q.add_scale = m.cfg.mlp_residual_scale; q.norm_scale = m.cfg.ln_scale;
+            q.out_codes = m.a_h; q.out_sf = m.sf_h;
+            TRY(rowquant_dispatch(FE_ADD_ABSMEAN, q, st));
+        }
+    }
+    TRY(noisy(KC_GEMM_HEAD, m.a_h, m.sf_h, H, m.q_head, m.sfq_head, m.qe_head, m.sfe_head, V, m.s_h, m.qkv, V));
+    TimedScope ts_ce(m, KC_CROSS_ENTROPY, st, 2);
+    return bnf4_cross_entropy_population(m.qkv, V, m.head_bias, m.hb_noise + static_cast<size_t>(pair) * V, sigma, m.targets, V, 2, R, m.ce_partial,
+                                         losses_out, st);
+}
+
 }  // namespace
 }  // namespace bnf4
 
@@ -454,7 +634,26 @@ int update_z(Model& m, const float* pair_weights, int shard, int nshards, float*
     }
     float* zb = z_ext != nullptr ? z_ext : m.Z_all;
     TimedScope ts(m, KC_UPDATE_Z, st, 4);
-    TRY(z_lowrank_launch(pair_weights, dtab, h.data(), static_cast<int>(h.size()), m.pairs_step, m.r, m.c_r, shard, nshards, st));
+    if (m.dense) {
+        // Z[i] = sum_p w_p noise(mix(seed_p, salt), i) per matrix: the reference's compute_z_sumsq (src/efla_lm_kernels.cu:1854-1890),
+        // rows of a sharded matrix by element range
+        const int L = m.L;
+        std::vector<uint64_t> salts = {kSaltEmb, kSaltWin};
+        for (int l = 0; l < L; ++l)
+            for (uint64_t sl : {kSaltWq, kSaltWk, kSaltWv, kSaltWbeta, kSaltFf1, kSaltFf2}) salts.push_back(mix_u64(static_cast<uint64_t>(l), sl));
+        salts.push_back(kSaltHead);
+        long long zo = 0;
+        for (size_t i = 0; i < h.size(); ++i) {
+            const long long n = static_cast<long long>(h[i].rows) * h[i].cols;
+            long long i0 = 0, cnt = n;
+            if (nshards > 1 && h[i].rows >= nshards && (h[i].rows % nshards) == 0) { cnt = n / nshards; i0 = shard * cnt; }
+            TRY(z_dense_launch(pair_weights, m.pair_seeds, salts[i], m.pairs_step, static_cast<int>(i0), static_cast<int>(cnt), m.cfg.use_clt, m.cfg.clt_k,
+                               zb + zo + i0, st));
+            zo += n;
+        }
+    } else {
+        TRY(z_lowrank_launch(pair_weights, dtab, h.data(), static_cast<int>(h.size()), m.pairs_step, m.r, m.c_r, shard, nshards, st));
+    }
     long long off = z_matrix_elems(m);
     for (const UpdVector& x : update_vectors(m)) {
         int i0 = 0, cnt = x.n;
@@ -522,7 +721,9 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     if (cfg->layers <= 0 || cfg->mlp_mult <= 0 || cfg->seq <= 0 || cfg->batch <= 0) return set_error(BNF4_ERR_INVALID, "model_create: bad shape");
     if (cfg->heads <= 0 || (cfg->hidden % cfg->heads) != 0 || ((cfg->hidden / cfg->heads) % 32) != 0)
         return set_error(BNF4_ERR_INVALID, "model_create: heads=%d needs head_dim %% 32 == 0", cfg->heads);
-    if (cfg->rank < 1 || cfg->rank > 4) return set_error(BNF4_ERR_INVALID, "model_create: rank=%d outside [1,4]", cfg->rank);
+    if (cfg->rank < 0 || cfg->rank > 4) return set_error(BNF4_ERR_INVALID, "model_create: rank=%d outside [0,4]", cfg->rank);
+    if (cfg->rank == 0 && ((cfg->batch * cfg->seq) % 128) != 0)
+        return set_error(BNF4_ERR_INVALID, "model_create: the dense (rank 0) mode needs batch * seq to be a multiple of 128");
     if (cfg->sigma_shift < 0 || cfg->sigma_shift > 30) return set_error(BNF4_ERR_INVALID, "model_create: sigma_shift");
     if (cfg->max_pairs <= 0) return set_error(BNF4_ERR_INVALID, "model_create: max_pairs");
     if (cfg->hidden > 4096) return set_error(BNF4_ERR_INVALID, "model_create: hidden above 4096");
@@ -531,7 +732,9 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     Model* m = new Model;
     m->cfg = *cfg;
     m->V = cfg->vocab; m->H = cfg->hidden; m->F = cfg->hidden * cfg->mlp_mult; m->L = cfg->layers; m->T = cfg->seq; m->B = cfg->batch;
-    m->R = m->B * m->T; m->FC = (3 * m->H + 1 + 31) & ~31; m->r = cfg->rank; m->hd = m->H / cfg->heads;
+    m->R = m->B * m->T; m->FC = (3 * m->H + 1 + 31) & ~31; m->hd = m->H / cfg->heads;
+    m->dense = cfg->rank == 0;
+    m->r = m->dense ? 1 : cfg->rank;  // the rank-r tables are sized for rank 1 (and left unused) in the dense mode
     m->s_h = 1.0f / std::sqrt(static_cast<float>(m->H));
     m->s_f = 1.0f / std::sqrt(static_cast<float>(m->F));
     m->sigma = 1.0f / static_cast<float>(1 << cfg->sigma_shift);
@@ -541,6 +744,7 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     const double row_bytes = m->H * (1.0 + 0.5625 + 4.0) + m->F * 0.5625 + m->FC * 4.0 + 20.0 * m->r;
     const int w_auto = static_cast<int>(std::min(256.0, std::max(2.0, 12e9 / (row_bytes * static_cast<double>(m->R)))));
     int W = cfg->wave_members > 0 ? cfg->wave_members : w_auto;
+    if (m->dense) W = 2;  // one pair per wave: its noise matrices exist once
     W = std::min(W, 2 * cfg->max_pairs);
     W = std::max(2, W & ~1);
     m->W = W;
@@ -582,6 +786,18 @@ int bnf4_model_create(const bnf4_model_cfg* cfg, void** handle) {
     }
     A_(qkv, Mr * m->FC); A_(y, Mr * H); A_(bb_eff, static_cast<size_t>(L) * W); A_(ce_partial, static_cast<size_t>(W) * 16); A_(losses, W);
     A_(t_a, Mr * 4 * r); A_(t_f, Mr * r);
+    if (m->dense) {
+        const DenseLayout lay = dense_layout(*m);
+        A_(E_all, lay.total);
+        A_(qe_win, hh / 2); A_(sfe_win, sf_bytes(H, H)); A_(qe_head, static_cast<size_t>(V) * H / 2); A_(sfe_head, sf_bytes(V, H));
+        m->qe_qkv.resize(L); m->sfe_qkv.resize(L); m->qe_ff1.resize(L); m->sfe_ff1.resize(L); m->qe_ff2.resize(L); m->sfe_ff2.resize(L);
+        for (int l = 0; l < L && !rc; ++l) {
+            A_(qe_qkv[l], static_cast<size_t>(m->FC) * H / 2); A_(sfe_qkv[l], sf_bytes(m->FC, H));
+            A_(qe_ff1[l], hf / 2); A_(sfe_ff1[l], sf_bytes(F, H)); A_(qe_ff2[l], hf / 2); A_(sfe_ff2[l], sf_bytes(H, F));
+        }
+        A_(noise_descs, 3 + 6 * static_cast<size_t>(L));
+        A_(ff1_f, Mr * F); A_(ff1_q, Mr * F);
+    }
     A_(Z, static_cast<size_t>(T) * H + V + L); A_(sumsq, 1); A_(inv_rms, 1);
     {
         size_t zn = static_cast<size_t>(V) + L + static_cast<size_t>(T) * H;
@@ -760,11 +976,15 @@ int bnf4_model_prepare_step_range(void* handle, uint64_t seed, uint64_t epoch, i
     m.pairs_step = pairs;
     m.eval_begin = eval_begin;
     m.eval_end = eval_begin + eval_count;
+    m.step_seed = seed;
+    m.step_epoch = epoch;
     TRY(bnf4_fill_pair_seeds(seed, epoch, pairs, m.pair_seeds, stream));
     TimedScope ts(m, KC_GEN_NOISE, S(stream), 3);
-    // rank-r factors of all pairs (the update reads them all) ...
-    gen_noise_kernel<<<dim3(m.gen_blocks_factors, pairs), 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, 0, 0, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
-    TRY(check_launch("gen_noise_kernel"));
+    // rank-r factors of all pairs (the update reads them all; the dense mode has none) ...
+    if (!m.dense) {
+        gen_noise_kernel<<<dim3(m.gen_blocks_factors, pairs), 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, 0, 0, m.pair_seeds, m.cfg.use_clt, m.cfg.clt_k);
+        TRY(check_launch("gen_noise_kernel"));
+    }
     // ... and the per-pair vectors only for the pairs this process evaluates
     if (eval_count > 0) {
         gen_noise_kernel<<<dim3(m.gen_blocks - m.gen_blocks_factors, eval_count), 256, 0, S(stream)>>>(m.gen_descs, m.gen_block_map, m.gen_blocks_factors,
@@ -786,6 +1006,10 @@ int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* l
     if (pair_count > 0 && (pair_begin < m.eval_begin || pair_begin + pair_count > m.eval_end))
         return set_error(BNF4_ERR_INVALID, "model_eval_pairs: pairs [%d,%d) outside the range [%d,%d) the step was prepared for", pair_begin,
                          pair_begin + pair_count, m.eval_begin, m.eval_end);
+    if (m.dense) {
+        for (int p = 0; p < pair_count; ++p) TRY(run_pair_dense(m, pair_begin + p, losses + 2 * static_cast<size_t>(p), S(stream)));
+        return BNF4_OK;
+    }
     const int wave_pairs = m.W / 2;
     for (int p = 0; p < pair_count; p += wave_pairs) {
         const int np = std::min(wave_pairs, pair_count - p);

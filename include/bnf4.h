@@ -401,7 +401,9 @@ typedef struct bnf4_model_cfg {
     int seq;          /* T */
     int batch;        /* B */
     int heads;        /* head_dim = H / heads; 1 reproduces the reference */
-    int rank;         /* rank of the per-member perturbation, 1..4 */
+    int rank;         /* rank of the per-member perturbation, 1..4; 0 = the reference driver's dense form: one materialised CLT
+                         noise matrix per weight matrix and pair, applied as a second GEMM with beta = 1 (one pair per wave,
+                         batch * seq a multiple of 128; a reference-exact mode, not a fast one) */
     int sigma_shift;  /* sigma = 2^-sigma_shift */
     int use_clt;
     int clt_k;

@@ -64,6 +64,55 @@ def test_member_losses_match_oracle(cfg_kw):
     assert np.abs(losses[0::2] - losses[1::2]).min() > 0
 
 
+@pytest.mark.parametrize("cfg_kw", [
+    dict(hidden=128, layers=2, seq=16, batch=8, heads=1, rank=0, max_pairs=3),
+    dict(hidden=256, layers=1, seq=32, batch=4, heads=4, rank=0, max_pairs=2),
+])
+def test_dense_perturbation_mode_matches_oracle(cfg_kw):
+    """rank = 0: the reference driver's own perturbation (a dense CLT noise matrix per weight matrix and pair, applied as a second
+    GEMM with beta = 1, src/train_efla_lm.cpp:2359-2367) in the batched layer-major driver. Member losses against the oracle's
+    dense forward, then one ES update against the oracle's dense noise sums (the reference's compute_z_sumsq form)."""
+    import torch
+    from bitnet_nvfp4_b200 import host
+    cfg, w, tok, tgt, model = make(cfg_kw)
+    seed, epoch, pairs = 1, 3, cfg.max_pairs
+    model.prepare_step(seed, epoch, pairs)
+    losses = model.eval_pairs(0, pairs).cpu().numpy()
+    assert host.device_error() == 0
+    om = orc.OracleModel(oracle_cfg(cfg), w)
+    for p in range(pairs):
+        ps = orc.mix(seed, orc.mix(epoch, p))
+        for s, anti in enumerate((1, -1)):
+            ref = om.forward(tok, tgt, ps, anti)
+            assert abs(losses[2 * p + s] - ref) <= 1e-4 * abs(ref), (p, anti, losses[2 * p + s], ref)
+            assert abs(om.forward(tok, tgt, ps, anti, token_major=True) - ref) <= 1e-6 * abs(ref)
+    # update: Z[i] = sum_p w_p noise(mix(seed_p, salt), i), RMS-EMA, gated round-clip -- bit for bit
+    V, H, L, F, T = cfg.vocab, cfg.hidden, cfg.layers, cfg.hidden * cfg.mlp_mult, cfg.seq
+    pw = orc.shape_pair_weights(np.random.default_rng(5).standard_normal(pairs).astype(np.float32))
+    model.update(torch.from_numpy(pw).cuda(), lr=0.8, thresh=0.008)
+    seeds = orc.fill_pair_seeds(seed, epoch, pairs)
+    thresh = float(np.float32(0.008) * np.sqrt(np.float32(pairs)))
+    ref_w = {k: v.copy() for k, v in w.items()}
+
+    def upd(name, sub, salt, n):
+        wv = ref_w[name] if sub is None else ref_w[name][sub]
+        Z, ss = orc.compute_z_sumsq(pw, seeds, salt, n)
+        inv, _ = orc.update_inv_rms(ss, 0.0, True, 0.95, 1e-3, n)
+        wf = wv.reshape(-1)
+        orc.update_shadow_ternary(wf, wf.astype(np.float32), Z, inv, 0.8, thresh)
+
+    upd("emb", None, SALT["emb"], V * H)
+    upd("win", None, SALT["win"], H * H)
+    for l in range(L):
+        for name, n in (("wq", H * H), ("wk", H * H), ("wv", H * H), ("wbeta", H), ("ff1", F * H), ("ff2", H * F)):
+            upd(name, l, orc.mix(l, SALT[name]), n)
+    upd("head", None, SALT["head"], V * H)
+    got = model.get_weights()
+    for name in ("emb", "win", "wq", "wk", "wv", "wbeta", "ff1", "ff2", "head"):
+        assert np.array_equal(got[name], ref_w[name]), name
+    assert sum(int((got[n] != w[n]).sum()) for n in ("emb", "win", "ff1")) > 0
+
+
 def test_config1_population_of_64():
     """BASELINE configuration 1 as written: pop = 64 (32 antithetic pairs) of the default model (4 layers, hidden 512, 8 heads of
     64, MLP 1024, batch 32, seq 128, Zipf tokens seed 123): every member's mean cross-entropy within 1e-4 relative of the
