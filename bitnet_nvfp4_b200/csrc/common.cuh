@@ -303,14 +303,11 @@ __device__ __forceinline__ void quant_block16(const int (&w)[4], float row_scale
 // through the L1: the 16 values of a block share one amax, i.e. one 128-byte row.
 // ---------------------------------------------------------------------------------------------
 constexpr int kQuantLutCodeBytes = 128 * 128;
-// A second form of the same table follows the first one, meant to be copied to shared memory: rows of
-// kQuantLutSignedStride bytes indexed by v + 128 (v = -127..127) that already carry the sign bit, then the 128 scale
-// bytes again. The stride of 260 bytes spreads the rows of neighbouring amax values over different banks.
-constexpr int kQuantLutSignedOffset = kQuantLutCodeBytes + 128;
-constexpr int kQuantLutSignedStride = 260;
-constexpr int kQuantLutSignedSfOffset = 128 * kQuantLutSignedStride;            // relative to the signed block
-constexpr int kQuantLutSignedBytes = kQuantLutSignedSfOffset + 128;             // 33408, a multiple of 16
-constexpr int kQuantLutBytes = kQuantLutSignedOffset + kQuantLutSignedBytes;
+// A compact per-block table follows the first one, meant to be copied to shared memory: for every amax one 8-byte
+// entry {fl(1 / decoded scale) as fp32 bits, scale byte}. With it the codes need no per-element look-up (e2m1x8_int below).
+constexpr int kQuantBlockTabOffset = kQuantLutCodeBytes + 128;
+constexpr int kQuantBlockTabBytes = 128 * 8;
+constexpr int kQuantLutBytes = kQuantBlockTabOffset + kQuantBlockTabBytes;
 // Device pointer to the table of the current device (allocated and filled on first use); nullptr + error on failure.
 const uint8_t* get_quant_lut();
 
@@ -334,6 +331,41 @@ __device__ __forceinline__ void quant_block16_lut(const int (&a)[16], const uint
     }
     code_lo = lo;
     code_hi = hi;
+}
+
+// e2m1 codes of eight integers held as floats (|n| <= 127) under the block's reciprocal scale r = fl(1 / scale), low nibble
+// first: the result of e2m1(n / scale) with IEEE division. n * r is formed with one rounding onto a grid of 2^-12 (fused
+// multiply-add with 1.5 * 2^11, then subtracted again): a quotient that lies exactly on a rounding boundary of e2m1 (a
+// multiple of 1/4) lands on it exactly, and any other quotient is at least 2^-6 away from every boundary (n is an integer,
+// the scale has four significant bits), so the conversion instruction rounds as the division would have.
+constexpr float kCodeSnap = 3072.0f;
+__device__ __forceinline__ uint32_t e2m1x8_int(const float* n, float r) {
+    float2 q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        q[i] = __fadd2_rn(__ffma2_rn(make_float2(n[2 * i], n[2 * i + 1]), make_float2(r, r), make_float2(kCodeSnap, kCodeSnap)),
+                          make_float2(-kCodeSnap, -kCodeSnap));
+    uint32_t out;
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+        : "=r"(out)
+        : "f"(q[0].x), "f"(q[0].y), "f"(q[1].x), "f"(q[1].y), "f"(q[2].x), "f"(q[2].y), "f"(q[3].x), "f"(q[3].y));
+    return out;
+}
+// The same for values still biased by kRoundBias (bit pattern = kRoundBiasBits + n).
+__device__ __forceinline__ uint32_t e2m1x8_biased(const float* tb, float r) {
+    float n[8];
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+        const float2 u = __fadd2_rn(make_float2(tb[i], tb[i + 1]), make_float2(-kRoundBias, -kRoundBias));
+        n[i] = u.x;
+        n[i + 1] = u.y;
+    }
+    return e2m1x8_int(n, r);
 }
 
 // Host twin of ue4m3_encode (used to build the table).

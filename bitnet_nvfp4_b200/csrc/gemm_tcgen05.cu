@@ -157,11 +157,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
-    return v;
-}
 // prmt.b32 in its default mode: a selector nibble with bit 3 set replicates the sign of the selected byte
 __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
@@ -355,10 +350,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         bool ok = true;
         int it = 0;
         if constexpr (EPI == EPI_GELU_FP4) {
-            // The block quantiser's table (signed form, 33 KB) lives in the staging area the fp32 epilogue would use.
-            const int4* src = reinterpret_cast<const int4*>(args.lut + kQuantLutSignedOffset);
-            int4* dst = reinterpret_cast<int4*>(smem_gen + kSmemEpi);
-            for (int i = ew * 32 + lane; i < kQuantLutSignedBytes / 16; i += kEpiWarps * 32) dst[i] = __ldg(src + i);
+            // The block quantiser's table ({1 / scale, scale byte} per amax, 1 KB) lives in the staging area the fp32 epilogue would use.
+            if (ew * 32 + lane < 128)
+                reinterpret_cast<uint2*>(smem_gen + kSmemEpi)[ew * 32 + lane] =
+                    __ldg(reinterpret_cast<const uint2*>(args.lut + kQuantBlockTabOffset) + ew * 32 + lane);
             asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
         }
         // Perturbation context of one tile: this thread's row (projections t, sign, pair) and, when all rows of the tile
@@ -654,10 +649,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 // boundary is flagged and redone with the tanhf form (about one group in a thousand). tb holds the rounded
                 // values still biased by 1.5 * 2^23: the low byte of the bit pattern is the int8.
                 const bool lower_clamp = p.act_scale > 700.0f;
-                const uint32_t lut_s = smem_base + kSmemEpi;
-                const uint32_t kBias = static_cast<uint32_t>(kRoundBiasBits);
-                const uint32_t row_c = lut_s + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
-                const uint32_t sf_c = lut_s + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
+                // entry address from the bit pattern of (amax + kRoundBias): (bits - kRoundBiasBits) * 8, folded into one constant
+                const uint32_t tab_c = smem_base + kSmemEpi - (static_cast<uint32_t>(kRoundBiasBits) << 3);
                 int w[8];
                 uint32_t sfv[2] = {0u, 0u}, codes[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
@@ -695,19 +688,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         w[4 * blk + g] = static_cast<int>(__byte_perm(__byte_perm(__float_as_uint(tb[4 * g]), __float_as_uint(tb[4 * g + 1]), 0x0040),
                                                                       __byte_perm(__float_as_uint(tb[4 * g + 2]), __float_as_uint(tb[4 * g + 3]), 0x0040), 0x5410));
                     if constexpr (EPI == EPI_GELU_FP4) {
-                        // code(v) = table[amax][v + 128] and scale byte = table_sf[amax], addressed straight from the biased bit
-                        // patterns: bits(t) - kRoundBiasBits is the integer.
-                        const uint32_t ab = __float_as_uint(am + kRoundBias);
-                        sfv[blk] = lds_u8(ab + sf_c);
-                        const uint32_t rowbase = ab * static_cast<uint32_t>(kQuantLutSignedStride) + row_c;
-                        uint32_t cl[8], ch[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            cl[e] = lds_u8(__float_as_uint(tb[e]) + rowbase) << (4 * e);
-                            ch[e] = lds_u8(__float_as_uint(tb[8 + e]) + rowbase) << (4 * e);
-                        }
-                        codes[2 * blk] = ((cl[0] | cl[1]) | (cl[2] | cl[3])) | ((cl[4] | cl[5]) | (cl[6] | cl[7]));
-                        codes[2 * blk + 1] = ((ch[0] | ch[1]) | (ch[2] | ch[3])) | ((ch[4] | ch[5]) | (ch[6] | ch[7]));
+                        // {1 / scale, scale byte} of the block from the table; the codes from the conversion instruction
+                        // applied to n / scale (e2m1x8_int)
+                        uint32_t rbits, sbyte;
+                        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(rbits), "=r"(sbyte) : "r"((__float_as_uint(am + kRoundBias) << 3) + tab_c));
+                        sfv[blk] = sbyte;
+                        codes[2 * blk] = e2m1x8_biased(tb, __uint_as_float(rbits));
+                        codes[2 * blk + 1] = e2m1x8_biased(tb + 8, __uint_as_float(rbits));
                     }
                 }
                 if (row_ok && p.d_i8 != nullptr) {

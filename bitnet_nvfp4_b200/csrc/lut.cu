@@ -1,5 +1,6 @@
 // Host-built lookup table of the NVFP4 block quantiser for int8 inputs (see quant_block16_lut in common.cuh).
 
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -27,12 +28,12 @@ const uint8_t* get_quant_lut() {
         if (sf == 0.0f) { sq = 0x38u; sf = 1.0f; }
         h[kQuantLutCodeBytes + amax] = static_cast<uint8_t>(sq);
         for (int a = 0; a < 128; ++a) h[amax * 128 + a] = static_cast<uint8_t>(e2m1_encode(static_cast<float>(a) / sf) & 7u);
-        uint8_t* srow = h.data() + kQuantLutSignedOffset + amax * kQuantLutSignedStride;
-        for (int v = -128; v < 128; ++v) {
-            const int mag = v < 0 ? (v == -128 ? 127 : -v) : v;
-            srow[v + 128] = static_cast<uint8_t>(h[amax * 128 + mag] | (v < 0 ? 8u : 0u));
-        }
-        h[kQuantLutSignedOffset + kQuantLutSignedSfOffset + amax] = static_cast<uint8_t>(sq);
+        const float rcp = 1.0f / sf;
+        uint32_t rcp_bits;
+        memcpy(&rcp_bits, &rcp, 4);
+        uint8_t* entry = h.data() + kQuantBlockTabOffset + amax * 8;
+        memcpy(entry, &rcp_bits, 4);
+        memcpy(entry + 4, &sq, 4);
     }
     uint8_t* d = nullptr;
     if (check_cuda(cudaMalloc(&d, kQuantLutBytes), "cudaMalloc(quant lut)")) return nullptr;

@@ -276,30 +276,25 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
 // fp32 ("v"), or biased by 1.5 * 2^23 ("t = v + M", whose low byte is the int8), so that
 //   * bytes become floats with one byte-permute and one subtraction, and floats become bytes with a byte-permute;
 //   * rint() is an addition of M (round-to-nearest-even, like cvt.rni), clip8(rint(x)) = rint(clamp(x, +-127));
-//   * the block maximum is a float max, and the code / scale-byte tables are addressed by bit patterns;
-// and the table lives in shared memory, loaded once by a persistent CTA that then walks rows with a grid stride.
+//   * the block maximum is a float max; its bit pattern addresses a 1 KB shared-memory table of {1 / scale, scale byte},
+//     and the sixteen codes come from the conversion instruction applied to n * (1 / scale) (e2m1x8_int);
+// the table is loaded once by a persistent CTA that then walks rows with a grid stride.
 // Requirements (checked by the host; otherwise rowquant_kernel runs): 16-byte aligned rows, cols_in == cols_out <= 2048.
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t lds_u8(uint32_t saddr) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(saddr));
+__device__ __forceinline__ uint2 lds_u64(uint32_t saddr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr));
     return v;
 }
 // Element ownership as in rowquant_kernel: lane l owns the 16-element scale blocks l, l + 32, ... (NB of them).
 // NV = upper bound of p.nvec this instance handles (4 or kMaxTVec): the projection loops carry no tests beyond it.
 template <int FE, int NB, int NV>
 __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowquant_fast_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
-    __shared__ __align__(16) uint8_t lut_s[kQuantLutSignedBytes];
-    {
-        const int4* src = reinterpret_cast<const int4*>(lut + kQuantLutSignedOffset);
-        int4* dst = reinterpret_cast<int4*>(lut_s);
-        for (int i = threadIdx.x; i < kQuantLutSignedBytes / 16; i += blockDim.x) dst[i] = __ldg(src + i);
-    }
+    __shared__ __align__(16) uint2 tab_s[128];  // per amax: {bits of fl(1 / scale), scale byte}
+    if (threadIdx.x < 128) tab_s[threadIdx.x] = __ldg(reinterpret_cast<const uint2*>(lut + kQuantBlockTabOffset) + threadIdx.x);
     __syncthreads();
-    const uint32_t lut_a = static_cast<uint32_t>(__cvta_generic_to_shared(lut_s));
-    const uint32_t kBias = static_cast<uint32_t>(kRoundBiasBits);
-    const uint32_t row_c = lut_a + 128u - kBias - kBias * static_cast<uint32_t>(kQuantLutSignedStride);
-    const uint32_t sf_c = lut_a + static_cast<uint32_t>(kQuantLutSignedSfOffset) - kBias;
+    // entry address from the bit pattern of (amax + kRoundBias): (bits - kRoundBiasBits) * 8, folded into one constant
+    const uint32_t tab_c = static_cast<uint32_t>(__cvta_generic_to_shared(tab_s)) - (static_cast<uint32_t>(kRoundBiasBits) << 3);
     const float M = kRoundBias;
     constexpr bool kNorm = (FE == FE_ADD_ABSMEAN || FE == FE_POS_GELU_ABSMEAN || FE == FE_ABSMEAN);
 
@@ -523,24 +518,22 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 if (p.out_q != nullptr)
                     *reinterpret_cast<int4*>(p.out_q + static_cast<size_t>(row) * p.ld_q + k0) =
                         make_int4(static_cast<int>(w[0]), static_cast<int>(w[1]), static_cast<int>(w[2]), static_cast<int>(w[3]));
-                const uint32_t ab = __float_as_uint(am + M);
-                sfb = lds_u8(ab + sf_c);
-                const uint32_t rowbase = ab * static_cast<uint32_t>(kQuantLutSignedStride) + row_c;
-                uint32_t lo = 0, hi = 0;
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    lo |= lds_u8(__float_as_uint(tq[e]) + rowbase) << (4 * e);
-                    hi |= lds_u8(__float_as_uint(tq[8 + e]) + rowbase) << (4 * e);
+                const uint2 ent = lds_u64((__float_as_uint(am + M) << 3) + tab_c);
+                sfb = ent.y;
+                const float rs = __uint_as_float(ent.x);
+                uint32_t lo, hi;
+                if constexpr (kNorm) {
+                    lo = e2m1x8_biased(tq, rs);
+                    hi = e2m1x8_biased(tq + 8, rs);
+                } else {  // the values are integers already
+                    lo = e2m1x8_int(vf[i], rs);
+                    hi = e2m1x8_int(vf[i] + 8, rs);
                 }
                 *reinterpret_cast<uint2*>(p.out_codes + (static_cast<size_t>(row) * p.cols_out + k0) / 2) = make_uint2(lo, hi);
             }
-            // four neighbouring lanes hold the four scale bytes of one 32-bit word of the atom layout
-            const int base_lane = lane & ~3;
-            uint32_t word = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) word |= (__shfl_sync(0xffffffffu, sfb, base_lane + j) & 0xffu) << (8 * j);
-            if (active && (lane & 3) == 0)
-                *reinterpret_cast<uint32_t*>(p.out_sf + sf_offset(static_cast<int>(row), kb, k_atoms)) = word;
+            // one byte per lane: four neighbouring lanes fill one 32-bit word of the atom layout, the warp touches the same
+            // eight sectors a word store would
+            if (active) p.out_sf[sf_offset(static_cast<int>(row), kb, k_atoms)] = static_cast<uint8_t>(sfb);
 
             if (p.nvec > 0 && active) {
                 const int8_t* tv = p.tvec + static_cast<size_t>(pair) * p.tvec_pair_stride + k0;

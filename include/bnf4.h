@@ -326,8 +326,16 @@ int bnf4_init_shadow_from_weights(const int8_t* w, float* shadow, int n, void* s
 int bnf4_fill_pair_seeds(uint64_t base_seed, uint64_t epoch, int pairs, uint64_t* out, void* stream);
 /* reference: compute_z_sumsq src/efla_lm_kernels.cu:2042-2059 (kernel :1854-1890).
  * Z[i] = sum_p w_p * noise(mix(seed_p, salt), i) (p ascending, fused multiply-add); sum(Z^2) is ADDED to *sumsq.
- * The sum of squares is reduced in a fixed order (per-256 tree, then block partials in double). Uses a
- * library-owned scratch buffer for the block partials (allocated with cudaMalloc on first use and grown on demand). */
+ * The sum of squares is reduced in a fixed order (per-256 tree, then block partials in double).
+ * Scratch: the block partials go to ONE library-owned buffer per device, shared by this function,
+ * bnf4_compute_z_sumsq_lowrank and bnf4_sumsq on every stream and host thread (256 KiB allocated with cudaMalloc on the
+ * first call, enough for n <= 16,777,216). Consequences for the caller:
+ *   - two of these calls that may overlap in time (different streams, or threads without ordering) race on the
+ *     partials: order them, as for bnf4_compute_z_sumsq_static;
+ *   - a call with a larger n than any before grows the buffer: cudaDeviceSynchronize, cudaFree, cudaMalloc in the
+ *     middle of the stream. That is not allowed during stream capture and waits for every stream of the device; make
+ *     one call with the largest n during set-up (bnf4_sumsq on any buffer of that size will do), or use the _static
+ *     entry point, which never allocates. The batched driver (bnf4_model_*) keeps its own buffers and never comes here. */
 int bnf4_compute_z_sumsq(const float* pair_weights, const uint64_t* pair_seeds, uint64_t salt, int pairs, int n,
                          int use_clt, int clt_k, float* Z, float* sumsq, void* stream);
 /* No counterpart in the reference. Same arguments, arithmetic and result as bnf4_compute_z_sumsq, for callers that

@@ -43,6 +43,58 @@ def test_quantize_a_bit_exact(H, rows, k):
     assert same(sf, rs)
 
 
+def every_block_maximum_and_value():
+    """16-element blocks covering every (block maximum, value) combination: the first element is +-amax, the other fifteen
+    walk through all values of magnitude <= amax (exact ties of value / scale and negative values that quantise to zero
+    included)."""
+    blocks = []
+    for amax in range(0, 128):
+        vals = np.arange(-amax, amax + 1, dtype=np.int64)
+        for lead in (amax, -amax):
+            for o in range(0, len(vals), 15):
+                chunk = vals[o:o + 15]
+                blk = np.zeros(16, dtype=np.int64)
+                blk[0] = lead
+                blk[1:1 + len(chunk)] = chunk
+                blocks.append(blk)
+    return blocks
+
+
+def test_quantize_a_every_block_maximum_and_value(H):
+    blocks = every_block_maximum_and_value()
+    k = 512
+    while len(blocks) % (k // 16):
+        blocks.append(np.zeros(16, dtype=np.int64))
+    x = np.stack(blocks).reshape(-1, k).astype(np.int8)
+    codes, sf = H.nvfp4_quantize_a(dev(x))
+    rc, rs = orc.quantize_rowmajor(x)
+    assert same(codes, rc)
+    assert same(sf, rs)
+
+
+def test_absmean_rows_every_block_maximum_and_value(H):
+    """The same blocks through the float-domain quantiser of int8 rows (codes from the conversion instruction applied to
+    value x 1 / scale): one block per otherwise empty row of 2048 columns, so that the abs-mean clamps to 1 and the values pass
+    the normalisation unchanged; the block sits at a different position in every row."""
+    import torch
+    blocks = every_block_maximum_and_value()
+    hid = 2048
+    rows = len(blocks)
+    x = np.zeros((rows, hid), dtype=np.int8)
+    for i, blk in enumerate(blocks):
+        pos = (i * 7) % (hid // 16)
+        x[i, 16 * pos:16 * pos + 16] = blk
+    assert np.abs(x.astype(np.int32)).sum(axis=1).max() < hid
+    yq = torch.zeros((rows, hid), dtype=torch.int8, device="cuda")
+    codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
+    sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
+    H.rowquant(H.FE_ABSMEAN, rows=rows, cols_in=hid, cols_out=hid, in_i8=dev(x), ld_in=hid, norm_scale=1.0,
+               out_q=yq, ld_q=hid, out_codes=codes, out_sf=sf)
+    rq, rc, rs = orc.absmean_norm_q(x.copy(), None, 0.0, 1.0)
+    assert same(yq, x)
+    assert same(yq, rq) and same(codes, rc) and same(sf, rs)
+
+
 def test_quantize_b_ternary_and_kin_smaller(H):
     rng = np.random.default_rng(5)
     w = rng.integers(-1, 2, (1568, 512)).astype(np.int8)
