@@ -192,6 +192,14 @@ struct KernelArgs {
     int n_tiles;  // tiles along N; blockIdx.x = m_tile * n_tiles + n_tile (N fastest: CTAs that share A rows run together)
 };
 
+// One lane of a converged warp (the same one every time in practice). The role loops below run in all 32 lanes with
+// warp-uniform control flow and values, and only the issuing instructions sit under this predicate: addresses, descriptors and
+// counters then qualify for the uniform datapath instead of being moved there instruction by instruction from a divergent lane.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -244,9 +252,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
 
     if (warp == 0) {
         // ------------------------------ producer ------------------------------
-        if (lane == 0) {
-            // like the MMA issuer, this thread shares an issue port with busy epilogue warps: running indices instead of
-            // divisions, addresses advanced by constants
+        {
+            // running indices instead of divisions, addresses advanced by constants
             int kc = 0;  // k-block counter across tiles
             int s = 0;
             uint32_t empty_parity = 1;  // parity of the phase that precedes the first completion: the first pass does not wait
@@ -264,17 +271,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 int atoms_left = args.k_atoms;
                 for (int ks = 0; ks < num_ks; ++ks, ++kc) {
                     if (kc >= kStages) {
-                        ok = mbar_wait(bar_empty + 8 * s, empty_parity, 1);
+                        ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * s, empty_parity, 1));
                         if (!ok) break;
                     }
                     const uint32_t sf_bytes_stage = static_cast<uint32_t>(min(4, atoms_left)) * 512u;
                     atoms_left -= 4;
                     const uint32_t bar = bar_full + 8 * s;
-                    mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
-                    tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, my, bar);
-                    tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, ny, bar);
-                    bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_src, sf_bytes_stage, bar);
-                    bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_src, sf_bytes_stage, bar);
+                    if (elect_one()) {
+                        mbar_expect_tx(bar, kStageABytes + kStageBBytes + 2 * sf_bytes_stage);
+                        tma_load_2d(smem_base + kSmemA + s * kStageABytes, &map_a, ks * 128, my, bar);
+                        tma_load_2d(smem_base + kSmemB + s * kStageBBytes, &map_b, ks * 128, ny, bar);
+                        bulk_load_1d(smem_base + kSmemSfa + s * kStageSfBytes, sfa_src, sf_bytes_stage, bar);
+                        bulk_load_1d(smem_base + kSmemSfb + s * kStageSfBytes, sfb_src, sf_bytes_stage, bar);
+                    }
+                    __syncwarp();
                     sfa_src += 2048;
                     sfb_src += 2048;
                     if (++s == kStages) { s = 0; empty_parity ^= 1u; }
@@ -283,10 +293,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            // This single thread's issue rate bounds the mainloop (it shares an issue port with four busy epilogue warps), so
-            // the loop is kept lean: descriptors are a stage-0 constant plus a stage / K-step increment of the 14-bit
-            // start-address field (bytes >> 4), and the four K-steps of a full stage are unrolled.
+        {
+            // The issue rate of this role bounds the mainloop (it shares an issue port with four busy epilogue warps), so the loop
+            // is kept lean: descriptors are a stage-0 constant plus a stage / K-step increment of the 14-bit start-address field
+            // (bytes >> 4), and the four K-steps of a full stage are unrolled.
             const uint64_t adesc0 = smem_desc(smem_base + kSmemA, 16, 1024, kLayoutSw128);
             const uint64_t bdesc0 = smem_desc(smem_base + kSmemB, 16, 1024, kLayoutSw128);
             const uint64_t sfadesc0 = smem_desc(smem_base + kSmemSfa, 0, 128, kLayoutNone);
@@ -298,13 +308,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
                 const int buf = it & 1;
                 if (it >= 2) {  // the epilogue must have drained this accumulator (tile it-2)
-                    ok = mbar_wait(bar_acc_empty + 8 * buf, ((it >> 1) - 1) & 1, 4);
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_acc_empty + 8 * buf, ((it >> 1) - 1) & 1, 4));
                     if (!ok) break;
                     tc_fence_after();
                 }
                 const uint32_t acc_col = tmem_base + kAccCol + buf * BN;
                 for (int ks = 0; ks < num_ks; ++ks, ++kc) {
-                    ok = mbar_wait(bar_full + 8 * s, full_parity, 2);
+                    ok = __all_sync(0xffffffffu, mbar_wait(bar_full + 8 * s, full_parity, 2));
                     if (!ok) break;
                     tc_fence_after();
                     const int nk = min(4, (p.k - ks * BK) / UMMA_K);
@@ -314,30 +324,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     const uint64_t sfb_d = sfbdesc0 + static_cast<uint64_t>(s * (kStageSfBytes >> 4));
                     const uint64_t a_d = adesc0 + static_cast<uint64_t>(s * (kStageABytes >> 4));
                     const uint64_t b_d = bdesc0 + static_cast<uint64_t>(s * (kStageBBytes >> 4));
-                    if (nk == 4) {
+                    if (elect_one()) {
+                        if (nk == 4) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
-                            tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
-                        }
-                        tc_mma_nvf4(acc_col, a_d, b_d, kIdesc, t_sfa, t_sfb, ks > 0 ? 1u : 0u);
+                            for (int j = 0; j < 4; ++j) {
+                                tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
+                                tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            }
+                            tc_mma_nvf4(acc_col, a_d, b_d, kIdesc, t_sfa, t_sfb, ks > 0 ? 1u : 0u);
 #pragma unroll
-                        for (int j = 1; j < 4; ++j)
-                            tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
-                                        t_sfa + 4 * j, t_sfb + 4 * j, 1u);
-                    } else {
-                        for (int j = 0; j < nk; ++j) {
-                            tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
-                            tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            for (int j = 1; j < 4; ++j)
+                                tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
+                                            t_sfa + 4 * j, t_sfb + 4 * j, 1u);
+                        } else {
+                            for (int j = 0; j < nk; ++j) {
+                                tc_cp_sf(t_sfa + 4 * j, sfa_d + static_cast<uint64_t>(j * (512 >> 4)));
+                                tc_cp_sf(t_sfb + 4 * j, sfb_d + static_cast<uint64_t>(j * (512 >> 4)));
+                            }
+                            for (int j = 0; j < nk; ++j)
+                                tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
+                                            t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
                         }
-                        for (int j = 0; j < nk; ++j)
-                            tc_mma_nvf4(acc_col, a_d + static_cast<uint64_t>(j * (32 >> 4)), b_d + static_cast<uint64_t>(j * (32 >> 4)), kIdesc,
-                                        t_sfa + 4 * j, t_sfb + 4 * j, (ks > 0 || j > 0) ? 1u : 0u);
+                        tc_commit(bar_empty + 8 * s);  // frees this smem stage once the MMAs above have read it
+                        if (ks == num_ks - 1) tc_commit(bar_acc_full + 8 * buf);  // accumulator of this tile complete
                     }
-                    tc_commit(bar_empty + 8 * s);  // frees this smem stage once the MMAs above have read it
+                    __syncwarp();
                     if (++s == kStages) { s = 0; full_parity ^= 1u; }
                 }
-                if (ok) tc_commit(bar_acc_full + 8 * buf);  // accumulator of this tile complete
             }
         }
     } else {
