@@ -362,6 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         uint8_t* epi_gen = smem_gen + kSmemEpi + ew * kEpiBufBytes;
         bool ok = true;
         int it = 0;
+        int stage_half = 0;  // EPI_F16: which half of the staging buffer the next store uses
         if constexpr (EPI == EPI_GELU_FP4) {
             // The block quantiser's table ({1 / scale, scale byte} per amax, 1 KB) lives in the staging area the fp32 epilogue would use.
             if (ew * 32 + lane < 128)
@@ -447,10 +448,34 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
             }
         };
+        // The common case (rank 1, tiles inside one member) with as few instructions as possible: this phase sits on the serial
+        // path of every tile.
+        const bool fast_ctx = p.rank == 1 && tile_uniform_member;
+        const int* t_row = p.rank > 0 ? p.lora_t + static_cast<size_t>(row_in_tile) * p.t_stride : nullptr;
+        auto fetch_fast = [&](const TileIdx& t, bool valid, LoraCtx& cx) {
+            cx.pair = 0;
+            cx.lsign = 0.0f;
+            cx.tr[0] = 0;
+            cx.aval[0] = 0;
+            cx.a_staged = true;
+            if (!valid) return;
+            const int m0_ = t.m_tile * BM, col0_ = t.n_tile * BN + c * 32;
+            while (m0_ >= trk_end) { ++trk_member; trk_end += p.rows_per_member; }
+            cx.pair = trk_member >> 1;
+            if (m0_ + row_in_tile < p.m && col0_ < p.n) {
+                const int g = p.group_cols > 0 ? static_cast<int>(__umulhi(static_cast<uint32_t>(col0_), group_magic)) : 0;
+                cx.tr[0] = __ldg(t_row + static_cast<size_t>(m0_) * p.t_stride + g);
+                cx.lsign = (trk_member & 1) ? -p.lora_scale : p.lora_scale;
+            }
+            if (col0_ + lane < p.n) cx.aval[0] = __ldg(p.lora_A + static_cast<size_t>(cx.pair) * p.lora_A_pair_stride + col0_ + lane);
+        };
         TileIdx cur_t{static_cast<int>(blockIdx.x / static_cast<unsigned>(args.n_tiles)), static_cast<int>(blockIdx.x % static_cast<unsigned>(args.n_tiles))};
         TileIdx nxt_t = cur_t;
         LoraCtx nxt;
-        fetch_ctx(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
+        nxt.tr[1] = nxt.tr[2] = nxt.tr[3] = 0;
+        nxt.aval[1] = nxt.aval[2] = nxt.aval[3] = 0;
+        if (fast_ctx) fetch_fast(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
+        else fetch_ctx(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
             cur_t = nxt_t;
@@ -463,10 +488,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
 
             const int pair = nxt.pair;
             const float lsign = nxt.lsign;
-            const float tr[4] = {static_cast<float>(nxt.tr[0]), static_cast<float>(nxt.tr[1]), static_cast<float>(nxt.tr[2]), static_cast<float>(nxt.tr[3])};
+            float tr[4] = {static_cast<float>(nxt.tr[0]), 0.0f, 0.0f, 0.0f};
             const bool a_staged = nxt.a_staged;
             float* loraA_sh = reinterpret_cast<float*>(smem_gen + kSmemLora) + ew * 4 * 32;  // this warp's [4][32]
-            if (p.rank > 0) {
+            if (fast_ctx) {
+                __syncwarp();  // the previous tile's reads are done
+                loraA_sh[lane] = static_cast<float>(nxt.aval[0]);
+                __syncwarp();
+                fetch_fast(nxt_t, tile + static_cast<int>(gridDim.x) < total_tiles, nxt);
+            } else if (p.rank > 0) {
+                tr[1] = static_cast<float>(nxt.tr[1]);
+                tr[2] = static_cast<float>(nxt.tr[2]);
+                tr[3] = static_cast<float>(nxt.tr[3]);
                 __syncwarp();  // the previous tile's reads are done
                 if (a_staged) {
 #pragma unroll
@@ -591,12 +624,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
             } else if constexpr (EPI == EPI_F16) {
                 if (col0 < p.n_f16) {
-                    // 32 rows x 32 halves staged as 64-byte rows, then one TMA store (clips at M; n_f16 is a multiple of 32)
-                    if (it > 0) {
-                        if (lane == 0) bulk_wait_read<0>();
-                        __syncwarp();
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(epi_gen + lane * 64);
+                    // 32 rows x 32 halves staged as 64-byte rows, then one TMA store (clips at M; n_f16 is a multiple of 32).
+                    // Two staging halves alternate, so only the store before the previous one has to have left shared memory.
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+                    uint4* dst = reinterpret_cast<uint4*>(epi_gen + stage_half * 2048 + lane * 64);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int jj = j;
@@ -608,9 +640,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&map_d, epi_buf, col0, m0 + q * 32);
+                        tma_store_2d(&map_d, epi_buf + stage_half * 2048, col0, m0 + q * 32);
                         bulk_commit();
                     }
+                    stage_half ^= 1;
                 } else if (row_ok) {
                     float* drow = p.d + static_cast<size_t>(row) * p.ldd + (col0 - p.n_f16);
 #pragma unroll
