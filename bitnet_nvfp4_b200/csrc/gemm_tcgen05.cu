@@ -163,6 +163,20 @@ __device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t se
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
+// Four bytes of the int8 residual stream updated with four accumulators: clip8(old + rint(v * add_scale)). rint is the low 16
+// bits of the biased float (the product is clamped first so that the field cannot wrap), added to the sign-extended old
+// bytes and clipped with packed 16-bit integer operations, two elements per instruction.
+__device__ __forceinline__ uint32_t resid_add_word(uint32_t old4, float v0, float v1, float v2, float v3, float add_scale) {
+    const uint32_t t0 = __float_as_uint(fminf(fmaxf(__fmul_rn(v0, add_scale), -512.0f), 512.0f) + kRoundBias);
+    const uint32_t t1 = __float_as_uint(fminf(fmaxf(__fmul_rn(v1, add_scale), -512.0f), 512.0f) + kRoundBias);
+    const uint32_t t2 = __float_as_uint(fminf(fmaxf(__fmul_rn(v2, add_scale), -512.0f), 512.0f) + kRoundBias);
+    const uint32_t t3 = __float_as_uint(fminf(fmaxf(__fmul_rn(v3, add_scale), -512.0f), 512.0f) + kRoundBias);
+    const uint32_t r01 = __byte_perm(t0, t1, 0x5410), r23 = __byte_perm(t2, t3, 0x5410);
+    const uint32_t o01 = prmt_b32(old4, 0u, 0x9180u), o23 = prmt_b32(old4, 0u, 0xB3A2u);
+    const uint32_t s01 = __vmins2(__viaddmax_s16x2(r01, o01, 0xff81ff81u), 0x007f007fu);
+    const uint32_t s23 = __vmins2(__viaddmax_s16x2(r23, o23, 0xff81ff81u), 0x007f007fu);
+    return __byte_perm(s01, s23, 0x6420);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading byte
@@ -471,6 +485,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         };
         TileIdx cur_t{static_cast<int>(blockIdx.x / static_cast<unsigned>(args.n_tiles)), static_cast<int>(blockIdx.x % static_cast<unsigned>(args.n_tiles))};
         TileIdx nxt_t = cur_t;
+        // EPI_ADD_I8 through TMA: this warp's 32 x 32-byte box of the residual stream is loaded one tile ahead into one of
+        // three 1 KB buffers (each with its own mbarrier), updated in place and stored from there. A lane-per-row access to
+        // global memory touches 32 lines per instruction and kept the load/store unit busy for a third of the tile period.
+        const bool res_tma = EPI == EPI_ADD_I8 && args.use_tma_store != 0;
+        const uint32_t rbar = epi_buf + 3072;
+        int rb_cur = 0, rb_last = 2;
+        uint32_t r_par = 0;  // bit b: parity of the phase to wait for on buffer b
+        bool have_cur = false, have_nxt = false;
+        auto issue_res_load = [&](const TileIdx& t, bool valid) {
+            const int col0_ = t.n_tile * BN + c * 32;
+            have_nxt = valid && col0_ < p.n;
+            if (!have_nxt) return;
+            rb_last = rb_last == 2 ? 0 : rb_last + 1;
+            if (lane == 0) {
+                bulk_wait_read<1>();  // the store that last read this buffer (three tiles back) has left shared memory
+                mbar_expect_tx(rbar + 8 * rb_last, 1024);
+                tma_load_2d(epi_buf + rb_last * 1024, &map_d, col0_, t.m_tile * BM + q * 32, rbar + 8 * rb_last);
+            }
+        };
+        if constexpr (EPI == EPI_ADD_I8) {
+            if (res_tma) {
+                if (lane == 0) {
+                    mbar_init(rbar, 1);
+                    mbar_init(rbar + 8, 1);
+                    mbar_init(rbar + 16, 1);
+                    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                    fence_async_smem();
+                }
+                __syncwarp();
+                issue_res_load(cur_t, static_cast<int>(blockIdx.x) < total_tiles);
+            }
+        }
         LoraCtx nxt;
         nxt.tr[1] = nxt.tr[2] = nxt.tr[3] = 0;
         nxt.aval[1] = nxt.aval[2] = nxt.aval[3] = 0;
@@ -514,7 +560,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             int4 res0 = make_int4(0, 0, 0, 0), res1 = make_int4(0, 0, 0, 0);
             bool res_vec = false;
             if constexpr (EPI == EPI_ADD_I8) {
-                if (row_ok && chunk_ok) {
+                if (res_tma) {
+                    have_cur = have_nxt;
+                    rb_cur = rb_last;
+                    issue_res_load(nxt_t, tile + static_cast<int>(gridDim.x) < total_tiles);
+                } else if (row_ok && chunk_ok) {
                     const int8_t* xr = p.resid + static_cast<size_t>(row) * p.ld_resid + col0;
                     res_vec = ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && (col0 + 32 <= p.n);
                     if (res_vec) {
@@ -651,26 +701,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         if (col0 + j < p.n) drow[j] = v[j];
                 }
             } else if constexpr (EPI == EPI_ADD_I8) {
-                if (row_ok) {
+                if (res_tma) {
+                    if (have_cur) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(rbar + 8 * rb_cur, (r_par >> rb_cur) & 1u, 5));
+                        if (!ok) break;
+                        r_par ^= 1u << rb_cur;
+                        int4* rrow = reinterpret_cast<int4*>(epi_gen + rb_cur * 1024 + lane * 32);
+                        res0 = rrow[0];
+                        res1 = rrow[1];
+                        const uint32_t rw[8] = {static_cast<uint32_t>(res0.x), static_cast<uint32_t>(res0.y), static_cast<uint32_t>(res0.z), static_cast<uint32_t>(res0.w),
+                                                static_cast<uint32_t>(res1.x), static_cast<uint32_t>(res1.y), static_cast<uint32_t>(res1.z), static_cast<uint32_t>(res1.w)};
+                        uint32_t upd[8];
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) upd[g] = resid_add_word(rw[g], v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3], p.add_scale);
+                        rrow[0] = make_int4(static_cast<int>(upd[0]), static_cast<int>(upd[1]), static_cast<int>(upd[2]), static_cast<int>(upd[3]));
+                        rrow[1] = make_int4(static_cast<int>(upd[4]), static_cast<int>(upd[5]), static_cast<int>(upd[6]), static_cast<int>(upd[7]));
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {  // clips at M and N
+                            tma_store_2d(&map_d, epi_buf + rb_cur * 1024, col0, m0 + q * 32);
+                            bulk_commit();
+                        }
+                    }
+                } else if (row_ok) {
                     int8_t* xr = p.resid + static_cast<size_t>(row) * p.ld_resid + col0;
                     if (res_vec) {
                         const uint32_t rw[8] = {static_cast<uint32_t>(res0.x), static_cast<uint32_t>(res0.y), static_cast<uint32_t>(res0.z), static_cast<uint32_t>(res0.w),
                                                 static_cast<uint32_t>(res1.x), static_cast<uint32_t>(res1.y), static_cast<uint32_t>(res1.z), static_cast<uint32_t>(res1.w)};
-                        // rint(v * add_scale) as the low 16 bits of the biased float, added to the sign-extended old bytes
-                        // and clipped with packed 16-bit integer operations (two elements per instruction)
                         uint32_t upd[8];
 #pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            uint32_t tb[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)  // clamped first: the 16-bit field below must not wrap for huge products
-                                tb[e] = __float_as_uint(fminf(fmaxf(__fmul_rn(v[4 * g + e], p.add_scale), -512.0f), 512.0f) + kRoundBias);
-                            const uint32_t r01 = __byte_perm(tb[0], tb[1], 0x5410), r23 = __byte_perm(tb[2], tb[3], 0x5410);
-                            const uint32_t o01 = prmt_b32(rw[g], 0u, 0x9180u), o23 = prmt_b32(rw[g], 0u, 0xB3A2u);
-                            const uint32_t s01 = __vmins2(__viaddmax_s16x2(r01, o01, 0xff81ff81u), 0x007f007fu);
-                            const uint32_t s23 = __vmins2(__viaddmax_s16x2(r23, o23, 0xff81ff81u), 0x007f007fu);
-                            upd[g] = __byte_perm(s01, s23, 0x6420);
-                        }
+                        for (int g = 0; g < 8; ++g) upd[g] = resid_add_word(rw[g], v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3], p.add_scale);
                         reinterpret_cast<int4*>(xr)[0] = make_int4(static_cast<int>(upd[0]), static_cast<int>(upd[1]), static_cast<int>(upd[2]), static_cast<int>(upd[3]));
                         reinterpret_cast<int4*>(xr)[1] = make_int4(static_cast<int>(upd[4]), static_cast<int>(upd[5]), static_cast<int>(upd[6]), static_cast<int>(upd[7]));
                     } else {
@@ -776,7 +836,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
             }
         }
-        if constexpr (EPI == EPI_F32 || EPI == EPI_F16) {
+        if constexpr (EPI == EPI_F32 || EPI == EPI_F16 || EPI == EPI_ADD_I8) {
             if (args.use_tma_store) {
                 if (lane == 0) bulk_wait_read<0>();
                 __syncwarp();
@@ -903,6 +963,12 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
                          static_cast<uint64_t>(p.ld_f16) * 2, 32, 32, "D (fp16)", CU_TENSOR_MAP_SWIZZLE_NONE);
         if (rc) return rc;
         args.use_tma_store = 1;
+    } else if (p.epilogue == EPI_ADD_I8 && (reinterpret_cast<uintptr_t>(p.resid) & 15) == 0 && (p.ld_resid % 16) == 0) {
+        // the residual stream enters and leaves through 32-row x 32-byte boxes
+        rc = make_map_2d(&md, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.resid, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.m),
+                         static_cast<uint64_t>(p.ld_resid), 32, 32, "residual stream", CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        args.use_tma_store = g_gemm_allow_tma_store != 0;
     } else {
         md = ma;  // unused
     }
