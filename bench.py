@@ -333,6 +333,12 @@ def main():
     ap.add_argument("--half", action="store_true", help="--kernel efla: q | k | v and the output as IEEE halves")
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--fe", default="add", choices=["add", "norm"])
+    ap.add_argument("--train", action="store_true",
+                    help="the reference driver's epoch loop instead of the timed step: a fresh batch per epoch, ES step, loss of the updated "
+                         "model on the training batch, periodic validation loss; reports the reference's tok/s_eval and tok/s_total")
+    ap.add_argument("--epochs", type=int, default=5)
+    ap.add_argument("--val-every", type=int, default=1)
+    ap.add_argument("--corpus", default="", help="--train: a byte corpus file (e.g. Tiny Shakespeare); default: the seeded synthetic Zipf corpus")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -416,6 +422,31 @@ def main():
 
     model = population.PopulationModel(cfg)
     model.set_weights(weights)
+    if args.train:
+        # the reference's per-epoch log (src/train_efla_lm.cpp:5733-5800) for `--epochs` epochs, then one JSON line with the
+        # throughput definitions of :5786-5792 averaged over the epochs after the first
+        from bitnet_nvfp4_b200 import trainer
+        data = synth.load_corpus(args.corpus) if args.corpus else corpus
+        tc = trainer.TrainConfig(epochs=args.epochs, pairs=pairs_total, seed=1, val_every=args.val_every)
+        recs = trainer.train(model, data, tc, rank=rank, world=world, log=lambda line: print(line, file=sys.stderr))
+        code = bhost.device_error()
+        if code != 0:
+            raise SystemExit(f"a bounded wait expired inside a kernel (code {code}): results invalid")
+        if rank == 0:
+            tail = recs[1:] if len(recs) > 1 else recs
+            mean = lambda k: sum(r[k] for r in tail) / len(tail)
+            print(json.dumps({
+                "metric": "tok/s_total of the training loop (population evaluation + update + train/val evaluation, per epoch wall time)",
+                "value": mean("tok_s_total"), "unit": "tokens/s", "tok_s_eval": mean("tok_s_eval"), "n_gpus": world, "epochs": args.epochs,
+                "higher_is_better": True, "dtype": DTYPE, "data": args.corpus or "synthetic", "config": config,
+                "train_loss_first": recs[0]["train_loss"], "train_loss_last": recs[-1]["train_loss"],
+                "val_loss_last": next((r["val_loss"] for r in reversed(recs) if "val_loss" in r), None),
+                "epoch_wall_ms": mean("wall_s") * 1e3, "eval_ms": mean("eval_s") * 1e3, "update_ms": mean("update_s") * 1e3,
+                "train_eval_ms": mean("train_s") * 1e3, "val_eval_ms": mean("val_s") * 1e3}))
+        model.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
     tok_d = torch.from_numpy(tok).cuda()
     tgt_d = torch.from_numpy(tgt).cuda()
     tok_h = torch.from_numpy(tok).pin_memory()

@@ -319,14 +319,24 @@ def gather_z_shards(z_all: torch.Tensor, entries, rank: int, world: int, group=N
 
 def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world: int = 1, group=None, lr: float = 0.8,
             thresh: float = 0.008, fitness_mode: int = 2, fitness_clip: float = 3.0, losses_out: torch.Tensor | None = None,
-            shard_update: bool = True, spans: list | None = None, **update_kw) -> torch.Tensor:
+            shard_update: bool = True, spans: list | None = None, marks: dict | None = None, **update_kw) -> torch.Tensor:
     """One ES step on this rank: evaluate this rank's pairs, all-gather the per-member losses over `group`
     (torch.distributed), shape the fitness and apply the identical deterministic update on every rank. With more than one
     rank the noise sums of the update are computed by rows across the ranks and all-gathered (shard_update=False replicates
     them like the reference does); either way every rank ends with the same bits.
     `model` is a PopulationModel (or any object with prepare_step / eval_pairs / update). Returns all 2*pairs_total losses.
-    `spans`: optional list that receives (name, start event, end event) around every collective (CUDA devices only)."""
+    `spans`: optional list that receives (name, start event, end event) around every collective (CUDA devices only).
+    `marks`: optional dict that receives the host-clock durations "eval_s" (noise + evaluation + loss gather, the reference's
+    eval_s) and "update_s" (shaping + update); asking for them adds two device synchronisations."""
+    import time
     import torch.distributed as dist
+
+    def _now():
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        return time.perf_counter()
+
+    t_start = _now() if marks is not None else 0.0
     begin, count = shard_pairs(pairs_total, rank, world)
     if world > 1 and hasattr(model, "prepare_step_range"):
         model.prepare_step_range(seed, epoch, pairs_total, begin, count)
@@ -347,11 +357,15 @@ def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world
             losses = torch.cat([parts[r][: 2 * shard_pairs(pairs_total, r, world)[1]] for r in range(world)])
     else:
         losses = mine
+    t_eval = _now() if marks is not None else 0.0
     weights = shape_fitness(fitness_from_losses(losses), fitness_mode, fitness_clip)
     if world > 1 and shard_update and hasattr(model, "update_sharded"):
         model.update_sharded(weights, rank, world, group, lr=lr, thresh=thresh, **({"spans": spans} if spans is not None else {}), **update_kw)
     else:
         model.update(weights, lr=lr, thresh=thresh, **update_kw)
+    if marks is not None:
+        marks["eval_s"] = t_eval - t_start
+        marks["update_s"] = _now() - t_eval
     return losses
 
 

@@ -22,6 +22,20 @@ def splitmix64_stream(seed: int, n: int) -> np.ndarray:
         return z ^ (z >> np.uint64(31))
 
 
+def mix(a: int, b: int) -> int:
+    """The reference's seed mixer (src/rng.h:14-29): seeds of an epoch's batch, of a pair, of a matrix."""
+    m = (1 << 64) - 1
+    a &= m
+    b &= m
+    x = a ^ ((b + 0x9E3779B97F4A7C15 + (a << 6) + (a >> 2)) & m)
+    x ^= x >> 33
+    x = (x * 0xFF51AFD7ED558CCD) & m
+    x ^= x >> 33
+    x = (x * 0xC4CEB9FE1A85EC53) & m
+    x ^= x >> 33
+    return x
+
+
 def ternary_from_u64(x: np.ndarray) -> np.ndarray:
     r = (x & np.uint64(0xFF)).astype(np.int32)
     return np.where(r < 85, -1, np.where(r < 170, 0, 1)).astype(np.int8)

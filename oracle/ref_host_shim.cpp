@@ -64,6 +64,10 @@ REF_API uint64_t ref_count_parameters(int vocab, int hidden, int layers, int mlp
     cfg.vocab = vocab; cfg.hidden = hidden; cfg.layers = layers; cfg.mlp_mult = mlp_mult; cfg.seq_len = seq; cfg.train_pos = train_pos != 0;
     return count_parameters(cfg);
 }
+// The reference's per-epoch schedule of lr / update threshold / sigma (src/train_efla_lm.cpp:405-418); schedule = its enum value.
+REF_API float ref_schedule_value(float start, float end, int schedule, float t01) {
+    return schedule_value(start, end, static_cast<TrainConfig::Schedule>(schedule), t01);
+}
 // The reference's batch sampler on a corpus file (src/dataset.cpp:39-54). Returns 0 on success.
 REF_API int ref_sample_batch_packed(const char* path, int batch, int seq_len, uint64_t seed, uint8_t* inputs, uint8_t* targets) {
     ByteDataset ds;

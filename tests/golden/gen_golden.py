@@ -128,9 +128,16 @@ def gen_ref_host():
         corpus.tofile(f)
         for i, sd in enumerate(sb_seed):
             assert L.ref_sample_batch_packed(str(f).encode(), 32, 128, int(sd), sb_tok[i].ctypes.data, sb_tgt[i].ctypes.data) == 0
+    # per-epoch schedules: (start, end, schedule enum, t01) -> value
+    L.ref_schedule_value.restype = C.c_float
+    L.ref_schedule_value.argtypes = [C.c_float, C.c_float, C.c_int, C.c_float]
+    sched_in = np.array([(st, en, sc, t) for (st, en) in [(0.8, 0.05), (0.008, -1.0), (3.0, 5.0), (0.0, 0.5), (0.5, 0.0)]
+                         for sc in range(4) for t in (0.0, 1.0 / 3.0, 0.5, 0.9, 1.0, 1.5)], np.float32)
+    sched_out = np.array([L.ref_schedule_value(float(a_), float(b_), int(c_), float(d_)) for a_, b_, c_, d_ in sched_in], np.float32)
     np.savez_compressed(HERE / "ref_host.npz", mix_a=a, mix_b=b, mix=mix, sm_seed=sm_seed, sm_out=sm_out, tern_in=tern_in, tern=tern,
                         nh_seed=nh_seed, nh=nh, init=init, init_scale=init_scale, fit=fit, shaped=shaped, ce_logits=logits, ce_bias=bias,
-                        ce_noise=bnoise, ce_y=ys, ce=ce, nparams=nparams, fused_cols=fused_cols, sb_seed=sb_seed, sb_tok=sb_tok, sb_tgt=sb_tgt)
+                        ce_noise=bnoise, ce_y=ys, ce=ce, nparams=nparams, fused_cols=fused_cols, sb_seed=sb_seed, sb_tok=sb_tok, sb_tgt=sb_tgt,
+                        sched_in=sched_in, sched_out=sched_out)
     print("ref_host.npz", (HERE / "ref_host.npz").stat().st_size, "bytes")
 
 
