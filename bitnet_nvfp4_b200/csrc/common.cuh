@@ -143,10 +143,18 @@ __device__ __forceinline__ float gelu_q8_fast(float x, float act_scale, bool& ok
     clamped = fc;
     return t;
 }
+// max(a, b, c) in one instruction (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
 // Two values at a time with packed fp32 instructions (each half rounds like the scalar instruction, so the biased results
-// equal gelu_q8_fast's). `back` receives the rounded integers as floats. The boundary test is done on squares:
-// ok iff d^2 + tol < 1/4, which is stricter than |d| < 1/2 - tol for the same tol = 2e-6 (1 + |x act_scale|).
-__device__ __forceinline__ void gelu_q8_fast2(float x0, float x1, float act_scale, bool lower_clamp, bool& ok, float& t0, float& t1,
+// equal gelu_q8_fast's). `back` receives the rounded integers as floats. The boundary test is done on squares and as a
+// running maximum: a value is safe iff d^2 + tol < 1/4 (stricter than |d| < 1/2 - tol for the same tol = 2e-6 (1 + |x act_scale|));
+// `worst` accumulates max(d^2 + 2e-6 |x act_scale|) over the caller's group, to be compared once with kGeluSafe.
+constexpr float kGeluSafe = 0.25f - 2e-6f;
+__device__ __forceinline__ void gelu_q8_fast2(float x0, float x1, float act_scale, bool lower_clamp, float& worst, float& t0, float& t1,
                                               float& back0, float& back1) {
     const float kB = 2.0f * 0.7978845608028654f * 1.4426950408889634f;  // 2 c log2(e)
     const float kA = kB * 0.044715f;
@@ -171,8 +179,7 @@ __device__ __forceinline__ void gelu_q8_fast2(float x0, float x1, float act_scal
     const float2 back = __fadd2_rn(t, make_float2(-kRoundBias, -kRoundBias));
     const float2 d = __fadd2_rn(f, make_float2(-back.x, -back.y));
     const float2 d2 = __fmul2_rn(d, d);
-    const float lim = 0.25f - 2e-6f;
-    ok = ok && (fmaf(fabsf(xs.x), 2e-6f, d2.x) < lim) && (fmaf(fabsf(xs.y), 2e-6f, d2.y) < lim);
+    worst = fmax3(worst, fmaf(fabsf(xs.x), 2e-6f, d2.x), fmaf(fabsf(xs.y), 2e-6f, d2.y));
     t0 = t.x; t1 = t.y;
     back0 = back.x; back1 = back.y;
 }

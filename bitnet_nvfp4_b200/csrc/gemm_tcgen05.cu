@@ -767,12 +767,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const int j = 16 * blk + 4 * g;
-                        bool fast_ok = true;
+                        float worst = 0.0f;
                         float fc[4];  // the rounded integers as floats
-                        gelu_q8_fast2(v[j], v[j + 1], p.act_scale, lower_clamp, fast_ok, tb[4 * g], tb[4 * g + 1], fc[0], fc[1]);
-                        gelu_q8_fast2(v[j + 2], v[j + 3], p.act_scale, lower_clamp, fast_ok, tb[4 * g + 2], tb[4 * g + 3], fc[2], fc[3]);
-                        bad |= fast_ok ? 0u : (1u << g);
-                        am = fmaxf(fmaxf(am, fmaxf(fabsf(fc[0]), fabsf(fc[1]))), fmaxf(fabsf(fc[2]), fabsf(fc[3])));
+                        gelu_q8_fast2(v[j], v[j + 1], p.act_scale, lower_clamp, worst, tb[4 * g], tb[4 * g + 1], fc[0], fc[1]);
+                        gelu_q8_fast2(v[j + 2], v[j + 3], p.act_scale, lower_clamp, worst, tb[4 * g + 2], tb[4 * g + 3], fc[2], fc[3]);
+                        bad |= worst < kGeluSafe ? 0u : (1u << g);
+                        am = fmax3(fmax3(am, fabsf(fc[0]), fabsf(fc[1])), fabsf(fc[2]), fabsf(fc[3]));
                     }
                     if (bad != 0) {
 #pragma unroll

@@ -117,6 +117,8 @@ struct Model {
     float *upd_partial, *upd_inv;
     ZLowrankDesc *zdesc, *zdesc_ext;  // device tables of the update's matrices: Z inside Z_all / inside a caller's buffer
     int launches_per_wave = 0;
+    float* h_step = nullptr;    // bnf4_model_es_step: pinned losses [2 * max_pairs] + pair weights [max_pairs]
+    float* d_step_w = nullptr;  // ... and the shaped pair weights on the device
     // dense (rank 0) mode: the reference driver's own perturbation, one materialised noise matrix per weight matrix and pair,
     // applied as a second GEMM with beta = 1 (src/train_efla_lm.cpp:2359-2367). One pair per wave.
     bool dense = false;
@@ -707,6 +709,8 @@ int bnf4_model_destroy(void* handle) {
     Model* m = M(handle);
     cudaDeviceSynchronize();
     for (void* p : m->allocs) cudaFree(p);
+    if (m->h_step) cudaFreeHost(m->h_step);
+    if (m->d_step_w) cudaFree(m->d_step_w);
     for (cudaEvent_t e : m->free_events) cudaEventDestroy(e);
     for (const Model::Span& sp : m->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
     delete m;
@@ -1076,6 +1080,54 @@ int bnf4_model_update_apply(void* handle, const float* pair_weights, const float
     Model& m = *M(handle);
     if (m.pairs_step <= 0) return set_error(BNF4_ERR_INVALID, "model_update_apply: no prepared step");
     return update_apply(m, pair_weights, z_all, u, S(stream));
+}
+
+int bnf4_model_es_step(void* handle, const bnf4_es_step_cfg* cfg, const bnf4_collectives* coll, float* d_losses_all, void* stream) {
+    if (!handle || !cfg || !d_losses_all) return set_error(BNF4_ERR_INVALID, "model_es_step: null argument");
+    Model& m = *M(handle);
+    const int world = cfg->world, rank = cfg->rank, pairs = cfg->pairs;
+    if (world < 1 || rank < 0 || rank >= world) return set_error(BNF4_ERR_INVALID, "model_es_step: rank %d of %d", rank, world);
+    if (pairs <= 0 || (pairs % world) != 0) return set_error(BNF4_ERR_INVALID, "model_es_step: pairs=%d must be a positive multiple of world=%d", pairs, world);
+    if (world > 1 && (!coll || !coll->allgather_inplace)) return set_error(BNF4_ERR_INVALID, "model_es_step: more than one rank needs the all-gather callback");
+    cudaStream_t st = S(stream);
+    const int count = pairs / world, begin = rank * count;
+    TRY(bnf4_model_prepare_step_range(handle, cfg->seed, cfg->epoch, pairs, begin, count, stream));
+    TRY(bnf4_model_eval_pairs(handle, begin, count, d_losses_all + 2 * static_cast<size_t>(begin), stream));
+    if (world > 1 && coll->allgather_inplace(coll->ctx, d_losses_all, 2 * static_cast<size_t>(count) * sizeof(float), stream) != 0)
+        return set_error(BNF4_ERR_CUDA, "model_es_step: the all-gather of the losses failed");
+    // fitness shaping on the host, like the reference (src/train_efla_lm.cpp:5466, 5476): f_p = -(loss+ - loss-)
+    if (m.h_step == nullptr) {
+        TRY(check_cuda(cudaMallocHost(&m.h_step, 3 * static_cast<size_t>(m.cfg.max_pairs) * sizeof(float)), "cudaMallocHost(es_step)"));
+        TRY(check_cuda(cudaMalloc(&m.d_step_w, static_cast<size_t>(m.cfg.max_pairs) * sizeof(float)), "cudaMalloc(es_step)"));
+    }
+    float* h_losses = m.h_step;
+    float* h_w = m.h_step + 2 * static_cast<size_t>(m.cfg.max_pairs);
+    TRY(check_cuda(cudaMemcpyAsync(h_losses, d_losses_all, 2 * static_cast<size_t>(pairs) * sizeof(float), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(losses)"));
+    TRY(check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize"));
+    for (int p = 0; p < pairs; ++p) h_w[p] = -(h_losses[2 * p] - h_losses[2 * p + 1]);
+    TRY(bnf4_shape_pair_weights(h_w, pairs, cfg->fitness_mode, cfg->fitness_clip));
+    TRY(check_cuda(cudaMemcpyAsync(m.d_step_w, h_w, static_cast<size_t>(pairs) * sizeof(float), cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(pair weights)"));
+    if (world == 1) {
+        TRY(update_z(m, m.d_step_w, 0, 1, nullptr, st));
+        return update_apply(m, m.d_step_w, m.Z_all, &cfg->update, st);
+    }
+    // Z by rows over the ranks into the model's own buffer (the layout does not depend on the number of shards), gathered in place
+    TRY(update_z(m, m.d_step_w, rank, world, m.Z_all, st));
+    const std::vector<UpdMatrix> mats = update_matrices(m);
+    const std::vector<UpdVector> vecs = update_vectors(m);
+    if (coll->group_begin && coll->group_begin(coll->ctx) != 0) return set_error(BNF4_ERR_CUDA, "model_es_step: group_begin failed");
+    long long off = 0;
+    int failed = 0;
+    for (size_t i = 0; i < mats.size() + vecs.size() && !failed; ++i) {
+        const bool is_mat = i < mats.size();
+        const long long n = is_mat ? static_cast<long long>(mats[i].rows) * mats[i].cols : vecs[i - mats.size()].n;
+        const bool sharded = is_mat ? (mats[i].rows >= world && (mats[i].rows % world) == 0) : vector_sharded(vecs[i - mats.size()].n, world);
+        if (sharded) failed = coll->allgather_inplace(coll->ctx, m.Z_all + off, static_cast<size_t>(n / world) * sizeof(float), stream);
+        off += n;
+    }
+    if (coll->group_end && coll->group_end(coll->ctx) != 0) failed = 1;
+    if (failed) return set_error(BNF4_ERR_CUDA, "model_es_step: the all-gather of the noise sums failed");
+    return update_apply(m, m.d_step_w, m.Z_all, &cfg->update, st);
 }
 
 int bnf4_model_set_timing(void* handle, int enable) {

@@ -38,7 +38,25 @@ class UpdateCfg(C.Structure):
                 ("adaptive_eps", c_float), ("train_pos", c_int)]
 
 
+_ALLGATHER_FN = C.CFUNCTYPE(c_int, c_void_p, c_void_p, C.c_size_t, c_void_p)
+_GROUP_FN = C.CFUNCTYPE(c_int, c_void_p)
+
+
+class Collectives(C.Structure):
+    """bnf4_collectives"""
+
+    _fields_ = [("ctx", c_void_p), ("allgather_inplace", _ALLGATHER_FN), ("group_begin", _GROUP_FN), ("group_end", _GROUP_FN)]
+
+
+class EsStepCfg(C.Structure):
+    """bnf4_es_step_cfg"""
+
+    _fields_ = [("seed", C.c_uint64), ("epoch", C.c_uint64), ("pairs", c_int), ("rank", c_int), ("world", c_int), ("fitness_mode", c_int),
+                ("fitness_clip", c_float), ("update", UpdateCfg)]
+
+
 _l.register({
+    "bnf4_model_es_step": (c_int, [c_void_p, C.POINTER(EsStepCfg), C.POINTER(Collectives), c_void_p, c_void_p]),
     "bnf4_model_create": (c_int, [C.POINTER(ModelCfg), C.POINTER(c_void_p)]),
     "bnf4_model_destroy": (c_int, [c_void_p]),
     "bnf4_model_device_bytes": (C.c_size_t, [c_void_p]),
@@ -366,6 +384,59 @@ def es_step(model, seed: int, epoch: int, pairs_total: int, rank: int = 0, world
     if marks is not None:
         marks["eval_s"] = t_eval - t_start
         marks["update_s"] = _now() - t_eval
+    return losses
+
+
+class _DevBytes:
+    """A raw device range as an object torch.as_tensor accepts."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def torch_collectives(rank: int, world: int, group=None):
+    """bnf4_collectives over torch.distributed (NCCL): what a C++ host writes with ncclAllGather / ncclGroupStart / ncclGroupEnd.
+    Returns the struct and the objects that must stay alive while it is in use."""
+    import torch.distributed as dist
+    state = {"batch": None}
+
+    def allgather(_ctx, recv, bytes_per_rank, _stream_ptr):
+        try:
+            full = torch.as_tensor(_DevBytes(recv, bytes_per_rank * world), device="cuda")
+            dist.all_gather_into_tensor(full, full[rank * bytes_per_rank:(rank + 1) * bytes_per_rank], group=group)
+            return 0
+        except Exception:  # an exception must not cross the C boundary
+            import traceback
+            traceback.print_exc()
+            return 1
+
+    def begin(_ctx):
+        if dist.get_backend(group) == "nccl" and hasattr(dist, "_coalescing_manager"):
+            state["batch"] = dist._coalescing_manager(group=group, device=torch.device("cuda", torch.cuda.current_device()), async_ops=False)
+            state["batch"].__enter__()
+        return 0
+
+    def end(_ctx):
+        if state["batch"] is not None:
+            state["batch"].__exit__(None, None, None)
+            state["batch"] = None
+        return 0
+
+    fns = (_ALLGATHER_FN(allgather), _GROUP_FN(begin), _GROUP_FN(end))
+    return Collectives(None, *fns), fns
+
+
+def es_step_native(model: "PopulationModel", seed: int, epoch: int, pairs_total: int, rank: int = 0, world: int = 1, group=None,
+                   lr: float = 0.8, thresh: float = 0.008, fitness_mode: int = 2, fitness_clip: float = 3.0,
+                   losses_out: torch.Tensor | None = None, use_adaptive=True, adaptive_beta=0.95, adaptive_eps=1e-3, train_pos=True) -> torch.Tensor:
+    """es_step through the single C entry point bnf4_model_es_step: the rank orchestration runs inside the library and only the
+    collectives come back to the host as callbacks. Same results as es_step, bit for bit."""
+    losses = losses_out if losses_out is not None else torch.empty(2 * pairs_total, dtype=torch.float32, device="cuda")
+    cfg = EsStepCfg(seed, epoch, pairs_total, rank, world, fitness_mode, fitness_clip,
+                    UpdateCfg(lr, thresh, int(use_adaptive), adaptive_beta, adaptive_eps, int(train_pos)))
+    coll, keep = (torch_collectives(rank, world, group) if world > 1 else (None, None))
+    _l.check(model.lib.bnf4_model_es_step(model.h, C.byref(cfg), C.byref(coll) if coll is not None else None, losses.data_ptr(), _stream()))
+    del keep
     return losses
 
 

@@ -492,6 +492,35 @@ int bnf4_model_update_z_layout(void* handle, int nshards, int max_entries, long 
                                long long* total_elems);
 int bnf4_model_update_z(void* handle, const float* pair_weights, int shard, int nshards, float* z_all, void* stream);
 int bnf4_model_update_apply(void* handle, const float* pair_weights, const float* z_all, const bnf4_update_cfg* ucfg, void* stream);
+
+/* The whole ES step of one rank in ONE call, for hosts that run one process per GPU (what population.es_step does over
+ * torch.distributed, and what replaces the body of the reference's epoch loop between eval_worker and the vector updates,
+ * src/train_efla_lm.cpp:5344-5657): noise for the step -> this rank's pairs [rank * pairs / world, (rank + 1) * pairs / world)
+ * -> all-gather of the per-member losses -> f_p = -(loss+ - loss-) shaped on the host (bnf4_shape_pair_weights; one stream
+ * synchronisation and a round trip of 8 * pairs bytes, as the reference) -> noise sums Z by rows over the ranks -> in-place
+ * all-gather of every sharded Z -> apply. The library links no communication library: the caller supplies the two
+ * collectives as callbacks over its own communicator (NCCL: ncclAllGather with sendbuff = recv + rank * bytes_per_rank).
+ * Every rank must make the call with the same cfg except `rank`; all ranks end with identical weights, bit-identical to
+ * the single-process step. world == 1 needs no callbacks (coll may be NULL). pairs must be a multiple of world (ragged
+ * shards: compose the calls above by hand). d_losses_all receives all 2 * pairs losses on every rank. */
+typedef struct bnf4_collectives {
+    void* ctx;
+    /* In place, on `stream`: rank r's block is the bytes_per_rank bytes at d_recv + r * bytes_per_rank. 0 = success. */
+    int (*allgather_inplace)(void* ctx, void* d_recv, size_t bytes_per_rank, void* stream);
+    /* Optional brackets around the batch of Z all-gathers (ncclGroupStart / ncclGroupEnd); either may be NULL. */
+    int (*group_begin)(void* ctx);
+    int (*group_end)(void* ctx);
+} bnf4_collectives;
+typedef struct bnf4_es_step_cfg {
+    uint64_t seed;
+    uint64_t epoch;
+    int pairs;          /* of the whole population */
+    int rank, world;
+    int fitness_mode;   /* BNF4_FITNESS_* */
+    float fitness_clip;
+    bnf4_update_cfg update;
+} bnf4_es_step_cfg;
+int bnf4_model_es_step(void* handle, const bnf4_es_step_cfg* cfg, const bnf4_collectives* coll, float* d_losses_all, void* stream);
 /* Debug/verification access to an internal wave buffer by name ("x_q", "a_h", "sf_h", "a_f", "sf_f", "qkv", "y",
  * "t_a", "t_f", "losses"): copies min(bytes, size) bytes to host. Synchronises. */
 int bnf4_model_read_buffer(void* handle, const char* name, void* h_dst, size_t bytes);

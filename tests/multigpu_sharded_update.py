@@ -4,8 +4,9 @@
         tests/multigpu_sharded_update.py
 
 Every rank runs the same two ES steps twice on two models: once with the noise sums of the update computed by rows across
-the ranks and all-gathered (the default with more than one rank), once replicated. Weights and optimiser state must be
-bit-identical between the two and across ranks. test_gpu_population.py runs this file when two GPUs are visible.
+the ranks and all-gathered (the default with more than one rank), once replicated, once through the single C entry point
+bnf4_model_es_step with the collectives as callbacks. Weights and optimiser state must be bit-identical between the three and
+across ranks. test_gpu_population.py runs this file when two GPUs are visible.
 """
 import os
 import sys
@@ -26,18 +27,23 @@ def main():
     w = synth.init_weights(cfg)
     tok, tgt = synth.sample_batch(synth.zipf_corpus(1 << 16, 1.1, 123), cfg.batch, cfg.seq, 123)
     models = []
-    for shard_update in (True, False):
+    for mode in ("sharded", "replicated", "single call"):
         m = population.PopulationModel(cfg)
         m.set_weights(w)
         m.set_tokens(tok, tgt)
         for epoch in range(2):
-            population.es_step(m, 1, epoch, 8, rank, world, shard_update=shard_update)
+            if mode == "single call":  # bnf4_model_es_step with the collectives supplied as callbacks
+                population.es_step_native(m, 1, epoch, 8, rank, world)
+            else:
+                population.es_step(m, 1, epoch, 8, rank, world, shard_update=(mode == "sharded"))
         models.append(m)
-    wa, wb = models[0].get_weights(), models[1].get_weights()
+    wa, wb, wc = (m.get_weights() for m in models)
     for k in wa:
         assert np.array_equal(wa[k], wb[k]), k
-    (sa, ea), (sb, eb) = models[0].get_optimizer_state(), models[1].get_optimizer_state()
+        assert np.array_equal(wa[k], wc[k]), k
+    (sa, ea), (sb, eb), (sc, ec) = (m.get_optimizer_state() for m in models)
     assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
+    assert np.array_equal(sa, sc) and np.array_equal(ea, ec)
     assert any((wa[k] != w[k]).any() for k in ("emb", "win", "ff1"))
     # the same bits on every rank
     digest = torch.tensor([float(np.abs(sa).sum()), float(sum(int(np.abs(wa[k].astype(np.int64)).sum()) for k in wa if wa[k].dtype == np.int8))],

@@ -273,6 +273,35 @@ def test_checkpoint_resume_is_bit_identical(tmp_path):
     assert (sa != np.round(sa)).any()  # the shadows really carry fractional state
 
 
+
+def test_single_call_es_step_equals_the_composed_calls():
+    """bnf4_model_es_step (noise, evaluation, host-side shaping, update in one C call) against population.es_step, which composes
+    the same phases from Python: losses and weights bit-identical over two steps."""
+    from bitnet_nvfp4_b200 import population, synth
+    cfg = population.Config(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=8)
+    w = synth.init_weights(cfg)
+    tok, tgt = synth.sample_batch(synth.zipf_corpus(1 << 16, 1.1, 123), cfg.batch, cfg.seq, 7)
+    out = []
+    for native in (False, True):
+        m = population.PopulationModel(cfg)
+        m.set_weights(w)
+        m.set_tokens(tok, tgt)
+        step = population.es_step_native if native else population.es_step
+        losses = [step(m, 3, e, 8, lr=0.5, thresh=0.004).cpu().numpy().copy() for e in range(2)]
+        out.append((losses, m.get_weights(), m.get_optimizer_state()))
+        m.close()
+    (la, wa, (sa, ea)), (lb, wb, (sb, eb)) = out
+    assert all(np.array_equal(x, y) for x, y in zip(la, lb))
+    assert all(np.array_equal(wa[k], wb[k]) for k in wa)
+    assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
+    # argument checks of the entry point
+    m = population.PopulationModel(cfg)
+    m.set_weights(w)
+    m.set_tokens(tok, tgt)
+    with pytest.raises(Exception):
+        population.es_step_native(m, 3, 0, 7, rank=0, world=2)   # pairs not a multiple of world
+    m.close()
+
 @pytest.mark.parametrize("nshards", [2, 4])
 def test_sharded_update_is_bit_identical(nshards):
     """Z of every ternary matrix computed in row shards (one call per emulated rank into one buffer, which is what the
