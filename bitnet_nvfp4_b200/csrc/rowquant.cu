@@ -281,6 +281,8 @@ __global__ void __launch_bounds__(256) rowquant_kernel(const RowQuantParams p, c
 // the table is loaded once by a persistent CTA that then walks rows with a grid stride.
 // Requirements (checked by the host; otherwise rowquant_kernel runs): 16-byte aligned rows, cols_in == cols_out <= 2048.
 // ------------------------------------------------------------------------------------------------
+// |b0| + |b1| + |b2| + |b3| of four signed bytes: sum of absolute differences between the bytes offset by 128 and 128
+__device__ __forceinline__ uint32_t abs_sum_bytes4(uint32_t w) { return __vsadu4(w ^ 0x80808080u, 0x80808080u); }
 __device__ __forceinline__ uint2 lds_u64(uint32_t saddr) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(saddr));
@@ -302,6 +304,8 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
     const int nblk = p.cols_out >> 4;
     const int k_atoms = sf_k_atoms(p.cols_out);
     const unsigned rows = static_cast<unsigned>(p.rows);
+    const bool cols_pow2 = (p.cols_in & (p.cols_in - 1)) == 0;
+    const float inv_cols = 1.0f / static_cast<float>(p.cols_in);
     for (unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8u) {
         const int member = p.rows_per_member > 0 ? static_cast<int>(row / static_cast<unsigned>(p.rows_per_member)) : 0;
         const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
@@ -310,7 +314,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
 
         // ---------------- stage 1: integer values of the row as floats ----------------
         float vf[NB][16];
-        float sum_abs = 0.0f;
+        uint32_t sum_abs = 0;  // sum of |value| over this lane's elements (exact integer)
         int tok = 0;
         float a_r[4] = {0.f, 0.f, 0.f, 0.f};
         if constexpr (FE == FE_EMBED_LOWRANK) {
@@ -338,8 +342,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     bytes4_to_float(rw[q], &vf[i][4 * q]);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) sum_abs += fabsf(vf[i][4 * q + j]);
+                    sum_abs += abs_sum_bytes4(rw[q]);
                 }
             } else if constexpr (FE == FE_ADD_ABSMEAN) {
                 int8_t* xr = p.inout_i8 + static_cast<size_t>(row) * p.cols_in;
@@ -377,10 +380,9 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                         const float2 vv = __fadd2_rn(make_float2(tb[j], tb[j + 1]), make_float2(-M, -M));
                         vf[i][4 * q + j] = vv.x;
                         vf[i][4 * q + j + 1] = vv.y;
-                        sum_abs += fabsf(vv.x);
-                        sum_abs += fabsf(vv.y);
                     }
                     upd[q] = biased4_to_bytes(tb[0], tb[1], tb[2], tb[3]);
+                    sum_abs += abs_sum_bytes4(upd[q]);
                 }
                 *reinterpret_cast<int4*>(xr + k0) = make_int4(static_cast<int>(upd[0]), static_cast<int>(upd[1]), static_cast<int>(upd[2]), static_cast<int>(upd[3]));
             } else if constexpr (FE == FE_POS_GELU_ABSMEAN) {
@@ -425,11 +427,9 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                         gelu_q8_exact4(x[0], x[1], x[2], x[3], p.act_scale, tb, fcx);
                     }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        vf[i][4 * q + j] = tb[j] - M;
-                        sum_abs += fabsf(vf[i][4 * q + j]);
-                    }
+                    for (int j = 0; j < 4; ++j) vf[i][4 * q + j] = tb[j] - M;
                     resid[q] = biased4_to_bytes(tb[0], tb[1], tb[2], tb[3]);
+                    sum_abs += abs_sum_bytes4(resid[q]);
                 }
                 // residual stream = the pre-norm values
                 *reinterpret_cast<int4*>(p.inout_i8 + static_cast<size_t>(row) * p.cols_in + k0) =
@@ -474,8 +474,9 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
         // ---------------- stage 2: abs-mean normalisation (integer-exact row sum) ----------------
         float inv = 1.0f;
         if constexpr (kNorm) {
-            const int total = __reduce_add_sync(0xffffffffu, __float2int_rn(sum_abs));
-            float abs_mean = __fdiv_rn(static_cast<float>(total), static_cast<float>(p.cols_in));
+            const int total = static_cast<int>(__reduce_add_sync(0xffffffffu, sum_abs));
+            // a power-of-two column count divides exactly by multiplication
+            float abs_mean = cols_pow2 ? __fmul_rn(static_cast<float>(total), inv_cols) : __fdiv_rn(static_cast<float>(total), static_cast<float>(p.cols_in));
             if (abs_mean < 1.0f) abs_mean = 1.0f;
             inv = __fdiv_rn(p.norm_scale, abs_mean);
         }
