@@ -416,13 +416,12 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                         for (int j = 0; j < 4; ++j) pv[j] = fmaf(ns, pnf[j], pv[j]);
                     }
                     float x[4], tb[4], fc[4];
-                    bool fast_ok = true;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        x[j] = ff[j] + pv[j];
-                        tb[j] = gelu_q8_fast(x[j], p.act_scale, fast_ok, fc[j]);
-                    }
-                    if (!fast_ok) {
+                    for (int j = 0; j < 4; ++j) x[j] = ff[j] + pv[j];
+                    float worst = 0.0f;  // packed evaluation, two values per call; one boundary test per four
+                    gelu_q8_fast2(x[0], x[1], p.act_scale, true, worst, tb[0], tb[1], fc[0], fc[1]);
+                    gelu_q8_fast2(x[2], x[3], p.act_scale, true, worst, tb[2], tb[3], fc[2], fc[3]);
+                    if (!(worst < kGeluSafe)) {
                         float fcx[4];
                         gelu_q8_exact4(x[0], x[1], x[2], x[3], p.act_scale, tb, fcx);
                     }
