@@ -149,6 +149,52 @@ def test_two_ranks_agree_with_one(pairs):
     assert any((w0[k] != w[k]).any() for k in ("emb", "win", "head"))
 
 
+class TrainableEvaluator(OracleEvaluator):
+    """The evaluator with the two calls the epoch loop adds: a new batch, and the loss of the unperturbed model."""
+
+    def set_tokens(self, tokens, targets):
+        self.tok, self.tgt = np.ascontiguousarray(tokens), np.ascontiguousarray(targets)
+
+    def eval_base(self):
+        return torch.tensor([orc.OracleModel(self._ocfg(), self.w).forward(self.tok, self.tgt, 0, 0)], dtype=torch.float32)
+
+
+def _train_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    from bitnet_nvfp4_b200 import synth, trainer
+    cfg, w, tok, tgt = _setup()
+    ev = TrainableEvaluator(cfg, w, tok, tgt)
+    recs = trainer.train(ev, synth.zipf_corpus(1 << 14), trainer.TrainConfig(epochs=2, pairs=4, seed=9, val_every=2), rank=rank, world=world)
+    q.put((rank, [(r["train_loss"], r.get("val_loss")) for r in recs], {k: ev.w[k].copy() for k in ("emb", "win", "head")}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def test_epoch_loop_on_two_ranks_equals_one():
+    """trainer.train over gloo: both ranks log the same train / validation losses as a single-rank run and end with its weights."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_train_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=240) for _ in range(2)], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    import queue as _queue
+    single = _queue.Queue()
+    _train_worker(0, 1, port, single)
+    _, ref_losses, ref_w = single.get()
+    for _, losses, wts in res:
+        assert losses == ref_losses
+        assert all(np.array_equal(wts[k], ref_w[k]) for k in ref_w)
+    assert ref_losses[0][1] is not None and ref_losses[1][1] is None  # validation on epoch 0 only (val_every = 2)
+
+
 def test_shard_pairs_partitions():
     from bitnet_nvfp4_b200 import population
     for total in (1, 5, 1024, 1023):
