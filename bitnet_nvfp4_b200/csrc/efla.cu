@@ -423,6 +423,10 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sad
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
 }
 
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t saddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+
 template <bool IN16, bool OUT16>
 __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const EflaParams p) {
     constexpr int HD = 64;
@@ -517,6 +521,12 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
     const uint32_t ak_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ak_sh)) +
                              static_cast<uint32_t>(((lm_j & 1) * 8 + lm_r) * kCkHStride + (lm_j >> 1) * 8) * 2u;
 
+    // V read and Y written through transposing matrix loads / stores: matrix j = lane / 8 covers tokens 8 (j >> 1) .. + 7 and
+    // columns 16 mt + 8 (j & 1) .. + 7; a thread's register pair is (column g, tokens 2 tq and 2 tq + 1): the accumulator layout
+    const uint32_t v_addr = static_cast<uint32_t>(__cvta_generic_to_shared(rawvh)) +
+                            static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kCkVStrideH + (lm_j & 1) * 8) * 2u;
+    const uint32_t y_addr = static_cast<uint32_t>(__cvta_generic_to_shared(y_sh)) +
+                            static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kCkYStrideH + (lm_j & 1) * 8) * 2u;
     issue_chunk(0);
     for (int t0 = 0; t0 < p.T; t0 += kChunk) {
         cp_async_wait<0>();
@@ -580,23 +590,35 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
         }
         // ---------------- W^T starts as V^T: element (n, token) of this lane's accumulator positions ----------------
         float Wc[4][2][4];
+        if constexpr (IN16) {
+            // rows past the end of the sequence may hold stale halves: their columns of W are never used (alpha = 0 masks
+            // them out of L and P, and their outputs are not written), but they must be finite
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+            for (int mt = 0; mt < 4; ++mt) {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, v_addr + mt * 32);
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int tok = 8 * nt + 2 * tq + e;
-                const bool valid = t0 + tok < p.T;
+                for (int nt = 0; nt < 2; ++nt) {
+                    const bool valid0 = t0 + 8 * nt + 2 * tq < p.T, valid1 = t0 + 8 * nt + 2 * tq + 1 < p.T;
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&vf[2 * nt])), hi = __half22float2(*reinterpret_cast<const __half2*>(&vf[2 * nt + 1]));
+                    Wc[mt][nt][0] = valid0 ? lo.x : 0.0f; Wc[mt][nt][1] = valid1 ? lo.y : 0.0f;
+                    Wc[mt][nt][2] = valid0 ? hi.x : 0.0f; Wc[mt][nt][3] = valid1 ? hi.y : 0.0f;
+                }
+            }
+        } else {
 #pragma unroll
-                for (int mt = 0; mt < 4; ++mt) {
-                    if constexpr (IN16) {
-                        Wc[mt][nt][e] = valid ? __half2float(rawvh[tok * kCkVStrideH + 16 * mt + g]) : 0.0f;
-                        Wc[mt][nt][2 + e] = valid ? __half2float(rawvh[tok * kCkVStrideH + 16 * mt + 8 + g]) : 0.0f;
-                    } else {
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int tok = 8 * nt + 2 * tq + e;
+                    const bool valid = t0 + tok < p.T;
+#pragma unroll
+                    for (int mt = 0; mt < 4; ++mt) {
                         Wc[mt][nt][e] = valid ? rawv[tok * kCkVStride + 16 * mt + g] : 0.0f;
                         Wc[mt][nt][2 + e] = valid ? rawv[tok * kCkVStride + 16 * mt + 8 + g] : 0.0f;
                     }
                 }
-            }
+        }
         __syncwarp();  // the raw tiles are free, the prepared operands are visible
         issue_chunk(t0 + kChunk);
 
@@ -690,20 +712,22 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
                     mma_f16_16816(Yc[nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], qf[ks][2 * nt], qf[ks][2 * nt + 1]);
+            if constexpr (OUT16) {  // staged as halves (one transposing matrix store per 16 columns), written out row by row below
+                stmatrix_x4_trans(y_addr + mt * 32, pack_half2(Yc[0][0], Yc[0][1]), pack_half2(Yc[0][2], Yc[0][3]), pack_half2(Yc[1][0], Yc[1][1]),
+                                  pack_half2(Yc[1][2], Yc[1][3]));
+            } else {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int tl = 8 * nt + 2 * tq + e;
-                    if constexpr (OUT16) {  // staged as halves, written out row by row below
-                        y_sh[tl * kCkYStrideH + 16 * mt + g] = __float2half_rn(Yc[nt][e]);
-                        y_sh[tl * kCkYStrideH + 16 * mt + 8 + g] = __float2half_rn(Yc[nt][2 + e]);
-                    } else if (t0 + tl < p.T) {
-                        float* orow = ob + static_cast<size_t>(t0 + tl) * p.ld_out + 16 * mt + g;
-                        orow[0] = Yc[nt][e];
-                        orow[8] = Yc[nt][2 + e];
+                    for (int e = 0; e < 2; ++e) {
+                        const int tl = 8 * nt + 2 * tq + e;
+                        if (t0 + tl < p.T) {
+                            float* orow = ob + static_cast<size_t>(t0 + tl) * p.ld_out + 16 * mt + g;
+                            orow[0] = Yc[nt][e];
+                            orow[8] = Yc[nt][2 + e];
+                        }
                     }
-                }
+            }
         }
         if constexpr (OUT16) {
             __syncwarp();
