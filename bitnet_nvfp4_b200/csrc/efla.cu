@@ -755,6 +755,311 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
     cp_async_wait<0>();
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The chunked scan for the case the batched driver runs: method 1 (k is used unscaled), q | k | v as halves. The chunk's
+// recurrence is rewritten so that every tensor-core operand is a tile as it arrived from global memory:
+//   with  U~_t = a_t U_t  (U the per-token updates, a_t = alpha_t):
+//       (I + diag(a) G_strict) U~ = diag(a) W,     W = V - K S0,  G = K K^T
+//       Y = diag(q_inv) (Q S0 + (Q K^T, lower triangle incl. diagonal) U~),        S += K^T U~
+// so K and Q enter the MMAs unscaled (ldmatrix straight from the raw tiles), alpha scales rows of G and columns of W^T, and the
+// query normalisation scales the finished output. No prepared operand tiles are written: the preparation phase only
+// computes the per-token scalars. The raw k tile is double-buffered because the state update at the end of a chunk still
+// reads it while the next chunk is being fetched.
+// ------------------------------------------------------------------------------------------------
+constexpr int kM1Stride = 72;  // halves per row of the raw tiles: conflict-free for ldmatrix rows and for the 16-byte reads of eight rows
+constexpr int kM1RawQ = 0;
+constexpr int kM1RawK = kM1RawQ + kChunk * kM1Stride * 2;       // two buffers
+constexpr int kM1RawV = kM1RawK + 2 * kChunk * kM1Stride * 2;
+constexpr int kM1Y = kM1RawV + kChunk * kM1Stride * 2;          // output staging
+constexpr int kM1Beta = kM1Y + kChunk * kM1Stride * 2;
+constexpr int kM1Alpha = kM1Beta + kChunk * 4;
+constexpr int kM1Qinv = kM1Alpha + kChunk * 4;
+constexpr int kM1L = kM1Qinv + kChunk * 4;
+constexpr int kM1T = kM1L + kChunk * kChunk * 4;
+constexpr int kM1P = kM1T + kChunk * kCkTStride * 2;
+constexpr int kM1WarpBytes = kM1P + kChunk * kCkTStride * 2;
+constexpr int kM1SmemBytes = kChunkWarps * kM1WarpBytes;
+static_assert(kM1WarpBytes % 16 == 0 && kM1L % 16 == 0 && kM1T % 16 == 0 && kM1Beta % 16 == 0, "16-byte aligned shared-memory regions");
+
+template <bool OUT16>
+__global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(const EflaParams p) {
+    constexpr int HD = 64;
+    extern __shared__ __align__(16) uint8_t scan_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t* wsm = scan_smem + warp * kM1WarpBytes;
+    __half* rawq = reinterpret_cast<__half*>(wsm + kM1RawQ);
+    __half* rawk = reinterpret_cast<__half*>(wsm + kM1RawK);   // + buffer * kChunk * kM1Stride
+    __half* rawv = reinterpret_cast<__half*>(wsm + kM1RawV);
+    __half* y_sh = reinterpret_cast<__half*>(wsm + kM1Y);
+    float* beta_sh = reinterpret_cast<float*>(wsm + kM1Beta);
+    float* alpha_sh = reinterpret_cast<float*>(wsm + kM1Alpha);
+    float* qinv_sh = reinterpret_cast<float*>(wsm + kM1Qinv);
+    float* L_sh = reinterpret_cast<float*>(wsm + kM1L);
+    __half* t_sh = reinterpret_cast<__half*>(wsm + kM1T);
+    __half* p_sh = reinterpret_cast<__half*>(wsm + kM1P);
+    const long long unit = static_cast<long long>(blockIdx.x) * kChunkWarps + warp;  // (sequence, head)
+    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
+    const long long seq = unit / p.heads;
+    const int h = static_cast<int>(unit - seq * p.heads);
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
+    const int g = lane >> 2, tq = lane & 3;
+
+    uint32_t Sh[4][4][4];  // state S^T as A fragments, as in efla_chunk16_kernel
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
+
+    const size_t row0 = static_cast<size_t>(seq) * p.T;
+    const __half* qbh = static_cast<const __half*>(p.q) + row0 * p.ld_qkv + h * HD;
+    const __half* kbh = static_cast<const __half*>(p.k) + row0 * p.ld_qkv + h * HD;
+    const __half* vbh = static_cast<const __half*>(p.v) + row0 * p.ld_qkv + h * HD;
+    const float* bb = p.beta_raw + row0 * p.ld_beta;
+    float* ob = static_cast<float*>(p.out) + row0 * p.ld_out + h * HD;
+    __half* obh = static_cast<__half*>(p.out) + row0 * p.ld_out + h * HD;
+
+    // asynchronous copy of one chunk's q, k, v, beta rows (16-byte pieces, eight per 128-byte row); rows past the end of the
+    // sequence are zero-filled so that everything derived from them stays finite
+    auto issue_chunk = [&](int t0, int kbuf) {
+        const int piece = lane & 7, rsel = lane >> 3;
+        __half* rk = rawk + kbuf * kChunk * kM1Stride;
+#pragma unroll
+        for (int j = 0; j < kChunk / 4; ++j) {
+            const int r = 4 * j + rsel;
+            if (t0 + r < p.T) {
+                const size_t o = static_cast<size_t>(t0 + r) * p.ld_qkv + 8 * piece;
+                cp_async16(rawq + r * kM1Stride + 8 * piece, qbh + o);
+                cp_async16(rk + r * kM1Stride + 8 * piece, kbh + o);
+                cp_async16(rawv + r * kM1Stride + 8 * piece, vbh + o);
+            } else {
+                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(rawq + r * kM1Stride + 8 * piece) = z;
+                *reinterpret_cast<uint4*>(rk + r * kM1Stride + 8 * piece) = z;
+                *reinterpret_cast<uint4*>(rawv + r * kM1Stride + 8 * piece) = z;
+            }
+        }
+        if (lane < kChunk && t0 + lane < p.T) cp_async4(beta_sh + lane, bb + static_cast<size_t>(t0 + lane) * p.ld_beta);
+        cp_async_commit();
+    };
+
+    // ldmatrix row addresses of this lane: matrix j = lane / 8, row lane % 8
+    const int lm_j = lane >> 3, lm_r = lane & 7;
+    // tiles stored [token][d]: matrices (tokens 0-7 | d 0-7), (0-7 | 8-15), (8-15 | 0-7), (8-15 | 8-15) of a 16-wide d block
+    const uint32_t lm_tok_off = static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kM1Stride + (lm_j & 1) * 8) * 2u;
+    const uint32_t q_addr = static_cast<uint32_t>(__cvta_generic_to_shared(rawq)) + lm_tok_off;
+    const uint32_t k_addr0 = static_cast<uint32_t>(__cvta_generic_to_shared(rawk)) + lm_tok_off;
+    const uint32_t lm_ts_off = static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kCkTStride + (lm_j & 1) * 8) * 2u;
+    const uint32_t t_addr = static_cast<uint32_t>(__cvta_generic_to_shared(t_sh)) + lm_ts_off;
+    const uint32_t p_addr = static_cast<uint32_t>(__cvta_generic_to_shared(p_sh)) + lm_ts_off;
+    // K read transposed: matrices (tokens 0-7 | d-tile), (8-15 | d-tile), (0-7 | d-tile + 1), (8-15 | d-tile + 1)
+    const uint32_t kt_addr0 = static_cast<uint32_t>(__cvta_generic_to_shared(rawk)) +
+                              static_cast<uint32_t>(((lm_j & 1) * 8 + lm_r) * kM1Stride + (lm_j >> 1) * 8) * 2u;
+    // V read and Y written through transposing matrix loads / stores (tokens 8 (j >> 1) .., columns 16 mt + 8 (j & 1) ..)
+    const uint32_t v_addr = static_cast<uint32_t>(__cvta_generic_to_shared(rawv)) + lm_tok_off;
+    const uint32_t y_addr = static_cast<uint32_t>(__cvta_generic_to_shared(y_sh)) + lm_tok_off;
+    constexpr uint32_t kKBufBytes = kChunk * kM1Stride * 2;
+
+    issue_chunk(0, 0);
+    int kbuf = 0;
+    for (int t0 = 0; t0 < p.T; t0 += kChunk, kbuf ^= 1) {
+        cp_async_wait<0>();
+        __syncwarp();
+        const __half* rk = rawk + kbuf * kChunk * kM1Stride;
+        // ---------------- per-token scalars: lanes tt and tt + 16 share token tt, alternate 16-byte pieces ----------------
+        {
+            const int tt = lane & 15, hh = lane >> 4;
+            const bool valid = t0 + tt < p.T;
+            float qss = 0.0f, kss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 a = *reinterpret_cast<const uint4*>(rawq + tt * kM1Stride + (2 * j + hh) * 8);
+                const uint4 b = *reinterpret_cast<const uint4*>(rk + tt * kM1Stride + (2 * j + hh) * 8);
+                const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[e])), fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
+                    qss = fmaf(fa.x, fa.x, qss); qss = fmaf(fa.y, fa.y, qss);
+                    kss = fmaf(fb.x, fb.x, kss); kss = fmaf(fb.y, fb.y, kss);
+                }
+            }
+            qss += __shfl_xor_sync(0xffffffffu, qss, 16);
+            kss += __shfl_xor_sync(0xffffffffu, kss, 16);
+            const float q_inv = rsqrtf(qss + p.eps);
+            const float lambda = kss < p.eps ? p.eps : kss;
+            const float beta = sigmoidf_dev((valid ? beta_sh[tt] : 0.0f) + beta_bias);
+            const float alpha = valid ? -expm1f(-(beta * lambda)) / (lambda + p.eps) : 0.0f;
+            if (hh == 0) {
+                alpha_sh[tt] = alpha;
+                qinv_sh[tt] = q_inv;
+            }
+        }
+        // ---------------- operand fragments straight from the raw tiles; W^T starts as -V^T ----------------
+        uint32_t kf[4][4], qf[4][4];  // per 16-wide d block: B fragments {b0, b1} for tokens 0-7 (regs 0, 1) and 8-15 (regs 2, 3)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            ldmatrix_x4(kf[ks], k_addr0 + kbuf * kKBufBytes + ks * 32);
+            ldmatrix_x4(qf[ks], q_addr + ks * 32);
+        }
+        float Wc[4][2][4];  // -(V - K S0)^T = S0^T K^T - V^T
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            uint32_t vf[4];
+            ldmatrix_x4_trans(vf, v_addr + mt * 32);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&vf[2 * nt])), hi = __half22float2(*reinterpret_cast<const __half2*>(&vf[2 * nt + 1]));
+                Wc[mt][nt][0] = -lo.x; Wc[mt][nt][1] = -lo.y;
+                Wc[mt][nt][2] = -hi.x; Wc[mt][nt][3] = -hi.y;
+            }
+        }
+        __syncwarp();  // q, v and the scalars' inputs are consumed; alpha / q_inv are visible
+        if (t0 + kChunk < p.T) issue_chunk(t0 + kChunk, kbuf ^ 1);
+
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+                    mma_f16_16816(Wc[mt][nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+        float Gc[2][4], Xc[2][4];  // rows t = g (+ 8 for i >= 2), columns s = 8 nt + 2 tq + (i & 1);  Xc = q_t . k_s
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Gc[nt][i] = Xc[nt][i] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                mma_f16_16816(Gc[nt], kf[ks][0], kf[ks][2], kf[ks][1], kf[ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+                mma_f16_16816(Xc[nt], qf[ks][0], qf[ks][2], qf[ks][1], qf[ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+            }
+        // L[t][s] = a_t G[t][s] (s < t) in fp32 for the substitution; P[t][s] = q_t . k_s (s <= t) in fp16
+        {
+            const float a_lo = alpha_sh[g], a_hi = alpha_sh[g + 8];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                const int s0 = 8 * nt + 2 * tq;
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr) {
+                    const int t = g + 8 * hr;
+                    const float at = hr ? a_hi : a_lo;
+                    const float l0 = s0 < t ? at * Gc[nt][2 * hr] : 0.0f, l1 = s0 + 1 < t ? at * Gc[nt][2 * hr + 1] : 0.0f;
+                    const float p0 = s0 <= t ? Xc[nt][2 * hr] : 0.0f, p1 = s0 + 1 <= t ? Xc[nt][2 * hr + 1] : 0.0f;
+                    *reinterpret_cast<float2*>(L_sh + t * kChunk + s0) = make_float2(l0, l1);
+                    *reinterpret_cast<uint32_t*>(p_sh + t * kCkTStride + s0) = pack_half2(p0, p1);
+                }
+            }
+        }
+        __syncwarp();
+        // ---------------- T = (I + L)^-1 by forward substitution, lane c owns column c ----------------
+        {
+            const int c = lane & 15;
+            float col[kChunk];
+#pragma unroll
+            for (int t = 0; t < kChunk; ++t) {
+                float acc = t == c ? 1.0f : 0.0f;
+#pragma unroll
+                for (int s4 = 0; s4 < t; s4 += 4) {
+                    const float4 lv = *reinterpret_cast<const float4*>(L_sh + t * kChunk + s4);
+                    acc = fmaf(-lv.x, col[s4], acc);
+                    if (s4 + 1 < t) acc = fmaf(-lv.y, col[s4 + 1], acc);
+                    if (s4 + 2 < t) acc = fmaf(-lv.z, col[s4 + 2], acc);
+                    if (s4 + 3 < t) acc = fmaf(-lv.w, col[s4 + 3], acc);
+                }
+                col[t] = acc;
+            }
+            if (lane < kChunk) {
+#pragma unroll
+                for (int t = 0; t < kChunk; ++t) t_sh[t * kCkTStride + c] = __float2half_rn(col[t]);
+            }
+        }
+        __syncwarp();
+        uint32_t tf[4], pf[4];
+        ldmatrix_x4(tf, t_addr);
+        ldmatrix_x4(pf, p_addr);
+        // ---------------- U~^T = (diag(a) W)^T T^T: the columns (tokens) of -W^T are scaled by -a ----------------
+        float na[2][2], qi[2][2];  // [nt][e]: token 8 nt + 2 tq + e
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const float2 al = *reinterpret_cast<const float2*>(alpha_sh + 8 * nt + 2 * tq);
+            const float2 q2 = *reinterpret_cast<const float2*>(qinv_sh + 8 * nt + 2 * tq);
+            na[nt][0] = -al.x; na[nt][1] = -al.y;
+            qi[nt][0] = q2.x; qi[nt][1] = q2.y;
+        }
+        uint32_t Up[4][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            const uint32_t w0 = pack_half2(na[0][0] * Wc[mt][0][0], na[0][1] * Wc[mt][0][1]), w1 = pack_half2(na[0][0] * Wc[mt][0][2], na[0][1] * Wc[mt][0][3]);
+            const uint32_t w2 = pack_half2(na[1][0] * Wc[mt][1][0], na[1][1] * Wc[mt][1][1]), w3 = pack_half2(na[1][0] * Wc[mt][1][2], na[1][1] * Wc[mt][1][3]);
+            float Uc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) mma_f16_16816_zero(Uc[nt], w0, w1, w2, w3, tf[2 * nt], tf[2 * nt + 1]);
+            Up[mt][0] = pack_half2(Uc[0][0], Uc[0][1]); Up[mt][1] = pack_half2(Uc[0][2], Uc[0][3]);
+            Up[mt][2] = pack_half2(Uc[1][0], Uc[1][1]); Up[mt][3] = pack_half2(Uc[1][2], Uc[1][3]);
+        }
+        // ---------------- Y^T = (S0^T Q^T + U~^T P^T) diag(q_inv) ----------------
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            float Yc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) mma_f16_16816_zero(Yc[nt], Up[mt][0], Up[mt][1], Up[mt][2], Up[mt][3], pf[2 * nt], pf[2 * nt + 1]);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+                    mma_f16_16816(Yc[nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], qf[ks][2 * nt], qf[ks][2 * nt + 1]);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                Yc[nt][0] *= qi[nt][0]; Yc[nt][1] *= qi[nt][1];
+                Yc[nt][2] *= qi[nt][0]; Yc[nt][3] *= qi[nt][1];
+            }
+            if constexpr (OUT16) {
+                stmatrix_x4_trans(y_addr + mt * 32, pack_half2(Yc[0][0], Yc[0][1]), pack_half2(Yc[0][2], Yc[0][3]), pack_half2(Yc[1][0], Yc[1][1]),
+                                  pack_half2(Yc[1][2], Yc[1][3]));
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int tl = 8 * nt + 2 * tq + e;
+                        if (t0 + tl < p.T) {
+                            float* orow = ob + static_cast<size_t>(t0 + tl) * p.ld_out + 16 * mt + g;
+                            orow[0] = Yc[nt][e];
+                            orow[8] = Yc[nt][2 + e];
+                        }
+                    }
+            }
+        }
+        if constexpr (OUT16) {
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // 16 rows x 128 bytes: 16-byte pieces, eight per row
+                const int tl = 4 * j + (lane >> 3), piece = lane & 7;
+                if (t0 + tl < p.T)
+                    *reinterpret_cast<uint4*>(obh + static_cast<size_t>(t0 + tl) * p.ld_out + 8 * piece) =
+                        *reinterpret_cast<const uint4*>(y_sh + tl * kM1Stride + 8 * piece);
+            }
+        }
+        // ---------------- S^T += U~^T K: fp16 accumulators = the state registers, rounded once per chunk ----------------
+#pragma unroll
+        for (int dp = 0; dp < 4; ++dp) {
+            uint32_t af[4];
+            ldmatrix_x4_trans(af, kt_addr0 + kbuf * kKBufBytes + dp * 32);
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                mma_f16acc_16816(Sh[mt][dp][0], Sh[mt][dp][1], Up[mt][0], Up[mt][1], Up[mt][2], Up[mt][3], af[0], af[1]);
+                mma_f16acc_16816(Sh[mt][dp][2], Sh[mt][dp][3], Up[mt][0], Up[mt][1], Up[mt][2], Up[mt][3], af[2], af[3]);
+            }
+        }
+        __syncwarp();  // the staging tile and this chunk's k buffer are free for the chunk after the next
+    }
+    cp_async_wait<0>();
+}
+
 }  // namespace
 
 int g_efla_chunked = 1;  // host toggle (option "efla_chunked"): what BNF4_EFLA_AUTO picks for heads of 64 with on-chip state
@@ -789,6 +1094,8 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
             if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
             if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
             if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCkSmemBytes), "cudaFuncSetAttribute(efla_chunk16_kernel)");
+            if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_m1_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kM1SmemBytes), "cudaFuncSetAttribute(efla_chunk16_m1_kernel)");
+            if (!rc) rc = check_cuda(cudaFuncSetAttribute(efla_chunk16_m1_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kM1SmemBytes), "cudaFuncSetAttribute(efla_chunk16_m1_kernel)");
             if (rc) return rc;
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
@@ -796,7 +1103,10 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
             if (p.qkv_f16 && ((p.ld_qkv % 8) != 0)) return set_error(BNF4_ERR_INVALID, "efla: fp16 q, k, v need ld_qkv %% 8 == 0");
             if (p.out_f16 && (((p.ld_out % 8) != 0) || (reinterpret_cast<uintptr_t>(p.out) & 15))) return set_error(BNF4_ERR_INVALID, "efla: fp16 output needs 16-byte aligned rows");
             const unsigned grid = static_cast<unsigned>(ctas);
-            if (p.qkv_f16 && p.out_f16) efla_chunk16_kernel<true, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
+            if (p.qkv_f16 && p.method == 1) {  // the batched driver's case: raw-operand kernel
+                if (p.out_f16) efla_chunk16_m1_kernel<true><<<grid, kChunkWarps * 32, kM1SmemBytes, stream>>>(p);
+                else efla_chunk16_m1_kernel<false><<<grid, kChunkWarps * 32, kM1SmemBytes, stream>>>(p);
+            } else if (p.qkv_f16 && p.out_f16) efla_chunk16_kernel<true, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
             else if (p.qkv_f16) efla_chunk16_kernel<true, false><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
             else if (p.out_f16) efla_chunk16_kernel<false, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
             else efla_chunk16_kernel<false, false><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
