@@ -867,35 +867,6 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
     for (int t0 = 0; t0 < p.T; t0 += kChunk, kbuf ^= 1) {
         cp_async_wait<0>();
         __syncwarp();
-        const __half* rk = rawk + kbuf * kChunk * kM1Stride;
-        // ---------------- per-token scalars: lanes tt and tt + 16 share token tt, alternate 16-byte pieces ----------------
-        {
-            const int tt = lane & 15, hh = lane >> 4;
-            const bool valid = t0 + tt < p.T;
-            float qss = 0.0f, kss = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint4 a = *reinterpret_cast<const uint4*>(rawq + tt * kM1Stride + (2 * j + hh) * 8);
-                const uint4 b = *reinterpret_cast<const uint4*>(rk + tt * kM1Stride + (2 * j + hh) * 8);
-                const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[e])), fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
-                    qss = fmaf(fa.x, fa.x, qss); qss = fmaf(fa.y, fa.y, qss);
-                    kss = fmaf(fb.x, fb.x, kss); kss = fmaf(fb.y, fb.y, kss);
-                }
-            }
-            qss += __shfl_xor_sync(0xffffffffu, qss, 16);
-            kss += __shfl_xor_sync(0xffffffffu, kss, 16);
-            const float q_inv = rsqrtf(qss + p.eps);
-            const float lambda = kss < p.eps ? p.eps : kss;
-            const float beta = sigmoidf_dev((valid ? beta_sh[tt] : 0.0f) + beta_bias);
-            const float alpha = valid ? -expm1f(-(beta * lambda)) / (lambda + p.eps) : 0.0f;
-            if (hh == 0) {
-                alpha_sh[tt] = alpha;
-                qinv_sh[tt] = q_inv;
-            }
-        }
         // ---------------- operand fragments straight from the raw tiles; W^T starts as -V^T ----------------
         uint32_t kf[4][4], qf[4][4];  // per 16-wide d block: B fragments {b0, b1} for tokens 0-7 (regs 0, 1) and 8-15 (regs 2, 3)
 #pragma unroll
@@ -915,7 +886,15 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
                 Wc[mt][nt][2] = -hi.x; Wc[mt][nt][3] = -hi.y;
             }
         }
-        __syncwarp();  // q, v and the scalars' inputs are consumed; alpha / q_inv are visible
+        // The squared norms of k and q are the diagonals of K K^T and Q Q^T, which the tensor cores produce below. They land in
+        // the eight lanes with tq == g / 2 (tokens g and g + 8); each hands token g + 8 to its neighbour lane ^ 1, so sixteen
+        // lanes run the scalar chain for one token each. Those lanes take their beta now: the next chunk's copy overwrites it.
+        const bool diag_lane = tq == (g >> 1);
+        const bool helper_lane = (tq ^ 1) == (g >> 1);
+        const int my_tok = g + (helper_lane ? 8 : 0);
+        float braw = 0.0f;
+        if ((diag_lane || helper_lane) && t0 + my_tok < p.T) braw = beta_sh[my_tok];
+        __syncwarp();  // q, v and beta are consumed
         if (t0 + kChunk < p.T) issue_chunk(t0 + kChunk, kbuf ^ 1);
 
 #pragma unroll
@@ -925,18 +904,34 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
                     mma_f16_16816(Wc[mt][nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
-        float Gc[2][4], Xc[2][4];  // rows t = g (+ 8 for i >= 2), columns s = 8 nt + 2 tq + (i & 1);  Xc = q_t . k_s
+        float Gc[2][4], Xc[2][4], Qc[2][4];  // rows t = g (+ 8 for i >= 2), columns s = 8 nt + 2 tq + (i & 1);  Xc = q_t . k_s, Qc = q_t . q_s
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) Gc[nt][i] = Xc[nt][i] = 0.0f;
+            for (int i = 0; i < 4; ++i) Gc[nt][i] = Xc[nt][i] = Qc[nt][i] = 0.0f;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
                 mma_f16_16816(Gc[nt], kf[ks][0], kf[ks][2], kf[ks][1], kf[ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
                 mma_f16_16816(Xc[nt], qf[ks][0], qf[ks][2], qf[ks][1], qf[ks][3], kf[ks][2 * nt], kf[ks][2 * nt + 1]);
+                mma_f16_16816(Qc[nt], qf[ks][0], qf[ks][2], qf[ks][1], qf[ks][3], qf[ks][2 * nt], qf[ks][2 * nt + 1]);
             }
+        // ---------------- per-token scalars from the diagonals (exact fp16 products accumulated in fp32) ----------------
+        {
+            const int e = g & 1;
+            float kss = e ? Gc[0][1] : Gc[0][0], qss = e ? Qc[0][1] : Qc[0][0];              // token g (valid in the diagonal lanes)
+            const float kss_hi = e ? Gc[1][3] : Gc[1][2], qss_hi = e ? Qc[1][3] : Qc[1][2];  // token g + 8
+            const float k_from = __shfl_xor_sync(0xffffffffu, kss_hi, 1), q_from = __shfl_xor_sync(0xffffffffu, qss_hi, 1);
+            if (helper_lane) { kss = k_from; qss = q_from; }
+            if (diag_lane || helper_lane) {
+                const float lambda = kss < p.eps ? p.eps : kss;
+                const float beta = sigmoidf_dev(braw + beta_bias);
+                alpha_sh[my_tok] = t0 + my_tok < p.T ? -expm1f(-(beta * lambda)) / (lambda + p.eps) : 0.0f;
+                qinv_sh[my_tok] = rsqrtf(qss + p.eps);
+            }
+        }
+        __syncwarp();
         // L[t][s] = a_t G[t][s] (s < t) in fp32 for the substitution; P[t][s] = q_t . k_s (s <= t) in fp16
         {
             const float a_lo = alpha_sh[g], a_hi = alpha_sh[g + 8];
