@@ -852,7 +852,9 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
     const uint32_t q_addr = static_cast<uint32_t>(__cvta_generic_to_shared(rawq)) + lm_tok_off;
     const uint32_t k_addr0 = static_cast<uint32_t>(__cvta_generic_to_shared(rawk)) + lm_tok_off;
     const uint32_t lm_ts_off = static_cast<uint32_t>(((lm_j >> 1) * 8 + lm_r) * kCkTStride + (lm_j & 1) * 8) * 2u;
-    const uint32_t t_addr = static_cast<uint32_t>(__cvta_generic_to_shared(t_sh)) + lm_ts_off;
+    // T^T read transposed: matrices (s 0-7 | t 0-7), (s 8-15 | t 0-7), (s 0-7 | t 8-15), (s 8-15 | t 8-15)
+    const uint32_t tt_addr = static_cast<uint32_t>(__cvta_generic_to_shared(t_sh)) +
+                             static_cast<uint32_t>(((lm_j & 1) * 8 + lm_r) * kCkTStride + (lm_j >> 1) * 8) * 2u;
     const uint32_t p_addr = static_cast<uint32_t>(__cvta_generic_to_shared(p_sh)) + lm_ts_off;
     // K read transposed: matrices (tokens 0-7 | d-tile), (8-15 | d-tile), (0-7 | d-tile + 1), (8-15 | d-tile + 1)
     const uint32_t kt_addr0 = static_cast<uint32_t>(__cvta_generic_to_shared(rawk)) +
@@ -942,7 +944,8 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
                 for (int hr = 0; hr < 2; ++hr) {
                     const int t = g + 8 * hr;
                     const float at = hr ? a_hi : a_lo;
-                    const float l0 = s0 < t ? at * Gc[nt][2 * hr] : 0.0f, l1 = s0 + 1 < t ? at * Gc[nt][2 * hr + 1] : 0.0f;
+                    // the substitution reads L below the diagonal only: no mask needed there; P feeds an MMA and is masked
+                    const float l0 = at * Gc[nt][2 * hr], l1 = at * Gc[nt][2 * hr + 1];
                     const float p0 = s0 <= t ? Xc[nt][2 * hr] : 0.0f, p1 = s0 + 1 <= t ? Xc[nt][2 * hr + 1] : 0.0f;
                     *reinterpret_cast<float2*>(L_sh + t * kChunk + s0) = make_float2(l0, l1);
                     *reinterpret_cast<uint32_t*>(p_sh + t * kCkTStride + s0) = pack_half2(p0, p1);
@@ -967,14 +970,18 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
                 }
                 col[t] = acc;
             }
-            if (lane < kChunk) {
+            if (lane < kChunk) {  // the column as one row of T^T: sixteen halves, two 16-byte stores
+                uint32_t w[8];
 #pragma unroll
-                for (int t = 0; t < kChunk; ++t) t_sh[t * kCkTStride + c] = __float2half_rn(col[t]);
+                for (int t = 0; t < kChunk; t += 2) w[t >> 1] = pack_half2(col[t], col[t + 1]);
+                uint4* dst = reinterpret_cast<uint4*>(t_sh + c * kCkTStride);
+                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
         }
         __syncwarp();
         uint32_t tf[4], pf[4];
-        ldmatrix_x4(tf, t_addr);
+        ldmatrix_x4_trans(tf, tt_addr);  // T^T stored [s][t]: transposed on the way in, the fragments are those of T stored [t][s]
         ldmatrix_x4(pf, p_addr);
         // ---------------- U~^T = (diag(a) W)^T T^T: the columns (tokens) of -W^T are scaled by -a ----------------
         float na[2][2], qi[2][2];  // [nt][e]: token 8 nt + 2 tq + e
