@@ -928,8 +928,10 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
             if (helper_lane) { kss = k_from; qss = q_from; }
             if (diag_lane || helper_lane) {
                 const float lambda = kss < p.eps ? p.eps : kss;
-                const float beta = sigmoidf_dev(braw + beta_bias);
-                alpha_sh[my_tok] = t0 + my_tok < p.T ? -expm1f(-(beta * lambda)) / (lambda + p.eps) : 0.0f;
+                // sigmoid and the final quotient with the fast exponential / division (about 2 ulp each: far below the fp16
+                // rounding of every operand alpha touches); expm1f keeps its accuracy for small beta * lambda
+                const float beta = __fdividef(1.0f, 1.0f + __expf(-(braw + beta_bias)));
+                alpha_sh[my_tok] = t0 + my_tok < p.T ? __fdividef(-expm1f(-(beta * lambda)), lambda + p.eps) : 0.0f;
                 qinv_sh[my_tok] = rsqrtf(qss + p.eps);
             }
         }
