@@ -997,8 +997,11 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
         uint32_t Up[4][4];
 #pragma unroll
         for (int mt = 0; mt < 4; ++mt) {
-            const uint32_t w0 = pack_half2(na[0][0] * Wc[mt][0][0], na[0][1] * Wc[mt][0][1]), w1 = pack_half2(na[0][0] * Wc[mt][0][2], na[0][1] * Wc[mt][0][3]);
-            const uint32_t w2 = pack_half2(na[1][0] * Wc[mt][1][0], na[1][1] * Wc[mt][1][1]), w3 = pack_half2(na[1][0] * Wc[mt][1][2], na[1][1] * Wc[mt][1][3]);
+            // packed fp32 pairs (tokens 2 tq and 2 tq + 1): each half rounds like the scalar multiply
+            const float2 na0 = make_float2(na[0][0], na[0][1]), na1 = make_float2(na[1][0], na[1][1]);
+            const float2 x0 = __fmul2_rn(na0, make_float2(Wc[mt][0][0], Wc[mt][0][1])), x1 = __fmul2_rn(na0, make_float2(Wc[mt][0][2], Wc[mt][0][3]));
+            const float2 x2 = __fmul2_rn(na1, make_float2(Wc[mt][1][0], Wc[mt][1][1])), x3 = __fmul2_rn(na1, make_float2(Wc[mt][1][2], Wc[mt][1][3]));
+            const uint32_t w0 = pack_half2(x0.x, x0.y), w1 = pack_half2(x1.x, x1.y), w2 = pack_half2(x2.x, x2.y), w3 = pack_half2(x3.x, x3.y);
             float Uc[2][4];
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) mma_f16_16816_zero(Uc[nt], w0, w1, w2, w3, tf[2 * nt], tf[2 * nt + 1]);
@@ -1018,8 +1021,9 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
                     mma_f16_16816(Yc[nt], Sh[mt][ks][0], Sh[mt][ks][1], Sh[mt][ks][2], Sh[mt][ks][3], qf[ks][2 * nt], qf[ks][2 * nt + 1]);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                Yc[nt][0] *= qi[nt][0]; Yc[nt][1] *= qi[nt][1];
-                Yc[nt][2] *= qi[nt][0]; Yc[nt][3] *= qi[nt][1];
+                const float2 q2 = make_float2(qi[nt][0], qi[nt][1]);
+                const float2 lo = __fmul2_rn(q2, make_float2(Yc[nt][0], Yc[nt][1])), hi = __fmul2_rn(q2, make_float2(Yc[nt][2], Yc[nt][3]));
+                Yc[nt][0] = lo.x; Yc[nt][1] = lo.y; Yc[nt][2] = hi.x; Yc[nt][3] = hi.y;
             }
             if constexpr (OUT16) {
                 stmatrix_x4_trans(y_addr + mt * 32, pack_half2(Yc[0][0], Yc[0][1]), pack_half2(Yc[0][2], Yc[0][3]), pack_half2(Yc[1][0], Yc[1][1]),
