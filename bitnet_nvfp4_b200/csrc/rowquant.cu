@@ -305,9 +305,14 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
     const int k_atoms = sf_k_atoms(p.cols_out);
     const unsigned rows = static_cast<unsigned>(p.rows);
     const bool cols_pow2 = (p.cols_in & (p.cols_in - 1)) == 0;
+    // token / position indices wrap at powers of two in every model configuration: masks instead of divisions per row
+    const bool row_mod_pow2 = p.row_mod > 0 && (p.row_mod & (p.row_mod - 1)) == 0;
+    const bool pos_mod_pow2 = p.pos_mod > 0 && (p.pos_mod & (p.pos_mod - 1)) == 0;
+    const int rpm_shift = (p.rows_per_member > 0 && (p.rows_per_member & (p.rows_per_member - 1)) == 0) ? __ffs(p.rows_per_member) - 1 : -1;
     const float inv_cols = 1.0f / static_cast<float>(p.cols_in);
     for (unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8u) {
-        const int member = p.rows_per_member > 0 ? static_cast<int>(row / static_cast<unsigned>(p.rows_per_member)) : 0;
+        // rows per member is a power of two in every model configuration: a shift instead of a division per row
+        const int member = p.rows_per_member > 0 ? static_cast<int>(rpm_shift >= 0 ? row >> rpm_shift : row / static_cast<unsigned>(p.rows_per_member)) : 0;
         const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
         const int pair = member >> 1;
         const float ns = p.rows_per_member > 0 ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
@@ -318,7 +323,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
         int tok = 0;
         float a_r[4] = {0.f, 0.f, 0.f, 0.f};
         if constexpr (FE == FE_EMBED_LOWRANK) {
-            const int trow = p.row_mod > 0 ? static_cast<int>(row % static_cast<unsigned>(p.row_mod)) : static_cast<int>(row);
+            const int trow = p.row_mod > 0 ? static_cast<int>(row_mod_pow2 ? row & static_cast<unsigned>(p.row_mod - 1) : row % static_cast<unsigned>(p.row_mod)) : static_cast<int>(row);
             tok = static_cast<int>(p.tokens[static_cast<size_t>(trow) * p.token_stride]);
             if (ns != 0.0f) {
                 const int8_t* A = p.embA + static_cast<size_t>(pair) * p.embA_pair_stride + static_cast<size_t>(tok) * p.rank;
@@ -388,11 +393,11 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
             } else if constexpr (FE == FE_POS_GELU_ABSMEAN) {
                 size_t in_row = static_cast<size_t>(row);
                 if (p.gather_rows > 0) {  // per-member table of rows indexed by token
-                    const unsigned ti = p.row_mod > 0 ? row % static_cast<unsigned>(p.row_mod) : row;
+                    const unsigned ti = p.row_mod > 0 ? (row_mod_pow2 ? row & static_cast<unsigned>(p.row_mod - 1) : row % static_cast<unsigned>(p.row_mod)) : row;
                     in_row = static_cast<size_t>(member) * p.gather_rows + p.tokens[static_cast<size_t>(ti) * p.token_stride];
                 }
                 const float* src = p.in_f32 + in_row * p.ld_in;
-                const int prow = p.pos_mod > 0 ? (row_in_member % p.pos_mod) : 0;
+                const int prow = p.pos_mod > 0 ? (pos_mod_pow2 ? row_in_member & (p.pos_mod - 1) : row_in_member % p.pos_mod) : 0;
                 const float* pos = p.pos + static_cast<size_t>(prow) * p.cols_in;
                 uint32_t pw[4] = {0x0u, 0x0u, 0x0u, 0x0u};
                 const bool has_pn = p.pos_noise != nullptr;
