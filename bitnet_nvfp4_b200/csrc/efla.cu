@@ -448,9 +448,11 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_kernel(const
     static_assert(kChunk * kCkYStrideH * 2 <= 2 * kChunk * kCkHStride * 2, "output staging fits the -K / Q^ region");
     const long long unit = static_cast<long long>(blockIdx.x) * kChunkWarps + warp;  // (sequence, head)
     if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
-    const long long seq = unit / p.heads;
-    const int h = static_cast<int>(unit - seq * p.heads);
-    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
+    // the grid has fewer than 2^32 / 4 CTAs: 32-bit divisions (a 64-bit one costs more than a chunk's scalar work)
+    const unsigned useq = static_cast<unsigned>(unit) / static_cast<unsigned>(p.heads);
+    const long long seq = useq;
+    const int h = static_cast<int>(static_cast<unsigned>(unit) - useq * static_cast<unsigned>(p.heads));
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[useq / static_cast<unsigned>(p.seqs_per_bias)] : p.beta_bias;
     const int g = lane >> 2, tq = lane & 3;
 
     // state S^T as A fragments: Sh[mt][ks][i] holds S[d][n] for n = 16 mt + g (+ 8 for odd i), d = 16 ks + 2 tq + {0, 1} (+ 8 for i >= 2)
@@ -800,9 +802,11 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
     __half* p_sh = reinterpret_cast<__half*>(wsm + kM1P);
     const long long unit = static_cast<long long>(blockIdx.x) * kChunkWarps + warp;  // (sequence, head)
     if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
-    const long long seq = unit / p.heads;
-    const int h = static_cast<int>(unit - seq * p.heads);
-    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[seq / p.seqs_per_bias] : p.beta_bias;
+    // the grid has fewer than 2^32 / 4 CTAs: 32-bit divisions (a 64-bit one costs more than a chunk's scalar work)
+    const unsigned useq = static_cast<unsigned>(unit) / static_cast<unsigned>(p.heads);
+    const long long seq = useq;
+    const int h = static_cast<int>(static_cast<unsigned>(unit) - useq * static_cast<unsigned>(p.heads));
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[useq / static_cast<unsigned>(p.seqs_per_bias)] : p.beta_bias;
     const int g = lane >> 2, tq = lane & 3;
 
     uint32_t Sh[4][4][4];  // state S^T as A fragments, as in efla_chunk16_kernel
@@ -1088,6 +1092,7 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
     if (regs_ok && p.variant != BNF4_EFLA_GENERIC) {
         const bool chunked = p.variant == BNF4_EFLA_CHUNKED || (p.variant == BNF4_EFLA_AUTO && g_efla_chunked != 0);
         const long long units = p.seqs * static_cast<long long>(p.heads);
+        if (units > 0x7fffffffLL) return set_error(BNF4_ERR_INVALID, "efla: more than 2^31 (sequence, head) units in one call");
         const long long ctas = (units + kScanWarps - 1) / kScanWarps;
         static_assert(kScanWarps == kChunkWarps, "one grid computation for both register-state kernels");
         // function attributes are per device: set once for each device this process uses
