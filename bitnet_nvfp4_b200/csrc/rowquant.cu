@@ -512,7 +512,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                     for (int e = 0; e < 16; e += 2) {  // packed fp32 pairs: each half rounds like the scalar instruction
                         float2 n = make_float2(vf[i][e], vf[i][e + 1]);
                         if constexpr (kNorm) n = __fmul2_rn(n, make_float2(inv, inv));
-                        am = fmaxf(am, fmaxf(fabsf(n.x), fabsf(n.y)));
+                        am = fmax3(am, fabsf(n.x), fabsf(n.y));
                         const float2 t2 = __fadd2_rn(n, make_float2(M, M));
                         tq[e] = t2.x;
                         tq[e + 1] = t2.y;
@@ -566,6 +566,12 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
 #pragma unroll
             for (int vg = 0; vg < NV / 4; ++vg) {
                 if (4 * vg < p.nvec) {
+                    if (p.nvec == 4 && vg == 0 && (reinterpret_cast<uintptr_t>(p.t_out) & 15) == 0) {  // the four column groups of the fused q | k | v | beta projection: one 16-byte store
+                        const int t0 = __reduce_add_sync(0xffffffffu, tacc[0]), t1 = __reduce_add_sync(0xffffffffu, tacc[1]);
+                        const int t2 = __reduce_add_sync(0xffffffffu, tacc[2]), t3 = __reduce_add_sync(0xffffffffu, tacc[3]);
+                        if (lane == 0) *reinterpret_cast<int4*>(p.t_out + static_cast<size_t>(row) * 4) = make_int4(t0, t1, t2, t3);
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int v = 4 * vg + j;
@@ -610,7 +616,7 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
             int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
             if (!rc) rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
             if (rc) return rc;
-            // persistent CTAs: exactly as many as are resident at once (each holds a 33 KB copy of the table)
+            // persistent CTAs: exactly as many as are resident at once (each loads its 1 KB copy of the table once)
             auto run = [&](auto kernel) -> int {
                 int per_sm = 0;
                 int rc2 = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, warps * 32, 0), "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
