@@ -317,6 +317,7 @@ def main():
                          "batch 16, rank-4 perturbations")
     ap.add_argument("--wave", type=int, default=0, help="members per wave (0 = library default)")
     ap.add_argument("--exact-scan", action="store_true", help="per-token EFLA kernel (fp16 state rounding after every token) instead of the chunked one")
+    ap.add_argument("--graph", action="store_true", help="replay every wave of the evaluation as one CUDA graph (the reference's --cuda_graph)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-pairs", type=int, default=6, help="largest CPU sample, in antithetic pairs (about 2 s of CPU work each on 16 threads)")
     ap.add_argument("--cpu-seconds", type=float, default=20.0, help="CPU work per sample the reference arm / CPU baseline aims for")
@@ -422,6 +423,8 @@ def main():
 
     model = population.PopulationModel(cfg)
     model.set_weights(weights)
+    if args.graph:
+        model.set_graph(True)
     if args.train:
         # the reference's per-epoch log (src/train_efla_lm.cpp:5733-5800) for `--epochs` epochs, then one JSON line with the
         # throughput definitions of :5786-5792 averaged over the epochs after the first
@@ -592,6 +595,8 @@ def main():
         "tokens_per_s_eval": tokens_per_s_eval, "device_bytes": model.device_bytes, "wave_members": wave_members,
         "efla_scan_kernel": "per-token (fp16 state rounding every token)" if args.exact_scan else "chunked (16 tokens per step, fp16 state rounding every chunk)",
     }
+    if args.graph:
+        out["cuda_graph_launches"] = model.graph_launches
     if world > 1:
         out["allgather_exposed_ms"] = coll_ms.get("loss_allgather")
         out["collectives_exposed_ms"] = coll_ms

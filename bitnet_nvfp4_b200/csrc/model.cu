@@ -130,6 +130,28 @@ struct Model {
     float* ff1_f = nullptr;                  // [2R][F] fp32 base product of ff1
     int8_t* ff1_q = nullptr;                 // [2R][F] int8 GELU output
 
+    // optional replay of a wave's launch sequence as a CUDA graph (the reference's --cuda_graph, src/train_efla_lm.cpp:3779-3819):
+    // a wave is identified by everything its launches take from the host; the first run of a wave is eager (it fills lazily
+    // built tables and sets function attributes), the second is captured on a private stream, later ones are graph launches.
+    // A captured wave leaves its losses in the model's own buffer; a small copy behind the graph takes them to the caller's.
+    struct WaveGraph {
+        int p0, nm, opt_tma, opt_chunked;
+        uint32_t sigma_bits;
+        int seen = 0;         // eager runs so far
+        bool failed = false;  // the capture was refused: this wave stays eager
+        cudaGraphExec_t exec = nullptr;
+        int launches = 0;
+    };
+    bool use_graph = false;
+    std::vector<WaveGraph> graphs;
+    cudaStream_t cap_stream = nullptr;
+    long long graph_launches = 0;
+    void drop_graphs() {
+        for (WaveGraph& g : graphs)
+            if (g.exec) cudaGraphExecDestroy(g.exec);
+        graphs.clear();
+    }
+
     // optional per-kernel-class timing with CUDA events on the launching stream
     bool timing = false;
     struct Span { int cls; cudaEvent_t a, b; };
@@ -386,6 +408,49 @@ int run_wave(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStrea
     return BNF4_OK;
 }
 
+// run_wave, replayed from a captured graph when the model's graph mode is on (never while the timing breakdown records events:
+// events recorded during a capture cannot be read back). Results are those of the eager launches: same kernels, same arguments.
+int run_wave_cached(Model& m, int p0, int nm, float sigma, float* losses_out, cudaStream_t st) {
+    if (!m.use_graph || m.timing) return run_wave(m, p0, nm, sigma, losses_out, st);
+    const uint32_t sb = __builtin_bit_cast(uint32_t, sigma);
+    Model::WaveGraph* e = nullptr;
+    for (Model::WaveGraph& g : m.graphs)
+        if (g.p0 == p0 && g.nm == nm && g.sigma_bits == sb && g.opt_tma == g_gemm_allow_tma_store && g.opt_chunked == g_efla_chunked) e = &g;
+    if (e == nullptr) {
+        if (m.graphs.size() >= 1024) m.drop_graphs();  // more distinct waves than any population makes: start over
+        Model::WaveGraph g = {};
+        g.p0 = p0; g.nm = nm; g.sigma_bits = sb; g.opt_tma = g_gemm_allow_tma_store; g.opt_chunked = g_efla_chunked;
+        m.graphs.push_back(g);
+        e = &m.graphs.back();
+    }
+    if (e->failed || e->seen == 0) {
+        ++e->seen;
+        return run_wave(m, p0, nm, sigma, losses_out, st);
+    }
+    if (e->exec == nullptr) {
+        if (m.cap_stream == nullptr && cudaStreamCreateWithFlags(&m.cap_stream, cudaStreamNonBlocking) != cudaSuccess) m.cap_stream = nullptr;
+        cudaGraph_t graph = nullptr;
+        bool ok = m.cap_stream != nullptr && cudaStreamBeginCapture(m.cap_stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if (ok) {
+            const int rc = run_wave(m, p0, nm, sigma, m.losses, m.cap_stream);  // nothing executes: the launches become nodes
+            ok = cudaStreamEndCapture(m.cap_stream, &graph) == cudaSuccess && graph != nullptr && rc == BNF4_OK;
+        }
+        if (ok) ok = cudaGraphInstantiate(&e->exec, graph, 0) == cudaSuccess;
+        if (graph) cudaGraphDestroy(graph);
+        if (!ok) {
+            cudaGetLastError();
+            e->exec = nullptr;
+            e->failed = true;
+            return run_wave(m, p0, nm, sigma, losses_out, st);
+        }
+        e->launches = m.launches_per_wave;
+    }
+    m.launches_per_wave = e->launches;
+    ++m.graph_launches;
+    TRY(check_cuda(cudaGraphLaunch(e->exec, st), "cudaGraphLaunch(wave)"));
+    if (losses_out == m.losses) return BNF4_OK;
+    return check_cuda(cudaMemcpyAsync(losses_out, m.losses, static_cast<size_t>(nm) * sizeof(float), cudaMemcpyDeviceToDevice, st), "cudaMemcpyAsync(wave losses)");
+}
 
 // Offsets of the matrices inside E_all, in the order emb, win, per layer (wq, wk, wv, wbeta, ff1, ff2), head.
 struct DenseLayout {
@@ -708,6 +773,8 @@ int bnf4_model_destroy(void* handle) {
     if (!handle) return BNF4_OK;
     Model* m = M(handle);
     cudaDeviceSynchronize();
+    m->drop_graphs();
+    if (m->cap_stream) cudaStreamDestroy(m->cap_stream);
     for (void* p : m->allocs) cudaFree(p);
     if (m->h_step) cudaFreeHost(m->h_step);
     if (m->d_step_w) cudaFree(m->d_step_w);
@@ -1017,7 +1084,7 @@ int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* l
     const int wave_pairs = m.W / 2;
     for (int p = 0; p < pair_count; p += wave_pairs) {
         const int np = std::min(wave_pairs, pair_count - p);
-        TRY(run_wave(m, pair_begin + p, 2 * np, m.sigma, losses + 2 * static_cast<size_t>(p), S(stream)));
+        TRY(run_wave_cached(m, pair_begin + p, 2 * np, m.sigma, losses + 2 * static_cast<size_t>(p), S(stream)));
     }
     return BNF4_OK;
 }
@@ -1025,7 +1092,7 @@ int bnf4_model_eval_pairs(void* handle, int pair_begin, int pair_count, float* l
 int bnf4_model_eval_base(void* handle, float* loss, void* stream) {
     if (!handle || !loss) return set_error(BNF4_ERR_INVALID, "model_eval_base: null argument");
     Model& m = *M(handle);
-    TRY(run_wave(m, 0, 2, 0.0f, m.losses, S(stream)));
+    TRY(run_wave_cached(m, 0, 2, 0.0f, m.losses, S(stream)));
     return check_cuda(cudaMemcpyAsync(loss, m.losses, sizeof(float), cudaMemcpyDeviceToDevice, S(stream)), "cudaMemcpyAsync(loss)");
 }
 
@@ -1139,6 +1206,19 @@ int bnf4_model_set_timing(void* handle, int enable) {
     m.spans.clear();
     return BNF4_OK;
 }
+
+int bnf4_model_set_graph(void* handle, int enable) {
+    if (!handle) return set_error(BNF4_ERR_INVALID, "model_set_graph: null handle");
+    Model& m = *M(handle);
+    if (enable == 0 && m.use_graph) {
+        TRY(check_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));  // a cached graph may still be running
+        m.drop_graphs();
+    }
+    m.use_graph = enable != 0;
+    return BNF4_OK;
+}
+
+long long bnf4_model_graph_launches(void* handle) { return handle ? M(handle)->graph_launches : 0; }
 
 int bnf4_model_num_kernel_classes(void) { return kNumClasses; }
 const char* bnf4_model_kernel_class_name(int cls) { return (cls >= 0 && cls < kNumClasses) ? kClassNames[cls] : ""; }

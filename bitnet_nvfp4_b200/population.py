@@ -79,6 +79,8 @@ _l.register({
     "bnf4_model_get_optimizer_state": (c_int, [c_void_p, c_void_p, c_void_p]),
     "bnf4_model_set_optimizer_state": (c_int, [c_void_p, c_void_p, c_void_p]),
     "bnf4_model_set_timing": (c_int, [c_void_p, c_int]),
+    "bnf4_model_set_graph": (c_int, [c_void_p, c_int]),
+    "bnf4_model_graph_launches": (C.c_longlong, [c_void_p]),
     "bnf4_model_num_kernel_classes": (c_int, []),
     "bnf4_model_kernel_class_name": (C.c_char_p, [c_int]),
     "bnf4_model_get_timing": (c_int, [c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_longlong), c_int]),
@@ -269,6 +271,15 @@ class PopulationModel:
         with _span(spans, "z_allgather"):
             gather_z_shards(self._z_all, self._z_entries, rank, world, group)
         _l.check(self.lib.bnf4_model_update_apply(self.h, pair_weights.data_ptr(), self._z_all.data_ptr(), C.byref(u), _stream()))
+
+    def set_graph(self, enable: bool):
+        """Replay every wave of the evaluation as one CUDA graph (the reference's --cuda_graph, src/train_efla_lm.cpp:3779-3819):
+        first run of a wave eager, second captured, then one graph launch per wave. Same results as the eager launches."""
+        _l.check(self.lib.bnf4_model_set_graph(self.h, int(enable)))
+
+    @property
+    def graph_launches(self) -> int:
+        return int(self.lib.bnf4_model_graph_launches(self.h))
 
     def set_timing(self, enable: bool):
         _l.check(self.lib.bnf4_model_set_timing(self.h, int(enable)))

@@ -534,6 +534,16 @@ int bnf4_model_get_optimizer_state(void* handle, float* h_shadow, float* h_ema);
 int bnf4_model_set_optimizer_state(void* handle, const float* h_shadow, const float* h_ema);
 /* Members evaluated per wave (the configured value, or the library's choice when the configuration says 0). */
 int bnf4_model_wave_members(void* handle);
+/* CUDA-graph replay of the evaluation (replaces the reference's --cuda_graph mode, get_or_create_graph in
+ * src/train_efla_lm.cpp:3779-3819). When enabled, bnf4_model_eval_pairs / _eval_base / _es_step launch each wave of members
+ * as one graph: a wave (its first pair, member count, sigma) runs eagerly the first time it is seen, is captured
+ * on a stream of the library's own the second time, and is a single cudaGraphLaunch into the caller's stream from then on (the
+ * per-step noise and the re-quantised weights live at fixed addresses, so a captured wave stays valid across steps). Same
+ * kernels, same arguments, same results. The rank-0 (dense) mode and runs with the timing breakdown enabled stay eager; a wave
+ * whose capture the runtime refuses stays eager too. Disabling synchronises the device and drops the cached graphs.
+ * bnf4_model_graph_launches counts the graph launches since the model was created. */
+int bnf4_model_set_graph(void* handle, int enable);
+long long bnf4_model_graph_launches(void* handle);
 /* Optional timing breakdown: when enabled, the driver brackets every kernel class with CUDA events on the launching
  * stream. bnf4_model_get_timing synchronises and returns accumulated milliseconds and launches per class since the
  * last bnf4_model_set_timing call. */

@@ -302,6 +302,34 @@ def test_single_call_es_step_equals_the_composed_calls():
         population.es_step_native(m, 3, 0, 7, rank=0, world=2)   # pairs not a multiple of world
     m.close()
 
+def test_graph_replay_equals_the_eager_launches():
+    """Graph mode (every wave of the evaluation replayed as one CUDA graph, the reference's --cuda_graph) against the eager
+    launches over four ES steps of two waves each: losses, weights and optimiser state bit-identical; the first step of a wave
+    is eager, the second is captured, so six of the eight waves and two of the three base evaluations are graph launches."""
+    from bitnet_nvfp4_b200 import population, synth
+    cfg = population.Config(hidden=128, layers=2, seq=16, batch=4, heads=2, rank=1, max_pairs=8, wave_members=8)
+    w = synth.init_weights(cfg)
+    tok, tgt = synth.sample_batch(synth.zipf_corpus(1 << 16, 1.1, 123), cfg.batch, cfg.seq, 7)
+    out = []
+    for graph in (False, True):
+        m = population.PopulationModel(cfg)
+        m.set_weights(w)
+        m.set_tokens(tok, tgt)
+        m.set_graph(graph)
+        losses = [population.es_step(m, 3, e, 8, lr=0.5, thresh=0.004).cpu().numpy().copy() for e in range(4)]
+        base = [m.eval_base().cpu().numpy().copy() for _ in range(3)]
+        assert m.graph_launches == (8 if graph else 0)
+        out.append((losses + base, m.get_weights(), m.get_optimizer_state()))
+        m.set_graph(False)   # drops the cached graphs; the model stays usable
+        out[-1][0].append(m.eval_base().cpu().numpy().copy())
+        m.close()
+    (la, wa, (sa, ea)), (lb, wb, (sb, eb)) = out
+    assert all(np.array_equal(x, y) for x, y in zip(la, lb))
+    assert not np.array_equal(la[0], la[1])   # the steps really differ
+    assert all(np.array_equal(wa[k], wb[k]) for k in wa)
+    assert np.array_equal(sa, sb) and np.array_equal(ea, eb)
+
+
 @pytest.mark.parametrize("nshards", [2, 4])
 def test_sharded_update_is_bit_identical(nshards):
     """Z of every ternary matrix computed in row shards (one call per emulated rank into one buffer, which is what the
