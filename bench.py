@@ -290,16 +290,21 @@ def run_kernel(args):
         codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
         sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
         t = torch.zeros(rows, 4, dtype=torch.int32, device="cuda")
+        nvec = 4 if args.fe == "norm" else (1 if args.half else 4)   # the step's: 4 fused q | k | v | beta projections; 1 for ff1
         common = dict(rows=rows, cols_in=hid, cols_out=hid, rows_per_member=4096, ld_in=hid, norm_scale=1.0, out_codes=codes, out_sf=sf,
-                      tvec=tv, tvec_pair_stride=4 * hid, nvec=4, t_out=t)
+                      tvec=tv, tvec_pair_stride=4 * hid, nvec=nvec, t_out=t)
         if args.fe == "norm":   # abs-mean norm of int8 rows (after the residual-add GEMM epilogue)
             run = lambda: H.rowquant(H.FE_ABSMEAN, in_i8=x, **common)
             nbytes = rows * (hid + hid // 2 + hid // 16 + 16)
+        elif args.half:         # residual add of a branch travelling as IEEE halves (the scan's output in the step) + abs-mean norm
+            yh = (yv * 0.01).half()
+            run = lambda: H.rowquant(H.FE_ADD_ABSMEAN, sigma=0.125, inout_i8=x, in_f32=yh, in_f16=1, add_scale=100.0, **common)
+            nbytes = rows * (2 * hid + hid + hid + hid // 2 + hid // 16 + 4)
         else:                   # residual add of an fp32 branch + abs-mean norm
             run = lambda: H.rowquant(H.FE_ADD_ABSMEAN, sigma=0.125, inout_i8=x, in_f32=yv, add_scale=1.0, **common)
             nbytes = rows * (4 * hid + hid + hid + hid // 2 + hid // 16 + 16)
         ms = _event_ms(run, args.iters)
-        out.update(case=f"rows={rows} hidden={hid} front-end={args.fe}", ms=ms, achieved=nbytes / ms / 1e6, unit="GB/s", frac=nbytes / ms / 1e6 / peaks["hbm_gbs"])
+        out.update(case=f"rows={rows} hidden={hid} front-end={args.fe}" + (" half branch" if args.half and args.fe == "add" else ""), ms=ms, achieved=nbytes / ms / 1e6, unit="GB/s", frac=nbytes / ms / 1e6 / peaks["hbm_gbs"])
     assert H.device_error() == 0
     print(json.dumps(out))
 
@@ -331,7 +336,7 @@ def main():
     ap.add_argument("--k", type=int, default=512)
     ap.add_argument("--rank", type=int, default=-1, help="--kernel gemm / --sweep: rank of the perturbation term (defaults 1 / 4)")
     ap.add_argument("--epilogue", default="f32", choices=["f32", "f16", "gelu_i8", "gelu_fp4", "add_i8"])
-    ap.add_argument("--half", action="store_true", help="--kernel efla: q | k | v and the output as IEEE halves")
+    ap.add_argument("--half", action="store_true", help="--kernel efla: q | k | v and the output as IEEE halves; --kernel rowquant --fe add: the branch as halves")
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--fe", default="add", choices=["add", "norm"])
     ap.add_argument("--train", action="store_true",

@@ -317,6 +317,20 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
         const int pair = member >> 1;
         const float ns = p.rows_per_member > 0 ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
 
+        // The row this warp takes next starts its trip from DRAM to L2 now: a warp holds one row's loads at a time, too few
+        // bytes in flight to cover the DRAM latency with the narrow inputs (int8 rows, a branch travelling as halves).
+        if constexpr (FE == FE_ADD_ABSMEAN || FE == FE_ABSMEAN) {
+            const unsigned nrow = row + gridDim.x * 8u;
+            if (nrow < rows && lane * 16 < p.cols_in) {
+                if constexpr (FE == FE_ABSMEAN) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.in_i8 + static_cast<size_t>(nrow) * p.ld_in + lane * 16));
+                } else if (p.in_f16) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.inout_i8 + static_cast<size_t>(nrow) * p.cols_in + lane * 16));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const __half*>(p.in_f32) + static_cast<size_t>(nrow) * p.ld_in + lane * 16));
+                }
+            }
+        }
+
         // ---------------- stage 1: integer values of the row as floats ----------------
         float vf[NB][16];
         uint32_t sum_abs = 0;  // sum of |value| over this lane's elements (exact integer)
