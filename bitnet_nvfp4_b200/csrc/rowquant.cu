@@ -321,12 +321,17 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
         // bytes in flight to cover the DRAM latency with the narrow inputs (int8 rows, a branch travelling as halves).
         if constexpr (FE == FE_ADD_ABSMEAN || FE == FE_ABSMEAN) {
             const unsigned nrow = row + gridDim.x * 8u;
-            if (nrow < rows && lane * 16 < p.cols_in) {
-                if constexpr (FE == FE_ABSMEAN) {
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.in_i8 + static_cast<size_t>(nrow) * p.ld_in + lane * 16));
-                } else if (p.in_f16) {
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.inout_i8 + static_cast<size_t>(nrow) * p.cols_in + lane * 16));
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const __half*>(p.in_f32) + static_cast<size_t>(nrow) * p.ld_in + lane * 16));
+            if (nrow < rows) {
+#pragma unroll
+                for (int i = 0; i < NB; ++i) {
+                    const int k0 = (lane + 32 * i) << 4;
+                    if (k0 >= p.cols_in) continue;
+                    if constexpr (FE == FE_ABSMEAN) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.in_i8 + static_cast<size_t>(nrow) * p.ld_in + k0));
+                    } else if (p.in_f16) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.inout_i8 + static_cast<size_t>(nrow) * p.cols_in + k0));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const __half*>(p.in_f32) + static_cast<size_t>(nrow) * p.ld_in + k0));
+                    }
                 }
             }
         }
