@@ -222,7 +222,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // CTAs working at the same time share rows of A through L2). Three roles run concurrently on different tiles:
 // the producer prefetches operands up to kStages k-blocks ahead, the MMA warp fills one of two TMEM
 // accumulators while the sixteen epilogue warps drain the other one.
-template <int EPI>
+// R4: the instance for rank-4 perturbation terms (its epilogue applies the four factors with packed multiply-adds); every other
+// rank runs the R4 = false instance, whose code is what it was before the specialisation existed.
+template <int EPI, bool R4>
 __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ CUtensorMap map_b,
                                                                  const __grid_constant__ CUtensorMap map_d,
@@ -603,7 +605,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             }
             if (p.rank > 0 && row_ok) {
                 // sum_r t[r]*A[n][r] is an integer below 2^24: float products and sums are exact
-                if (a_staged && p.rank == 1) {
+                if constexpr (R4) {
+                    if (a_staged) {
+                        const float2 ls2 = make_float2(lsign, lsign);
+                        const float2 t0 = make_float2(tr[0], tr[0]), t1 = make_float2(tr[1], tr[1]), t2 = make_float2(tr[2], tr[2]), t3 = make_float2(tr[3], tr[3]);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 a0 = *reinterpret_cast<const float4*>(loraA_sh + 4 * j), a1 = *reinterpret_cast<const float4*>(loraA_sh + 32 + 4 * j);
+                            const float4 a2 = *reinterpret_cast<const float4*>(loraA_sh + 64 + 4 * j), a3 = *reinterpret_cast<const float4*>(loraA_sh + 96 + 4 * j);
+                            float2 lo = __fmul2_rn(t0, make_float2(a0.x, a0.y)), hi = __fmul2_rn(t0, make_float2(a0.z, a0.w));
+                            lo = __ffma2_rn(t1, make_float2(a1.x, a1.y), lo); hi = __ffma2_rn(t1, make_float2(a1.z, a1.w), hi);
+                            lo = __ffma2_rn(t2, make_float2(a2.x, a2.y), lo); hi = __ffma2_rn(t2, make_float2(a2.z, a2.w), hi);
+                            lo = __ffma2_rn(t3, make_float2(a3.x, a3.y), lo); hi = __ffma2_rn(t3, make_float2(a3.z, a3.w), hi);
+                            lo = __ffma2_rn(ls2, lo, make_float2(v[4 * j + 0], v[4 * j + 1]));
+                            hi = __ffma2_rn(ls2, hi, make_float2(v[4 * j + 2], v[4 * j + 3]));
+                            v[4 * j + 0] = lo.x; v[4 * j + 1] = lo.y; v[4 * j + 2] = hi.x; v[4 * j + 3] = hi.y;
+                        }
+                    } else {
+                        const int8_t* Ap = p.lora_A + static_cast<size_t>(pair) * p.lora_A_pair_stride + static_cast<size_t>(col0) * 4;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) {
+                                float pert = 0.0f;
+#pragma unroll
+                                for (int r = 0; r < 4; ++r) pert = fmaf(tr[r], static_cast<float>(Ap[j * 4 + r]), pert);
+                                v[j] = fmaf(lsign, pert, v[j]);
+                            }
+                        }
+                    }
+                } else if (a_staged && p.rank == 1) {
                     const float2 tr2 = make_float2(tr[0], tr[0]), ls2 = make_float2(lsign, lsign);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -887,7 +917,7 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint
     return BNF4_OK;
 }
 
-template <int EPI>
+template <int EPI, bool R4>
 int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const KernelArgs& args, dim3 grid,
              cudaStream_t stream) {
     // function attributes are per device: set once for each device this process uses
@@ -895,11 +925,11 @@ int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError(), "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
+        const cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI, R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_nvfp4_kernel)");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    gemm_nvfp4_kernel<EPI><<<grid, kThreads, kSmemAlloc, stream>>>(ma, mb, md, args);
+    gemm_nvfp4_kernel<EPI, R4><<<grid, kThreads, kSmemAlloc, stream>>>(ma, mb, md, args);
     return check_launch("gemm_nvfp4_kernel");
 }
 
@@ -983,11 +1013,11 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     if (rc) return rc;
     const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
     switch (p.epilogue) {
-        case EPI_F32: return launch_t<EPI_F32>(ma, mb, md, args, grid, stream);
-        case EPI_GELU_I8: return launch_t<EPI_GELU_I8>(ma, mb, md, args, grid, stream);
-        case EPI_GELU_FP4: return launch_t<EPI_GELU_FP4>(ma, mb, md, args, grid, stream);
-        case EPI_ADD_I8: return launch_t<EPI_ADD_I8>(ma, mb, md, args, grid, stream);
-        case EPI_F16: return launch_t<EPI_F16>(ma, mb, md, args, grid, stream);
+        case EPI_F32: return p.rank == 4 ? launch_t<EPI_F32, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, false>(ma, mb, md, args, grid, stream);
+        case EPI_GELU_I8: return p.rank == 4 ? launch_t<EPI_GELU_I8, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, false>(ma, mb, md, args, grid, stream);
+        case EPI_GELU_FP4: return p.rank == 4 ? launch_t<EPI_GELU_FP4, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_FP4, false>(ma, mb, md, args, grid, stream);
+        case EPI_ADD_I8: return p.rank == 4 ? launch_t<EPI_ADD_I8, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_ADD_I8, false>(ma, mb, md, args, grid, stream);
+        case EPI_F16: return p.rank == 4 ? launch_t<EPI_F16, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_F16, false>(ma, mb, md, args, grid, stream);
     }
     return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: unknown epilogue %d", p.epilogue);
 }
