@@ -222,9 +222,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // CTAs working at the same time share rows of A through L2). Three roles run concurrently on different tiles:
 // the producer prefetches operands up to kStages k-blocks ahead, the MMA warp fills one of two TMEM
 // accumulators while the sixteen epilogue warps drain the other one.
-// R4: the instance for rank-4 perturbation terms (its epilogue applies the four factors with packed multiply-adds); every other
-// rank runs the R4 = false instance, whose code is what it was before the specialisation existed.
-template <int EPI, bool R4>
+// RK: 4 = the instance for rank-4 perturbation terms (its epilogue applies the four factors with packed multiply-adds);
+// 1 = the instance for the batched driver's common case (rank 1, no C operand, every 128-row tile inside one member), which carries
+// none of the general paths; 0 = everything else.
+template <int EPI, int RK>
 __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                  const __grid_constant__ CUtensorMap map_b,
                                                                  const __grid_constant__ CUtensorMap map_d,
@@ -466,7 +467,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         };
         // The common case (rank 1, tiles inside one member) with as few instructions as possible: this phase sits on the serial
         // path of every tile.
-        const bool fast_ctx = p.rank == 1 && tile_uniform_member;
+        constexpr bool R4 = RK == 4, R1 = RK == 1;
+        const bool fast_ctx = R1 || (p.rank == 1 && tile_uniform_member);
         const int* t_row = p.rank > 0 ? p.lora_t + static_cast<size_t>(row_in_tile) * p.t_stride : nullptr;
         auto fetch_fast = [&](const TileIdx& t, bool valid, LoraCtx& cx) {
             cx.pair = 0;
@@ -522,7 +524,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
         LoraCtx nxt;
         nxt.tr[1] = nxt.tr[2] = nxt.tr[3] = 0;
         nxt.aval[1] = nxt.aval[2] = nxt.aval[3] = 0;
-        if (fast_ctx) fetch_fast(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
+        if (R1 || fast_ctx) fetch_fast(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
         else fetch_ctx(cur_t, static_cast<int>(blockIdx.x) < total_tiles, nxt);
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             float tr[4] = {static_cast<float>(nxt.tr[0]), 0.0f, 0.0f, 0.0f};
             const bool a_staged = nxt.a_staged;
             float* loraA_sh = reinterpret_cast<float*>(smem_gen + kSmemLora) + ew * 4 * 32;  // this warp's [4][32]
-            if (fast_ctx) {
+            if (R1 || fast_ctx) {
                 __syncwarp();  // the previous tile's reads are done
                 loraA_sh[lane] = static_cast<float>(nxt.aval[0]);
                 __syncwarp();
@@ -597,13 +599,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 v[j] = t2.x;
                 v[j + 1] = t2.y;
             }
-            if (p.beta != 0.0f && row_ok) {
+            if (!R1 && p.beta != 0.0f && row_ok) {
                 const float* crow = p.c + static_cast<size_t>(row) * p.ldc + col0;
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                     if (col0 + j < p.n) v[j] = fmaf(p.beta, crow[j], v[j]);
             }
-            if (p.rank > 0 && row_ok) {
+            if ((R1 || p.rank > 0) && row_ok) {
                 // sum_r t[r]*A[n][r] is an integer below 2^24: float products and sums are exact
                 if constexpr (R4) {
                     if (a_staged) {
@@ -633,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                             }
                         }
                     }
-                } else if (a_staged && p.rank == 1) {
+                } else if (R1 || (a_staged && p.rank == 1)) {
                     const float2 tr2 = make_float2(tr[0], tr[0]), ls2 = make_float2(lsign, lsign);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
@@ -917,7 +919,7 @@ int make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint
     return BNF4_OK;
 }
 
-template <int EPI, bool R4>
+template <int EPI, int RK>
 int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md, const KernelArgs& args, dim3 grid,
              cudaStream_t stream) {
     // function attributes are per device: set once for each device this process uses
@@ -925,11 +927,11 @@ int launch_t(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& md
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return check_cuda(cudaGetLastError(), "cudaGetDevice");
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI, R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
+        const cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<EPI, RK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_nvfp4_kernel)");
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    gemm_nvfp4_kernel<EPI, R4><<<grid, kThreads, kSmemAlloc, stream>>>(ma, mb, md, args);
+    gemm_nvfp4_kernel<EPI, RK><<<grid, kThreads, kSmemAlloc, stream>>>(ma, mb, md, args);
     return check_launch("gemm_nvfp4_kernel");
 }
 
@@ -1012,12 +1014,13 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
     if (rc) return rc;
     const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
+    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0) ? 1 : 0);
     switch (p.epilogue) {
-        case EPI_F32: return p.rank == 4 ? launch_t<EPI_F32, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, false>(ma, mb, md, args, grid, stream);
-        case EPI_GELU_I8: return p.rank == 4 ? launch_t<EPI_GELU_I8, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, false>(ma, mb, md, args, grid, stream);
-        case EPI_GELU_FP4: return p.rank == 4 ? launch_t<EPI_GELU_FP4, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_FP4, false>(ma, mb, md, args, grid, stream);
-        case EPI_ADD_I8: return p.rank == 4 ? launch_t<EPI_ADD_I8, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_ADD_I8, false>(ma, mb, md, args, grid, stream);
-        case EPI_F16: return p.rank == 4 ? launch_t<EPI_F16, true>(ma, mb, md, args, grid, stream) : launch_t<EPI_F16, false>(ma, mb, md, args, grid, stream);
+        case EPI_F32: return rk == 4 ? launch_t<EPI_F32, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_F32, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, 0>(ma, mb, md, args, grid, stream));
+        case EPI_GELU_I8: return rk == 4 ? launch_t<EPI_GELU_I8, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_GELU_I8, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, 0>(ma, mb, md, args, grid, stream));
+        case EPI_GELU_FP4: return rk == 4 ? launch_t<EPI_GELU_FP4, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_GELU_FP4, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_FP4, 0>(ma, mb, md, args, grid, stream));
+        case EPI_ADD_I8: return rk == 4 ? launch_t<EPI_ADD_I8, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_ADD_I8, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_ADD_I8, 0>(ma, mb, md, args, grid, stream));
+        case EPI_F16: return rk == 4 ? launch_t<EPI_F16, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_F16, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_F16, 0>(ma, mb, md, args, grid, stream));
     }
     return set_error(BNF4_ERR_INVALID, "gemm_nvfp4: unknown epilogue %d", p.epilogue);
 }
