@@ -786,7 +786,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 // branch between groups, so the scheduler interleaves them); a group with a value too close to a rounding
                 // boundary is flagged and redone with the tanhf form (about one group in a thousand). tb holds the rounded
                 // values still biased by 1.5 * 2^23: the low byte of the bit pattern is the int8.
-                const bool lower_clamp = p.act_scale > 700.0f;
+                const bool lower_clamp = !R1 && p.act_scale > 700.0f;  // gelu(x) >= -0.17 |x|: only a huge act_scale reaches -127 (those calls run the general instance)
                 // entry address from the bit pattern of (amax + kRoundBias): (bits - kRoundBiasBits) * 8, folded into one constant
                 const uint32_t tab_c = smem_base + kSmemEpi - (static_cast<uint32_t>(kRoundBiasBits) << 3);
                 int w[8];
@@ -1014,7 +1014,8 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
     if (rc) return rc;
     const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
-    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0) ? 1 : 0);
+    const bool gelu = p.epilogue == EPI_GELU_FP4 || p.epilogue == EPI_GELU_I8;
+    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && !(gelu && p.act_scale > 700.0f)) ? 1 : 0);
     switch (p.epilogue) {
         case EPI_F32: return rk == 4 ? launch_t<EPI_F32, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_F32, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, 0>(ma, mb, md, args, grid, stream));
         case EPI_GELU_I8: return rk == 4 ? launch_t<EPI_GELU_I8, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_GELU_I8, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, 0>(ma, mb, md, args, grid, stream));
