@@ -777,7 +777,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                 }
             } else {
                 // GELU -> int8 (reference: src/cuda_kernels.cu:3178-3194; tanh-form GELU, clip to +-127)
-                if (col0 + 32 > p.n) {
+                if (!R1 && col0 + 32 > p.n) {  // (the rank-1 instance runs with n a multiple of 32)
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (col0 + j >= p.n) v[j] = 0.0f;  // gelu(0) = 0
@@ -835,7 +835,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         codes[2 * blk + 1] = e2m1x8_biased(tb + 8, __uint_as_float(rbits));
                     }
                 }
-                if (row_ok && p.d_i8 != nullptr) {
+                if (!(R1 && EPI == EPI_GELU_FP4) && row_ok && p.d_i8 != nullptr) {  // (the rank-1 FP4 instance writes no int8 copy)
                     int8_t* drow = p.d_i8 + static_cast<size_t>(row) * p.ld_i8 + col0;
                     if (((reinterpret_cast<uintptr_t>(drow) & 15) == 0) && col0 + 32 <= p.n) {
                         reinterpret_cast<int4*>(drow)[0] = make_int4(w[0], w[1], w[2], w[3]);
@@ -855,7 +855,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                             static_cast<uint16_t>(s0 | (s1 << 8));
                         if (p.next_nvec > 0) {
                             const int8_t* tv = p.next_tvec + static_cast<size_t>(pair) * p.next_tvec_pair_stride + col0;
-                            for (int vv = 0; vv < p.next_nvec; ++vv) {
+                            const int nv_ = R1 ? 1 : p.next_nvec;  // (the rank-1 instance runs with at most one projection)
+                            for (int vv = 0; vv < nv_; ++vv) {
                                 const int4* bv = reinterpret_cast<const int4*>(tv + static_cast<size_t>(vv) * p.n);
                                 const int4 b0 = __ldg(bv), b1 = __ldg(bv + 1);
                                 int a = 0;
@@ -1015,7 +1016,8 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     if (rc) return rc;
     const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
     const bool gelu = p.epilogue == EPI_GELU_FP4 || p.epilogue == EPI_GELU_I8;
-    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && !(gelu && p.act_scale > 700.0f)) ? 1 : 0);
+    const bool gelu_plain = !gelu || (p.act_scale <= 700.0f && (p.n % 32) == 0 && p.next_nvec <= 1 && (p.epilogue != EPI_GELU_FP4 || p.d_i8 == nullptr));
+    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && gelu_plain) ? 1 : 0);
     switch (p.epilogue) {
         case EPI_F32: return rk == 4 ? launch_t<EPI_F32, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_F32, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, 0>(ma, mb, md, args, grid, stream));
         case EPI_GELU_I8: return rk == 4 ? launch_t<EPI_GELU_I8, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_GELU_I8, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, 0>(ma, mb, md, args, grid, stream));
