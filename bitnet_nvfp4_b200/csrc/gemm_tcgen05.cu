@@ -480,7 +480,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             const int m0_ = t.m_tile * BM, col0_ = t.n_tile * BN + c * 32;
             while (m0_ >= trk_end) { ++trk_member; trk_end += p.rows_per_member; }
             cx.pair = trk_member >> 1;
-            if (m0_ + row_in_tile < p.m && col0_ < p.n) {
+            if ((R1 || m0_ + row_in_tile < p.m) && col0_ < p.n) {
                 const int g = p.group_cols > 0 ? static_cast<int>(__umulhi(static_cast<uint32_t>(col0_), group_magic)) : 0;
                 cx.tr[0] = __ldg(t_row + static_cast<size_t>(m0_) * p.t_stride + g);
                 cx.lsign = (trk_member & 1) ? -p.lora_scale : p.lora_scale;
@@ -532,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
             advance(nxt_t);
             const int m0 = cur_t.m_tile * BM, n0 = cur_t.n_tile * BN;
             const long long row = static_cast<long long>(m0) + row_in_tile;
-            const bool row_ok = row < p.m;
+            const bool row_ok = R1 || row < p.m;  // (the rank-1 instance runs with m a multiple of the tile height)
             const int col0 = n0 + c * 32;
             const bool chunk_ok = col0 < p.n;  // warp-uniform
 
@@ -1017,7 +1017,7 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
     const bool gelu = p.epilogue == EPI_GELU_FP4 || p.epilogue == EPI_GELU_I8;
     const bool gelu_plain = !gelu || (p.act_scale <= 700.0f && (p.n % 32) == 0 && p.next_nvec <= 1 && (p.epilogue != EPI_GELU_FP4 || p.d_i8 == nullptr));
-    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && gelu_plain) ? 1 : 0);
+    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && (p.m % BM) == 0 && gelu_plain) ? 1 : 0);
     switch (p.epilogue) {
         case EPI_F32: return rk == 4 ? launch_t<EPI_F32, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_F32, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, 0>(ma, mb, md, args, grid, stream));
         case EPI_GELU_I8: return rk == 4 ? launch_t<EPI_GELU_I8, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_GELU_I8, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, 0>(ma, mb, md, args, grid, stream));
