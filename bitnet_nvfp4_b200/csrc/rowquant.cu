@@ -290,7 +290,9 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t saddr) {
 }
 // Element ownership as in rowquant_kernel: lane l owns the 16-element scale blocks l, l + 32, ... (NB of them).
 // NV = upper bound of p.nvec this instance handles (4 or kMaxTVec): the projection loops carry no tests beyond it.
-template <int FE, int NB, int NV>
+// MODEL: the instance for the calls of the batched driver (power-of-two columns, rows per member, token and position counts;
+// exactly NV projections; no int8 copy; the residual branch as halves), which carries none of the corresponding tests.
+template <int FE, int NB, int NV, bool MODEL = false>
 __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowquant_fast_kernel(const RowQuantParams p, const uint8_t* __restrict__ lut) {
     __shared__ __align__(16) uint2 tab_s[128];  // per amax: {bits of fl(1 / scale), scale byte}
     if (threadIdx.x < 128) tab_s[threadIdx.x] = __ldg(reinterpret_cast<const uint2*>(lut + kQuantBlockTabOffset) + threadIdx.x);
@@ -304,18 +306,18 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
     const int nblk = p.cols_out >> 4;
     const int k_atoms = sf_k_atoms(p.cols_out);
     const unsigned rows = static_cast<unsigned>(p.rows);
-    const bool cols_pow2 = (p.cols_in & (p.cols_in - 1)) == 0;
+    const bool cols_pow2 = MODEL || (p.cols_in & (p.cols_in - 1)) == 0;
     // token / position indices wrap at powers of two in every model configuration: masks instead of divisions per row
-    const bool row_mod_pow2 = p.row_mod > 0 && (p.row_mod & (p.row_mod - 1)) == 0;
-    const bool pos_mod_pow2 = p.pos_mod > 0 && (p.pos_mod & (p.pos_mod - 1)) == 0;
+    const bool row_mod_pow2 = MODEL || (p.row_mod > 0 && (p.row_mod & (p.row_mod - 1)) == 0);
+    const bool pos_mod_pow2 = MODEL || (p.pos_mod > 0 && (p.pos_mod & (p.pos_mod - 1)) == 0);
     const int rpm_shift = (p.rows_per_member > 0 && (p.rows_per_member & (p.rows_per_member - 1)) == 0) ? __ffs(p.rows_per_member) - 1 : -1;
     const float inv_cols = 1.0f / static_cast<float>(p.cols_in);
     for (unsigned row = blockIdx.x * 8u + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8u) {
         // rows per member is a power of two in every model configuration: a shift instead of a division per row
-        const int member = p.rows_per_member > 0 ? static_cast<int>(rpm_shift >= 0 ? row >> rpm_shift : row / static_cast<unsigned>(p.rows_per_member)) : 0;
-        const int row_in_member = p.rows_per_member > 0 ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
+        const int member = (MODEL || p.rows_per_member > 0) ? static_cast<int>((MODEL || rpm_shift >= 0) ? row >> rpm_shift : row / static_cast<unsigned>(p.rows_per_member)) : 0;
+        const int row_in_member = (MODEL || p.rows_per_member > 0) ? static_cast<int>(row - static_cast<unsigned>(member) * static_cast<unsigned>(p.rows_per_member)) : static_cast<int>(row);
         const int pair = member >> 1;
-        const float ns = p.rows_per_member > 0 ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
+        const float ns = (MODEL || p.rows_per_member > 0) ? ((member & 1) ? -p.sigma : p.sigma) : p.sigma * static_cast<float>(p.anti_fixed);
 
         // The row this warp takes next starts its trip from DRAM to L2 now: a warp holds one row's loads at a time, too few
         // bytes in flight to cover the DRAM latency with the narrow inputs (int8 rows, a branch travelling as halves).
@@ -328,7 +330,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                     if (k0 >= p.cols_in) continue;
                     if constexpr (FE == FE_ABSMEAN) {
                         asm volatile("prefetch.global.L2 [%0];" ::"l"(p.in_i8 + static_cast<size_t>(nrow) * p.ld_in + k0));
-                    } else if (p.in_f16) {
+                    } else if (MODEL || p.in_f16) {
                         asm volatile("prefetch.global.L2 [%0];" ::"l"(p.inout_i8 + static_cast<size_t>(nrow) * p.cols_in + k0));
                         asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const __half*>(p.in_f32) + static_cast<size_t>(nrow) * p.ld_in + k0));
                     }
@@ -374,7 +376,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 const int4 raw = *reinterpret_cast<const int4*>(xr + k0);
                 const uint32_t rw[4] = {static_cast<uint32_t>(raw.x), static_cast<uint32_t>(raw.y), static_cast<uint32_t>(raw.z), static_cast<uint32_t>(raw.w)};
                 float4 y4[4];
-                if (p.in_f16) {  // the branch output as IEEE halves (exact widening)
+                if (MODEL || p.in_f16) {  // the branch output as IEEE halves (exact widening)
                     const uint4* yh = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.in_f32) + static_cast<size_t>(row) * p.ld_in + k0);
                     const uint4 h0 = __ldcs(yh), h1 = __ldcs(yh + 1);
                     const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) w[q] = biased4_to_bytes(tq[4 * q], tq[4 * q + 1], tq[4 * q + 2], tq[4 * q + 3]);
-                if (p.out_q != nullptr)
+                if (!MODEL && p.out_q != nullptr)
                     *reinterpret_cast<int4*>(p.out_q + static_cast<size_t>(row) * p.ld_q + k0) =
                         make_int4(static_cast<int>(w[0]), static_cast<int>(w[1]), static_cast<int>(w[2]), static_cast<int>(w[3]));
                 const uint2 ent = lds_u64((__float_as_uint(am + M) << 3) + tab_c);
@@ -559,7 +561,21 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
             // eight sectors a word store would
             if (active) p.out_sf[sf_offset(static_cast<int>(row), kb, k_atoms)] = static_cast<uint8_t>(sfb);
 
-            if (p.nvec > 0 && active) {
+            if constexpr (MODEL) {
+                if (active) {
+                    const int8_t* tv = p.tvec + static_cast<size_t>(pair) * p.tvec_pair_stride + k0;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        const int4 bv = *reinterpret_cast<const int4*>(tv + static_cast<size_t>(v) * p.cols_out);
+                        int a = tacc[v];
+                        a = __dp4a(static_cast<int>(w[0]), bv.x, a);
+                        a = __dp4a(static_cast<int>(w[1]), bv.y, a);
+                        a = __dp4a(static_cast<int>(w[2]), bv.z, a);
+                        a = __dp4a(static_cast<int>(w[3]), bv.w, a);
+                        tacc[v] = a;
+                    }
+                }
+            } else if (p.nvec > 0 && active) {
                 const int8_t* tv = p.tvec + static_cast<size_t>(pair) * p.tvec_pair_stride + k0;
 #pragma unroll
                 for (int vg = 0; vg < NV / 4; ++vg) {
@@ -581,7 +597,19 @@ __global__ void __launch_bounds__(256, (NB <= 1 ? 4 : (NB <= 2 ? 2 : 1))) rowqua
                 }
             }
         }
-        if (p.nvec > 0) {
+        if constexpr (MODEL) {
+            if constexpr (NV == 4) {
+                const int t0 = __reduce_add_sync(0xffffffffu, tacc[0]), t1 = __reduce_add_sync(0xffffffffu, tacc[1]);
+                const int t2 = __reduce_add_sync(0xffffffffu, tacc[2]), t3 = __reduce_add_sync(0xffffffffu, tacc[3]);
+                if (lane == 0) *reinterpret_cast<int4*>(p.t_out + static_cast<size_t>(row) * 4) = make_int4(t0, t1, t2, t3);
+            } else {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    const int tot = __reduce_add_sync(0xffffffffu, tacc[v]);
+                    if (lane == 0) p.t_out[static_cast<size_t>(row) * NV + v] = tot;
+                }
+            }
+        } else if (p.nvec > 0) {
 #pragma unroll
             for (int vg = 0; vg < NV / 4; ++vg) {
                 if (4 * vg < p.nvec) {
@@ -644,6 +672,19 @@ int launch(const RowQuantParams& p, cudaStream_t stream) {
                 kernel<<<grid, warps * 32, 0, stream>>>(p, lut);
                 return BNF4_OK;
             };
+            // the batched driver's calls at hidden <= 512: see MODEL above
+            auto pow2 = [](long long v) { return v > 0 && (v & (v - 1)) == 0; };
+            bool model = nblk <= 32 && (FE == FE_ADD_ABSMEAN || FE == FE_ABSMEAN || FE == FE_POS_GELU_ABSMEAN) && pow2(p.cols_in) && pow2(p.rows_per_member) &&
+                         p.out_q == nullptr && (p.nvec == 1 || p.nvec == 4) && p.tvec != nullptr && p.t_out != nullptr && al16(p.t_out);
+            if (FE == FE_ADD_ABSMEAN) model = model && p.in_f16 != 0;
+            if (FE == FE_POS_GELU_ABSMEAN) model = model && pow2(p.pos_mod) && (p.gather_rows <= 0 || pow2(p.row_mod));
+            if constexpr (FE == FE_ADD_ABSMEAN || FE == FE_ABSMEAN || FE == FE_POS_GELU_ABSMEAN) {
+                if (model) {
+                    rc = p.nvec == 1 ? run(rowquant_fast_kernel<FE, 1, 1, true>) : run(rowquant_fast_kernel<FE, 1, 4, true>);
+                    if (rc) return rc;
+                    return check_launch("rowquant_fast_kernel");
+                }
+            }
             if (p.nvec <= 4) {
                 if (nblk <= 32) rc = run(rowquant_fast_kernel<FE, 1, 4>);
                 else if (nblk <= 64) rc = run(rowquant_fast_kernel<FE, 2, 4>);
