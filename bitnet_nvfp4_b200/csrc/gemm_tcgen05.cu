@@ -726,6 +726,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         bulk_commit();
                     }
                     stage_half ^= 1;
+                } else if (R1) {  // (the rank-1 instance runs with at most one fp32 column behind the halves)
+                    if (col0 == p.n_f16) p.d[static_cast<size_t>(row) * p.ldd] = v[0];
                 } else if (row_ok) {
                     float* drow = p.d + static_cast<size_t>(row) * p.ldd + (col0 - p.n_f16);
 #pragma unroll
@@ -853,7 +855,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_nvfp4_kernel(const __grid_co
                         const int kb = col0 >> 4;
                         *reinterpret_cast<uint16_t*>(p.d_sf + sf_offset(static_cast<int>(row), kb, sf_k_atoms(p.n))) =
                             static_cast<uint16_t>(s0 | (s1 << 8));
-                        if (p.next_nvec > 0) {
+                        if (R1 || p.next_nvec > 0) {  // (the rank-1 FP4 instance always feeds one projection)
                             const int8_t* tv = p.next_tvec + static_cast<size_t>(pair) * p.next_tvec_pair_stride + col0;
                             const int nv_ = R1 ? 1 : p.next_nvec;  // (the rank-1 instance runs with at most one projection)
                             for (int vv = 0; vv < nv_; ++vv) {
@@ -1016,8 +1018,8 @@ int gemm_nvfp4_launch(const GemmParams& p, cudaStream_t stream) {
     if (rc) return rc;
     const dim3 grid(static_cast<unsigned>(std::min<long long>(tiles, sms)), 1, 1);
     const bool gelu = p.epilogue == EPI_GELU_FP4 || p.epilogue == EPI_GELU_I8;
-    const bool gelu_plain = !gelu || (p.act_scale <= 700.0f && (p.n % 32) == 0 && p.next_nvec <= 1 && (p.epilogue != EPI_GELU_FP4 || p.d_i8 == nullptr));
-    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && (p.m % BM) == 0 && gelu_plain) ? 1 : 0);
+    const bool gelu_plain = !gelu || (p.act_scale <= 700.0f && (p.n % 32) == 0 && (p.epilogue == EPI_GELU_FP4 ? (p.next_nvec == 1 && p.d_i8 == nullptr) : p.next_nvec <= 1));
+    const int rk = p.rank == 4 ? 4 : ((p.rank == 1 && p.beta == 0.0f && p.rows_per_member > 0 && (p.rows_per_member % BM) == 0 && (p.m % BM) == 0 && gelu_plain && (p.epilogue != EPI_F16 || p.n - p.n_f16 <= 1)) ? 1 : 0);
     switch (p.epilogue) {
         case EPI_F32: return rk == 4 ? launch_t<EPI_F32, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_F32, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_F32, 0>(ma, mb, md, args, grid, stream));
         case EPI_GELU_I8: return rk == 4 ? launch_t<EPI_GELU_I8, 4>(ma, mb, md, args, grid, stream) : (rk == 1 ? launch_t<EPI_GELU_I8, 1>(ma, mb, md, args, grid, stream) : launch_t<EPI_GELU_I8, 0>(ma, mb, md, args, grid, stream));
