@@ -36,7 +36,7 @@ NOMINAL_HBM_GBS = 8000.0
 DTYPE = "nvfp4 (e2m1 x ue4m3) with fp32 accumulation"
 # DRAM bytes (read + write) per row of one launch, from ncu captures of smaller launches of the same kernels (traffic
 # grows in proportion to rows); None where no capture of the current kernel exists
-NCU_DRAM_BYTES_PER_ROW = {"gemm_ff1_gelu_fp4": 21.41e6 / 65536, "efla_scan": 247.71e6 / 65536, "gemm_qkv": 168.35e6 / 65536}
+NCU_DRAM_BYTES_PER_ROW = {"gemm_ff1_gelu_fp4": 21.81e6 / 65536, "efla_scan": 247.71e6 / 65536, "gemm_qkv": 166.76e6 / 65536}
 
 
 def load_peaks():
