@@ -800,36 +800,32 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
     float* L_sh = reinterpret_cast<float*>(wsm + kM1L);
     __half* t_sh = reinterpret_cast<__half*>(wsm + kM1T);
     __half* p_sh = reinterpret_cast<__half*>(wsm + kM1P);
-    const long long unit = static_cast<long long>(blockIdx.x) * kChunkWarps + warp;  // (sequence, head)
-    if (unit >= p.seqs * static_cast<long long>(p.heads)) return;
-    // the grid has fewer than 2^32 / 4 CTAs: 32-bit divisions (a 64-bit one costs more than a chunk's scalar work)
-    const unsigned useq = static_cast<unsigned>(unit) / static_cast<unsigned>(p.heads);
-    const long long seq = useq;
-    const int h = static_cast<int>(static_cast<unsigned>(unit) - useq * static_cast<unsigned>(p.heads));
-    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[useq / static_cast<unsigned>(p.seqs_per_bias)] : p.beta_bias;
+    // Persistent warps: each walks (sequence, head) units with a grid stride and fetches the first chunk of its next unit while the
+    // last chunk of the present one is computed, so that no unit starts with an exposed trip to DRAM.
+    const unsigned total_units = static_cast<unsigned>(p.seqs * static_cast<long long>(p.heads));  // below 2^31 (checked by the host)
+    const unsigned unit_stride = gridDim.x * kChunkWarps;
+    unsigned unit = blockIdx.x * kChunkWarps + warp;
+    if (unit >= total_units) return;
     const int g = lane >> 2, tq = lane & 3;
-
-    uint32_t Sh[4][4][4];  // state S^T as A fragments, as in efla_chunk16_kernel
-#pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
-
-    const size_t row0 = static_cast<size_t>(seq) * p.T;
-    const __half* qbh = static_cast<const __half*>(p.q) + row0 * p.ld_qkv + h * HD;
-    const __half* kbh = static_cast<const __half*>(p.k) + row0 * p.ld_qkv + h * HD;
-    const __half* vbh = static_cast<const __half*>(p.v) + row0 * p.ld_qkv + h * HD;
-    const float* bb = p.beta_raw + row0 * p.ld_beta;
-    float* ob = static_cast<float*>(p.out) + row0 * p.ld_out + h * HD;
-    __half* obh = static_cast<__half*>(p.out) + row0 * p.ld_out + h * HD;
+    // first row of a unit's sequence and its head (32-bit division: a 64-bit one costs more than a chunk's scalar work)
+    struct UnitAt { size_t row0; int h; unsigned useq; };
+    auto unit_at = [&](unsigned u) {
+        UnitAt a;
+        a.useq = u / static_cast<unsigned>(p.heads);
+        a.h = static_cast<int>(u - a.useq * static_cast<unsigned>(p.heads));
+        a.row0 = static_cast<size_t>(a.useq) * p.T;
+        return a;
+    };
 
     // asynchronous copy of one chunk's q, k, v, beta rows (16-byte pieces, eight per 128-byte row); rows past the end of the
     // sequence are zero-filled so that everything derived from them stays finite
-    auto issue_chunk = [&](int t0, int kbuf) {
+    auto issue_chunk = [&](const UnitAt& ua, int t0, int kbuf) {
         const int piece = lane & 7, rsel = lane >> 3;
         __half* rk = rawk + kbuf * kChunk * kM1Stride;
+        const __half* qbh = static_cast<const __half*>(p.q) + ua.row0 * p.ld_qkv + ua.h * HD;
+        const __half* kbh = static_cast<const __half*>(p.k) + ua.row0 * p.ld_qkv + ua.h * HD;
+        const __half* vbh = static_cast<const __half*>(p.v) + ua.row0 * p.ld_qkv + ua.h * HD;
+        const float* bb = p.beta_raw + ua.row0 * p.ld_beta;
 #pragma unroll
         for (int j = 0; j < kChunk / 4; ++j) {
             const int r = 4 * j + rsel;
@@ -868,8 +864,20 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
     const uint32_t y_addr = static_cast<uint32_t>(__cvta_generic_to_shared(y_sh)) + lm_tok_off;
     constexpr uint32_t kKBufBytes = kChunk * kM1Stride * 2;
 
-    issue_chunk(0, 0);
     int kbuf = 0;
+    issue_chunk(unit_at(unit), 0, 0);
+    for (; unit < total_units; unit += unit_stride) {
+    const UnitAt ua = unit_at(unit);
+    const float beta_bias = p.beta_bias_seq != nullptr ? p.beta_bias_seq[ua.useq / static_cast<unsigned>(p.seqs_per_bias)] : p.beta_bias;
+    float* ob = static_cast<float*>(p.out) + ua.row0 * p.ld_out + ua.h * HD;
+    __half* obh = static_cast<__half*>(p.out) + ua.row0 * p.ld_out + ua.h * HD;
+    uint32_t Sh[4][4][4];  // state S^T as A fragments, as in efla_chunk16_kernel
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) Sh[mt][ks][i] = 0u;
     for (int t0 = 0; t0 < p.T; t0 += kChunk, kbuf ^= 1) {
         cp_async_wait<0>();
         __syncwarp();
@@ -901,7 +909,8 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
         float braw = 0.0f;
         if ((diag_lane || helper_lane) && t0 + my_tok < p.T) braw = beta_sh[my_tok];
         __syncwarp();  // q, v and beta are consumed
-        if (t0 + kChunk < p.T) issue_chunk(t0 + kChunk, kbuf ^ 1);
+        if (t0 + kChunk < p.T) issue_chunk(ua, t0 + kChunk, kbuf ^ 1);
+        else if (unit + unit_stride < total_units) issue_chunk(unit_at(unit + unit_stride), 0, kbuf ^ 1);
 
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
@@ -1069,6 +1078,7 @@ __global__ void __launch_bounds__(kChunkWarps * 32, 2) efla_chunk16_m1_kernel(co
         }
         __syncwarp();  // the staging tile and this chunk's k buffer are free for the chunk after the next
     }
+    }
     cp_async_wait<0>();
 }
 
@@ -1116,9 +1126,13 @@ int efla_launch(const EflaParams& p, cudaStream_t stream) {
             if (p.qkv_f16 && ((p.ld_qkv % 8) != 0)) return set_error(BNF4_ERR_INVALID, "efla: fp16 q, k, v need ld_qkv %% 8 == 0");
             if (p.out_f16 && (((p.ld_out % 8) != 0) || (reinterpret_cast<uintptr_t>(p.out) & 15))) return set_error(BNF4_ERR_INVALID, "efla: fp16 output needs 16-byte aligned rows");
             const unsigned grid = static_cast<unsigned>(ctas);
-            if (p.qkv_f16 && p.method == 1) {  // the batched driver's case: raw-operand kernel
-                if (p.out_f16) efla_chunk16_m1_kernel<true><<<grid, kChunkWarps * 32, kM1SmemBytes, stream>>>(p);
-                else efla_chunk16_m1_kernel<false><<<grid, kChunkWarps * 32, kM1SmemBytes, stream>>>(p);
+            if (p.qkv_f16 && p.method == 1) {  // the batched driver's case: raw-operand kernel, persistent warps (two CTAs per SM)
+                int sms = 0;
+                rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "cudaDeviceGetAttribute");
+                if (rc) return rc;
+                const unsigned pgrid = std::min(grid, static_cast<unsigned>(2 * sms));
+                if (p.out_f16) efla_chunk16_m1_kernel<true><<<pgrid, kChunkWarps * 32, kM1SmemBytes, stream>>>(p);
+                else efla_chunk16_m1_kernel<false><<<pgrid, kChunkWarps * 32, kM1SmemBytes, stream>>>(p);
             } else if (p.qkv_f16 && p.out_f16) efla_chunk16_kernel<true, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
             else if (p.qkv_f16) efla_chunk16_kernel<true, false><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
             else if (p.out_f16) efla_chunk16_kernel<false, true><<<grid, kChunkWarps * 32, kCkSmemBytes, stream>>>(p);
