@@ -254,3 +254,40 @@ def test_gemm_rejects_bad_arguments(H):
         H.gemm_ternary_f_nvfp4(z, z, z, z, 16, 16, 48, 1.0)  # k not a multiple of 64
     with pytest.raises(lib.Bnf4Error):
         H.gemm_ternary_f_nvfp4(z, z, z, z, 16, 16, 64, 1.0, 1.0, None)  # beta without C
+
+
+def test_gemm_kernel_instances_agree(H):
+    """The kernel instance for the batched driver's calls (rank 1, m a multiple of 128, tiles inside one member) against the general
+    instance: the same call with its last row dropped (m = 511) runs the general instance, and the 511 common rows of every epilogue's
+    output must be bit-identical."""
+    import torch
+    rng = np.random.default_rng(1234)
+    R, members, n, k = 128, 4, 512, 512
+    m = members * R
+    x, w, a, sfa, b, sfb = make_operands(rng, m, n, k)
+    A = torch.from_numpy(rng.integers(-4, 5, (members // 2, n, 1)).astype(np.int8)).cuda()
+    t = torch.from_numpy(rng.integers(-1000, 1000, (m, 1)).astype(np.int32)).cuda()
+    tv = torch.from_numpy(rng.integers(-4, 5, (members // 2, 1, n)).astype(np.int8)).cuda()
+    resid0 = torch.from_numpy(rng.integers(-100, 101, (m, n)).astype(np.int8)).cuda()
+    alpha = float(np.float32(1.0) / np.sqrt(np.float32(k)))
+    base = dict(a=dev(a), b=dev(b), sfa=dev(sfa), sfb=dev(sfb), n=n, k=k, alpha=alpha, rank=1, rows_per_member=R, lora_t=t, t_stride=1,
+                lora_A=A, lora_A_pair_stride=n, lora_scale=0.01)
+    out = {}
+    for rows in (m, m - 1):
+        d = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+        H.gemm_nvfp4_ex(**base, m=rows, d=d, ldd=n, epilogue=H.EPI_F32)
+        d16 = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        H.gemm_nvfp4_ex(**base, m=rows, d_f16=d16, ld_f16=n, n_f16=n, epilogue=H.EPI_F16)
+        res = resid0.clone()
+        H.gemm_nvfp4_ex(**base, m=rows, resid=res, ld_resid=n, add_scale=0.0625, epilogue=H.EPI_ADD_I8)
+        codes = torch.zeros(m * n // 2, dtype=torch.uint8, device="cuda")
+        sf = torch.zeros(H.sf_bytes(m, n), dtype=torch.uint8, device="cuda")
+        nt = torch.zeros((m, 1), dtype=torch.int32, device="cuda")
+        H.gemm_nvfp4_ex(**base, m=rows, epilogue=H.EPI_GELU_FP4, act_scale=4.0, d_codes=codes, d_sf=sf, next_tvec=tv,
+                        next_tvec_pair_stride=n, next_nvec=1, next_t=nt)
+        assert H.device_error() == 0
+        out[rows] = (d, d16, res, codes.view(m, n // 2), nt)
+    keep = m - 1
+    for full, part in zip(out[m], out[m - 1]):
+        assert torch.equal(full[:keep], part[:keep])
+    assert out[m][0][keep].abs().sum() > 0 and out[m - 1][0][keep].abs().sum() == 0   # the dropped row really was not computed
