@@ -318,3 +318,38 @@ def test_absmean_int8_rows_with_projections(H, hid, nvec):
     assert same(yq, rq) and same(codes, rc) and same(sf, rs)
     tref = np.concatenate([rq[m * R:(m + 1) * R].astype(np.int32) @ tvec[m // 2].astype(np.int32).T for m in range(2 * pairs)])
     assert same(tout, tref)
+
+
+@pytest.mark.parametrize("fe", ["absmean", "add_half"])
+def test_rowquant_model_instance_agrees_with_the_general_one(fe):
+    """The row-quantiser instance for the batched driver's calls (power-of-two shapes, exactly 1 or 4 projections, no int8 copy) against
+    the general instance, which the same call takes as soon as it also asks for the int8 copy: codes, scales, projections and the
+    residual stream must be bit-identical."""
+    import torch
+    from bitnet_nvfp4_b200 import host as H
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rows, hid, rpm = 8192, 512, 4096
+    nvec = 4 if fe == "absmean" else 1
+    x0 = torch.randint(-127, 128, (rows, hid), dtype=torch.int8, device="cuda", generator=g)
+    yh = (torch.randn(rows, hid, device="cuda", generator=g) * 0.2).half()
+    tv = torch.randint(-4, 5, (rows // (2 * rpm), nvec, hid), dtype=torch.int8, device="cuda", generator=g)
+    outs = []
+    for general in (False, True):
+        x = x0.clone()
+        codes = torch.zeros(rows * hid // 2, dtype=torch.uint8, device="cuda")
+        sf = torch.zeros(H.sf_bytes(rows, hid), dtype=torch.uint8, device="cuda")
+        t = torch.zeros(rows, nvec, dtype=torch.int32, device="cuda")
+        q = torch.zeros(rows, hid, dtype=torch.int8, device="cuda")
+        kw = dict(rows=rows, cols_in=hid, cols_out=hid, rows_per_member=rpm, ld_in=hid, norm_scale=24.0, out_codes=codes, out_sf=sf,
+                  tvec=tv, tvec_pair_stride=nvec * hid, nvec=nvec, t_out=t)
+        if general:
+            kw.update(out_q=q, ld_q=hid)
+        if fe == "absmean":
+            H.rowquant(H.FE_ABSMEAN, in_i8=x, **kw)
+        else:
+            H.rowquant(H.FE_ADD_ABSMEAN, sigma=0.125, inout_i8=x, in_f32=yh, in_f16=1, add_scale=100.0, **kw)
+        assert H.device_error() == 0
+        outs.append((codes, sf, t, x))
+    for u, v in zip(*outs):
+        assert torch.equal(u, v)
+    assert outs[0][2].abs().sum() > 0
